@@ -1,0 +1,173 @@
+"""The rows of one step and their metadata, on the host and on the device.
+
+A step is a list of (request, its next tokens, wanted places).  All rows are laid end
+to end, ``[T]``; per sequence the step records where its rows start, how many
+positions the cache already holds, its state slot and its block-table row.  Everything
+is packed into ONE int32 staging block in pinned host memory and copied to the device
+with one transfer; the kernels read slices of that block.  The layout depends only on
+(T, S, table width), so a captured step of the same shape finds every array at the same
+address.
+
+The reference uploads ids, positions and bounds as three small arrays and packs page
+tables with device-to-device copies (crates/shiso-engine/src/stack.rs:513-544,843-870;
+crates/shiso-engine/src/rows.rs:92-111), always after pages were claimed and before any
+launch (stack.rs:1018-1033); the same order is kept here.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places (indices into
+    ``tokens``) whose logits are wanted."""
+
+    request: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepMeta:
+    """Device arrays (int32) of one step plus the host facts kernels are launched with."""
+
+    num_tokens: int
+    num_seqs: int
+    num_wanted: int
+    token_ids: torch.Tensor  # [T]
+    positions: torch.Tensor  # [T] absolute position of each row
+    seq_of_token: torch.Tensor  # [T] index of the row's sequence in this step
+    q_start: torch.Tensor  # [S + 1] first row of each sequence
+    start_pos: torch.Tensor  # [S] positions the cache held before this step
+    state_slots: torch.Tensor  # [S]
+    want_rows: torch.Tensor  # [W] rows whose logits are wanted
+    block_tables: list  # per paged group: [S, width]
+    max_q_len: int
+    max_context: int  # most positions any sequence can see after this step
+    all_decode: bool  # every sequence brings exactly one token
+    h_q_start: list = field(default_factory=list)
+    h_start_pos: list = field(default_factory=list)
+    requests: list = field(default_factory=list)
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+class MetaLayout:
+    """Offsets (in int32 elements) of every array inside the staging block."""
+
+    def __init__(self, num_tokens: int, num_seqs: int, num_wanted_cap: int, num_groups: int, width: int):
+        t, s = _align(num_tokens), _align(num_seqs)
+        self.token_ids = 0
+        self.positions = t
+        self.seq_of_token = 2 * t
+        self.q_start = 3 * t
+        self.start_pos = self.q_start + _align(num_seqs + 1)
+        self.state_slots = self.start_pos + s
+        self.want_rows = self.state_slots + s
+        self.tables = self.want_rows + _align(num_wanted_cap)
+        self.table_elems = _align(num_seqs * width)
+        self.total = self.tables + num_groups * self.table_elems
+
+
+class StepBuilder:
+    """Builds ``StepMeta`` from entries and the cache manager's holdings."""
+
+    def __init__(self, cache, device, max_tokens: int, max_seqs: int, fixed_table_width: Optional[int] = None):
+        self.cache = cache
+        self.device = torch.device(device)
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs
+        self.num_groups = len(cache.groups)
+        self.fixed_width = fixed_table_width
+        width = fixed_table_width or cache.max_blocks
+        cap = MetaLayout(max_tokens, max_seqs, max_tokens, self.num_groups, width).total
+        pin = self.device.type == "cuda"
+        self._staging = [torch.zeros(cap, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._events = [None, None]
+        self._turn = 0
+        self.device_block = torch.zeros(cap, dtype=torch.int32, device=self.device)
+
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepMeta:
+        """``starts[i]`` = positions the cache held for entry ``i`` before this step."""
+        num_seqs = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        num_tokens = sum(lens)
+        num_wanted = sum(len(e.want) for e in entries)
+        if num_seqs == 0 or num_tokens == 0:
+            raise ValueError("a step needs at least one token")
+        if num_tokens > self.max_tokens or num_seqs > self.max_seqs:
+            raise ValueError(
+                f"step of {num_tokens} tokens in {num_seqs} sequences exceeds the engine's "
+                f"limits ({self.max_tokens} tokens, {self.max_seqs} sequences)"
+            )
+        requests = [e.request for e in entries]
+        width = self.fixed_width or self.cache.max_blocks_held(requests)
+        lay = MetaLayout(num_tokens, num_seqs, num_wanted, self.num_groups, width)
+
+        turn = self._turn
+        self._turn ^= 1
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        stage = self._staging[turn]
+        host = stage.numpy()
+
+        q_start = np.zeros(num_seqs + 1, dtype=np.int32)
+        np.cumsum(lens, out=q_start[1:])
+        host[lay.q_start : lay.q_start + num_seqs + 1] = q_start
+        host[lay.start_pos : lay.start_pos + num_seqs] = starts
+        host[lay.state_slots : lay.state_slots + num_seqs] = [self.cache.slot_of(r) for r in requests]
+        want_at = lay.want_rows
+        for i, e in enumerate(entries):
+            a, b = int(q_start[i]), int(q_start[i + 1])
+            host[lay.token_ids + a : lay.token_ids + b] = e.tokens
+            host[lay.positions + a : lay.positions + b] = np.arange(starts[i], starts[i] + lens[i], dtype=np.int32)
+            host[lay.seq_of_token + a : lay.seq_of_token + b] = i
+            for w in e.want:
+                if not 0 <= w < lens[i]:
+                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {lens[i]} tokens")
+                host[want_at] = a + w
+                want_at += 1
+        for g in range(self.num_groups):
+            at = lay.tables + g * lay.table_elems
+            self.cache.fill_block_tables(requests, g, host[at : at + num_seqs * width].reshape(num_seqs, width))
+
+        dev = self.device_block
+        dev[: lay.total].copy_(stage[: lay.total], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[turn] = ev
+
+        def part(at, n):
+            return dev[at : at + n]
+
+        return StepMeta(
+            num_tokens=num_tokens,
+            num_seqs=num_seqs,
+            num_wanted=num_wanted,
+            token_ids=part(lay.token_ids, num_tokens),
+            positions=part(lay.positions, num_tokens),
+            seq_of_token=part(lay.seq_of_token, num_tokens),
+            q_start=part(lay.q_start, num_seqs + 1),
+            start_pos=part(lay.start_pos, num_seqs),
+            state_slots=part(lay.state_slots, num_seqs),
+            want_rows=part(lay.want_rows, num_wanted),
+            block_tables=[
+                part(lay.tables + g * lay.table_elems, num_seqs * width).view(num_seqs, width)
+                for g in range(self.num_groups)
+            ],
+            max_q_len=max(lens),
+            max_context=max(s + n for s, n in zip(starts, lens)),
+            all_decode=all(n == 1 for n in lens),
+            h_q_start=q_start.tolist(),
+            h_start_pos=list(starts),
+            requests=requests,
+        )

@@ -1,0 +1,216 @@
+"""Interfaces of the parts a model is put together from, and their registries.
+
+A part is built from a ``PartSpec`` (its sizes and constants) and a ``BuildEnv``
+(compute dtype, device, the kernel table).  It lists the tensors it needs, is
+handed them by name after loading, says what cache it needs, and runs on the
+rows of one step.  No part knows which model it is in.
+
+Kinds of part and what each must provide:
+
+``Norm``             ``apply(x)``, ``add_apply(residual, delta, rows=None)``
+``PositionEncoding`` ``rotary()`` - the per-pair frequencies the fused kernel rotates by
+``Mixer``            ``cache_spec()``, ``forward(x, step, cache)``
+``FeedForward``      ``forward(x, step)``
+``Block``            ``forward(stream, step, cache)`` - the arrangement of the above
+``Embedding``        ``forward(step)`` -> float32 residual rows
+``Head``             ``forward(x)`` -> float32 logits
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Optional
+
+import torch
+
+from ..weights.spec import TensorSpec
+from .plan import PartSpec
+
+
+@dataclass
+class BuildEnv:
+    """What every part needs to know about where it runs."""
+
+    dtype: torch.dtype  # compute dtype: activations between kernels, 16-bit weights
+    device: torch.device
+    ops: Any  # the kernel table (shiso_llm_b200.kernels.ops, or a stand-in in CPU tests)
+
+    def empty(self, shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+
+# --------------------------------------------------------------------------- cache needs
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values of every position, in pages.  ``window`` = how many of the most
+    recent positions are ever read again (None: all of them)."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """Per-request state of fixed size (float32 elements), zero for a new request."""
+
+    shape: tuple[int, ...]
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+
+# --------------------------------------------------------------------------- part classes
+
+
+class Part:
+    """Common protocol: tensors wanted, tensors bound."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        self.spec = spec
+        self.env = env
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Receives every loaded tensor by name; keep what ``tensor_specs`` named."""
+
+    def sub_parts(self) -> list["Part"]:
+        return []
+
+
+class Norm(Part):
+    def apply(self, x: torch.Tensor) -> torch.Tensor:
+        """Normalises float32 rows ``x[T, size]``; returns compute-dtype rows."""
+        raise NotImplementedError
+
+    def add_apply(self, residual: torch.Tensor, delta: torch.Tensor, rows: Optional[torch.Tensor] = None):
+        """``residual += delta`` (float32, in place) and returns norm(residual).
+
+        With ``rows`` (int32 row numbers) only those rows are summed and normalised,
+        into a ``[len(rows), size]`` result, and ``residual`` is left untouched."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary(self):
+        """``(inv_freq, rotary_dim)``: the encoding rotates the pairs ``(i, i + rotary_dim/2)``
+        of every query and key head by the angle ``position * inv_freq[i]`` (float32
+        ``[rotary_dim / 2]`` on the device); ``(None, 0)`` leaves heads as they are.
+        The fused norm + rotate + store kernel applies it."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        """``PagedKV``, ``FixedState`` or ``None``."""
+        return None
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        """``x[T, hidden]`` (compute dtype, already normalised) -> mixer output ``[T, hidden]``.
+
+        ``cache`` is this run entry's view of the cache (``PagedKVView`` or
+        ``FixedStateView``), or ``None``; ``cache.owner`` is False when the entry
+        borrows another entry's cache and must not write it."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, step) -> torch.Tensor:
+        """Float32 residual rows ``[T, hidden]`` for ``step.token_ids``."""
+        raise NotImplementedError
+
+    def table(self) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """``x[R, hidden]`` (compute dtype) -> float32 logits ``[R, vocab]``."""
+        raise NotImplementedError
+
+
+class Stream:
+    """The residual stream between blocks.
+
+    ``residual`` is float32 ``[T, hidden]``.  ``pending`` is a block output not yet
+    added: the next norm adds it while it normalises (one fused kernel), which is how
+    the reference closes every block (crates/shiso-engine/src/layers.rs:2476-2498)."""
+
+    def __init__(self, residual: torch.Tensor):
+        self.residual = residual
+        self.pending: Optional[torch.Tensor] = None
+
+    def normed(self, norm: Norm) -> torch.Tensor:
+        if self.pending is None:
+            return norm.apply(self.residual)
+        delta, self.pending = self.pending, None
+        return norm.add_apply(self.residual, delta)
+
+    def add(self, delta: torch.Tensor) -> None:
+        if self.pending is not None:
+            raise RuntimeError("a block output is already waiting to be added to the residual")
+        self.pending = delta
+
+
+class Block(Part):
+    def mixer_part(self) -> Mixer:
+        raise NotImplementedError
+
+    def forward(self, stream: Stream, step, cache) -> None:
+        raise NotImplementedError
+
+
+# --------------------------------------------------------------------------- registries
+
+
+class Registry:
+    """Name -> factory(spec, env, ...) for one kind of part."""
+
+    def __init__(self, what: str):
+        self.what = what
+        self._factories: dict[str, Callable] = {}
+
+    def register(self, kind: str, factory: Callable = None):
+        def add(f):
+            if kind in self._factories:
+                raise ValueError(f"{self.what} {kind!r} is registered already")
+            self._factories[kind] = f
+            return f
+
+        return add if factory is None else add(factory)
+
+    def unregister(self, kind: str) -> None:
+        self._factories.pop(kind, None)
+
+    def build(self, spec: PartSpec, env: BuildEnv, *args, **kwargs):
+        factory = self._factories.get(spec.kind)
+        if factory is None:
+            raise KeyError(
+                f"no {self.what} named {spec.kind!r}; registered: {', '.join(sorted(self._factories))}"
+            )
+        return factory(spec, env, *args, **kwargs)
+
+    def kinds(self) -> list[str]:
+        return sorted(self._factories)
+
+
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+BLOCKS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")

@@ -1,0 +1,80 @@
+"""The model: parts assembled from a plan, run in the plan's order.
+
+Nothing here names an architecture.  ``Model`` builds one block per layer of the
+plan, collects the tensors they ask for, binds them after loading, reports the cache
+need of every run entry, and runs a step: embedding, the run order, and the final
+norm + head for the rows whose logits are wanted.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..weights.spec import TensorSpec
+from .base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, Stream
+from .plan import ModelPlan
+
+
+class Model:
+    def __init__(self, plan: ModelPlan, env: BuildEnv):
+        self.plan = plan
+        self.env = env
+        self.embedding = EMBEDDINGS.build(plan.embedding, env)
+        self.blocks = [BLOCKS.build(layer.block, env, layer) for layer in plan.layers]
+        self.final_norm = NORMS.build(plan.final_norm, env)
+        self.head = HEADS.build(plan.head, env)
+        self.bound = False
+
+    # ------------------------------------------------------------------ weights
+
+    def parts(self):
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        specs = []
+        for part in self.parts():
+            specs += part.tensor_specs()
+        return specs
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        for part in self.parts():
+            part.bind(tensors)
+        self.bound = True
+
+    # ------------------------------------------------------------------ cache needs
+
+    def cache_needs(self) -> list:
+        """Per run entry: the cache its mixer needs, or None (also for a borrowing entry)."""
+        needs = []
+        for entry in self.plan.order:
+            if entry.cache_of is not None:
+                needs.append(None)
+            else:
+                needs.append(self.blocks[entry.layer].mixer_part().cache_spec())
+        return needs
+
+    # ------------------------------------------------------------------ one step
+
+    def forward(self, step, cache) -> Optional[torch.Tensor]:
+        """Runs the rows of ``step`` through every run entry; returns float32 logits
+        ``[len(step.want_rows), vocab]`` or None when no row is wanted."""
+        if not self.bound:
+            raise RuntimeError("the model has no weights yet: load or bind them first")
+        stream = Stream(self.embedding.forward(step))
+        for pos, entry in enumerate(self.plan.order):
+            if entry.cache_of is None:
+                view = cache.view(pos)
+            else:
+                view = cache.view(entry.cache_of, owner=False)
+            self.blocks[entry.layer].forward(stream, step, view)
+        if step.num_wanted == 0:
+            return None
+        rows = step.want_rows
+        if stream.pending is not None:
+            delta, stream.pending = stream.pending, None
+            normed = self.final_norm.add_apply(stream.residual, delta, rows)
+        else:
+            normed = self.final_norm.apply(self.env.ops.gather_rows(stream.residual, rows))
+        return self.head.forward(normed)
