@@ -8,3 +8,20 @@ CUDA kernels for sm_100a (``csrc`` through ``kernels``).
 """
 
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # Imported lazily so that `import shiso_llm_b200` stays light (no torch import).
+    if name in ("LLM", "Output"):
+        from . import api
+
+        return getattr(api, name)
+    if name == "SamplingParams":
+        from .sampling.params import SamplingParams
+
+        return SamplingParams
+    if name in ("Engine", "EngineOptions", "StepEntry"):
+        from . import engine
+
+        return getattr(engine, name)
+    raise AttributeError(name)

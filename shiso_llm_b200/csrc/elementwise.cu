@@ -1,0 +1,129 @@
+// Row kernels: embedding gather, RMS norm, fused residual-add + RMS norm, SwiGLU.
+//
+// Formulas follow the reference's kernels: y = x * rsqrt(mean(x^2) + eps) * w with
+// the weight multiplying directly (kernels/cuda/generic/norm.cuh:39-95); the fused
+// close stores the sum and normalises the stored sum (norm.cuh:105-165);
+// silu(g) * u with silu(z) = z / (1 + exp(-z)) and no clamp
+// (kernels/cuda/generic/glu.cuh:35-57).  The residual stream is float in both
+// compute types, so the sum a + b is formed and kept in 32-bit.
+#include "common.cuh"
+
+// --------------------------------------------------------------------------- embedding
+
+template <typename WT>
+__global__ void embed_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
+                             float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    const bool valid = id >= 0 && id < vocab;  // the host refuses such ids; never read outside
+    const WT* row = table + (size_t)(valid ? id : 0) * hidden;
+    float* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? to_f32(row[i]) : 0.0f;
+}
+
+SHISO_API int shiso_embed(const int* ids, const void* table, int table_dtype, float* out,
+                          int tokens, int hidden, int vocab, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == SHISO_F32)
+        embed_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+    else if (table_dtype == SHISO_BF16)
+        embed_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+    else
+        return SHISO_ERR_DTYPE;
+    return launch_status();
+}
+
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,
+                                   float* __restrict__ out, int hidden) {
+    const float* s = src + (size_t)rows[blockIdx.x] * hidden;
+    float* d = out + (size_t)blockIdx.x * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) d[i] = s[i];
+}
+
+SHISO_API int shiso_gather_rows(const float* src, const int* rows, float* out, int count, int hidden,
+                                cudaStream_t stream) {
+    if (count <= 0) return SHISO_OK;
+    gather_rows_kernel<<<count, 256, 0, stream>>>(src, rows, out, hidden);
+    return launch_status();
+}
+
+// --------------------------------------------------------------------------- RMS norm
+
+// One block per row.  With `delta`: sum = residual + delta is formed in float; when
+// `rows` is null the sum is written back to `residual` (the stream moves on), else
+// row blockIdx.x of the output is the norm of source row rows[blockIdx.x] and the
+// residual is left alone (used for the final norm of the wanted rows only).
+template <typename AT>
+__global__ void rmsnorm_kernel(float* __restrict__ residual, const AT* __restrict__ delta,
+                               const int* __restrict__ rows, const float* __restrict__ w,
+                               AT* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = residual + (size_t)src_row * hidden;
+    const AT* d = delta ? delta + (size_t)src_row * hidden : nullptr;
+    AT* o = out + (size_t)blockIdx.x * hidden;
+    extern __shared__ float row_cache[];  // hidden floats: the summed row
+
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = r[i];
+        if (d) {
+            v += to_f32(d[i]);
+            if (!rows) r[i] = v;
+        }
+        row_cache[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<AT>(row_cache[i] * inv * w[i]);
+}
+
+SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows, const float* w, void* out,
+                            int act_dtype, int out_rows, int hidden, float eps, cudaStream_t stream) {
+    if (out_rows <= 0) return SHISO_OK;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return SHISO_ERR_SHAPE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (act_dtype == SHISO_F32) {
+        auto k = rmsnorm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<out_rows, threads, smem, stream>>>(residual, (const float*)delta, rows, w, (float*)out, hidden, eps);
+    } else if (act_dtype == SHISO_BF16) {
+        auto k = rmsnorm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<out_rows, threads, smem, stream>>>(residual, (const __nv_bfloat16*)delta, rows, w, (__nv_bfloat16*)out, hidden, eps);
+    } else {
+        return SHISO_ERR_DTYPE;
+    }
+    return launch_status();
+}
+
+// --------------------------------------------------------------------------- SwiGLU
+
+template <typename AT>
+__global__ void swiglu_kernel(const AT* __restrict__ gate_up, AT* __restrict__ out, int inter, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / inter;
+    const int c = (int)(i - t * inter);
+    const AT* row = gate_up + (size_t)t * 2 * inter;
+    const float g = to_f32(row[c]);
+    const float u = to_f32(row[inter + c]);
+    const float silu = g / (1.0f + expf(-g));
+    out[i] = from_f32<AT>(silu * u);
+}
+
+SHISO_API int shiso_swiglu(const void* gate_up, void* out, int act_dtype, int tokens, int inter, cudaStream_t stream) {
+    const long long total = (long long)tokens * inter;
+    if (total <= 0) return SHISO_OK;
+    const unsigned blocks = ceil_div_u(total, 256);
+    if (act_dtype == SHISO_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (act_dtype == SHISO_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    else
+        return SHISO_ERR_DTYPE;
+    return launch_status();
+}

@@ -1,0 +1,225 @@
+// Token selection on the device, one block per row of float logits.
+//
+// Greedy: the lowest id attaining the highest finite logit; a row with no finite entry
+// yields id 0 (crates/shiso-engine/src/sampling.rs:91-154).
+//
+// Stochastic: the keyed rule of the reference (sampling.rs:720-862): over the candidates
+// the request allows the token is argmax(logit / temperature + G(key, position, id)) with G
+// a Gumbel variate from a hash of the three, so the draw depends only on the row, the
+// key and the position - not on the batch or on how the work was cut.  The candidate set
+// is described by thresholds so that no sort is needed:
+//   top-k  keeps every token whose logit is >= the k-th largest logit (ties stay in);
+//   top-p  keeps every token whose logit is >= the logit at which the mass, summed from
+//          the largest logit down over the top-k set, first reaches top_p of that set;
+//   min-p  keeps tokens with exp((l - max) / T) >= min_p.
+// Masses are summed as 2^-40 fixed-point integers, so the sums and therefore the
+// thresholds do not depend on the order in which threads add.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+
+struct Best {
+    float v;
+    int i;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ Best block_best(Best mine, Best* scratch /* 32 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, mine.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, mine.i, o);
+        mine = better(mine, other);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = mine;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    Best r = (lane < nwarps) ? scratch[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, r.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, r.i, o);
+        r = better(r, other);
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    __shared__ Best scratch[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    Best mine{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (isfinite(v) && v > mine.v) mine = Best{v, i};  // ascending i: the first maximum stays
+    }
+    const Best r = block_best(mine, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = (r.i == 0x7fffffff) ? 0 : r.i;
+}
+
+// ---- keyed noise ------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x ^= x >> 30;
+    x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27;
+    x *= 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+// A uniform in (0, 1) from (key, position, id): three rounds of the splitmix64 finalizer,
+// the top 24 bits, offset half a step from both ends (sampling.rs:893-912).
+__device__ __forceinline__ float keyed_uniform(unsigned long long key, unsigned position, unsigned id) {
+    unsigned long long x = mix64(key + 0x9E3779B97F4A7C15ull);
+    x = mix64(x ^ ((unsigned long long)position * 0xD1B54A32D192ED03ull));
+    x = mix64(x ^ (unsigned long long)id);
+    return ((float)(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+// Order-preserving map float -> uint32 (larger float, larger key).
+__device__ __forceinline__ unsigned orderable(float v) {
+    const unsigned b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long fixed_mass(float scaled /* (l - max) / T <= 0 */) {
+    return (unsigned long long)(expf(scaled) * 1099511627776.0f);  // 2^40
+}
+
+// Finds the largest key K such that sum over {key >= K} of weight >= target, by four
+// 8-bit radix passes; weight is 1 (count, for top-k) or the fixed-point mass (top-p).
+// Only entries with key >= floor_key take part.  All threads return the same K.
+template <bool MASS>
+__device__ unsigned radix_threshold(const float* __restrict__ row, int vocab, float max_logit, float inv_t,
+                                    unsigned floor_key, unsigned long long target,
+                                    unsigned long long* hist /* 256 */, unsigned* shared_u /* 2 */) {
+    unsigned prefix = 0, prefix_mask = 0;
+    unsigned long long above = 0;  // weight of entries whose key is above the current prefix bucket
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (!isfinite(v)) continue;
+            const unsigned key = orderable(v);
+            if (key < floor_key || (key & prefix_mask) != prefix) continue;
+            const unsigned long long wgt = MASS ? fixed_mass((v - max_logit) * inv_t) : 1ull;
+            atomicAdd(&hist[(key >> shift) & 0xffu], wgt);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long run = above;
+            int pick = 0;
+            for (int b = 255; b >= 0; --b) {
+                if (run + hist[b] >= target) {
+                    pick = b;
+                    break;
+                }
+                run += hist[b];
+                pick = b;  // falls to bucket 0 when the target is never reached
+            }
+            shared_u[0] = (unsigned)pick;
+            // 64-bit value handed back through two words
+            hist[0] = run;
+        }
+        __syncthreads();
+        const unsigned pick = shared_u[0];
+        above = hist[0];
+        __syncthreads();
+        prefix |= pick << shift;
+        prefix_mask |= 0xffu << shift;
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature, const int* __restrict__ top_k,
+              const float* __restrict__ top_p, const float* __restrict__ min_p,
+              const long long* __restrict__ keys, const int* __restrict__ positions, int* __restrict__ out, int vocab) {
+    __shared__ Best scratch[32];
+    __shared__ unsigned long long hist[256];
+    __shared__ unsigned shared_u[2];
+    __shared__ unsigned long long total_mass;
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+
+    Best mine{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (isfinite(v) && v > mine.v) mine = Best{v, i};
+    }
+    const Best top = block_best(mine, scratch);
+    const float temp = temperature[r];
+    if (top.i == 0x7fffffff || !(temp > 0.0f)) {
+        if (threadIdx.x == 0) out[r] = (top.i == 0x7fffffff) ? 0 : top.i;
+        return;
+    }
+    const float inv_t = 1.0f / temp;
+    float p_keep = top_p[r];
+    if (!(p_keep > 0.0f) || p_keep > 1.0f) p_keep = 1.0f;
+    const float floor_p = fmaxf(min_p[r], 0.0f);
+    int k = top_k[r];
+    if (k < 0) k = 0;
+    if (k > vocab) k = vocab;
+
+    unsigned floor_key = 0;  // keep keys >= floor_key
+    if (k > 0) floor_key = radix_threshold<false>(row, vocab, top.v, inv_t, 0u, (unsigned long long)k, hist, shared_u);
+    if (p_keep < 1.0f) {
+        if (threadIdx.x == 0) total_mass = 0;
+        __syncthreads();
+        unsigned long long part = 0;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (isfinite(v) && orderable(v) >= floor_key) part += fixed_mass((v - top.v) * inv_t);
+        }
+        atomicAdd(&total_mass, part);
+        __syncthreads();
+        // smallest integer target with target / total >= p_keep, formed in double
+        const unsigned long long target = (unsigned long long)ceil((double)p_keep * (double)total_mass);
+        const unsigned nucleus = radix_threshold<true>(row, vocab, top.v, inv_t, floor_key, target, hist, shared_u);
+        if (nucleus > floor_key) floor_key = nucleus;
+    }
+    const float log_floor = floor_p > 0.0f ? logf(floor_p) : -INFINITY;
+
+    const unsigned long long key = (unsigned long long)keys[r];
+    const unsigned position = (unsigned)positions[r];
+    Best pick{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (!isfinite(v) || orderable(v) < floor_key) continue;
+        const float scaled = (v - top.v) * inv_t;
+        if (scaled < log_floor && i != top.i) continue;
+        const float u = keyed_uniform(key, position, (unsigned)i);
+        const float score = scaled - logf(-logf(u));
+        if (score > pick.v) pick = Best{score, i};
+    }
+    const Best chosen = block_best(pick, scratch);
+    if (threadIdx.x == 0) out[r] = (chosen.i == 0x7fffffff) ? top.i : chosen.i;
+}
+
+}  // namespace
+
+SHISO_API int shiso_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+    if (rows <= 0) return SHISO_OK;
+    if (vocab <= 0) return SHISO_ERR_SHAPE;
+    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab);
+    return launch_status();
+}
+
+SHISO_API int shiso_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                           const float* min_p, const long long* keys, const int* positions, int* out, int rows,
+                           int vocab, cudaStream_t stream) {
+    if (rows <= 0) return SHISO_OK;
+    if (vocab <= 0) return SHISO_ERR_SHAPE;
+    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, temperature, top_k, top_p, min_p, keys, positions, out, vocab);
+    return launch_status();
+}

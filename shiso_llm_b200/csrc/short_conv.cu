@@ -1,0 +1,111 @@
+// Gated short convolution over the rows of one step, every sequence with its own state.
+//
+// proj[t] = [b | c | x] (3H wide).  u = b * x is the gated input; the request's state
+// keeps the last taps-1 values of u, oldest first, in float
+// (kernels/metal/dense/dense_short_conv.metal:10-15,55,61-67).
+//   y[t, ch] = c[t, ch] * (sum_j w[ch, j] * u[t - (taps-1) + j, ch] + bias[ch])
+// with u before the portion's first row taken from the state.  The reference walks a
+// portion serially, one thread a channel (.metal:45-60); here the output kernel is
+// parallel over rows and channels, and a second kernel rewrites the states afterwards
+// (stream order guarantees every read of the old state has finished).
+//
+// The sum runs j = 0 .. taps-1 in that order for every row, so a row's result does not
+// depend on where the step was cut.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 8;
+
+// u at relative time `rel` of a sequence whose rows start at `first`: from this step's
+// rows when rel >= 0, else from the state (index taps-1+rel).
+template <typename AT>
+__device__ __forceinline__ float gated_input(const AT* __restrict__ proj, const float* __restrict__ state_row,
+                                             int first, int rel, int ch, int hidden, int taps, long long state_stride_t) {
+    if (rel >= 0) {
+        const AT* row = proj + (size_t)(first + rel) * 3 * hidden;
+        return to_f32(row[ch]) * to_f32(row[2 * hidden + ch]);
+    }
+    return state_row[(size_t)(taps - 1 + rel) * state_stride_t + ch];
+}
+
+template <typename AT>
+__global__ void short_conv_out_kernel(const AT* __restrict__ proj, const float* __restrict__ w,
+                                      const float* __restrict__ bias, const float* __restrict__ state,
+                                      long long slot_stride, const int* __restrict__ seq_of_token,
+                                      const int* __restrict__ q_start, const int* __restrict__ slots,
+                                      AT* __restrict__ y, int hidden, int taps) {
+    const int t = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (ch >= hidden) return;
+    const int s = seq_of_token[t];
+    const int first = q_start[s];
+    const float* state_row = state + (size_t)slots[s] * slot_stride;
+    const int rel_now = t - first;
+    float acc = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int rel = rel_now - (taps - 1) + j;
+        const float u = gated_input(proj, state_row, first, rel, ch, hidden, taps, hidden);
+        acc = fmaf(w[(size_t)ch * taps + j], u, acc);
+    }
+    if (bias) acc += bias[ch];
+    const float c = to_f32(proj[(size_t)t * 3 * hidden + hidden + ch]);
+    y[(size_t)t * hidden + ch] = from_f32<AT>(c * acc);
+}
+
+// New state = the last taps-1 values of (old state ++ this step's u).  One thread owns a
+// (sequence, channel) pair and reads everything it needs before it writes.
+template <typename AT>
+__global__ void short_conv_state_kernel(const AT* __restrict__ proj, float* __restrict__ state,
+                                        long long slot_stride, const int* __restrict__ q_start,
+                                        const int* __restrict__ slots, int hidden, int taps) {
+    const int s = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (ch >= hidden) return;
+    const int first = q_start[s];
+    const int n = q_start[s + 1] - first;
+    float* state_row = state + (size_t)slots[s] * slot_stride;
+    float next[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j) {
+        if (j < taps - 1) {
+            const int rel = n - (taps - 1) + j;
+            next[j] = gated_input(proj, state_row, first, rel, ch, hidden, taps, hidden);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+        if (j < taps - 1) state_row[(size_t)j * hidden + ch] = next[j];
+}
+
+}  // namespace
+
+// state: float [slots, taps-1, hidden] with `slot_stride` floats between slots (the rows
+// of one slot are contiguous).
+SHISO_API int shiso_short_conv(const void* proj, int act_dtype, const float* w, const float* bias, float* state,
+                               long long slot_stride, const int* seq_of_token, const int* q_start,
+                               const int* slots, void* y, int tokens, int seqs, int hidden, int taps,
+                               int update_state, cudaStream_t stream) {
+    if (tokens <= 0 || seqs <= 0) return SHISO_OK;
+    if (taps < 2 || taps > MAX_TAPS) return SHISO_ERR_SHAPE;
+    const int threads = 128;
+    dim3 grid_out(tokens, ceil_div_u(hidden, threads));
+    dim3 grid_state(seqs, ceil_div_u(hidden, threads));
+    if (act_dtype == SHISO_F32) {
+        short_conv_out_kernel<float><<<grid_out, threads, 0, stream>>>(
+            (const float*)proj, w, bias, state, slot_stride, seq_of_token, q_start, slots, (float*)y, hidden, taps);
+        if (update_state)
+            short_conv_state_kernel<float><<<grid_state, threads, 0, stream>>>(
+                (const float*)proj, state, slot_stride, q_start, slots, hidden, taps);
+    } else if (act_dtype == SHISO_BF16) {
+        short_conv_out_kernel<__nv_bfloat16><<<grid_out, threads, 0, stream>>>(
+            (const __nv_bfloat16*)proj, w, bias, state, slot_stride, seq_of_token, q_start, slots,
+            (__nv_bfloat16*)y, hidden, taps);
+        if (update_state)
+            short_conv_state_kernel<__nv_bfloat16><<<grid_state, threads, 0, stream>>>(
+                (const __nv_bfloat16*)proj, state, slot_stride, q_start, slots, hidden, taps);
+    } else {
+        return SHISO_ERR_DTYPE;
+    }
+    return launch_status();
+}

@@ -138,6 +138,8 @@ class Engine:
             seen.add(e.request)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.request!r}: a step brings at least one token")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab_size:
+                raise ValueError(f"request {e.request!r}: a token id lies outside the vocabulary of {self.vocab_size}")
         # Admission check for the whole step before anything is claimed.
         self._check_room(entries)
         starts = []

@@ -1,0 +1,68 @@
+"""Loads the kernel library and declares its C entry points.
+
+There is no fallback: if the library cannot be built or loaded, or no CUDA device is
+present, ``library()`` raises and every op with it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from .build import BuildError, library_path
+
+_LIB = None
+
+P = c_void_p
+I = c_int
+F = c_float
+LL = c_longlong
+
+_SIGNATURES = {
+    "shiso_embed": [P, P, I, P, I, I, I, P],
+    "shiso_gather_rows": [P, P, P, I, I, P],
+    "shiso_rmsnorm": [P, P, P, P, P, I, I, I, F, P],
+    "shiso_swiglu": [P, P, I, I, I, P],
+    "shiso_gemm_simple": [P, I, P, I, P, P, I, I, I, I, P],
+    "shiso_short_conv": [P, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
+    "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
+    "shiso_argmax": [P, P, I, I, P],
+    "shiso_sample": [P, P, P, P, P, P, P, P, I, I, P],
+}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def library():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    try:
+        path = library_path()
+    except BuildError as e:
+        raise KernelLibraryError(f"the CUDA kernels are required and could not be built: {e}") from e
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from e
+    for name, argtypes in _SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:
+            raise KernelLibraryError(f"{path} does not export {name}; rebuild it") from e
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    _LIB = lib
+    return lib
+
+
+def declare(name: str, argtypes) -> None:
+    """Declares one more entry point (used by kernels added in their own files)."""
+    _SIGNATURES[name] = argtypes
+    if _LIB is not None:
+        fn = getattr(_LIB, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int

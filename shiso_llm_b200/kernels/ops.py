@@ -1,0 +1,271 @@
+"""The kernel table: one Python function per CUDA kernel, launched on the current stream.
+
+Every function checks shapes, types, contiguity and device, then calls the C launcher
+with raw pointers.  Nothing here computes on the CPU and nothing calls a library
+routine for the model's arithmetic; if the extension cannot be loaded the first call
+raises.  Inputs must be CUDA tensors.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .library import KernelLibraryError, library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+# How many kernels were launched through this table (bench.py reports it).
+launch_count = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_ERRORS = {
+    1001: "unsupported element type",
+    1002: "unsupported shape",
+    1003: "misaligned pointer or stride",
+    1004: "unsupported combination",
+}
+
+
+def require() -> None:
+    """Loads the extension now, or raises with the reason."""
+    if not torch.cuda.is_available():
+        raise KernelLibraryError("no CUDA device: this engine has no CPU path")
+    library()
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not float32 or bfloat16") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor, got one on {t.device}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: expected a contiguous tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name}: expected {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _done(status: int, what: str, launches: int = 1) -> None:
+    global launch_count
+    if status != 0:
+        why = _ERRORS.get(status)
+        if why is None:
+            why = f"CUDA error {status} at launch"
+        raise KernelError(f"{what}: {why} (status {status})")
+    launch_count += launches
+
+
+# --------------------------------------------------------------------------- rows
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    _check(ids, "ids", torch.int32, 1)
+    _check(table, "embedding table", None, 2)
+    tokens, (vocab, hidden) = ids.shape[0], table.shape
+    out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    _done(library().shiso_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), tokens, hidden, vocab, _stream()), "embed")
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _check(x, "x", torch.float32, 2)
+    _check(rows, "rows", torch.int32, 1)
+    out = torch.empty((rows.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
+    _done(library().shiso_gather_rows(_ptr(x), _ptr(rows), _ptr(out), rows.shape[0], x.shape[1], _stream()), "gather_rows")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    return add_rmsnorm(x, None, w, eps, out_dtype, None)
+
+
+def add_rmsnorm(residual, delta, w, eps, out_dtype, rows=None):
+    """``residual`` float32 [T, H]; ``delta`` [T, H] in the output type or None; returns
+    norm(residual + delta).  Without ``rows`` the sum is stored back into ``residual``."""
+    _check(residual, "residual", torch.float32, 2)
+    _check(w, "norm weight", torch.float32, 1)
+    tokens, hidden = residual.shape
+    if w.shape[0] != hidden:
+        raise KernelError(f"norm weight has {w.shape[0]} entries for rows of {hidden}")
+    if delta is not None:
+        _check(delta, "delta", out_dtype, 2)
+        if delta.shape != residual.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match the residual {tuple(residual.shape)}")
+    out_rows = tokens
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        out_rows = rows.shape[0]
+    out = torch.empty((out_rows, hidden), dtype=out_dtype, device=residual.device)
+    status = library().shiso_rmsnorm(
+        _ptr(residual), _ptr(delta), _ptr(rows), _ptr(w), _ptr(out), _code(out), out_rows, hidden, float(eps), _stream()
+    )
+    _done(status, "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    _check(gate_up, "gate_up", None, 2)
+    tokens, two_inter = gate_up.shape
+    if two_inter % 2:
+        raise KernelError(f"gate_up rows of {two_inter} cannot be split in two halves")
+    out = torch.empty((tokens, two_inter // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _done(library().shiso_swiglu(_ptr(gate_up), _ptr(out), _code(gate_up), tokens, two_inter // 2, _stream()), "swiglu")
+    return out
+
+
+# --------------------------------------------------------------------------- matrix products
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x[T, K] @ w[N, K]^T`` with float accumulation."""
+    _check(x, "x", None, 2)
+    _check(w, "w", None, 2)
+    tokens, k = x.shape
+    n, k2 = w.shape
+    if k != k2:
+        raise KernelError(f"x has rows of {k}, the matrix has rows of {k2}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
+    status = library().shiso_gemm_simple(
+        _ptr(x), _code(x), _ptr(w), _code(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _stream()
+    )
+    _done(status, "linear")
+    return out
+
+
+# --------------------------------------------------------------------------- short convolution
+
+
+def short_conv(proj, taps, bias, state, step):
+    """``proj[T, 3H]`` -> ``y[T, H]``; ``state`` is the float32 view ``[slots, taps-1, H]`` of
+    the slot buffer (rows of one slot contiguous) and is updated for the step's sequences."""
+    _check(proj, "proj", None, 2)
+    _check(taps, "conv taps", torch.float32, 2)
+    tokens, h3 = proj.shape
+    hidden, n_taps = taps.shape
+    if h3 != 3 * hidden:
+        raise KernelError(f"proj rows of {h3} are not 3 x {hidden}")
+    if state.dtype != torch.float32 or not state.is_cuda or state.dim() != 3:
+        raise KernelError("conv state: expected a float32 CUDA tensor [slots, taps-1, hidden]")
+    if state.shape[1:] != (n_taps - 1, hidden) or state.stride(2) != 1 or state.stride(1) != hidden:
+        raise KernelError(f"conv state of shape {tuple(state.shape)} / strides {state.stride()} does not fit {n_taps} taps x {hidden}")
+    if bias is not None:
+        _check(bias, "conv bias", torch.float32, 1)
+    y = torch.empty((tokens, hidden), dtype=proj.dtype, device=proj.device)
+    status = library().shiso_short_conv(
+        _ptr(proj), _code(proj), _ptr(taps), _ptr(bias), state.data_ptr(), state.stride(0),
+        _ptr(step.seq_of_token), _ptr(step.q_start), _ptr(step.state_slots), _ptr(y),
+        tokens, step.num_seqs, hidden, n_taps, 1, _stream(),
+    )
+    _done(status, "short_conv", 2)
+    return y
+
+
+# --------------------------------------------------------------------------- attention
+
+
+def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
+                       k_cache, v_cache, block_table, page_size, store):
+    _check(qkv, "qkv", None, 2)
+    tokens, width = qkv.shape
+    if width != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"qkv rows of {width} are not ({heads} + 2 x {kv_heads}) x {head_dim}")
+    for name, t in (("q norm weight", q_w), ("k norm weight", k_w)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != head_dim:
+                raise KernelError(f"{name} has {t.shape[0]} entries for heads of {head_dim}")
+    if rotary_dim:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.shape[0]} entries for a rotation over {rotary_dim}")
+    _check(block_table, "block table", torch.int32, 2)
+    do_store = bool(store) and kv_heads > 0
+    if do_store:
+        for name, t in (("k cache", k_cache), ("v cache", v_cache)):
+            _check(t, name, qkv.dtype, 4)
+            if t.shape[1:] != (page_size, kv_heads, head_dim):
+                raise KernelError(f"{name} of shape {tuple(t.shape)} does not fit pages of {page_size} x {kv_heads} x {head_dim}")
+    q = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    status = library().shiso_qk_norm_rope_store(
+        _ptr(qkv), _code(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq) if rotary_dim else 0,
+        _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), block_table.shape[1],
+        _ptr(k_cache) if do_store else 0, _ptr(v_cache) if do_store else 0, _ptr(q),
+        tokens, heads, kv_heads, head_dim, int(rotary_dim), page_size, float(eps), int(do_store), _stream(),
+    )
+    _done(status, "qk_norm_rope_store")
+    return q
+
+
+def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step):
+    _check(q, "q", None, 2)
+    tokens = q.shape[0]
+    if q.shape[1] != heads * head_dim:
+        raise KernelError(f"q rows of {q.shape[1]} are not {heads} x {head_dim}")
+    for name, t in (("k cache", k_cache), ("v cache", v_cache)):
+        _check(t, name, q.dtype, 4)
+        if t.shape[1:] != (page_size, kv_heads, head_dim):
+            raise KernelError(f"{name} of shape {tuple(t.shape)} does not fit pages of {page_size} x {kv_heads} x {head_dim}")
+    _check(block_table, "block table", torch.int32, 2)
+    out = torch.empty_like(q)
+    status = library().shiso_paged_attention(
+        _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(step.positions), _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, head_dim,
+        page_size, float(scale), int(window), _stream(),
+    )
+    _done(status, "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    _check(logits, "logits", torch.float32, 2)
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _done(library().shiso_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, keys, positions) -> torch.Tensor:
+    """Keyed sampling, one row per request: float32 ``temperature``/``top_p``/``min_p``,
+    int32 ``top_k`` (0 = off) and ``positions``, int64 ``keys``, all of length rows."""
+    _check(logits, "logits", torch.float32, 2)
+    rows = logits.shape[0]
+    for name, t, dt in (
+        ("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+        ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32),
+        ("keys", keys, torch.int64), ("positions", positions, torch.int32),
+    ):
+        _check(t, name, dt, 1)
+        if t.shape[0] != rows:
+            raise KernelError(f"{name} has {t.shape[0]} entries for {rows} rows")
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    status = library().shiso_sample(
+        _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(keys), _ptr(positions),
+        _ptr(out), rows, logits.shape[1], _stream(),
+    )
+    _done(status, "sample")
+    return out

@@ -1,0 +1,50 @@
+"""Sampling on the device for the rows of one step."""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .params import SamplingParams
+
+
+class DeviceSampler:
+    """Turns per-request parameters into the arrays the sampling kernel reads and picks one
+    token per logits row.  Rows that are all greedy take the argmax kernel."""
+
+    def __init__(self, ops, device):
+        self.ops = ops
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]) -> list[int]:
+        """``logits[R, V]`` float32 on the device; ``positions[r]`` is the position the
+        sampled token will occupy in its sequence.  Returns host ints."""
+        if logits.shape[0] != len(params):
+            raise ValueError(f"{logits.shape[0]} rows of logits for {len(params)} requests")
+        if all(p.greedy for p in params):
+            return self.ops.argmax(logits).tolist()
+        clamped = [p.clamped() for p in params]
+        host = torch.tensor(
+            [[c[0] if not p.greedy else 0.0, c[2], c[3]] for c, p in zip(clamped, params)], dtype=torch.float32
+        )
+        ints = torch.tensor([[c[1], pos] for c, pos in zip(clamped, positions)], dtype=torch.int32)
+        keys = torch.tensor([_as_signed(p.seed) for p in params], dtype=torch.int64)
+        dev = self.device
+        floats = host.to(dev, non_blocking=True)
+        ints = ints.to(dev, non_blocking=True)
+        picks = self.ops.sample(
+            logits,
+            floats[:, 0].contiguous(),
+            ints[:, 0].contiguous(),
+            floats[:, 1].contiguous(),
+            floats[:, 2].contiguous(),
+            keys.to(dev, non_blocking=True),
+            ints[:, 1].contiguous(),
+        )
+        return picks.tolist()
+
+
+def _as_signed(seed: int) -> int:
+    seed &= 0xFFFFFFFFFFFFFFFF
+    return seed - (1 << 64) if seed >= (1 << 63) else seed

@@ -1,0 +1,249 @@
+"""Every CUDA kernel alone against its plain PyTorch reference (tests/fake_kernels.py),
+at sizes other than the engine tests use: widths that are no power of two, head sizes in
+steps of 16, odd numbers of heads and groups, several sequences per launch, pages out of
+order, non-zero starting states.
+"""
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import fake_kernels as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from shiso_llm_b200.kernels import ops as table
+
+    table.require()
+    return table
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def close(got, want, dtype, what, rel32=2e-6, scale=None):
+    got, want = got.double().cpu(), want.double().cpu()
+    s = scale if scale is not None else max(want.abs().max().item(), 1e-6)
+    err = (got - want).abs().max().item()
+    # bfloat16 results carry one rounding of the output (2^-9 relative) plus the float32 sums
+    bound = rel32 * s if dtype == torch.float32 else 2 ** -8 * s
+    assert err <= bound, f"{what}: error {err:.3e} > {bound:.3e} (scale {s:.3e})"
+
+
+def make_step(q_lens, starts, page_size, num_pages, seed, num_slots=None, device="cuda"):
+    """Step metadata with shuffled, non-contiguous pages for each sequence."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    S = len(q_lens)
+    width = max(-(-(s + n) // page_size) for s, n in zip(starts, q_lens))
+    table = torch.full((S, width), -1, dtype=torch.int32)
+    for i, (s, n) in enumerate(zip(starts, q_lens)):
+        need = -(-(s + n) // page_size)
+        for b in range(need):
+            table[i, b] = perm.pop()
+    q_start = [0]
+    for n in q_lens:
+        q_start.append(q_start[-1] + n)
+    pos, seq = [], []
+    for i, (s, n) in enumerate(zip(starts, q_lens)):
+        pos += list(range(s, s + n))
+        seq += [i] * n
+    slots = torch.randperm(num_slots or S, generator=g)[:S].to(torch.int32)
+
+    def dev(x):
+        return torch.as_tensor(x, dtype=torch.int32).to(device)
+
+    cpu = SimpleNamespace(
+        num_tokens=q_start[-1], num_seqs=S, positions=dev(pos).cpu(), seq_of_token=dev(seq).cpu(),
+        q_start=dev(q_start).cpu(), state_slots=slots, start_pos=dev(starts).cpu(),
+    )
+    gpu = SimpleNamespace(
+        num_tokens=q_start[-1], num_seqs=S, positions=dev(pos), seq_of_token=dev(seq),
+        q_start=dev(q_start), state_slots=slots.to(device), start_pos=dev(starts),
+    )
+    return cpu, gpu, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    table = rnd((777, 200), dtype, 1)
+    ids = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32)
+    got = ops().embed(ids.cuda(), table.cuda())
+    assert torch.equal(got.cpu(), ref.embed(ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [96, 200, 2048, 5000])
+def test_rmsnorm_and_fused_add(dtype, hidden):
+    x = rnd((7, hidden), torch.float32, 2, 3.0)
+    delta = rnd((7, hidden), dtype, 3)
+    w = 1.0 + 0.2 * rnd((hidden,), torch.float32, 4)
+    eps = 1e-6
+    close(ops().rmsnorm(x.cuda(), w.cuda(), eps, dtype), ref.rmsnorm(x, w, eps, dtype), dtype, "rmsnorm")
+    res_gpu, res_cpu = x.clone().cuda(), x.clone()
+    got = ops().add_rmsnorm(res_gpu, delta.cuda(), w.cuda(), eps, dtype)
+    want = ref.add_rmsnorm(res_cpu, delta, w, eps, dtype)
+    close(got, want, dtype, "add_rmsnorm")
+    assert torch.equal(res_gpu.cpu(), res_cpu), "the stored sum must be the float32 sum"
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    res_gpu2 = x.clone().cuda()
+    got = ops().add_rmsnorm(res_gpu2, delta.cuda(), w.cuda(), eps, dtype, rows.cuda())
+    want = ref.add_rmsnorm(x.clone(), delta, w, eps, dtype, rows)
+    close(got, want, dtype, "add_rmsnorm rows")
+    assert torch.equal(res_gpu2.cpu(), x), "with rows the residual is left alone"
+    close(ops().gather_rows(x.cuda(), rows.cuda()), ref.gather_rows(x, rows), torch.float32, "gather_rows", rel32=0.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    gu = rnd((9, 2 * 300), dtype, 5, 2.0)
+    close(ops().swiglu(gu.cuda()), ref.swiglu(gu), dtype, "swiglu")
+
+
+@pytest.mark.parametrize("shape", [(1, 96, 64), (5, 1000, 96), (67, 130, 257), (130, 65, 48)])
+@pytest.mark.parametrize("xw", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_linear(shape, xw):
+    T, N, K = shape
+    xd, wd = xw
+    x, w = rnd((T, K), xd, 6), rnd((N, K), wd, 7, 0.05)
+    for out_dtype in (xd, torch.float32):
+        got = ops().linear(x.cuda(), w.cuda(), out_dtype)
+        close(got, ref.linear(x, w, out_dtype), out_dtype, f"linear {shape} {xw} -> {out_dtype}", rel32=1e-5)
+
+
+def test_linear_rows_do_not_depend_on_the_batch():
+    x, w = rnd((70, 200), torch.float32, 8), rnd((150, 200), torch.float32, 9)
+    full = ops().linear(x.cuda(), w.cuda(), torch.float32)
+    one = ops().linear(x[33:34].contiguous().cuda(), w.cuda(), torch.float32)
+    assert torch.equal(full[33:34], one)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps,hidden,bias", [(3, 300, False), (4, 96, True), (2, 130, True), (8, 64, False)])
+def test_short_conv(dtype, taps, hidden, bias):
+    q_lens, starts = [4, 1, 3, 9, 2], [0, 5, 2, 0, 7]
+    cpu, gpu, _ = make_step(q_lens, starts, 4, 32, 10, num_slots=7)
+    T = cpu.num_tokens
+    proj = rnd((T, 3 * hidden), dtype, 11)
+    w = rnd((hidden, taps), torch.float32, 12)
+    b = rnd((hidden,), torch.float32, 13) if bias else None
+    # a slot buffer wider than this layer's state, as the cache manager lays it out
+    buf = rnd((7, 50 + (taps - 1) * hidden + 9), torch.float32, 14)
+    state_cpu = buf.clone()[:, 50 : 50 + (taps - 1) * hidden].unflatten(1, (taps - 1, hidden))
+    buf_gpu = buf.clone().cuda()
+    state_gpu = buf_gpu[:, 50 : 50 + (taps - 1) * hidden].unflatten(1, (taps - 1, hidden))
+    want = ref.short_conv(proj, w, b, state_cpu, cpu)
+    got = ops().short_conv(proj.cuda(), w.cuda(), b.cuda() if bias else None, state_gpu, gpu)
+    close(got, want, dtype, "short_conv y", rel32=4e-6)
+    # the new state is a copy of products of two stored values: exact in float32
+    assert torch.allclose(state_gpu.cpu(), state_cpu, rtol=0, atol=0 if dtype == torch.float32 else 1e-7)
+    untouched = torch.ones(7, dtype=torch.bool)
+    untouched[cpu.state_slots.long()] = False
+    assert torch.equal(buf_gpu.cpu()[untouched], buf[untouched]), "slots of other requests must not change"
+    assert torch.equal(buf_gpu.cpu()[:, :50], buf[:, :50]) and torch.equal(buf_gpu.cpu()[:, -9:], buf[:, -9:])
+
+
+def test_short_conv_portions_match_whole():
+    """Chunks [4, 1, 3] against one run of 8 from the same starting state."""
+    hidden, taps = 300, 3
+    proj = rnd((8, 3 * hidden), torch.float32, 15)
+    w = rnd((hidden, taps), torch.float32, 16)
+    start = rnd((1, taps - 1, hidden), torch.float32, 17)
+    cpu, gpu, _ = make_step([8], [0], 4, 8, 18, num_slots=1)
+    s_whole = start.clone().cuda()
+    y_whole = ops().short_conv(proj.cuda(), w.cuda(), None, s_whole, gpu)
+    s_cut = start.clone().cuda()
+    ys, at = [], 0
+    for n in (4, 1, 3):
+        _, g, _ = make_step([n], [at], 4, 8, 19, num_slots=1)
+        ys.append(ops().short_conv(proj[at : at + n].contiguous().cuda(), w.cuda(), None, s_cut, g))
+        at += n
+    assert torch.equal(torch.cat(ys), y_whole)
+    assert torch.equal(s_cut, s_whole)
+
+
+CASES = [  # heads, kv_heads, head_dim, page_size, rotary_dim
+    (4, 2, 16, 4, 16),
+    (3, 1, 32, 16, 32),
+    (6, 3, 48, 8, 32),
+    (5, 5, 80, 16, 80),
+    (8, 2, 64, 16, 64),
+    (2, 1, 256, 4, 128),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_norm_rope_store_then_attention(dtype, case):
+    heads, kv_heads, d, page, rot = case
+    q_lens, starts = [5, 1, 40, 2], [0, 37, 3, 130]
+    num_pages = 64
+    cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 20)
+    T = cpu.num_tokens
+    qkv = rnd((T, (heads + 2 * kv_heads) * d), dtype, 21)
+    qw = 1.0 + 0.2 * rnd((d,), torch.float32, 22)
+    kw = 1.0 + 0.2 * rnd((d,), torch.float32, 23)
+    theta = 10000.0
+    inv_freq = (theta ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float()
+    eps = 1e-5
+    # caches start filled with earlier positions' keys and values
+    k0, v0 = rnd((num_pages, page, kv_heads, d), dtype, 24), rnd((num_pages, page, kv_heads, d), dtype, 25)
+    kc, vc = k0.clone(), v0.clone()
+    kg, vg = k0.clone().cuda(), v0.clone().cuda()
+    want_q = ref.qk_norm_rope_store(qkv, heads, kv_heads, d, qw, kw, eps, inv_freq, rot, cpu, kc, vc, table, page, True)
+    got_q = ops().qk_norm_rope_store(
+        qkv.cuda(), heads, kv_heads, d, qw.cuda(), kw.cuda(), eps, inv_freq.cuda(), rot, gpu, kg, vg, table.cuda(), page, True
+    )
+    close(got_q, want_q, dtype, "q after norm and rotation", rel32=4e-6)
+    close(kg, kc, dtype, "k cache", rel32=4e-6)
+    assert torch.equal(vg.cpu(), vc), "values are stored raw"
+    written = (kc != k0).flatten(1).any(1)
+    assert torch.equal(kg.cpu()[~written], k0[~written]), "rows of other positions must not change"
+
+    scale = 1.0 / math.sqrt(d)
+    for window in (0, 7):
+        want = ref.paged_attention(want_q, heads, kv_heads, d, kc, vc, table, page, scale, window, cpu)
+        got = ops().paged_attention(want_q.cuda(), heads, kv_heads, d, kc.cuda(), vc.cuda(), table.cuda(), page, scale, window, gpu)
+        close(got, want, dtype, f"attention window {window}", rel32=4e-6)
+
+
+def test_attention_finds_a_far_key():
+    """One key among hundreds is made to stand out; the output must be (almost) its value."""
+    heads, kv_heads, d, page = 2, 1, 32, 16
+    n = 700
+    cpu, gpu, table = make_step([1], [n - 1], page, 64, 30)
+    k = rnd((64, page, kv_heads, d), torch.float32, 31, 0.1)
+    v = rnd((64, page, kv_heads, d), torch.float32, 32)
+    q = rnd((1, heads * d), torch.float32, 33, 0.1)
+    far = 3  # position 3, hundreds of keys back
+    row = table[0, far // page].item() * page + far % page
+    k.view(-1, kv_heads, d)[row, 0] = 40.0 * q[0, :d] / q[0, :d].norm()
+    q[0, :d] = 40.0 * q[0, :d] / q[0, :d].norm()
+    got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, 1.0, 0, gpu).cpu()
+    want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, 1.0, 0, cpu)
+    close(got, want, torch.float32, "far key", rel32=1e-5)
+    assert (got[0, :d] - v.view(-1, kv_heads, d)[row, 0]).abs().max() < 1e-3
+
+
+def test_argmax_ties_and_non_finite():
+    logits = rnd((5, 1000), torch.float32, 40)
+    logits[0, 17] = logits[0, 900] = 50.0  # tie: the lower id wins
+    logits[1, :] = float("-inf")  # nothing finite: id 0
+    logits[2, 3] = float("nan")
+    logits[3, 999] = 60.0
+    logits[4, 0] = float("inf")  # not finite, never chosen
+    got = ops().argmax(logits.cuda()).cpu().tolist()
+    want = []
+    for r in range(5):
+        row = logits[r].clone()
+        row[~torch.isfinite(row)] = float("-inf")
+        want.append(int(row.argmax()) if torch.isfinite(row).any() else 0)
+    assert got == want and got[0] == 17 and got[1] == 0 and got[3] == 999
