@@ -1,0 +1,365 @@
+#!/usr/bin/env python3
+"""Serving benchmark: decode and prefill throughput of an LFM2-1.2B-shaped model on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 (a step = one
+decode step over the cache of 2,048-token prompts), timed on the device with CUDA events
+around K steps; ``e2e`` is the same through the Python entry point (``LLM.step``: host
+token ids in, sampled ids out every step).  ``prefill`` is one 2,048-token prompt step;
+``roofline`` relates the decode step's mandatory bytes (every weight once, the live
+requests' cache) to the measured HBM bandwidth; ``points`` holds batch 1 and 64.
+
+Protocol after the reference's bench crate (crates/shiso-bench/src/measure.rs:10-33,62-77;
+decode.rs:12-22): warm-up discarded, greedy sampling with end-of-sequence ignored so every
+run takes every step.  The model's weights (1.8 GB) are read every step and exceed the
+126 MB L2, so consecutive steps do not reuse cached inputs.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+PROMPT_LEN = 2048
+NEW_TOKENS = 256
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for key in out:
+                if isinstance(data.get(key), (int, float)):
+                    out[key] = float(data[key])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for parts in self.samples:
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max_clock,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def model_costs(engine, config):
+    """Bytes a decode step must read that do not depend on the batch (weights, each once), the
+    cache bytes per token and per request, and the FLOPs of a prompt step of T tokens."""
+    from shiso_llm_b200.parts.base import FixedState, PagedKV
+    from shiso_llm_b200.weights.spec import MATRIX
+
+    specs = {s.name: s for s in engine.model.tensor_specs()}
+    embed_name = engine.model.plan.embedding.params["tensor"]
+    weight_bytes, gemm_params = 0, 0
+    itemsize = 2 if engine.env.dtype.itemsize == 2 else 4
+    for name, spec in specs.items():
+        n = 1
+        for d in spec.shape:
+            n *= d
+        if spec.role == MATRIX:
+            if name == embed_name:
+                continue  # only the looked-up rows are read; the head is counted below
+            weight_bytes += n * itemsize
+            gemm_params += n
+        else:
+            weight_bytes += n * 4
+    head_params = config.vocab_size * config.hidden_size
+    weight_bytes += head_params * itemsize  # the output head (the embedding table when tied)
+    kv_bytes_per_token, state_bytes = 0, 0
+    attn_layers = 0
+    for need in engine.model.cache_needs():
+        if isinstance(need, PagedKV):
+            kv_bytes_per_token += 2 * need.num_kv_heads * need.head_dim * itemsize
+            attn_layers += 1
+        elif isinstance(need, FixedState):
+            state_bytes += need.numel * 4 * 2  # read and written
+    return {
+        "weight_bytes": weight_bytes,
+        "gemm_params": gemm_params,
+        "head_params": head_params,
+        "kv_bytes_per_token": kv_bytes_per_token,
+        "state_bytes_per_request": state_bytes,
+        "attn_layers": attn_layers,
+    }
+
+
+def prefill_flops(costs, config, tokens):
+    gemm = 2.0 * tokens * costs["gemm_params"] + 2.0 * costs["head_params"]  # head: the last row only
+    heads, d = config.num_attention_heads, config.head_dim
+    attention = costs["attn_layers"] * 4.0 * heads * d * (tokens * (tokens + 1) / 2)
+    return gemm + attention
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--preset", default="lfm2-1.2b")
+    parser.add_argument("--layers", type=int, default=None, help="run only the first N layers (recorded in config)")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--points", default="1,64", help="other decode batch sizes to report")
+    parser.add_argument("--no-cuda-graphs", action="store_true")
+    parser.add_argument("--skip-prefill", action="store_true")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({
+            "impl": "reference",
+            "unavailable": "the reference is a Rust workspace and this image has no cargo/rustc; its LFM2 path is "
+                           "GGUF-quantized only and its short-conv kernel exists only for Metal, so it cannot run here",
+        }))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from shiso_llm_b200 import LLM, SamplingParams
+    from shiso_llm_b200.cli import preset_path
+    from shiso_llm_b200.config import plan_from_document
+    from shiso_llm_b200.engine import Engine, EngineOptions, StepEntry
+    from shiso_llm_b200.engine.batch import MetaLayout
+    from shiso_llm_b200.kernels import ops
+    from shiso_llm_b200.parts import BuildEnv, Model
+    from shiso_llm_b200.weights import random_device_tensors
+
+    with open(preset_path(args.preset)) as f:
+        document = json.load(f)
+    full_layers = document["num_hidden_layers"]
+    if args.layers is not None and args.layers < full_layers:
+        document["layer_types"] = document["layer_types"][: args.layers]
+        document["num_hidden_layers"] = args.layers
+    _, config, plan = plan_from_document(document)
+
+    device = torch.device("cuda:0")
+    batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip()]
+    max_batch = max(batches)
+    budget = PROMPT_LEN + NEW_TOKENS + 64
+    options = EngineOptions(
+        dtype="bfloat16", ctx=4096, page_size=16, kv_cache_tokens=max_batch * budget,
+        max_num_seqs=max_batch, max_num_batched_tokens=PROMPT_LEN, cuda_graphs=not args.no_cuda_graphs,
+    )
+    ops.require()
+    probe = Model(plan, BuildEnv(dtype=torch.bfloat16, device=device, ops=ops))
+    tensors = random_device_tensors(probe.tensor_specs(), 0, torch.bfloat16, device)
+    del probe
+    engine = Engine.from_plan(plan, tensors, options)
+    costs = model_costs(engine, config)
+    peak, peak_source = peaks()
+    gen = torch.Generator().manual_seed(1234)
+
+    def prompts(n):
+        return [torch.randint(0, config.vocab_size, (PROMPT_LEN,), generator=gen).tolist() for _ in range(n)]
+
+    def measure_decode(batch: int, steps: int, warmup: int) -> dict:
+        """Batch ``batch`` decode over 2,048-token prompts: end to end through LLM.step, then
+        device-timed through Engine.step on the same requests."""
+        llm = LLM(engine)
+        params = SamplingParams(temperature=0.0, max_new_tokens=NEW_TOKENS, ignore_eos=True)
+        for p in prompts(batch):
+            llm.add_request(p, params)
+        # prompts are admitted one per step; run until every request is decoding
+        while any(not r.decoding for r in llm.scheduler.running) or llm.scheduler.waiting:
+            llm.step()
+        for _ in range(warmup):
+            llm.step()
+        torch.cuda.synchronize()
+        clocks = ClockSampler()
+        clocks.start()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            llm.step()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        assert len(llm.scheduler.running) == batch, "a request ended inside the timed region"
+
+        # device-timed: the same requests, next tokens fed without waiting for the host
+        requests = list(llm.scheduler.running)
+        tokens = [r.tokens[-1] for r in requests]
+        entries = [StepEntry(r.id, [t], [0]) for r, t in zip(requests, tokens)]
+        for _ in range(3):
+            ops.argmax(engine.step(entries))
+        torch.cuda.synchronize()
+        launches_before = ops.launch_count
+        replays_before = engine.graphs.replays if engine.graphs else 0
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            ops.argmax(engine.step(entries))
+        end.record()
+        torch.cuda.synchronize()
+        device_ms = start.elapsed_time(end)
+        clock_info = clocks.stop()
+        launches = ops.launch_count - launches_before
+        if engine.graphs:
+            launches += (engine.graphs.replays - replays_before) * engine.graphs.launches(batch)
+        context = sum(engine.cache.length(r.id) for r in requests) / batch
+        for r in requests:
+            llm.abort(r.id)
+        step_bytes = costs["weight_bytes"] + batch * (context * costs["kv_bytes_per_token"] + costs["state_bytes_per_request"])
+        ms = device_ms / steps
+        return {
+            "batch": batch, "tok_s": batch * steps / (device_ms / 1e3), "ms_per_step": ms,
+            "e2e_tok_s": batch * steps / e2e_s, "e2e_ms_per_step": e2e_s / steps * 1e3,
+            "launches": launches, "context": context, "clocks": clock_info,
+            "bytes": step_bytes, "gbs": step_bytes / (ms / 1e3) / 1e9,
+            "h2d": 4 * MetaLayout(batch, batch, batch, len(engine.cache.groups), engine.cache.max_blocks).total,
+            "d2h": 4 * batch,
+        }
+
+    def measure_prefill(reps: int = 5, warmup: int = 3) -> dict:
+        times = []
+        for i in range(warmup + reps):
+            tokens = prompts(1)[0]
+            request = ("prefill", i)
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.step([StepEntry(request, tokens, [PROMPT_LEN - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.finish(request)
+            if i >= warmup:
+                times.append(start.elapsed_time(end))
+        ms = statistics.median(times)
+        flops = prefill_flops(costs, config, PROMPT_LEN)
+        return {
+            "value": PROMPT_LEN / (ms / 1e3), "tokens": PROMPT_LEN, "ms": ms,
+            "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12),
+            "tflops": flops / (ms / 1e3) / 1e12, "spread": max(times) / min(times) - 1.0,
+        }
+
+    main_point = measure_decode(args.batch, args.steps, args.warmup)
+    points = {}
+    for b in batches[1:]:
+        try:
+            points[f"decode_b{b}"] = measure_decode(b, args.steps, args.warmup)["tok_s"]
+        except Exception as e:  # a point that cannot run is reported, not hidden
+            points[f"decode_b{b}"] = None
+            points[f"decode_b{b}_error"] = f"{type(e).__name__}: {e}"[:200]
+    prefill = None if args.skip_prefill else measure_prefill()
+
+    line = {
+        "metric": "decode tok/s at batch 8 (LFM2-1.2B-shaped, bf16, 2048-token prompts)",
+        "value": main_point["tok_s"],
+        "unit": "tok/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": main_point["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": f"{args.preset} (random weights)",
+            "global_batch": args.batch,
+            "seq_len": 4096,
+            "parallelism": "single-gpu",
+            "layers_run": config.num_hidden_layers,
+            "layers_full": full_layers,
+            "hidden_size": config.hidden_size,
+            "intermediate_size": config.intermediate_size,
+            "heads": config.num_attention_heads,
+            "kv_heads": config.num_key_value_heads,
+            "head_dim": config.head_dim,
+            "vocab_size": config.vocab_size,
+            "conv_L_cache": config.conv_L_cache,
+            "attention_layers": costs["attn_layers"],
+            "prompt_len": PROMPT_LEN,
+            "mean_context": main_point["context"],
+            "page_size": 16,
+            "cuda_graphs": not args.no_cuda_graphs,
+            "l2": "inputs larger than L2 (1.8 GB of weights read per step)",
+            "peaks": peak_source,
+        },
+        "clocks": main_point["clocks"],
+        "e2e": {
+            "value": main_point["e2e_tok_s"], "unit": "tok/s", "ms_per_step": main_point["e2e_ms_per_step"],
+            "h2d_bytes_per_step": main_point["h2d"], "d2h_bytes_per_step": main_point["d2h"],
+        },
+        "gpu_launches": main_point["launches"],
+        "prefill": prefill,
+        "roofline": {
+            "bound": "hbm", "achieved": main_point["gbs"], "peak": peak["hbm_gbs"], "unit": "GB/s",
+            "frac": main_point["gbs"] / peak["hbm_gbs"], "bytes_per_step": main_point["bytes"],
+        },
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

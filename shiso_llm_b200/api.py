@@ -34,7 +34,7 @@ class Output:
 class LLM:
     def __init__(
         self,
-        model: str,
+        model: Union[str, Engine],
         dtype: str = "bfloat16",
         ctx: int = 4096,
         page_size: int = 16,
@@ -43,14 +43,24 @@ class LLM:
         max_num_batched_tokens: int = 2048,
         prefill_chunk: Optional[int] = None,
         on_exhaustion: str = "preempt",
+        cuda_graphs: bool = True,
         device: str = "cuda:0",
         ops=None,
     ):
-        options = EngineOptions(
-            dtype=dtype, ctx=ctx, page_size=page_size, kv_cache_tokens=kv_cache_tokens,
-            max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, device=device,
-        )
-        self.engine = Engine.from_folder(model, options, ops)
+        """``model`` is a model folder (config.json + *.safetensors), or an ``Engine`` that is
+        already built (then the engine's own options stand for dtype and cache sizes)."""
+        if isinstance(model, Engine):
+            self.engine = model
+            opts = model.options
+            ctx, max_num_seqs = opts.ctx, opts.max_num_seqs
+            max_num_batched_tokens = opts.max_num_batched_tokens
+        else:
+            options = EngineOptions(
+                dtype=dtype, ctx=ctx, page_size=page_size, kv_cache_tokens=kv_cache_tokens,
+                max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, device=device,
+                cuda_graphs=cuda_graphs,
+            )
+            self.engine = Engine.from_folder(model, options, ops)
         self.scheduler = Scheduler(
             self.engine.cache,
             SchedulerConfig(

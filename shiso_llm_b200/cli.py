@@ -1,0 +1,164 @@
+"""Command line: ``python -m shiso_llm_b200 generate|init-random|info``.
+
+The reference ships only ``shiso serve`` (crates/shiso-server/src/cli.rs:31-47); its
+engine options keep their names here where they exist there
+(crates/shiso-runtime/src/options.rs:75-320): ``-m/--model``, ``-c/--ctx``,
+``--max-num-seqs``, ``--kv-cache-tokens``, ``--max-num-batched-tokens``, and the sampling
+knobs of its requests (crates/shiso-ir/src/request.rs:33-85): ``--temperature``,
+``--top-k``, ``--top-p``, ``--min-p``, ``--seed``, ``--max-tokens``.  Prompts are token
+ids: this engine has no tokenizer.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+
+def preset_path(name: str) -> str:
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "config", "presets", name + ".json")
+
+
+def preset_names() -> list[str]:
+    d = os.path.dirname(preset_path("x"))
+    return sorted(f[:-5] for f in os.listdir(d) if f.endswith(".json"))
+
+
+def load_config_document(args) -> dict:
+    if args.config:
+        with open(args.config, "r", encoding="utf-8") as f:
+            return json.load(f)
+    path = preset_path(args.preset)
+    if not os.path.isfile(path):
+        raise SystemExit(f"unknown preset {args.preset!r}; available: {', '.join(preset_names())}")
+    with open(path, "r", encoding="utf-8") as f:
+        return json.load(f)
+
+
+def init_random(document: dict, seed: int, out: str, storage_dtype: str = "bfloat16", std: float = 0.02,
+                num_layers: int | None = None) -> None:
+    """Writes a model folder (config.json, model.safetensors) from a configuration and a seed."""
+    import torch
+
+    from .config import plan_from_document
+    from .parts import BuildEnv, Model
+    from .weights import random_tensors, write_model_folder
+
+    if num_layers is not None:
+        document = dict(document)
+        document["layer_types"] = list(document["layer_types"])[:num_layers]
+        document["num_hidden_layers"] = num_layers
+    _, _, plan = plan_from_document(document)
+    model = Model(plan, BuildEnv(dtype=torch.float32, device=torch.device("cpu"), ops=None))
+    write_model_folder(out, document, random_tensors(model.tensor_specs(), seed, std, storage_dtype))
+
+
+def cmd_init_random(args) -> int:
+    init_random(load_config_document(args), args.seed, args.out, args.storage_dtype, args.std, args.num_layers)
+    print(f"wrote {args.out}")
+    return 0
+
+
+def cmd_info(args) -> int:
+    from .config import load_config
+
+    arch, config = load_config(args.model)
+    plan = arch.build_plan(config)
+    print(json.dumps({"architecture": arch.name, "config": config.to_dict(),
+                      "layers": [layer.mixer.kind for layer in plan.layers]}, indent=2))
+    return 0
+
+
+def parse_prompts(args, vocab: int) -> list:
+    prompts = []
+    for text in args.prompt_ids or []:
+        prompts.append([int(t) for t in text.replace(",", " ").split()])
+    if args.prompt_len:
+        import torch
+
+        g = torch.Generator().manual_seed(args.prompt_seed)
+        for n in args.prompt_len:
+            prompts.append(torch.randint(0, vocab, (n,), generator=g).tolist())
+    if not prompts:
+        raise SystemExit("give --prompt-ids \"1,2,3\" (repeatable) or --prompt-len N (repeatable)")
+    return prompts
+
+
+def cmd_generate(args) -> int:
+    from .api import LLM
+    from .sampling import SamplingParams
+
+    llm = LLM(
+        args.model, dtype=args.dtype, ctx=args.ctx, page_size=args.page_size,
+        kv_cache_tokens=args.kv_cache_tokens, max_num_seqs=args.max_num_seqs,
+        max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk=args.prefill_chunk,
+        on_exhaustion=args.on_exhaustion, cuda_graphs=not args.no_cuda_graphs, device=args.device,
+    )
+    prompts = parse_prompts(args, llm.engine.vocab_size)
+    params = SamplingParams(
+        temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p, seed=args.seed,
+        max_new_tokens=args.max_tokens, stop_token_ids=tuple(args.stop_token_ids or ()), ignore_eos=args.ignore_eos,
+    )
+    started = time.time()
+    outputs = llm.generate(prompts, params)
+    elapsed = time.time() - started
+    for out in outputs:
+        print(json.dumps({"request": out.request_id, "prompt_tokens": len(out.prompt_token_ids),
+                          "token_ids": out.token_ids, "finish_reason": out.finish_reason, "error": out.error}))
+    produced = sum(len(o.token_ids) for o in outputs)
+    print(f"# {produced} tokens in {elapsed:.3f} s ({produced / max(elapsed, 1e-9):.1f} tok/s), "
+          f"stats {llm.scheduler.stats}", file=sys.stderr)
+    return 0
+
+
+def build_parser() -> argparse.ArgumentParser:
+    parser = argparse.ArgumentParser(prog="shiso_llm_b200", description=__doc__.split("\n\n")[0])
+    sub = parser.add_subparsers(dest="command", required=True)
+
+    g = sub.add_parser("generate", help="generate token ids for token-id prompts")
+    g.add_argument("-m", "--model", required=True, help="model folder (config.json + *.safetensors)")
+    g.add_argument("--prompt-ids", action="append", help="comma- or space-separated token ids; repeatable")
+    g.add_argument("--prompt-len", action="append", type=int, help="a uniform-random prompt of this length; repeatable")
+    g.add_argument("--prompt-seed", type=int, default=0)
+    g.add_argument("--max-tokens", type=int, default=16, help="new tokens per request")
+    g.add_argument("--temperature", type=float, default=0.0, help="<= 0 is greedy")
+    g.add_argument("--top-k", type=int, default=None)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--min-p", type=float, default=0.0)
+    g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--stop-token-ids", type=int, nargs="*")
+    g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    g.add_argument("-c", "--ctx", type=int, default=4096)
+    g.add_argument("--page-size", type=int, default=16)
+    g.add_argument("--kv-cache-tokens", type=int, default=None)
+    g.add_argument("--max-num-seqs", type=int, default=4)
+    g.add_argument("--max-num-batched-tokens", type=int, default=2048)
+    g.add_argument("--prefill-chunk", type=int, default=None)
+    g.add_argument("--on-exhaustion", choices=["preempt", "fail"], default="preempt")
+    g.add_argument("--no-cuda-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    g.add_argument("--device", default="cuda:0")
+    g.set_defaults(func=cmd_generate)
+
+    r = sub.add_parser("init-random", help="write a model folder with random weights")
+    r.add_argument("--preset", default="lfm2-1.2b", help=f"one of: {', '.join(preset_names())}")
+    r.add_argument("--config", help="a config.json to use instead of a preset")
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--out", required=True)
+    r.add_argument("--storage-dtype", choices=["bfloat16", "float32", "float16"], default="bfloat16")
+    r.add_argument("--std", type=float, default=0.02)
+    r.add_argument("--num-layers", type=int, default=None, help="keep only the first N layers")
+    r.set_defaults(func=cmd_init_random)
+
+    i = sub.add_parser("info", help="print a model folder's configuration and layer kinds")
+    i.add_argument("-m", "--model", required=True)
+    i.set_defaults(func=cmd_info)
+    return parser
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    return args.func(args)

@@ -60,6 +60,7 @@ class EngineOptions:
     max_num_seqs: int = 4
     max_num_batched_tokens: int = 2048
     device: str = "cuda:0"
+    cuda_graphs: bool = True  # replay captured graphs for steps of single decoded tokens
 
     def num_pages(self) -> int:
         tokens = self.kv_cache_tokens if self.kv_cache_tokens is not None else self.max_num_seqs * self.ctx
@@ -87,6 +88,29 @@ class Engine:
             cache, self.device, options.max_num_batched_tokens, options.max_num_seqs
         )
         self.steps_run = 0
+        self.graphs = None
+        if options.cuda_graphs and self.device.type == "cuda":
+            from .graphs import DecodeGraphs
+
+            decode_builder = StepBuilder(
+                cache, self.device, options.max_num_seqs, options.max_num_seqs, fixed_table_width=cache.max_blocks
+            )
+            self.graphs = DecodeGraphs(model, cache, decode_builder)
+
+    def warm_up(self) -> None:
+        """Runs a two-token request through a prompt step and a decode step and drops it, so
+        that every kernel has been loaded before the first graph capture."""
+        probe = ("__warm_up__",)
+        graphs, self.graphs = self.graphs, None
+        try:
+            self.step([StepEntry(probe, [0], [])])
+            self.step([StepEntry(probe, [0], [0])])
+        finally:
+            self.graphs = graphs
+            if self.cache.has(probe):
+                self.finish(probe)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ construction
 
@@ -113,7 +137,10 @@ class Engine:
             device,
             max_blocks_per_request=min(blocks_per_request, num_pages),
         )
-        return cls(model, cache, options)
+        engine = cls(model, cache, options)
+        if engine.graphs is not None:
+            engine.warm_up()
+        return engine
 
     @classmethod
     def from_folder(cls, model_dir: str, options: EngineOptions, ops=None) -> "Engine":
@@ -148,8 +175,14 @@ class Engine:
             for e in entries:
                 starts.append(self.cache.append(e.request, len(e.tokens)))
                 claimed.append(e.request)
-            meta = self.builder.build(entries, starts)
-            logits = self.model.forward(meta, self.cache)
+            if (
+                self.graphs is not None
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+            ):
+                logits = self.graphs.run(entries, starts)
+            else:
+                meta = self.builder.build(entries, starts)
+                logits = self.model.forward(meta, self.cache)
         except BaseException:
             for request in claimed:
                 self.cache.cancel(request)

@@ -7,7 +7,8 @@ One decision per step (``plan``), pure host bookkeeping over the cache manager's
    (crates/shiso-runtime/src/scheduler/batching.rs:3-11).
 2. What is left of the token budget (``max_num_batched_tokens``) goes to prompt portions:
    running requests still reading their prompt, oldest first, then waiting requests in
-   arrival order while a sequence slot, a state slot and pages for the portion are free.
+   arrival order while a sequence slot, a state slot and pages for all of the request's
+   tokens so far are free.
    A portion is at most ``prefill_chunk`` tokens and may end anywhere.  (The reference gives
    one prompt portion per tick to the oldest prefilling sequence only, batching.rs:219-227,
    and never mixes it with the decode pass; here both share one step.)
@@ -188,14 +189,18 @@ class Scheduler:
             ok, need = fits(req, 1)
             while not ok:
                 victim = self._victim(req, plan)
-                if cfg.on_exhaustion == "fail" or victim is None or victim is req:
+                alone = len([r for r in self.running if r.state == RUNNING]) <= 1
+                if cfg.on_exhaustion == "fail" or victim is None or alone:
                     self._fail(req, "kv pool: no free page for the next position", plan)
-                    break
-                self._preempt(victim, plan)
+                else:
+                    self._preempt(victim, plan)
+                # pages came back; those promised earlier in this plan stay promised
                 free = list(self.cache.free_pages())
-                for e in plan.entries:  # pages promised earlier in this plan stay promised
+                for e in plan.entries:
                     claim(self.cache.pages_needed(e.request.id, e.count))
                 free_slots = self.cache.slots.free_slots
+                if req.state != RUNNING:
+                    break
                 ok, need = fits(req, 1)
             if req.state != RUNNING:
                 continue
@@ -215,11 +220,15 @@ class Scheduler:
             budget -= count
 
         # 3. admissions in arrival order
-        while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs and free_slots > 0:
+        # (not in a step that had to preempt: the pages just freed are for the residents)
+        while (self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs and free_slots > 0
+               and not plan.preempted):
             req = self.waiting[0]
-            count = self._portion(req, min(req.remaining, budget, chunk), free)
-            if count <= 0:
+            # Pages for everything the request has so far must be free, not just for this
+            # portion: a request admitted on less would soon be preempted again.
+            if not fits(req, req.remaining)[0]:
                 break
+            count = min(req.remaining, budget, chunk)
             self.waiting.popleft()
             req.state = RUNNING
             self.running.append(req)

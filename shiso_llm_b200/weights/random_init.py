@@ -59,3 +59,22 @@ def write_model_folder(model_dir: str, config_document: Mapping, tensors: Mappin
         json.dump(dict(config_document), f, indent=2)
         f.write("\n")
     write_safetensors(os.path.join(model_dir, "model.safetensors"), dict(tensors), {"format": "pt"})
+
+
+def random_device_tensors(specs: Iterable[TensorSpec], seed: int, compute_dtype, device, std: float = 0.02) -> dict:
+    """Random weights made on the device, in the types the loader would hand out (matrices
+    in the compute type, vectors in float32): the same distribution as ``random_tensors``
+    without the trip through a file, for benchmarks of large shapes."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(int(seed))
+    out = {}
+    for spec in sorted(specs, key=lambda s: s.name):
+        dtype = torch.float32 if spec.role == VECTOR else compute_dtype
+        if spec.init == NORMAL:
+            t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen)
+        elif spec.init == ONES:
+            t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+        else:
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        out[spec.name] = t.to(dtype)
+    return out
