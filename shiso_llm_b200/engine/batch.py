@@ -53,6 +53,7 @@ class StepMeta:
     all_decode: bool  # every sequence brings exactly one token
     h_q_start: list = field(default_factory=list)
     h_start_pos: list = field(default_factory=list)
+    h_state_slots: list = field(default_factory=list)
     requests: list = field(default_factory=list)
 
 
@@ -123,7 +124,8 @@ class StepBuilder:
         np.cumsum(lens, out=q_start[1:])
         host[lay.q_start : lay.q_start + num_seqs + 1] = q_start
         host[lay.start_pos : lay.start_pos + num_seqs] = starts
-        host[lay.state_slots : lay.state_slots + num_seqs] = [self.cache.slot_of(r) for r in requests]
+        slots = [self.cache.slot_of(r) for r in requests]
+        host[lay.state_slots : lay.state_slots + num_seqs] = slots
         want_at = lay.want_rows
         for i, e in enumerate(entries):
             a, b = int(q_start[i]), int(q_start[i + 1])
@@ -169,5 +171,6 @@ class StepBuilder:
             all_decode=all(n == 1 for n in lens),
             h_q_start=q_start.tolist(),
             h_start_pos=list(starts),
+            h_state_slots=slots,
             requests=requests,
         )

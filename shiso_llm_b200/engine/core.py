@@ -89,7 +89,7 @@ class Engine:
         )
         self.steps_run = 0
         self.graphs = None
-        if options.cuda_graphs and self.device.type == "cuda":
+        if options.cuda_graphs and self.device.type == "cuda" and model.graph_safe:
             from .graphs import DecodeGraphs
 
             decode_builder = StepBuilder(

@@ -70,7 +70,14 @@ class FixedState:
 
 
 class Part:
-    """Common protocol: tensors wanted, tensors bound."""
+    """Common protocol: tensors wanted, tensors bound.
+
+    ``graph_safe``: the part's launches depend on the step only through device arrays
+    (positions, tables, slots), never through host values that change from step to step,
+    so a captured decode step can be replayed.  A part that loops on the host over the
+    step's sequences sets it to False and its model runs decode steps without graphs."""
+
+    graph_safe = True
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec

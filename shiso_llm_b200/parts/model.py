@@ -43,6 +43,15 @@ class Model:
             part.bind(tensors)
         self.bound = True
 
+    @property
+    def graph_safe(self) -> bool:
+        def walk(part):
+            yield part
+            for sub in part.sub_parts():
+                yield from walk(sub)
+
+        return all(p.graph_safe for top in self.parts() for p in walk(top))
+
     # ------------------------------------------------------------------ cache needs
 
     def cache_needs(self) -> list:

@@ -1,0 +1,205 @@
+"""The engine end to end, twice: on the CPU with the plain stand-in kernels (which checks the
+step function, the cache and the scheduler), and on the GPU with the CUDA kernels
+(``-m gpu``).  Same bodies, same tolerances.
+"""
+
+import pytest
+import torch
+
+import fake_kernels
+import helpers
+import plain_lfm2
+import replay
+import toy_parts
+from shiso_llm_b200 import LLM, SamplingParams
+from shiso_llm_b200.cache import OutOfPages
+from shiso_llm_b200.config import register_architecture, unregister_architecture
+from shiso_llm_b200.engine import Engine, EngineOptions, StepEntry
+from shiso_llm_b200.sampling import host as host_sampling
+from shiso_llm_b200.weights import random_tensors
+from tolerances import check_logits
+
+
+def _fake_sample(logits, temperature, top_k, top_p, min_p, keys, positions):
+    out = []
+    for r in range(logits.shape[0]):
+        p = SamplingParams(temperature=float(temperature[r]), top_k=int(top_k[r]), top_p=float(top_p[r]), min_p=float(min_p[r]))
+        out.append(host_sampling.keyed_sample(logits[r].numpy(), p, int(keys[r]), int(positions[r])))
+    return torch.tensor(out, dtype=torch.int32)
+
+
+fake_kernels.sample = _fake_sample
+
+BACKENDS = [pytest.param("cpu", id="plain-kernels-cpu"), pytest.param("cuda", id="cuda", marks=pytest.mark.gpu)]
+
+
+def backend_args(backend):
+    if backend == "cpu":
+        return {"ops": fake_kernels, "device": "cpu"}
+    return {"ops": None, "device": "cuda:0"}
+
+
+def dtypes(backend):
+    return ["float32"] if backend == "cpu" else ["float32", "bfloat16"]
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_every_cut_matches_the_plain_implementation(tmp_path, backend, name):
+    doc, seed = helpers.TINY[name]
+    tensors = helpers.make_folder(tmp_path, doc, seed)
+    lengths = [70, 40, 7, 33, 1]
+    requests = {f"r{i}": helpers.random_prompt(n, doc["vocab_size"], 10 + i) for i, n in enumerate(lengths)}
+    reference = {rid: plain_lfm2.plain_forward(doc, tensors, toks) for rid, toks in requests.items()}
+    for dtype in dtypes(backend):
+        engine = helpers.make_engine(tmp_path, dtype, page_size=4, kv_cache_tokens=192, ctx=128,
+                                     max_num_batched_tokens=128, **backend_args(backend))
+        steps, expect = [], []
+        for rid, toks in requests.items():
+            steps += helpers.whole(f"w-{rid}", toks)
+            expect.append((f"w-{rid}", rid))
+        steps += helpers.tail_one_by_one("t-r0", requests["r0"], 32)
+        steps += helpers.portions("p-r0", requests["r0"], [13, 2, 7, 1, 3])
+        steps += helpers.portions("p-r3", requests["r3"], [2])
+        expect += [("t-r0", "r0"), ("p-r0", "r0"), ("p-r3", "r3")]
+        steps += replay.mixed_trace({f"m-{k}": v for k, v in requests.items()}, 3, 192)
+        expect += [(f"m-{rid}", rid) for rid in requests]
+        rows = helpers.run_steps(engine, steps)
+        for trace_id, rid in expect:
+            got = replay.stack_rows(rows, trace_id, len(requests[rid]))
+            check_logits(got, reference[rid], dtype, f"{name} {dtype} {trace_id}")
+        assert engine.cache.free_pages() == [48] and engine.cache.slots.free_slots == 4
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_long_decoding_and_first_tokens(tmp_path, backend):
+    """400 tokens one by one (pages cross, the rotation reaches large angles), and the very
+    first positions of a sequence (conv state still empty, a single key)."""
+    doc, seed = helpers.TINY["B"]
+    tensors = helpers.make_folder(tmp_path, doc, seed)
+    toks = helpers.random_prompt(400, doc["vocab_size"], 5)
+    ref = plain_lfm2.plain_forward(doc, tensors, toks)
+    for dtype in dtypes(backend):
+        engine = helpers.make_engine(tmp_path, dtype, page_size=16, kv_cache_tokens=512, ctx=512,
+                                     max_num_batched_tokens=64, **backend_args(backend))
+        rows = helpers.run_steps(engine, helpers.portions("a", toks, [1]))
+        check_logits(replay.stack_rows(rows, "a", 400), ref, dtype, f"long decode {dtype}")
+        rows = helpers.run_steps(engine, helpers.portions("b", toks[:6], [1, 2, 3]))
+        check_logits(replay.stack_rows(rows, "b", 6), ref[:6], dtype, f"first tokens {dtype}")
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_greedy_generation_through_the_entry_point(tmp_path, backend):
+    for name in ("A", "B"):
+        doc, seed = helpers.TINY[name]
+        folder = tmp_path / name
+        tensors = helpers.make_folder(folder, doc, seed)
+        prompts = [helpers.random_prompt(n, doc["vocab_size"], 20 + n) for n in (5, 17, 33)]
+        want = [plain_lfm2.plain_greedy(doc, tensors, p, 16) for p in prompts]
+        llm = LLM(str(folder), dtype="float32", ctx=128, page_size=16, max_num_seqs=4, max_num_batched_tokens=32,
+                  prefill_chunk=13, **backend_args(backend))
+        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=16))
+        assert [o.token_ids for o in outs] == want and all(o.finish_reason == "length" for o in outs)
+        llm.engine.cache.check()
+        assert llm.engine.cache.slots.free_slots == 4
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_sampling_is_the_same_under_every_cut_and_after_preemption(tmp_path, backend):
+    """Tiny B's workload: prompts of 1, 7, 40, 64 and 100 tokens as a mixed batch with 13-token
+    portions beside decode, 24 steps at temperature 0.8 with seed 1; then again with a pool
+    so small that requests are preempted and recomputed."""
+    doc, seed = helpers.TINY["B"]
+    helpers.make_folder(tmp_path, doc, seed)
+    prompts = [helpers.random_prompt(n, doc["vocab_size"], 30 + n) for n in (1, 7, 40, 64, 100)]
+    params = SamplingParams(temperature=0.8, seed=1, max_new_tokens=24, top_k=200, top_p=0.95)
+    roomy = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, max_num_seqs=5, max_num_batched_tokens=256,
+                **backend_args(backend))
+    base = roomy.generate(prompts, params)
+    assert all(len(o.token_ids) == 24 and o.preemptions == 0 for o in base)
+    assert len({tuple(o.token_ids) for o in base}) == 5
+    cut = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=32,
+              prefill_chunk=13, **backend_args(backend))
+    assert [o.token_ids for o in cut.generate(prompts, params)] == [o.token_ids for o in base]
+    tight = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, kv_cache_tokens=208, max_num_seqs=4,
+                max_num_batched_tokens=32, prefill_chunk=13, **backend_args(backend))
+    outs = tight.generate(prompts, params)
+    assert [o.token_ids for o in outs] == [o.token_ids for o in base]
+    assert tight.scheduler.stats["preempted"] > 0
+    tight.engine.cache.check()
+    failing = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, kv_cache_tokens=208, max_num_seqs=4,
+                  max_num_batched_tokens=32, prefill_chunk=13, on_exhaustion="fail", **backend_args(backend))
+    outs = failing.generate(prompts, params)
+    assert any(o.finish_reason == "error" and "kv pool" in o.error for o in outs)
+    for o, b in zip(outs, base):
+        if o.finish_reason == "length":
+            assert o.token_ids == b.token_ids
+    assert failing.engine.cache.free_pages() == [13]
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_step_refusals_leave_the_cache_as_it_was(tmp_path, backend):
+    doc, seed = helpers.TINY["A"]
+    helpers.make_folder(tmp_path, doc, seed)
+    engine = helpers.make_engine(tmp_path, "float32", page_size=4, kv_cache_tokens=32, ctx=32, max_num_seqs=2,
+                                 max_num_batched_tokens=64, **backend_args(backend))
+    engine.step([StepEntry("a", [1, 2, 3, 4, 5], [4])])
+    before = (engine.cache.free_pages(), engine.cache.length("a"))
+    with pytest.raises(ValueError):
+        engine.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    with pytest.raises(ValueError):
+        engine.step([StepEntry("a", [512], [0])])
+    with pytest.raises(ValueError):
+        engine.step([StepEntry("a", [], [])])
+    with pytest.raises(ValueError):
+        engine.step([StepEntry("a", [1, 2], [2])])
+    with pytest.raises(OutOfPages):
+        engine.step([StepEntry("a", [1] * 20, []), StepEntry("b", [1] * 12, [])])
+    assert (engine.cache.free_pages(), engine.cache.length("a")) == before and not engine.cache.has("b")
+    engine.step([StepEntry("b", [1, 2], []), StepEntry("a", [7], [0])])
+    with pytest.raises(OutOfPages):
+        engine.step([StepEntry("c", [1], [0])])  # no state slot left
+    engine.finish("a")
+    engine.finish("b")
+    engine.cache.check()
+    assert engine.cache.free_pages() == [8]
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_toy_parts_register_build_and_step_without_touching_the_framework(backend):
+    """A mixer with state of its own, a routed feed-forward and another position encoding,
+    defined in tests/toy_parts.py; a run order that names a layer twice and lets a layer read
+    another entry's cache; a windowed cache group whose pages come back."""
+    toy_parts.register()
+    try:
+        plan = toy_parts.toy_plan()
+        args = backend_args(backend)
+        from shiso_llm_b200.parts import BuildEnv, Model
+
+        specs = Model(plan, BuildEnv(torch.float32, torch.device("cpu"), None)).tensor_specs()
+        stored = random_tensors(specs, 3, 0.08, "bfloat16", 0.1)
+        ids = helpers.random_prompt(45, toy_parts.VOCAB, 9)
+        ref = toy_parts.toy_reference(stored, ids)
+        options = EngineOptions(dtype="float32", ctx=64, page_size=4, kv_cache_tokens=64, max_num_seqs=2,
+                                max_num_batched_tokens=64, device=args["device"])
+        ops = args["ops"]
+        if ops is None:
+            from shiso_llm_b200.kernels import ops
+        from shiso_llm_b200.weights.loader import target_dtype
+
+        by_name = {s.name: s for s in specs}
+        tensors = {k: v.to(args["device"], target_dtype(by_name[k], v.dtype, torch.float32)) for k, v in stored.items()}
+        engine = Engine.from_plan(plan, tensors, options, ops)
+        assert engine.graphs is None  # the toy mixer is not graph-safe
+        needs = engine.model.cache_needs()
+        assert [type(n).__name__ for n in needs] == ["FixedState", "PagedKV", "FixedState", "NoneType"]
+        for cut in ([45], [1], [7, 2, 1, 13]):
+            rows = helpers.run_steps(engine, helpers.portions("t", ids, cut))
+            check_logits(replay.stack_rows(rows, "t", 45), ref, "float32", f"toy model cut {cut}")
+        # a window of 6 with pages of 4: at most 3 pages of the 12 a full cache would need
+        engine.step([StepEntry("w", ids, [])])
+        assert sum(p >= 0 for p in engine.cache.block_table("w", 0)) <= 3
+        engine.finish("w")
+        engine.cache.check()
+    finally:
+        toy_parts.unregister()

@@ -247,3 +247,45 @@ def test_argmax_ties_and_non_finite():
         row[~torch.isfinite(row)] = float("-inf")
         want.append(int(row.argmax()) if torch.isfinite(row).any() else 0)
     assert got == want and got[0] == 17 and got[1] == 0 and got[3] == 999
+
+
+def test_sample_kernel_follows_the_host_rule():
+    """The device sampler against the host statement of the same rule.  expf/logf differ from
+    NumPy in the last place, so the device's pick must be an allowed candidate whose score is
+    within rounding of the best score; with these seeds it is the same token."""
+    import numpy as np
+
+    from shiso_llm_b200.sampling import SamplingParams, candidate_mask, keyed_sample
+    from shiso_llm_b200.sampling.host import argmax as host_argmax, keyed_uniform
+
+    vocab = 3000
+    cases = [
+        SamplingParams(temperature=0.8, seed=1), SamplingParams(temperature=1.3, top_k=40, seed=2),
+        SamplingParams(temperature=0.7, top_p=0.8, seed=3), SamplingParams(temperature=1.0, min_p=0.05, seed=4),
+        SamplingParams(temperature=0.9, top_k=100, top_p=0.6, min_p=0.01, seed=2**63 + 5),
+        SamplingParams(temperature=0.0, seed=6), SamplingParams(temperature=2.0, top_k=1, seed=7),
+        SamplingParams(temperature=0.5, top_k=5000, top_p=1.5, min_p=-1.0, seed=8),
+    ]
+    logits = rnd((len(cases), vocab), torch.float32, 50, 2.5)
+    logits[1, 5] = logits[1, 9] = logits[1].max() + 1.0  # a tie at the top
+    logits[3, 100:200] = float("-inf")
+    logits[4, 7] = float("nan")
+    from shiso_llm_b200.sampling import DeviceSampler
+
+    sampler = DeviceSampler(ops(), "cuda")
+    same = 0
+    for position in (0, 1, 17, 4095):
+        picks = sampler.sample(logits.cuda(), cases, [position] * len(cases))
+        for r, (p, pick) in enumerate(zip(cases, picks)):
+            row = logits[r].numpy()
+            want = keyed_sample(row, p, p.seed, position)
+            if p.greedy:
+                assert pick == want == host_argmax(row)
+                continue
+            mask = candidate_mask(row, p)
+            assert mask[pick], f"row {r}: token {pick} is not an allowed candidate"
+            ids = np.nonzero(mask)[0]
+            score = (row[ids] - row[host_argmax(row)]) / np.float32(p.temperature) - np.log(-np.log(keyed_uniform(p.seed, position, ids)))
+            assert score[list(ids).index(pick)] >= score.max() - 1e-4
+            same += pick == want
+    assert same >= 4 * 6 - 1
