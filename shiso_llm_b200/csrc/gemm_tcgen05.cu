@@ -1,0 +1,457 @@
+// Y[T, N] = X[T, K] * W[N, K]^T for bfloat16 operands on the 5th-generation tensor cores.
+//
+// Layout of the work ("swap-AB"): the weight tile is the MMA's M operand (128 output
+// features x 64 k per stage) and the token tile is its N operand (BN tokens x 64 k, BN =
+// 16 .. 256), so one kernel serves a decode step (8 tokens: a 128 x 16 tile that streams
+// the weights once) and a prompt portion (2,048 tokens: 128 x 256 tiles).  Both operands
+// are K-major in shared memory, brought there by TMA with the 128-byte swizzle; the
+// accumulator D[feature, token] lives in tensor memory (TMEM, 128 lanes x BN columns of
+// float) and is read back with tcgen05.ld for the epilogue.  No multicast is used.
+//
+// Roles inside a CTA of 128 threads: lane 0 of warp 0 issues the TMA loads, lane 0 of warp 1
+// issues tcgen05.mma and commits; all four warps run the epilogue (warp q owns TMEM lanes
+// 32q .. 32q+31, i.e. features).  Stages are handed back and forth with mbarriers: `full`
+// (TMA bytes landed) and `empty` (tcgen05.commit: the MMAs that read the stage are done).
+//
+// Small token counts leave too few feature tiles to fill 148 SMs, so the K dimension can be
+// split over a thread-block cluster (up to 8 CTAs); the partial tiles are summed through
+// distributed shared memory in a fixed order, so the result does not depend on timing.
+//
+// Every wait is bounded by a clock limit; a wait that runs out sets a status word that the
+// host reads, frees the TMEM it holds and returns.
+//
+// The reference runs its prompt products through a scalar tile kernel or a dequantised
+// plane and a vendor SGEMM in 256-token bands (crates/shiso-engine/src/projection.rs:949-1070,
+// 1297-1304) and its decode products through matvec kernels (projection.rs:972-1069).
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int BM = 128;       // output features per CTA (MMA M)
+constexpr int BK = 64;        // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;    // k per tcgen05.mma of 16-bit operands
+constexpr int THREADS = 128;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;  // about a second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Waits for the phase with the given parity; false when the clock limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const unsigned long long start = clock64();
+    while (true) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes with
+// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading
+// byte offset is unused for swizzled K-major layouts, version 1, layout type 2 (128B swizzle).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (ignored)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // descriptor version
+    d |= (uint64_t)2 << 61;                 // 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: D float, A and B bfloat16, both K-major, M x N.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmParams {
+    void* y;
+    const float* bias;      // per output feature, or null
+    int* status;            // set non-zero when a wait ran out
+    int T, N, K;
+    int k_blocks_per_split;  // BK-blocks each CTA of a cluster handles
+    int out_f32;             // 1: float output, 0: bfloat16
+};
+
+template <typename OT>
+__device__ __forceinline__ void store_out(OT* y, size_t at, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* y, size_t at, float v) { y[at] = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* y, size_t at, float v) { y[at] = __float2bfloat16_rn(v); }
+
+template <int BN, int STAGES, int SPLITS>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    constexpr int A_BYTES = BM * BK * 2;
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two >= 32
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum_bar = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
+    int* failed = (int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int feature0 = blockIdx.x * BM;
+    const int token0 = blockIdx.y * BN;
+    const int split = SPLITS > 1 ? (int)blockIdx.z : 0;
+    const int total_kb = (p.K + BK - 1) / BK;
+    const int kb_begin = split * p.k_blocks_per_split;
+    int kb_count = total_kb - kb_begin;
+    if (kb_count > p.k_blocks_per_split) kb_count = p.k_blocks_per_split;
+    if (kb_count < 0) kb_count = 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum_bar, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA loads, one stage per 64-wide k block
+        for (int i = 0; i < kb_count; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
+                *failed = 1;
+                break;
+            }
+            uint8_t* a = smem + s * STAGE_BYTES;
+            mbar_expect_tx(&full[s], STAGE_BYTES);
+            const int k = (kb_begin + i) * BK;
+            tma_load_2d(a, &map_w, k, feature0, &full[s]);
+            tma_load_2d(a + A_BYTES, &map_x, k, token0, &full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        const uint32_t idesc = umma_idesc(BM, BN);
+        bool ok = true;
+        for (int i = 0; i < kb_count && ok; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
+                *failed = 1;
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+            const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t a_desc = umma_desc(a_addr + k * UMMA_K * 2);
+                const uint64_t b_desc = umma_desc(b_addr + k * UMMA_K * 2);
+                umma_bf16(tmem_base, a_desc, b_desc, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+        }
+        umma_commit(accum_bar);      // the accumulator is complete once every MMA is done
+    }
+    __syncwarp();
+
+    // ---- epilogue: every thread owns one feature (TMEM lane), columns are tokens
+    bool ready = true;
+    if (kb_count > 0) ready = mbar_wait(accum_bar, 0);
+    if (!ready) *failed = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    const bool bad = *failed != 0;
+    if (bad && threadIdx.x == 0 && p.status) atomicExch(p.status, 1);
+
+    const int feature = feature0 + warp * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+    if constexpr (SPLITS == 1) {
+        if (!bad) {
+            const float b = (p.bias && feature < p.N) ? p.bias[feature] : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 8) {
+                float v[8];
+                if (kb_count > 0) {
+                    tmem_ld8(lane_addr + c, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+                }
+                if (feature < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int token = token0 + c + j;
+                        if (token < p.T) {
+                            const size_t at = (size_t)token * p.N + feature;
+                            if (p.out_f32) store_out<float>((float*)p.y, at, v[j] + b);
+                            else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v[j] + b);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // Partial tiles go to this CTA's shared memory (token-major), the cluster meets, and
+        // CTA r sums tokens r, r + SPLITS, ... over the CTAs in rank order.
+        cg::cluster_group cluster = cg::this_cluster();
+        float* partial = (float*)smem;  // [BN][BM]; the stages are no longer in use
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 8) {
+            float v[8];
+            if (kb_count > 0 && !bad) {
+                tmem_ld8(lane_addr + c, v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) partial[(c + j) * BM + warp * 32 + lane] = v[j];
+        }
+        cluster.sync();
+        const unsigned rank = cluster.block_rank();
+        if (feature < p.N) {
+            const float b = p.bias ? p.bias[feature] : 0.0f;
+            for (int j = (int)rank; j < BN; j += SPLITS) {
+                const int token = token0 + j;
+                if (token >= p.T) break;
+                float sum = 0.0f;
+#pragma unroll
+                for (int r = 0; r < SPLITS; ++r) {
+                    const float* remote = cluster.map_shared_rank(partial, r);
+                    sum += remote[j * BM + warp * 32 + lane];
+                }
+                const size_t at = (size_t)token * p.N + feature;
+                if (p.out_f32) store_out<float>((float*)p.y, at, sum + b);
+                else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, sum + b);
+            }
+        }
+        cluster.sync();  // nobody leaves while its shared memory may still be read
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 10007u) ^ (size_t)k.box_rows;
+    }
+};
+
+// A [rows, cols] bf16 row-major matrix seen as tiles of box_rows x 64 with the 128B swizzle.
+bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex lock;
+    MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn encode = encode_fn();
+    if (!encode) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap map;
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return true;
+}
+
+template <int BN, int STAGES, int SPLITS>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    constexpr int PARTIAL_BYTES = SPLITS > 1 ? BN * BM * 4 : 0;
+    constexpr int TILE_BYTES = STAGES * STAGE_BYTES > PARTIAL_BYTES ? STAGES * STAGE_BYTES : PARTIAL_BYTES;
+    constexpr int SMEM = TILE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SPLITS>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div_u(p.N, BM), ceil_div_u(p.T, BN), SPLITS);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = SPLITS;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, p);
+    return (int)e;
+}
+
+int* status_word() {
+    static int* word = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
+        else word = nullptr;
+    });
+    return word;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this problem (bfloat16 operands, rows 16-byte aligned).
+SHISO_API int shiso_gemm_tcgen05_supported(int K, const void* x, const void* w) {
+    if (K % 8 != 0 || K < 8) return 0;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return 0;
+    return encode_fn() != nullptr ? 1 : 0;
+}
+
+// Reads and clears the status word: non-zero when a bounded wait inside a kernel ran out.
+SHISO_API int shiso_gemm_tcgen05_status() {
+    int* word = status_word();
+    if (!word) return -1;
+    int host = 0;
+    if (cudaMemcpy(&host, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (host) cudaMemset(word, 0, sizeof(int));
+    return host;
+}
+
+// x [T, K] bf16, w [N, K] bf16, y [T, N] bf16 (y_dtype 1) or float (y_dtype 0).
+SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
+                                 int K, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p;
+    p.y = y;
+    p.bias = bias;
+    p.status = status_word();
+    p.T = T;
+    p.N = N;
+    p.K = K;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    const int total_kb = (K + BK - 1) / BK;
+    p.k_blocks_per_split = total_kb;
+
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    if (!tensor_map(w, N, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
+
+    if (bn >= 128) {
+        if (bn == 128) return launch<128, 5, 1>(mw, mx, p, stream);
+        return launch<256, 4, 1>(mw, mx, p, stream);
+    }
+    // Few tokens: split K over a cluster until the grid covers the SMs (each CTA keeps >= 2 k blocks).
+    const int tiles = (int)ceil_div_u(N, BM) * (int)ceil_div_u(T, bn);
+    int splits = 1;
+    while (splits < 8 && tiles * splits * 2 <= sm_count + sm_count / 2 && total_kb / (splits * 2) >= 2) splits *= 2;
+    p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+#define SHISO_PICK(BN_)                                                        \
+    switch (splits) {                                                          \
+        case 1: return launch<BN_, 6, 1>(mw, mx, p, stream);                   \
+        case 2: return launch<BN_, 6, 2>(mw, mx, p, stream);                   \
+        case 4: return launch<BN_, 6, 4>(mw, mx, p, stream);                   \
+        default: return launch<BN_, 6, 8>(mw, mx, p, stream);                  \
+    }
+    if (bn == 16) { SHISO_PICK(16) }
+    if (bn == 32) { SHISO_PICK(32) }
+    SHISO_PICK(64)
+#undef SHISO_PICK
+}

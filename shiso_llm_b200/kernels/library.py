@@ -24,6 +24,9 @@ _SIGNATURES = {
     "shiso_rmsnorm": [P, P, P, P, P, I, I, I, F, P],
     "shiso_swiglu": [P, P, I, I, I, P],
     "shiso_gemm_simple": [P, I, P, I, P, P, I, I, I, I, P],
+    "shiso_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, P],
+    "shiso_gemm_tcgen05_supported": [I, P, P],
+    "shiso_gemm_tcgen05_status": [],
     "shiso_short_conv": [P, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, P],
     "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],

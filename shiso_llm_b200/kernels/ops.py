@@ -137,8 +137,22 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- matrix products
 
 
+_SM_COUNT = None
+
+
+def _sm_count() -> int:
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _SM_COUNT
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x[T, K] @ w[N, K]^T`` with float accumulation."""
+    """``x[T, K] @ w[N, K]^T`` with float accumulation.
+
+    bfloat16 x bfloat16 runs on the tensor cores (tcgen05, accumulators in TMEM); the true
+    32-bit path and mixed types run the CUDA-core kernel, whose rows do not depend on the
+    batch."""
     _check(x, "x", None, 2)
     _check(w, "w", None, 2)
     tokens, k = x.shape
@@ -148,11 +162,41 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     if bias is not None:
         _check(bias, "bias", torch.float32, 1)
     out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
-    status = library().shiso_gemm_simple(
+    lib = library()
+    if (
+        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w))
+    ):
+        status = lib.shiso_gemm_tcgen05(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _sm_count(), _stream()
+        )
+        _done(status, "linear (tcgen05)")
+        return out
+    status = lib.shiso_gemm_simple(
         _ptr(x), _code(x), _ptr(w), _code(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _stream()
     )
     _done(status, "linear")
     return out
+
+
+def linear_simple(x, w, out_dtype, bias=None):
+    """The CUDA-core product for any element types (used by tests to compare kernels)."""
+    _check(x, "x", None, 2)
+    _check(w, "w", None, 2)
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+    status = library().shiso_gemm_simple(
+        _ptr(x), _code(x), _ptr(w), _code(w), _ptr(bias), _ptr(out), _code(out), x.shape[0], w.shape[0], x.shape[1], _stream()
+    )
+    _done(status, "linear")
+    return out
+
+
+def check_kernel_status() -> None:
+    """Raises when a bounded wait inside a tensor-core kernel ran out since the last call.
+    Synchronises the device; not for use while a stream is being captured."""
+    status = library().shiso_gemm_tcgen05_status()
+    if status != 0:
+        raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (status {status}); its output is not valid")
 
 
 # --------------------------------------------------------------------------- short convolution
