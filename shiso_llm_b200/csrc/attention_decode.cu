@@ -1,0 +1,267 @@
+// Paged GQA attention for steps in which every sequence brings one token (decode), bfloat16.
+//
+// A decode step reads every live request's keys and values once; at batch 64 that is half
+// of the step's bytes, so the kernel is organised around reading the cache once and wide:
+// one CTA per (key range, KV head, sequence) serves all query heads of the group from the
+// same keys and values (the reference reads them once per query head:
+// kernels/cuda/dense/dense_attn.cuh:44-180), and the key range of a sequence is cut into
+// `splits` parts so that a few long sequences still fill 148 SMs.  Each part leaves an
+// unnormalised output with its running maximum and sum in scratch memory; a second kernel
+// merges the parts in index order.  The number of parts is fixed by the launch (capacity),
+// the cut points are computed on the device from the sequence's own length, so a captured
+// step serves any lengths.
+//
+// Scores: lane-per-key dot products against the float query in shared memory;
+// softmax statistics in float; P*V with one key per iteration, lanes across head columns.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+
+struct DecodeArgs {
+    const __nv_bfloat16* q;        // [T, heads * d]
+    const __nv_bfloat16* k_cache;  // [pages, page, kv_heads, d]
+    const __nv_bfloat16* v_cache;
+    const int* block_table;        // [S, width]
+    const int* positions;          // [T]
+    const int* seq_of_token;       // [T]
+    float* partial;                // [T, heads, splits, d + 2]
+    int width, heads, kv_heads, head_dim, page_size, splits, window;
+    float scale;
+};
+
+template <int GMAX, int DC>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_split_kernel(DecodeArgs a) {
+    extern __shared__ float smem[];
+    const int d = a.head_dim;
+    const int group = a.heads / a.kv_heads;
+    float* q_s = smem;                               // [GMAX][d]
+    float* p_s = q_s + GMAX * d;                     // [WARPS][GMAX][32]
+    int* row_s = (int*)(p_s + WARPS * GMAX * 32);    // [WARPS][32]
+    float* merge_ml = (float*)(row_s + WARPS * 32);  // [WARPS][GMAX][2]
+    float* merge_acc = merge_ml + WARPS * GMAX * 2;  // [WARPS][GMAX][DC * 64]
+
+    const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = a.positions[t];
+    const int lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
+    const int n_keys = pos + 1 - lo;
+    int chunk = (n_keys + a.splits - 1) / a.splits;
+    chunk = (chunk + 31) & ~31;
+    const int begin = lo + split * chunk;
+    const int end = min(begin + chunk, pos + 1);
+    const int* table = a.block_table + (size_t)a.seq_of_token[t] * a.width;
+
+    for (int i = threadIdx.x; i < group * d; i += blockDim.x) {
+        const int h = i / d, c = i % d;
+        q_s[h * d + c] = __bfloat162float(a.q[((size_t)t * a.heads + g * group + h) * d + c]);
+    }
+    __syncthreads();
+
+    float acc[GMAX][DC][2];
+    float run_max[GMAX], run_sum[GMAX];
+#pragma unroll
+    for (int h = 0; h < GMAX; ++h) {
+        run_max[h] = -INFINITY;
+        run_sum[h] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < DC; ++c) acc[h][c][0] = acc[h][c][1] = 0.0f;
+    }
+
+    for (int p0 = begin + warp * 32; p0 < end; p0 += WARPS * 32) {
+        const int p = p0 + lane;
+        const bool valid = p < end;
+        float score[GMAX];
+#pragma unroll
+        for (int h = 0; h < GMAX; ++h) score[h] = 0.0f;
+        int row = 0;
+        if (valid) {
+            row = table[p / a.page_size] * a.page_size + p % a.page_size;
+            const __nv_bfloat16* k_row = a.k_cache + ((size_t)row * a.kv_heads + g) * d;
+            for (int c = 0; c < d; c += 8) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(k_row + c);
+                const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                float kf[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(pairs[i]);
+                    kf[2 * i] = f.x;
+                    kf[2 * i + 1] = f.y;
+                }
+#pragma unroll
+                for (int h = 0; h < GMAX; ++h) {
+                    if (h < group) {
+                        const float4 q0 = *reinterpret_cast<const float4*>(q_s + h * d + c);
+                        const float4 q1 = *reinterpret_cast<const float4*>(q_s + h * d + c + 4);
+                        score[h] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] +
+                                    q1.x * kf[4] + q1.y * kf[5] + q1.z * kf[6] + q1.w * kf[7];
+                    }
+                }
+            }
+        }
+        row_s[warp * 32 + lane] = row;
+#pragma unroll
+        for (int h = 0; h < GMAX; ++h) {
+            if (h < group) {
+                const float s = valid ? score[h] * a.scale : -INFINITY;  // the scale meets the reduced dot
+                const float new_max = fmaxf(run_max[h], warp_max(s));
+                const float weight = valid ? expf(s - new_max) : 0.0f;
+                const float correction = expf(run_max[h] - new_max);
+                run_sum[h] = run_sum[h] * correction + warp_sum(weight);
+                run_max[h] = new_max;
+#pragma unroll
+                for (int c = 0; c < DC; ++c) {
+                    acc[h][c][0] *= correction;
+                    acc[h][c][1] *= correction;
+                }
+                p_s[(warp * GMAX + h) * 32 + lane] = weight;
+            }
+        }
+        __syncwarp();
+        const int count = min(32, end - p0);
+        for (int j = 0; j < count; ++j) {
+            const __nv_bfloat16* v_row = a.v_cache + ((size_t)row_s[warp * 32 + j] * a.kv_heads + g) * d;
+#pragma unroll
+            for (int c = 0; c < DC; ++c) {
+                const int col = c * 64 + lane * 2;
+                if (col < d) {
+                    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(v_row + col));
+#pragma unroll
+                    for (int h = 0; h < GMAX; ++h) {
+                        if (h < group) {
+                            const float w = p_s[(warp * GMAX + h) * 32 + j];
+                            acc[h][c][0] = fmaf(w, v.x, acc[h][c][0]);
+                            acc[h][c][1] = fmaf(w, v.y, acc[h][c][1]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // merge the four warps in warp order
+#pragma unroll
+    for (int h = 0; h < GMAX; ++h) {
+        if (h < group) {
+            if (lane == 0) {
+                merge_ml[(warp * GMAX + h) * 2] = run_max[h];
+                merge_ml[(warp * GMAX + h) * 2 + 1] = run_sum[h];
+            }
+#pragma unroll
+            for (int c = 0; c < DC; ++c) {
+                const int col = c * 64 + lane * 2;
+                if (col < d) {
+                    merge_acc[(warp * GMAX + h) * DC * 64 + col] = acc[h][c][0];
+                    merge_acc[(warp * GMAX + h) * DC * 64 + col + 1] = acc[h][c][1];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * d; i += blockDim.x) {
+        const int h = i / d, col = i % d;
+        float m = -INFINITY;
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge_ml[(w * GMAX + h) * 2]);
+        float sum = 0.0f, out = 0.0f;
+        for (int w = 0; w < WARPS; ++w) {
+            const float wm = merge_ml[(w * GMAX + h) * 2];
+            const float f = wm == -INFINITY ? 0.0f : expf(wm - m);
+            sum += f * merge_ml[(w * GMAX + h) * 2 + 1];
+            out += f * merge_acc[(w * GMAX + h) * DC * 64 + col];
+        }
+        float* dst = a.partial + (((size_t)t * a.heads + g * group + h) * a.splits + split) * (d + 2);
+        dst[col] = out;
+        if (col == 0) {
+            dst[d] = m;
+            dst[d + 1] = sum;
+        }
+    }
+}
+
+__global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int heads,
+                                    int head_dim, int splits) {
+    const int h = blockIdx.x, t = blockIdx.y;
+    const int d = head_dim;
+    const float* base = partial + ((size_t)t * heads + h) * splits * (d + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, base[s * (d + 2) + d]);
+    for (int col = threadIdx.x; col < d; col += blockDim.x) {
+        float sum = 0.0f, acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float sm = base[s * (d + 2) + d];
+            const float f = sm == -INFINITY ? 0.0f : expf(sm - m);
+            sum += f * base[s * (d + 2) + d + 1];
+            acc += f * base[s * (d + 2) + col];
+        }
+        out[((size_t)t * heads + h) * d + col] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+    }
+}
+
+template <int GMAX, int DC>
+int launch_split(const DecodeArgs& a, int tokens, cudaStream_t stream) {
+    const int d = a.head_dim;
+    const size_t smem = sizeof(float) * ((size_t)GMAX * d + WARPS * GMAX * 32 + WARPS * 32 + WARPS * GMAX * 2 +
+                                         (size_t)WARPS * GMAX * DC * 64);
+    auto kernel = decode_split_kernel<GMAX, DC>;
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+    }
+    dim3 grid(a.splits, a.kv_heads, tokens);
+    kernel<<<grid, WARPS * 32, smem, stream>>>(a);
+    return launch_status();
+}
+
+}  // namespace
+
+// Floats of scratch the caller must provide for `tokens` rows and `splits` parts.
+SHISO_API long long shiso_decode_attention_scratch_floats(int tokens, int heads, int head_dim, int splits) {
+    return (long long)tokens * heads * splits * (head_dim + 2);
+}
+
+SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                     int table_width, const int* positions, const int* seq_of_token, float* scratch,
+                                     void* out, int tokens, int heads, int kv_heads, int head_dim, int page_size,
+                                     float scale, int window, int splits, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (head_dim <= 0 || head_dim > 256 || head_dim % 16 || kv_heads <= 0 || heads % kv_heads || splits < 1)
+        return SHISO_ERR_SHAPE;
+    const int group = heads / kv_heads;
+    if (group > 8) return SHISO_ERR_UNSUPPORTED;
+    DecodeArgs a;
+    a.q = (const __nv_bfloat16*)q;
+    a.k_cache = (const __nv_bfloat16*)k_cache;
+    a.v_cache = (const __nv_bfloat16*)v_cache;
+    a.block_table = block_table;
+    a.positions = positions;
+    a.seq_of_token = seq_of_token;
+    a.partial = scratch;
+    a.width = table_width;
+    a.heads = heads;
+    a.kv_heads = kv_heads;
+    a.head_dim = head_dim;
+    a.page_size = page_size;
+    a.splits = splits;
+    a.window = window;
+    a.scale = scale;
+    const int gmax = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
+    const int dc = head_dim <= 64 ? 1 : head_dim <= 128 ? 2 : 4;
+    int status = SHISO_ERR_UNSUPPORTED;
+#define SHISO_CASE(G, C) if (gmax == G && dc == C) status = launch_split<G, C>(a, tokens, stream);
+    SHISO_CASE(1, 1) SHISO_CASE(1, 2) SHISO_CASE(1, 4)
+    SHISO_CASE(2, 1) SHISO_CASE(2, 2) SHISO_CASE(2, 4)
+    SHISO_CASE(4, 1) SHISO_CASE(4, 2) SHISO_CASE(4, 4)
+    SHISO_CASE(8, 1) SHISO_CASE(8, 2) SHISO_CASE(8, 4)
+#undef SHISO_CASE
+    if (status != 0) return status;
+    dim3 grid(heads, tokens);
+    decode_merge_kernel<<<grid, head_dim >= 128 ? 128 : 64, 0, stream>>>(scratch, (__nv_bfloat16*)out, heads, head_dim, splits);
+    return launch_status();
+}

@@ -263,7 +263,13 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
     return q
 
 
+MAX_DECODE_GROUP = 8  # query heads per KV head the decode kernel serves from one read
+
+
 def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step):
+    """Attention of every row over its sequence's cache.  Steps of single tokens in bfloat16
+    take the split-key decode kernel (keys and values read once per KV head); everything
+    else takes the general kernel."""
     _check(q, "q", None, 2)
     tokens = q.shape[0]
     if q.shape[1] != heads * head_dim:
@@ -274,7 +280,22 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
             raise KernelError(f"{name} of shape {tuple(t.shape)} does not fit pages of {page_size} x {kv_heads} x {head_dim}")
     _check(block_table, "block table", torch.int32, 2)
     out = torch.empty_like(q)
-    status = library().shiso_paged_attention(
+    lib = library()
+    if (
+        q.dtype == torch.bfloat16 and getattr(step, "all_decode", False)
+        and heads // kv_heads <= MAX_DECODE_GROUP and head_dim % 16 == 0
+    ):
+        capacity = block_table.shape[1] * page_size
+        splits = max(1, min(32, -(-2 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
+        scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
+        status = lib.shiso_decode_attention(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
+            _ptr(step.seq_of_token), _ptr(scratch), _ptr(out), tokens, heads, kv_heads, head_dim, page_size,
+            float(scale), int(window), splits, _stream(),
+        )
+        _done(status, "decode_attention", 2)
+        return out
+    status = lib.shiso_paged_attention(
         _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(step.positions), _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, head_dim,
         page_size, float(scale), int(window), _stream(),

@@ -289,3 +289,28 @@ def test_sample_kernel_follows_the_host_rule():
             assert score[list(ids).index(pick)] >= score.max() - 1e-4
             same += pick == want
     assert same >= 4 * 6 - 1
+
+
+@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (32, 8, 64, 16), (6, 6, 48, 8), (8, 1, 128, 16), (2, 1, 256, 4), (5, 5, 80, 16)])
+def test_decode_attention_split_keys(case):
+    """Steps of single tokens in bfloat16 take the split-key kernel: sequences of very
+    different lengths in one launch (one key, a page's edge, thousands of keys), windows."""
+    heads, kv_heads, d, page = case
+    starts = [0, page - 1, page, 700, 2100, 33]
+    num_pages = sum(-(-(s + 1) // page) for s in starts) + 3
+    cpu, gpu, table = make_step([1] * len(starts), starts, page, num_pages, 60)
+    cpu.all_decode = gpu.all_decode = True
+    dtype = torch.bfloat16
+    k = rnd((num_pages, page, kv_heads, d), dtype, 61)
+    v = rnd((num_pages, page, kv_heads, d), dtype, 62)
+    q = rnd((len(starts), heads * d), dtype, 63)
+    scale = 1.0 / math.sqrt(d)
+    for window in (0, 50):
+        want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, scale, window, cpu)
+        got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
+        close(got, want, dtype, f"decode attention {case} window {window}")
+        # the general kernel on the same inputs, for the difference between the two routes
+        gpu.all_decode = False
+        general = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
+        gpu.all_decode = True
+        close(got, general, dtype, "decode kernel against the general kernel")
