@@ -166,6 +166,9 @@ def main() -> int:
     parser.add_argument("--points", default="1,64", help="other decode batch sizes to report")
     parser.add_argument("--no-cuda-graphs", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--profiler-range", choices=["decode", "prefill"], default=None,
+                        help="bracket the device-timed decode steps (or the prefill steps) with cudaProfilerStart/Stop, "
+                             "for `ncu --profile-from-start off`")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -201,7 +204,7 @@ def main() -> int:
     _, config, plan = plan_from_document(document)
 
     device = torch.device("cuda:0")
-    batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip()]
+    batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip() and b.strip().lower() != "none"]
     max_batch = max(batches)
     budget = PROMPT_LEN + NEW_TOKENS + 64
     options = EngineOptions(
@@ -252,11 +255,15 @@ def main() -> int:
         launches_before = ops.launch_count
         replays_before = engine.graphs.replays if engine.graphs else 0
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if args.profiler_range == "decode" and batch == args.batch:
+            torch.cuda.cudart().cudaProfilerStart()
         start.record()
         for _ in range(steps):
             ops.argmax(engine.step(entries))
         end.record()
         torch.cuda.synchronize()
+        if args.profiler_range == "decode" and batch == args.batch:
+            torch.cuda.cudart().cudaProfilerStop()
         device_ms = start.elapsed_time(end)
         clock_info = clocks.stop()
         launches = ops.launch_count - launches_before
@@ -282,11 +289,16 @@ def main() -> int:
             tokens = prompts(1)[0]
             request = ("prefill", i)
             torch.cuda.synchronize()
+            profiled = args.profiler_range == "prefill" and i == warmup
+            if profiled:
+                torch.cuda.cudart().cudaProfilerStart()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             engine.step([StepEntry(request, tokens, [PROMPT_LEN - 1])])
             end.record()
             torch.cuda.synchronize()
+            if profiled:
+                torch.cuda.cudart().cudaProfilerStop()
             engine.finish(request)
             if i >= warmup:
                 times.append(start.elapsed_time(end))

@@ -31,17 +31,29 @@ struct DecodeArgs {
     float scale;
 };
 
-template <int GMAX, int DC>
+// D = head size (16, 32, 64, 128 or 256), GMAX = query heads per KV head, rounded up.
+//
+// Memory-level parallelism is what this kernel lives on, so both phases issue all their
+// loads before they use any.  Scores: lane-per-key, the key row read in 16-byte pieces, 8
+// of them in flight per lane.  P*V: the value rows of a 32-key group are read 16 bytes per
+// lane with D/8 lanes across a row, so 8 load instructions fetch the whole group; a lane
+// accumulates 8 columns of the rows it sees and the lanes that share columns are summed
+// once at the end.
+template <int D, int GMAX>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(DecodeArgs a) {
+    constexpr int LANES_PER_ROW = D / 8;                                   // 2 .. 32
+    constexpr int ROWS_PER_LOAD = 32 / LANES_PER_ROW;                      // 16 .. 1
+    constexpr int V_LOADS = 32 / ROWS_PER_LOAD;                            // loads per 32-key group
+    constexpr int K_CHUNK = D < 64 ? D : 64;                               // elements of a key row per batch of loads
+
     extern __shared__ float smem[];
-    const int d = a.head_dim;
     const int group = a.heads / a.kv_heads;
-    float* q_s = smem;                               // [GMAX][d]
-    float* p_s = q_s + GMAX * d;                     // [WARPS][GMAX][32]
+    float* q_s = smem;                               // [GMAX][D]
+    float* p_s = q_s + GMAX * D;                     // [WARPS][GMAX][32]
     int* row_s = (int*)(p_s + WARPS * GMAX * 32);    // [WARPS][32]
     float* merge_ml = (float*)(row_s + WARPS * 32);  // [WARPS][GMAX][2]
-    float* merge_acc = merge_ml + WARPS * GMAX * 2;  // [WARPS][GMAX][DC * 64]
+    float* merge_acc = merge_ml + WARPS * GMAX * 2;  // [WARPS][GMAX][D]
 
     const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -54,20 +66,22 @@ decode_split_kernel(DecodeArgs a) {
     const int end = min(begin + chunk, pos + 1);
     const int* table = a.block_table + (size_t)a.seq_of_token[t] * a.width;
 
-    for (int i = threadIdx.x; i < group * d; i += blockDim.x) {
-        const int h = i / d, c = i % d;
-        q_s[h * d + c] = __bfloat162float(a.q[((size_t)t * a.heads + g * group + h) * d + c]);
+    for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
+        const int h = i / D, c = i % D;
+        q_s[h * D + c] = __bfloat162float(a.q[((size_t)t * a.heads + g * group + h) * D + c]);
     }
     __syncthreads();
 
-    float acc[GMAX][DC][2];
+    const int my_col = (lane % LANES_PER_ROW) * 8;   // the 8 value columns this lane accumulates
+    const int my_sub = lane / LANES_PER_ROW;         // which row of each load this lane sees
+    float acc[GMAX][8];
     float run_max[GMAX], run_sum[GMAX];
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
         run_max[h] = -INFINITY;
         run_sum[h] = 0.0f;
 #pragma unroll
-        for (int c = 0; c < DC; ++c) acc[h][c][0] = acc[h][c][1] = 0.0f;
+        for (int c = 0; c < 8; ++c) acc[h][c] = 0.0f;
     }
 
     for (int p0 = begin + warp * 32; p0 < end; p0 += WARPS * 32) {
@@ -79,24 +93,30 @@ decode_split_kernel(DecodeArgs a) {
         int row = 0;
         if (valid) {
             row = table[p / a.page_size] * a.page_size + p % a.page_size;
-            const __nv_bfloat16* k_row = a.k_cache + ((size_t)row * a.kv_heads + g) * d;
-            for (int c = 0; c < d; c += 8) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(k_row + c);
-                const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                float kf[8];
+            const __nv_bfloat16* k_row = a.k_cache + ((size_t)row * a.kv_heads + g) * D;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(pairs[i]);
-                    kf[2 * i] = f.x;
-                    kf[2 * i + 1] = f.y;
-                }
+            for (int c0 = 0; c0 < D; c0 += K_CHUNK) {
+                uint4 raw[K_CHUNK / 8];
 #pragma unroll
-                for (int h = 0; h < GMAX; ++h) {
-                    if (h < group) {
-                        const float4 q0 = *reinterpret_cast<const float4*>(q_s + h * d + c);
-                        const float4 q1 = *reinterpret_cast<const float4*>(q_s + h * d + c + 4);
-                        score[h] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] +
-                                    q1.x * kf[4] + q1.y * kf[5] + q1.z * kf[6] + q1.w * kf[7];
+                for (int i = 0; i < K_CHUNK / 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(k_row + c0 + i * 8);
+#pragma unroll
+                for (int i = 0; i < K_CHUNK / 8; ++i) {
+                    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+                    float kf[8];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __bfloat1622float2(pairs[e]);
+                        kf[2 * e] = f.x;
+                        kf[2 * e + 1] = f.y;
+                    }
+#pragma unroll
+                    for (int h = 0; h < GMAX; ++h) {
+                        if (h < group) {
+                            const float4 q0 = *reinterpret_cast<const float4*>(q_s + h * D + c0 + i * 8);
+                            const float4 q1 = *reinterpret_cast<const float4*>(q_s + h * D + c0 + i * 8 + 4);
+                            score[h] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] +
+                                        q1.x * kf[4] + q1.y * kf[5] + q1.z * kf[6] + q1.w * kf[7];
+                        }
                     }
                 }
             }
@@ -112,57 +132,69 @@ decode_split_kernel(DecodeArgs a) {
                 run_sum[h] = run_sum[h] * correction + warp_sum(weight);
                 run_max[h] = new_max;
 #pragma unroll
-                for (int c = 0; c < DC; ++c) {
-                    acc[h][c][0] *= correction;
-                    acc[h][c][1] *= correction;
-                }
+                for (int c = 0; c < 8; ++c) acc[h][c] *= correction;
                 p_s[(warp * GMAX + h) * 32 + lane] = weight;
             }
         }
         __syncwarp();
         const int count = min(32, end - p0);
-        for (int j = 0; j < count; ++j) {
-            const __nv_bfloat16* v_row = a.v_cache + ((size_t)row_s[warp * 32 + j] * a.kv_heads + g) * d;
+        uint4 vraw[V_LOADS];
 #pragma unroll
-            for (int c = 0; c < DC; ++c) {
-                const int col = c * 64 + lane * 2;
-                if (col < d) {
-                    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(v_row + col));
+        for (int i = 0; i < V_LOADS; ++i) {
+            const int j = i * ROWS_PER_LOAD + my_sub;
+            vraw[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < count) {
+                const __nv_bfloat16* v_row = a.v_cache + ((size_t)row_s[warp * 32 + j] * a.kv_heads + g) * D;
+                vraw[i] = *reinterpret_cast<const uint4*>(v_row + my_col);
+            }
+        }
 #pragma unroll
-                    for (int h = 0; h < GMAX; ++h) {
-                        if (h < group) {
-                            const float w = p_s[(warp * GMAX + h) * 32 + j];
-                            acc[h][c][0] = fmaf(w, v.x, acc[h][c][0]);
-                            acc[h][c][1] = fmaf(w, v.y, acc[h][c][1]);
-                        }
-                    }
+        for (int i = 0; i < V_LOADS; ++i) {
+            const int j = i * ROWS_PER_LOAD + my_sub;  // weights of keys past `count` are zero
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&vraw[i]);
+            float vf[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(pairs[e]);
+                vf[2 * e] = f.x;
+                vf[2 * e + 1] = f.y;
+            }
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h) {
+                if (h < group) {
+                    const float w = p_s[(warp * GMAX + h) * 32 + j];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) acc[h][c] = fmaf(w, vf[c], acc[h][c]);
                 }
             }
         }
         __syncwarp();
     }
 
-    // merge the four warps in warp order
+    // lanes that hold the same columns (different rows) are summed, then the four warps merge
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
         if (h < group) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float v = acc[h][c];
+#pragma unroll
+                for (int o = LANES_PER_ROW; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                acc[h][c] = v;
+            }
             if (lane == 0) {
                 merge_ml[(warp * GMAX + h) * 2] = run_max[h];
                 merge_ml[(warp * GMAX + h) * 2 + 1] = run_sum[h];
             }
+            if (lane < LANES_PER_ROW) {
 #pragma unroll
-            for (int c = 0; c < DC; ++c) {
-                const int col = c * 64 + lane * 2;
-                if (col < d) {
-                    merge_acc[(warp * GMAX + h) * DC * 64 + col] = acc[h][c][0];
-                    merge_acc[(warp * GMAX + h) * DC * 64 + col + 1] = acc[h][c][1];
-                }
+                for (int c = 0; c < 8; ++c) merge_acc[(warp * GMAX + h) * D + my_col + c] = acc[h][c];
             }
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < group * d; i += blockDim.x) {
-        const int h = i / d, col = i % d;
+    for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
+        const int h = i / D, col = i % D;
         float m = -INFINITY;
         for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge_ml[(w * GMAX + h) * 2]);
         float sum = 0.0f, out = 0.0f;
@@ -170,13 +202,13 @@ decode_split_kernel(DecodeArgs a) {
             const float wm = merge_ml[(w * GMAX + h) * 2];
             const float f = wm == -INFINITY ? 0.0f : expf(wm - m);
             sum += f * merge_ml[(w * GMAX + h) * 2 + 1];
-            out += f * merge_acc[(w * GMAX + h) * DC * 64 + col];
+            out += f * merge_acc[(w * GMAX + h) * D + col];
         }
-        float* dst = a.partial + (((size_t)t * a.heads + g * group + h) * a.splits + split) * (d + 2);
+        float* dst = a.partial + (((size_t)t * a.heads + g * group + h) * a.splits + split) * (D + 2);
         dst[col] = out;
         if (col == 0) {
-            dst[d] = m;
-            dst[d + 1] = sum;
+            dst[D] = m;
+            dst[D + 1] = sum;
         }
     }
 }
@@ -200,12 +232,11 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bflo
     }
 }
 
-template <int GMAX, int DC>
+template <int D, int GMAX>
 int launch_split(const DecodeArgs& a, int tokens, cudaStream_t stream) {
-    const int d = a.head_dim;
-    const size_t smem = sizeof(float) * ((size_t)GMAX * d + WARPS * GMAX * 32 + WARPS * 32 + WARPS * GMAX * 2 +
-                                         (size_t)WARPS * GMAX * DC * 64);
-    auto kernel = decode_split_kernel<GMAX, DC>;
+    const size_t smem = sizeof(float) * ((size_t)GMAX * D + WARPS * GMAX * 32 + WARPS * 32 + WARPS * GMAX * 2 +
+                                         (size_t)WARPS * GMAX * D);
+    auto kernel = decode_split_kernel<D, GMAX>;
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -231,8 +262,9 @@ SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const v
                                      void* out, int tokens, int heads, int kv_heads, int head_dim, int page_size,
                                      float scale, int window, int splits, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
-    if (head_dim <= 0 || head_dim > 256 || head_dim % 16 || kv_heads <= 0 || heads % kv_heads || splits < 1)
-        return SHISO_ERR_SHAPE;
+    if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
+    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256)
+        return SHISO_ERR_UNSUPPORTED;  // other head sizes take the general kernel
     const int group = heads / kv_heads;
     if (group > 8) return SHISO_ERR_UNSUPPORTED;
     DecodeArgs a;
@@ -252,13 +284,11 @@ SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const v
     a.window = window;
     a.scale = scale;
     const int gmax = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
-    const int dc = head_dim <= 64 ? 1 : head_dim <= 128 ? 2 : 4;
     int status = SHISO_ERR_UNSUPPORTED;
-#define SHISO_CASE(G, C) if (gmax == G && dc == C) status = launch_split<G, C>(a, tokens, stream);
-    SHISO_CASE(1, 1) SHISO_CASE(1, 2) SHISO_CASE(1, 4)
-    SHISO_CASE(2, 1) SHISO_CASE(2, 2) SHISO_CASE(2, 4)
-    SHISO_CASE(4, 1) SHISO_CASE(4, 2) SHISO_CASE(4, 4)
-    SHISO_CASE(8, 1) SHISO_CASE(8, 2) SHISO_CASE(8, 4)
+#define SHISO_CASE(D_, G_) if (head_dim == D_ && gmax == G_) status = launch_split<D_, G_>(a, tokens, stream);
+#define SHISO_CASES(D_) SHISO_CASE(D_, 1) SHISO_CASE(D_, 2) SHISO_CASE(D_, 4) SHISO_CASE(D_, 8)
+    SHISO_CASES(16) SHISO_CASES(32) SHISO_CASES(64) SHISO_CASES(128) SHISO_CASES(256)
+#undef SHISO_CASES
 #undef SHISO_CASE
     if (status != 0) return status;
     dim3 grid(heads, tokens);

@@ -264,12 +264,16 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
 
 
 MAX_DECODE_GROUP = 8  # query heads per KV head the decode kernel serves from one read
+DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)  # other head sizes take the general kernel
+PREFILL_MAX_HEAD_DIM = 128  # the tiled prompt kernel keeps a row's output in registers
 
 
-def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step):
+def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step,
+                    general=False):
     """Attention of every row over its sequence's cache.  Steps of single tokens in bfloat16
-    take the split-key decode kernel (keys and values read once per KV head); everything
-    else takes the general kernel."""
+    take the split-key decode kernel (keys and values read once per KV head); other bfloat16
+    steps take the tiled tensor-core kernel; float32 and head sizes above 128 take the general
+    kernel.  ``general=True`` forces the general kernel (tests compare the routes)."""
     _check(q, "q", None, 2)
     tokens = q.shape[0]
     if q.shape[1] != heads * head_dim:
@@ -281,12 +285,14 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
     _check(block_table, "block table", torch.int32, 2)
     out = torch.empty_like(q)
     lib = library()
-    if (
+    if general:
+        pass
+    elif (
         q.dtype == torch.bfloat16 and getattr(step, "all_decode", False)
-        and heads // kv_heads <= MAX_DECODE_GROUP and head_dim % 16 == 0
+        and heads // kv_heads <= MAX_DECODE_GROUP and head_dim in DECODE_HEAD_DIMS
     ):
         capacity = block_table.shape[1] * page_size
-        splits = max(1, min(32, -(-2 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
+        splits = max(1, min(32, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 64)))
         scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
         status = lib.shiso_decode_attention(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
@@ -294,6 +300,19 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
             float(scale), int(window), splits, _stream(),
         )
         _done(status, "decode_attention", 2)
+        return out
+    elif q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= PREFILL_MAX_HEAD_DIM:
+        starts = getattr(step, "h_q_start", None)
+        if starts:
+            tiles = sum(-(-(b - a) // 64) for a, b in zip(starts[:-1], starts[1:]))
+        else:
+            tiles = tokens // 64 + step.num_seqs
+        status = lib.shiso_prefill_attention(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
+            _ptr(step.start_pos), _ptr(out), step.num_seqs, tiles, heads, kv_heads, head_dim, page_size,
+            float(scale), int(window), _stream(),
+        )
+        _done(status, "prefill_attention")
         return out
     status = lib.shiso_paged_attention(
         _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],

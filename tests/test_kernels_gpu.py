@@ -33,8 +33,10 @@ def close(got, want, dtype, what, rel32=2e-6, scale=None):
     got, want = got.double().cpu(), want.double().cpu()
     s = scale if scale is not None else max(want.abs().max().item(), 1e-6)
     err = (got - want).abs().max().item()
-    # bfloat16 results carry one rounding of the output (2^-9 relative) plus the float32 sums
-    bound = rel32 * s if dtype == torch.float32 else 2 ** -8 * s
+    # bfloat16: both sides round their result to bfloat16, so where the unrounded values
+    # straddle a rounding boundary they differ by one unit in the last place, which is between
+    # 2^-8 and 2^-7 of the value; one such unit at the largest value is the bound.
+    bound = rel32 * s if dtype == torch.float32 else 2 ** -7 * s
     assert err <= bound, f"{what}: error {err:.3e} > {bound:.3e} (scale {s:.3e})"
 
 
@@ -310,7 +312,57 @@ def test_decode_attention_split_keys(case):
         got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
         close(got, want, dtype, f"decode attention {case} window {window}")
         # the general kernel on the same inputs, for the difference between the two routes
-        gpu.all_decode = False
-        general = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
-        gpu.all_decode = True
+        general = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu,
+                                        general=True)
         close(got, general, dtype, "decode kernel against the general kernel")
+
+
+@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (8, 2, 64, 16), (6, 3, 48, 8), (5, 5, 80, 16), (4, 1, 128, 16), (2, 2, 112, 4)])
+def test_prefill_attention_tiles(case):
+    """Prompt portions in bfloat16 take the tiled tensor-core kernel: portions that span several
+    query tiles and many key tiles, portions that start deep in a sequence, single rows beside
+    them, windows that cut inside and between tiles."""
+    heads, kv_heads, d, page = case
+    q_lens, starts = [5, 1, 130, 64, 2, 65], [0, 37, 3, 70, 333, 0]
+    num_pages = sum(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 3
+    cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 70)
+    cpu.h_q_start = gpu.h_q_start = cpu.q_start.tolist()
+    dtype = torch.bfloat16
+    k = rnd((num_pages, page, kv_heads, d), dtype, 71)
+    v = rnd((num_pages, page, kv_heads, d), dtype, 72)
+    q = rnd((sum(q_lens), heads * d), dtype, 73)
+    scale = 1.0 / math.sqrt(d)
+    for window in (0, 100, 9):
+        want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, scale, window, cpu)
+        got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
+        close(got, want, dtype, f"tiled attention {case} window {window}")
+
+
+def test_prefill_attention_never_reads_outside_its_range():
+    """Cache rows the portion must not see hold NaN: pages of other requests, positions after
+    the portion, pages a window has passed (holes in the table)."""
+    heads, kv_heads, d, page = 4, 2, 64, 16
+    q_lens, starts = [70, 3], [60, 0]
+    num_pages = 16
+    cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 80)
+    cpu.h_q_start = gpu.h_q_start = cpu.q_start.tolist()
+    k = rnd((num_pages, page, kv_heads, d), torch.bfloat16, 81)
+    v = rnd((num_pages, page, kv_heads, d), torch.bfloat16, 82)
+    q = rnd((73, heads * d), torch.bfloat16, 83)
+    window = 40
+    want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, 0.125, window, cpu)
+    kn, vn = k.clone(), v.clone()
+    used = set()
+    for s, (start, n) in enumerate(zip(starts, q_lens)):
+        for p in range(max(0, start + 1 - window), start + n):
+            used.add((table[s, p // page].item(), p % page))
+    for pg in range(num_pages):
+        for r in range(page):
+            if (pg, r) not in used:
+                kn[pg, r] = float("nan")
+                vn[pg, r] = float("nan")
+    holes = table.clone()
+    holes[0, 0] = -1  # positions 0..15 of sequence 0 lie before every row's window
+    got = ops().paged_attention(q.cuda(), heads, kv_heads, d, kn.cuda(), vn.cuda(), holes.cuda(), page, 0.125, window, gpu)
+    assert torch.isfinite(got).all()
+    close(got, want, torch.bfloat16, "tiled attention with poisoned surroundings")
