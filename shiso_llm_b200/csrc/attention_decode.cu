@@ -13,7 +13,10 @@
 //
 // Scores: lane-per-key dot products against the float query in shared memory;
 // softmax statistics in float; P*V with one key per iteration, lanes across head columns.
+#include <stdio.h>
+
 #include "common.cuh"
+#include "no_alloc.h"
 
 namespace {
 
@@ -294,4 +297,62 @@ SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const v
     dim3 grid(heads, tokens);
     decode_merge_kernel<<<grid, head_dim >= 128 ? 128 : 64, 0, stream>>>(scratch, (__nv_bfloat16*)out, heads, head_dim, splits);
     return launch_status();
+}
+
+// ---------------------------------------------------------------------------- no allocation
+//
+// The variant for callers that must not allocate (see no_alloc.h): the same two kernels, with
+// the partial results in a fixed array of the device image.  In host code `no_alloc_scratch`
+// is only a handle for the symbol, not a device address; the address is asked for once per
+// device below and that pointer is what the kernels get.
+
+static __device__ __align__(256) float no_alloc_scratch[SHISO_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* no_alloc_address[MAX_DEVICES];  // per device, filled by the first call on that device
+thread_local char no_alloc_error[256] = "";
+}  // namespace
+
+SHISO_API const char* shiso_no_alloc_last_error(void) { return no_alloc_error; }
+
+SHISO_API int shiso_decode_attention_no_alloc(const void* q, const void* k_cache, const void* v_cache,
+                                              const int* block_table, int table_width, const int* positions,
+                                              const int* seq_of_token, void* out, int tokens, int heads, int kv_heads,
+                                              int head_dim, int page_size, float scale, int window, int splits,
+                                              cudaStream_t stream) {
+    no_alloc_error[0] = 0;
+    if (tokens <= 0) return SHISO_OK;
+    if (heads <= 0 || head_dim <= 0 || splits < 1) {
+        snprintf(no_alloc_error, sizeof(no_alloc_error), "heads, head_dim and splits must be positive");
+        return SHISO_ERR_SHAPE;
+    }
+    const long long need = shiso_decode_attention_scratch_floats(tokens, heads, head_dim, splits);
+    if (need > (long long)SHISO_NO_ALLOC_SCRATCH_FLOATS) {
+        snprintf(no_alloc_error, sizeof(no_alloc_error),
+                 "decode attention without allocation: %d tokens x %d heads x %d splits x (%d + 2) = %lld floats of "
+                 "scratch, the built-in array holds %d; use fewer splits or tokens, or the entry point that takes a scratch buffer",
+                 tokens, heads, splits, head_dim, need, (int)SHISO_NO_ALLOC_SCRATCH_FLOATS);
+        return SHISO_ERR_TOO_LARGE;
+    }
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MAX_DEVICES) {
+        snprintf(no_alloc_error, sizeof(no_alloc_error), "device index %d is outside the table of %d", device, MAX_DEVICES);
+        return SHISO_ERR_UNSUPPORTED;
+    }
+    if (no_alloc_address[device] == nullptr) {
+        // Set-up, once per device, with that device current: the symbol's address on THIS device.
+        float* address = nullptr;
+        e = cudaGetSymbolAddress((void**)&address, no_alloc_scratch);
+        if (e != cudaSuccess) {
+            snprintf(no_alloc_error, sizeof(no_alloc_error), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        no_alloc_address[device] = address;
+    }
+    return shiso_decode_attention(q, k_cache, v_cache, block_table, table_width, positions, seq_of_token,
+                                  no_alloc_address[device], out, tokens, heads, kv_heads, head_dim, page_size, scale,
+                                  window, splits, stream);
 }
