@@ -1,0 +1,178 @@
+// Y[T, N] = X[T, K] * W[N, K]^T for a handful of rows (T <= 32), bfloat16: the decode step's
+// matrix products, which are weight streaming.
+//
+// At these sizes a product is over in a few microseconds, so what counts is how soon the
+// weight bytes are in flight and how little else happens: no tensor map, no tensor memory,
+// no cluster.  A CTA owns 16 output features (or 8 gate + 8 up rows of a SwiGLU pair); its
+// four warps split K and every lane streams its 16-byte pieces of two weight rows straight
+// from global memory, many in flight, into mma.sync m16n8k16 (weights are the M operand,
+// tokens the N operand).  A lane's 8 consecutive k values feed two MMAs as (k0..k3 | k4..k7);
+// the activation fragment is loaded with the same permutation, so the sum over k is the same
+// set of products.  The four partial tiles are summed through shared memory in warp order,
+// so the result does not depend on timing.
+//
+// With `inter > 0` the weight is a [2 * inter, K] gate-over-up pair and the epilogue writes
+// silu(gate) * up (kernels/cuda/generic/glu.cuh:35-57) - the activation never leaves the chip.
+//
+// The reference's decode products are matvec kernels that re-read the weights per row block
+// (crates/shiso-engine/src/projection.rs:972-1069).
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS_K = 4;  // warps that split K
+
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load16(const __nv_bfloat16* p, bool valid) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) v = __ldg(reinterpret_cast<const uint4*>(p));
+    return v;
+}
+
+struct SkinnyArgs {
+    const __nv_bfloat16* x;  // [T, K]
+    const __nv_bfloat16* w;  // [N, K] (N = 2 * inter for a gate/up pair)
+    const float* bias;       // [N] or null (plain products only)
+    void* y;                 // [T, N] or [T, inter]
+    int T, N, K, inter, out_f32;
+};
+
+// NT = 8-token tiles (1, 2 or 4); UNROLL = 64-wide k blocks whose loads are issued together.
+template <int NT, int UNROLL>
+__global__ void __launch_bounds__(WARPS_K * 32)
+gemm_skinny_kernel(SkinnyArgs a) {
+    __shared__ float partial[WARPS_K][NT][32][4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const bool glu = a.inter > 0;
+    // rows of the 16 x K weight tile: g and g + 8
+    int row_lo, row_hi;
+    if (glu) {
+        row_lo = blockIdx.x * 8 + g;          // gate row
+        row_hi = a.inter + blockIdx.x * 8 + g;  // its up row
+    } else {
+        row_lo = blockIdx.x * 16 + g;
+        row_hi = row_lo + 8;
+    }
+    const int limit = glu ? a.inter : a.N;
+    const bool lo_ok = glu ? (blockIdx.x * 8 + g < limit) : (row_lo < limit);
+    const bool hi_ok = glu ? lo_ok : (row_hi < limit);
+    const __nv_bfloat16* w_lo = a.w + (size_t)row_lo * a.K;
+    const __nv_bfloat16* w_hi = a.w + (size_t)row_hi * a.K;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+
+    // warp w takes the 64-wide k blocks w, w + 4, ...; a lane owns 16 consecutive k of a block
+    for (int k0 = warp * 64; k0 < a.K; k0 += WARPS_K * 64 * UNROLL) {
+        uint4 wl[UNROLL][2], wh[UNROLL][2];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = k0 + u * WARPS_K * 64 + t4 * 16;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const bool in = k + h * 8 < a.K;
+                wl[u][h] = load16(w_lo + k + h * 8, in && lo_ok);
+                wh[u][h] = load16(w_hi + k + h * 8, in && hi_ok);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = k0 + u * WARPS_K * 64 + t4 * 16;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int token = n * 8 + g;
+                const __nv_bfloat16* x_row = a.x + (size_t)token * a.K + k;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 xv = load16(x_row + h * 8, token < a.T && k + h * 8 < a.K);
+                    mma_bf16(acc[n], wl[u][h].x, wh[u][h].x, wl[u][h].y, wh[u][h].y, xv.x, xv.y);
+                    mma_bf16(acc[n], wl[u][h].z, wh[u][h].z, wl[u][h].w, wh[u][h].w, xv.z, xv.w);
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) partial[warp][n][lane][e] = acc[n][e];
+    __syncthreads();
+    // every thread finishes one (n, lane, e) element per pass: NT * 128 elements, 128 threads
+    for (int i = threadIdx.x; i < NT * 128; i += WARPS_K * 32) {
+        const int n = i / 128, l = (i / 4) % 32, e = i % 4;
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS_K; ++w) sum += partial[w][n][l][e];
+        partial[0][n][l][e] = sum;  // only this thread touches this element
+    }
+    __syncthreads();
+    // c0: (row g, token 2t), c1: (row g, token 2t+1), c2: (row g+8, token 2t), c3: (row g+8, token 2t+1)
+    if (warp == 0) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int token = n * 8 + t4 * 2 + e;
+                if (token >= a.T) continue;
+                const float lo = partial[0][n][lane][e], hi = partial[0][n][lane][2 + e];
+                if (glu) {
+                    if (lo_ok) {
+                        const float v = lo / (1.0f + expf(-lo)) * hi;
+                        const size_t at = (size_t)token * a.inter + blockIdx.x * 8 + g;
+                        if (a.out_f32) ((float*)a.y)[at] = v;
+                        else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
+                    }
+                } else {
+                    if (lo_ok) {
+                        const float v = lo + (a.bias ? a.bias[row_lo] : 0.0f);
+                        const size_t at = (size_t)token * a.N + row_lo;
+                        if (a.out_f32) ((float*)a.y)[at] = v;
+                        else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
+                    }
+                    if (hi_ok) {
+                        const float v = hi + (a.bias ? a.bias[row_hi] : 0.0f);
+                        const size_t at = (size_t)token * a.N + row_hi;
+                        if (a.out_f32) ((float*)a.y)[at] = v;
+                        else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace
+
+// x [T, K] bf16 (T <= 32), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
+// inter == 0: y[T, N] = x w^T (+ bias).  inter > 0: N == 2 * inter, y[T, inter] = silu(x gate^T) * (x up^T).
+SHISO_API int shiso_gemm_skinny(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
+                                int K, int inter, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (T > 32 || K % 8 != 0 || K <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
+    if (inter > 0 && (N != 2 * inter || bias)) return SHISO_ERR_SHAPE;
+    SkinnyArgs a;
+    a.x = (const __nv_bfloat16*)x;
+    a.w = (const __nv_bfloat16*)w;
+    a.bias = bias;
+    a.y = y;
+    a.T = T;
+    a.N = N;
+    a.K = K;
+    a.inter = inter;
+    a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    const unsigned blocks = inter > 0 ? ceil_div_u(inter, 8) : ceil_div_u(N, 16);
+    const dim3 block(WARPS_K * 32);
+    if (T <= 8) gemm_skinny_kernel<1, 4><<<blocks, block, 0, stream>>>(a);
+    else if (T <= 16) gemm_skinny_kernel<2, 4><<<blocks, block, 0, stream>>>(a);
+    else gemm_skinny_kernel<4, 2><<<blocks, block, 0, stream>>>(a);
+    return launch_status();
+}

@@ -66,6 +66,46 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
     if (threadIdx.x == 0) out[blockIdx.x] = (r.i == 0x7fffffff) ? 0 : r.i;
 }
 
+// Greedy pick in two stages for wide vocabularies: a row is cut into chunks, one block each,
+// so that a handful of rows still keeps many SMs reading; the second stage picks among the
+// chunk winners (ascending chunk order, so the lower id still wins a tie).
+__global__ void __launch_bounds__(256)
+argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ best_v, int* __restrict__ best_i, int vocab,
+                    int chunk_len, int chunks) {
+    __shared__ Best scratch[32];
+    const int chunk = blockIdx.x, row_index = blockIdx.y;
+    const float* row = logits + (size_t)row_index * vocab;
+    const int begin = chunk * chunk_len, end = min(begin + chunk_len, vocab);
+    Best mine{-INFINITY, 0x7fffffff};
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        if (isfinite(v) && v > mine.v) mine = Best{v, i};
+    }
+    const Best r = block_best(mine, scratch);
+    if (threadIdx.x == 0) {
+        best_v[(size_t)row_index * chunks + chunk] = r.v;
+        best_i[(size_t)row_index * chunks + chunk] = r.i;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i,
+                                    int* __restrict__ out, int chunks) {
+    const int row_index = blockIdx.x;
+    Best mine{-INFINITY, 0x7fffffff};
+    for (int c = threadIdx.x; c < chunks; c += 32) {
+        const Best other{best_v[(size_t)row_index * chunks + c], best_i[(size_t)row_index * chunks + c]};
+        mine = better(mine, other);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, mine.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, mine.i, o);
+        mine = better(mine, other);
+    }
+    if (threadIdx.x == 0) out[row_index] = (mine.i == 0x7fffffff) ? 0 : mine.i;
+}
+
 // ---- keyed noise ------------------------------------------------------------------------
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
@@ -221,5 +261,18 @@ SHISO_API int shiso_sample(const float* logits, const float* temperature, const 
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0) return SHISO_ERR_SHAPE;
     sample_kernel<<<rows, THREADS, 0, stream>>>(logits, temperature, top_k, top_p, min_p, keys, positions, out, vocab);
+    return launch_status();
+}
+
+// Two-stage greedy pick; `scratch` holds rows * chunks floats followed by rows * chunks ints.
+SHISO_API int shiso_argmax_chunked(const float* logits, int* out, float* scratch, int rows, int vocab, int chunks,
+                                   cudaStream_t stream) {
+    if (rows <= 0) return SHISO_OK;
+    if (vocab <= 0 || chunks <= 0) return SHISO_ERR_SHAPE;
+    const int chunk_len = (vocab + chunks - 1) / chunks;
+    float* best_v = scratch;
+    int* best_i = (int*)(scratch + (size_t)rows * chunks);
+    argmax_chunk_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, best_v, best_i, vocab, chunk_len, chunks);
+    argmax_final_kernel<<<rows, 32, 0, stream>>>(best_v, best_i, out, chunks);
     return launch_status();
 }

@@ -78,6 +78,51 @@ __global__ void short_conv_state_kernel(const AT* __restrict__ proj, float* __re
         if (j < taps - 1) state_row[(size_t)j * hidden + ch] = next[j];
 }
 
+// Both in one launch for steps whose sequences bring only a few rows (decode): one thread owns a
+// (sequence, channel) pair, keeps the window of gated inputs in registers and walks the
+// sequence's rows in order, as the reference's kernel does for a whole portion
+// (kernels/metal/dense/dense_short_conv.metal:45-67).  Nothing else touches that pair's
+// state, so reading and rewriting it in one kernel is safe.
+template <typename AT>
+__global__ void short_conv_serial_kernel(const AT* __restrict__ proj, const float* __restrict__ w,
+                                         const float* __restrict__ bias, float* __restrict__ state,
+                                         long long slot_stride, const int* __restrict__ q_start,
+                                         const int* __restrict__ slots, AT* __restrict__ y, int hidden, int taps) {
+    const int s = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (ch >= hidden) return;
+    const int first = q_start[s];
+    const int n = q_start[s + 1] - first;
+    float* state_row = state + (size_t)slots[s] * slot_stride;
+    float window[MAX_TAPS], weight[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+        weight[j] = j < taps ? w[(size_t)ch * taps + j] : 0.0f;
+        window[j] = j < taps - 1 ? state_row[(size_t)j * hidden + ch] : 0.0f;
+    }
+    const float b = bias ? bias[ch] : 0.0f;
+    for (int i = 0; i < n; ++i) {
+        const AT* row = proj + (size_t)(first + i) * 3 * hidden;
+        const float u = to_f32(row[ch]) * to_f32(row[2 * hidden + ch]);
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) {
+            if (j < taps) {
+                const float v = j == taps - 1 ? u : window[j];
+                acc = fmaf(weight[j], v, acc);
+            }
+        }
+        y[(size_t)(first + i) * hidden + ch] = from_f32<AT>(to_f32(row[hidden + ch]) * (acc + b));
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS - 1; ++j) {
+            if (j < taps - 1) window[j] = j == taps - 2 ? u : window[j + 1];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+        if (j < taps - 1) state_row[(size_t)j * hidden + ch] = window[j];
+}
+
 }  // namespace
 
 // state: float [slots, taps-1, hidden] with `slot_stride` floats between slots (the rows
@@ -85,10 +130,22 @@ __global__ void short_conv_state_kernel(const AT* __restrict__ proj, float* __re
 SHISO_API int shiso_short_conv(const void* proj, int act_dtype, const float* w, const float* bias, float* state,
                                long long slot_stride, const int* seq_of_token, const int* q_start,
                                const int* slots, void* y, int tokens, int seqs, int hidden, int taps,
-                               int update_state, cudaStream_t stream) {
+                               int update_state, int max_rows_per_seq, cudaStream_t stream) {
     if (tokens <= 0 || seqs <= 0) return SHISO_OK;
     if (taps < 2 || taps > MAX_TAPS) return SHISO_ERR_SHAPE;
     const int threads = 128;
+    if (update_state && max_rows_per_seq > 0 && max_rows_per_seq <= 4) {
+        dim3 grid(seqs, ceil_div_u(hidden, threads));
+        if (act_dtype == SHISO_F32)
+            short_conv_serial_kernel<float><<<grid, threads, 0, stream>>>(
+                (const float*)proj, w, bias, state, slot_stride, q_start, slots, (float*)y, hidden, taps);
+        else if (act_dtype == SHISO_BF16)
+            short_conv_serial_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+                (const __nv_bfloat16*)proj, w, bias, state, slot_stride, q_start, slots, (__nv_bfloat16*)y, hidden, taps);
+        else
+            return SHISO_ERR_DTYPE;
+        return launch_status();
+    }
     dim3 grid_out(tokens, ceil_div_u(hidden, threads));
     dim3 grid_state(seqs, ceil_div_u(hidden, threads));
     if (act_dtype == SHISO_F32) {

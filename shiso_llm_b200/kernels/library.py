@@ -27,12 +27,14 @@ _SIGNATURES = {
     "shiso_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
     "shiso_gemm_tcgen05_status": [],
-    "shiso_short_conv": [P, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "shiso_gemm_skinny": [P, P, P, P, I, I, I, I, I, P],
+    "shiso_short_conv": [P, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, I, P],
     "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "shiso_decode_attention": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
     "shiso_prefill_attention": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "shiso_argmax": [P, P, I, I, P],
+    "shiso_argmax_chunked": [P, P, P, I, I, I, P],
     "shiso_sample": [P, P, P, P, P, P, P, P, I, I, P],
 }
 

@@ -138,6 +138,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 _SM_COUNT = None
+SKINNY_MAX_TOKENS = 16  # up to here a product is weight streaming and takes the skinny kernel
 
 
 def _sm_count() -> int:
@@ -163,10 +164,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         _check(bias, "bias", torch.float32, 1)
     out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
     lib = library()
-    if (
-        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-        and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w))
-    ):
+    both_bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if both_bf16 and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0:
+        status = lib.shiso_gemm_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _stream())
+        _done(status, "linear (skinny)")
+        return out
+    if both_bf16 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _sm_count(), _stream()
         )
@@ -177,6 +180,29 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     )
     _done(status, "linear")
     return out
+
+
+def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``silu(x @ gate^T) * (x @ up^T)`` for ``gate_up = [gate; up]`` of shape ``[2I, K]``.
+    For a handful of bfloat16 rows the activation is fused into the product's epilogue;
+    otherwise the product is followed by the activation kernel."""
+    _check(x, "x", None, 2)
+    _check(gate_up, "gate_up", None, 2)
+    tokens, k = x.shape
+    two_inter = gate_up.shape[0]
+    if two_inter % 2 or gate_up.shape[1] != k:
+        raise KernelError(f"gate/up matrix of shape {tuple(gate_up.shape)} does not fit rows of {k}")
+    if (
+        x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+        and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0
+    ):
+        out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
+        status = library().shiso_gemm_skinny(
+            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2, _stream()
+        )
+        _done(status, "linear_swiglu (skinny)")
+        return out
+    return swiglu(linear(x, gate_up, out_dtype))
 
 
 def linear_simple(x, w, out_dtype, bias=None):
@@ -221,7 +247,7 @@ def short_conv(proj, taps, bias, state, step):
     status = library().shiso_short_conv(
         _ptr(proj), _code(proj), _ptr(taps), _ptr(bias), state.data_ptr(), state.stride(0),
         _ptr(step.seq_of_token), _ptr(step.q_start), _ptr(step.state_slots), _ptr(y),
-        tokens, step.num_seqs, hidden, n_taps, 1, _stream(),
+        tokens, step.num_seqs, hidden, n_taps, 1, int(getattr(step, "max_q_len", 0)), _stream(),
     )
     _done(status, "short_conv", 2)
     return y
@@ -328,8 +354,15 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     _check(logits, "logits", torch.float32, 2)
-    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _done(library().shiso_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream()), "argmax")
+    rows, vocab = logits.shape
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if vocab >= 8192:
+        chunks = min(128, -(-vocab // 1024))
+        scratch = torch.empty((2 * rows * chunks,), dtype=torch.float32, device=logits.device)
+        status = library().shiso_argmax_chunked(_ptr(logits), _ptr(out), _ptr(scratch), rows, vocab, chunks, _stream())
+        _done(status, "argmax", 2)
+        return out
+    _done(library().shiso_argmax(_ptr(logits), _ptr(out), rows, vocab, _stream()), "argmax")
     return out
 
 

@@ -2,9 +2,9 @@
 
 The gate and up matrices are stored apart in the checkpoint and run as one paired
 projection (crates/shiso-engine/src/ffn.rs:234-239); here they are joined into one
-``[2I, H]`` matrix when bound, so one product yields ``[gate | up]`` rows and the
-activation kernel reads both halves (kernels/cuda/generic/glu.cuh:35-57: alpha 1,
-no clamp).
+``[2I, H]`` matrix when bound, so one product yields ``[gate | up]`` rows; the activation
+(kernels/cuda/generic/glu.cuh:35-57: alpha 1, no clamp) is applied in the product's epilogue
+for decode-sized batches and by a kernel of its own otherwise.
 """
 
 from __future__ import annotations
@@ -44,6 +44,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, step):
         ops = self.env.ops
-        gate_up = ops.linear(x, self.gate_up, self.env.dtype)
-        mid = ops.swiglu(gate_up)
+        mid = ops.linear_swiglu(x, self.gate_up, self.env.dtype)
         return ops.linear(mid, self.down, self.env.dtype)

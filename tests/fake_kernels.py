@@ -61,6 +61,13 @@ def swiglu(gate_up):
     return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
 
 
+def linear_swiglu(x, gate_up, out_dtype):
+    y = x.to(F64) @ gate_up.to(F64).T
+    inter = y.shape[1] // 2
+    g, u = y[:, :inter], y[:, inter:]
+    return (g / (1.0 + torch.exp(-g)) * u).to(out_dtype)
+
+
 def short_conv(proj, taps, bias, state, step):
     """y[t] = c[t] * (sum_j taps[:, j] * u[t - (L-1) + j] + bias); u = b * x; the state of
     each sequence's slot holds the last L-1 values of u (float32) and is updated."""

@@ -366,3 +366,55 @@ def test_prefill_attention_never_reads_outside_its_range():
     got = ops().paged_attention(q.cuda(), heads, kv_heads, d, kn.cuda(), vn.cuda(), holes.cuda(), page, 0.125, window, gpu)
     assert torch.isfinite(got).all()
     close(got, want, torch.bfloat16, "tiled attention with poisoned surroundings")
+
+
+@pytest.mark.parametrize("shape", [(1, 96, 64), (8, 2048, 2048), (5, 1000, 96), (8, 300, 200), (16, 2048, 5632), (13, 48, 264), (3, 16, 8)])
+def test_skinny_linear_and_fused_swiglu(shape):
+    """A handful of bfloat16 rows take the weight-streaming kernel; with a gate/up pair the
+    activation is applied in its epilogue."""
+    T, N, K = shape
+    x, w = rnd((T, K), torch.bfloat16, 90), rnd((N, K), torch.bfloat16, 91, 0.05)
+    bias = rnd((N,), torch.float32, 92)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        close(ops().linear(x.cuda(), w.cuda(), out_dtype), ref.linear(x, w, out_dtype), out_dtype, f"skinny linear {shape}", rel32=1e-5)
+    close(ops().linear(x.cuda(), w.cuda(), torch.float32, bias.cuda()), ref.linear(x, w, torch.float32, bias), torch.float32, "skinny bias", rel32=1e-5)
+    if N % 2 == 0:
+        got = ops().linear_swiglu(x.cuda(), w.cuda(), torch.bfloat16)
+        close(got, ref.linear_swiglu(x, w, torch.bfloat16), torch.bfloat16, f"fused swiglu {shape}")
+    big = rnd((40, K), torch.bfloat16, 93)  # above the skinny limit: product kernel + activation kernel
+    if N % 2 == 0:
+        close(ops().linear_swiglu(big.cuda(), w.cuda(), torch.bfloat16), ref.linear_swiglu(big, w, torch.bfloat16), torch.bfloat16, "unfused swiglu")
+
+
+def test_argmax_wide_vocabulary_two_stages():
+    logits = rnd((6, 65536), torch.float32, 95)
+    logits[0, 100] = logits[0, 60000] = 77.0  # a tie across chunks: the lower id
+    logits[1, 65535] = 88.0
+    logits[2, :] = float("-inf")
+    logits[3, 1023] = logits[3, 1024] = 66.0  # a tie at a chunk's edge
+    got = ops().argmax(logits.cuda()).cpu().tolist()
+    want = ref.argmax(torch.where(torch.isfinite(logits), logits, torch.full_like(logits, float("-inf")))).tolist()
+    want[2] = 0
+    assert got == want and got[0] == 100 and got[1] == 65535 and got[3] == 1023
+    odd = rnd((3, 9001), torch.float32, 96)
+    assert ops().argmax(odd.cuda()).cpu().tolist() == ref.argmax(odd).tolist()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_short_conv_few_rows_per_sequence_takes_the_serial_kernel(dtype):
+    """Steps whose sequences bring at most four rows run one fused kernel (output and state);
+    it must give what the two-kernel route gives, bit for bit in float32."""
+    taps, hidden = 3, 300
+    q_lens, starts = [1, 1, 4, 2, 1, 3], [0, 9, 2, 0, 77, 5]
+    cpu, gpu, _ = make_step(q_lens, starts, 4, 64, 97, num_slots=8)
+    proj = rnd((sum(q_lens), 3 * hidden), dtype, 98)
+    w, b = rnd((hidden, taps), torch.float32, 99), rnd((hidden,), torch.float32, 100)
+    start = rnd((8, taps - 1, hidden), torch.float32, 101)
+    s_ref, s_two, s_one = start.clone(), start.clone().cuda(), start.clone().cuda()
+    want = ref.short_conv(proj, w, b, s_ref, cpu)
+    two = ops().short_conv(proj.cuda(), w.cuda(), b.cuda(), s_two, gpu)
+    gpu.max_q_len = 4
+    one = ops().short_conv(proj.cuda(), w.cuda(), b.cuda(), s_one, gpu)
+    close(one, want, dtype, "serial short conv", rel32=4e-6)
+    assert torch.equal(one, two) and torch.equal(s_one, s_two)
+    assert torch.allclose(s_one.cpu(), s_ref, rtol=0, atol=1e-7)
