@@ -29,6 +29,7 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
                           int table_width, AT* __restrict__ k_cache, AT* __restrict__ v_cache,
                           AT* __restrict__ q_out, int tokens, int heads, int kv_heads, int head_dim,
                           int rotary_dim, int page_size, float eps, int store) {
+    pdl_begin();
     __shared__ float staged[WARPS][MAX_HEAD_DIM];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int units = heads + 2 * kv_heads;
@@ -87,6 +88,7 @@ paged_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache,
                        const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, AT* __restrict__ out, int tokens, int heads,
                        int kv_heads, int head_dim, int page_size, float scale, int window) {
+    pdl_begin();
     __shared__ float q_s[WARPS][MAX_HEAD_DIM];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long index = (long long)blockIdx.x * WARPS + warp;
@@ -160,12 +162,12 @@ SHISO_API int shiso_qk_norm_rope_store(const void* qkv, int act_dtype, const flo
     const long long units = (long long)tokens * (heads + 2 * kv_heads);
     const unsigned blocks = ceil_div_u(units, WARPS);
     if (act_dtype == SHISO_F32)
-        qk_norm_rope_store_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+        launch_kernel(qk_norm_rope_store_kernel<float>, blocks, WARPS * 32, 0, stream, 
             (const float*)qkv, q_w, k_w, inv_freq, positions, seq_of_token, block_table, table_width,
             (float*)k_cache, (float*)v_cache, (float*)q_out, tokens, heads, kv_heads, head_dim, rotary_dim,
             page_size, eps, store);
     else if (act_dtype == SHISO_BF16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+        launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
             (const __nv_bfloat16*)qkv, q_w, k_w, inv_freq, positions, seq_of_token, block_table, table_width,
             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (__nv_bfloat16*)q_out, tokens, heads, kv_heads,
             head_dim, rotary_dim, page_size, eps, store);
@@ -182,11 +184,11 @@ SHISO_API int shiso_paged_attention(const void* q, int act_dtype, const void* k_
     if (head_dim <= 0 || head_dim > MAX_HEAD_DIM || kv_heads <= 0 || heads % kv_heads) return SHISO_ERR_SHAPE;
     const unsigned blocks = ceil_div_u((long long)tokens * heads, WARPS);
     if (act_dtype == SHISO_F32)
-        paged_attention_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+        launch_kernel(paged_attention_kernel<float>, blocks, WARPS * 32, 0, stream, 
             (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table, table_width, positions,
             seq_of_token, (float*)out, tokens, heads, kv_heads, head_dim, page_size, scale, window);
     else if (act_dtype == SHISO_BF16)
-        paged_attention_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+        launch_kernel(paged_attention_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
             table_width, positions, seq_of_token, (__nv_bfloat16*)out, tokens, heads, kv_heads, head_dim,
             page_size, scale, window);

@@ -45,6 +45,7 @@ struct DecodeArgs {
 template <int D, int GMAX>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(DecodeArgs a) {
+    pdl_begin();
     constexpr int LANES_PER_ROW = D / 8;                                   // 2 .. 32
     constexpr int ROWS_PER_LOAD = 32 / LANES_PER_ROW;                      // 16 .. 1
     constexpr int V_LOADS = 32 / ROWS_PER_LOAD;                            // loads per 32-key group
@@ -218,6 +219,7 @@ decode_split_kernel(DecodeArgs a) {
 
 __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int heads,
                                     int head_dim, int splits) {
+    pdl_begin();
     const int h = blockIdx.x, t = blockIdx.y;
     const int d = head_dim;
     const float* base = partial + ((size_t)t * heads + h) * splits * (d + 2);
@@ -249,7 +251,7 @@ int launch_split(const DecodeArgs& a, int tokens, cudaStream_t stream) {
         }
     }
     dim3 grid(a.splits, a.kv_heads, tokens);
-    kernel<<<grid, WARPS * 32, smem, stream>>>(a);
+    launch_kernel(kernel, grid, WARPS * 32, smem, stream, a);
     return launch_status();
 }
 
@@ -295,7 +297,7 @@ SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const v
 #undef SHISO_CASE
     if (status != 0) return status;
     dim3 grid(heads, tokens);
-    decode_merge_kernel<<<grid, head_dim >= 128 ? 128 : 64, 0, stream>>>(scratch, (__nv_bfloat16*)out, heads, head_dim, splits);
+    launch_kernel(decode_merge_kernel, grid, head_dim >= 128 ? 128 : 64, 0, stream, scratch, (__nv_bfloat16*)out, heads, head_dim, splits);
     return launch_status();
 }
 

@@ -71,6 +71,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 flash_prefill_kernel(PrefillArgs a) {
+    pdl_begin();
     constexpr int ROW_BYTES = D * 2 + 16;  // 16 bytes of padding: ldmatrix rows fall on distinct banks
     constexpr int CHUNKS = D / 8;          // 16-byte pieces per row
     constexpr int KSTEPS = D / 16;
@@ -279,7 +280,7 @@ int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
         }
     }
     dim3 grid(tiles, a.heads);
-    kernel<<<grid, THREADS, SMEM, stream>>>(a);
+    launch_kernel(kernel, grid, THREADS, SMEM, stream, a);
     return launch_status();
 }
 

@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define SHISO_API extern "C" __attribute__((visibility("default")))
 
@@ -59,6 +60,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     float total = (lane < nwarps) ? scratch[lane] : 0.0f;
     total = warp_sum(total);
     return total;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel is launched so that it may start while its predecessor in the stream is still
+// finishing: it announces at once that its own successor may be scheduled
+// (griddepcontrol.launch_dependents) and waits for the predecessor to complete and flush
+// (griddepcontrol.wait) before it touches anything a predecessor may have written.  Work that
+// depends on no predecessor - address arithmetic, loads of weights - goes before the wait.
+// The wait is a no-op for a kernel launched without the attribute.  SHISO_PDL=0 turns the
+// attribute off.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_begin() {
+    pdl_trigger();
+    pdl_wait();
+}
+
+bool shiso_pdl_enabled();  // defined in elementwise.cu
+
+template <typename... KArgs, typename... Args>
+static inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = shiso_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in launch_status()
 }
 
 static inline int launch_status() {

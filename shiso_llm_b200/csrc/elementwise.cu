@@ -8,11 +8,20 @@
 // compute types, so the sum a + b is formed and kept in 32-bit.
 #include "common.cuh"
 
+bool shiso_pdl_enabled() {
+    static const bool enabled = [] {
+        const char* v = getenv("SHISO_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return enabled;
+}
+
 // --------------------------------------------------------------------------- embedding
 
 template <typename WT>
 __global__ void embed_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab) {
+    pdl_begin();
     const int t = blockIdx.x;
     int id = ids[t];
     const bool valid = id >= 0 && id < vocab;  // the host refuses such ids; never read outside
@@ -26,9 +35,9 @@ SHISO_API int shiso_embed(const int* ids, const void* table, int table_dtype, fl
     if (tokens <= 0) return SHISO_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == SHISO_F32)
-        embed_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        launch_kernel(embed_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab);
     else if (table_dtype == SHISO_BF16)
-        embed_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        launch_kernel(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();
@@ -36,6 +45,7 @@ SHISO_API int shiso_embed(const int* ids, const void* table, int table_dtype, fl
 
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,
                                    float* __restrict__ out, int hidden) {
+    pdl_begin();
     const float* s = src + (size_t)rows[blockIdx.x] * hidden;
     float* d = out + (size_t)blockIdx.x * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) d[i] = s[i];
@@ -44,7 +54,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __r
 SHISO_API int shiso_gather_rows(const float* src, const int* rows, float* out, int count, int hidden,
                                 cudaStream_t stream) {
     if (count <= 0) return SHISO_OK;
-    gather_rows_kernel<<<count, 256, 0, stream>>>(src, rows, out, hidden);
+    launch_kernel(gather_rows_kernel, count, 256, 0, stream, src, rows, out, hidden);
     return launch_status();
 }
 
@@ -58,6 +68,7 @@ template <typename AT>
 __global__ void rmsnorm_kernel(float* __restrict__ residual, const AT* __restrict__ delta,
                                const int* __restrict__ rows, const float* __restrict__ w,
                                AT* __restrict__ out, int hidden, float eps) {
+    pdl_begin();
     __shared__ float scratch[33];
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     float* r = residual + (size_t)src_row * hidden;
@@ -89,11 +100,11 @@ SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows,
     if (act_dtype == SHISO_F32) {
         auto k = rmsnorm_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<out_rows, threads, smem, stream>>>(residual, (const float*)delta, rows, w, (float*)out, hidden, eps);
+        launch_kernel(k, out_rows, threads, smem, stream, residual, (const float*)delta, rows, w, (float*)out, hidden, eps);
     } else if (act_dtype == SHISO_BF16) {
         auto k = rmsnorm_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<out_rows, threads, smem, stream>>>(residual, (const __nv_bfloat16*)delta, rows, w, (__nv_bfloat16*)out, hidden, eps);
+        launch_kernel(k, out_rows, threads, smem, stream, residual, (const __nv_bfloat16*)delta, rows, w, (__nv_bfloat16*)out, hidden, eps);
     } else {
         return SHISO_ERR_DTYPE;
     }
@@ -104,6 +115,7 @@ SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows,
 
 template <typename AT>
 __global__ void swiglu_kernel(const AT* __restrict__ gate_up, AT* __restrict__ out, int inter, long long total) {
+    pdl_begin();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / inter;
@@ -120,9 +132,9 @@ SHISO_API int shiso_swiglu(const void* gate_up, void* out, int act_dtype, int to
     if (total <= 0) return SHISO_OK;
     const unsigned blocks = ceil_div_u(total, 256);
     if (act_dtype == SHISO_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+        launch_kernel(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total);
     else if (act_dtype == SHISO_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+        launch_kernel(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();

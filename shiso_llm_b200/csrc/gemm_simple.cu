@@ -17,6 +17,7 @@ template <typename WT, typename XT, typename OT>
 __global__ void __launch_bounds__(256)
 gemm_simple_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ bias,
                    OT* __restrict__ y, int T, int N, int K) {
+    pdl_begin();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -74,7 +75,7 @@ gemm_simple_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const flo
 template <typename WT, typename XT, typename OT>
 int launch(const void* x, const void* w, const float* bias, void* y, int T, int N, int K, cudaStream_t stream) {
     dim3 grid(ceil_div_u(N, BN), ceil_div_u(T, BM));
-    gemm_simple_kernel<WT, XT, OT><<<grid, 256, 0, stream>>>((const XT*)x, (const WT*)w, bias, (OT*)y, T, N, K);
+    launch_kernel(gemm_simple_kernel<WT, XT, OT>, grid, 256, 0, stream, (const XT*)x, (const WT*)w, bias, (OT*)y, T, N, K);
     return launch_status();
 }
 

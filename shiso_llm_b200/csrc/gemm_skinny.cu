@@ -4,11 +4,11 @@
 // At these sizes a product is over in a few microseconds, so what counts is how soon the
 // weight bytes are in flight and how little else happens: no tensor map, no tensor memory,
 // no cluster.  A CTA owns 16 output features (or 8 gate + 8 up rows of a SwiGLU pair); its
-// four warps split K and every lane streams its 16-byte pieces of two weight rows straight
-// from global memory, many in flight, into mma.sync m16n8k16 (weights are the M operand,
+// 8 or 16 warps split K and every lane streams its 16-byte pieces of two weight rows straight
+// from global memory, all of a round in flight at once, into mma.sync m16n8k16 (weights are the M operand,
 // tokens the N operand).  A lane's 8 consecutive k values feed two MMAs as (k0..k3 | k4..k7);
 // the activation fragment is loaded with the same permutation, so the sum over k is the same
-// set of products.  The four partial tiles are summed through shared memory in warp order,
+// set of products.  The partial tiles are summed through shared memory in warp order,
 // so the result does not depend on timing.
 //
 // With `inter > 0` the weight is a [2 * inter, K] gate-over-up pair and the epilogue writes
@@ -20,7 +20,6 @@
 
 namespace {
 
-constexpr int WARPS_K = 4;  // warps that split K
 
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -29,9 +28,24 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 load16(const __nv_bfloat16* p, bool valid) {
+// Weights are never written while the engine runs: the read-only path may fetch them at any
+// time, also before this grid's predecessor has finished.
+__device__ __forceinline__ uint4 load_weight16(const __nv_bfloat16* p, bool valid) {
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (valid) v = __ldg(reinterpret_cast<const uint4*>(p));
+    return v;
+}
+
+// Activations were written by a predecessor grid that may still have been running when this
+// grid started: an ordinary (coherent) load, which the compiler keeps after the dependency wait.
+// The read-only path (ld.global.nc) must not be used here - it may be hoisted above the wait
+// and is not guaranteed to see the predecessor's writes.
+__device__ __forceinline__ uint4 load_activation16(const __nv_bfloat16* p, bool valid) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) {
+        asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    }
     return v;
 }
 
@@ -43,18 +57,21 @@ struct SkinnyArgs {
     int T, N, K, inter, out_f32;
 };
 
-// NT = 8-token tiles (1, 2 or 4); UNROLL = 64-wide k blocks whose loads are issued together.
-template <int NT, int UNROLL>
+// NT = 8-token tiles (1, 2 or 4); WARPS_K = warps that split K; UNROLL = 64-wide k blocks per
+// warp whose loads (weights and activations) are all issued before the first MMA.
+template <int NT, int WARPS_K, int UNROLL>
 __global__ void __launch_bounds__(WARPS_K * 32)
 gemm_skinny_kernel(SkinnyArgs a) {
     __shared__ float partial[WARPS_K][NT][32][4];
+    pdl_trigger();  // the successor may be scheduled; it waits for this grid before it reads
+    bool waited = false;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const bool glu = a.inter > 0;
     // rows of the 16 x K weight tile: g and g + 8
     int row_lo, row_hi;
     if (glu) {
-        row_lo = blockIdx.x * 8 + g;          // gate row
+        row_lo = blockIdx.x * 8 + g;            // gate row
         row_hi = a.inter + blockIdx.x * 8 + g;  // its up row
     } else {
         row_lo = blockIdx.x * 16 + g;
@@ -70,18 +87,24 @@ gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
     for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
 
-    // warp w takes the 64-wide k blocks w, w + 4, ...; a lane owns 16 consecutive k of a block
+    // warp w takes the 64-wide k blocks w, w + WARPS_K, ...; a lane owns 16 consecutive k of a block
     for (int k0 = warp * 64; k0 < a.K; k0 += WARPS_K * 64 * UNROLL) {
-        uint4 wl[UNROLL][2], wh[UNROLL][2];
+        uint4 wl[UNROLL][2], wh[UNROLL][2], xv[UNROLL][NT][2];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = k0 + u * WARPS_K * 64 + t4 * 16;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const bool in = k + h * 8 < a.K;
-                wl[u][h] = load16(w_lo + k + h * 8, in && lo_ok);
-                wh[u][h] = load16(w_hi + k + h * 8, in && hi_ok);
+                wl[u][h] = load_weight16(w_lo + k + h * 8, in && lo_ok);
+                wh[u][h] = load_weight16(w_hi + k + h * 8, in && hi_ok);
             }
+        }
+        if (!waited) {
+            // The weights above depend on no predecessor and are already on their way; the
+            // activations below were written by one.
+            pdl_wait();
+            waited = true;
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -89,24 +112,31 @@ gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const int token = n * 8 + g;
-                const __nv_bfloat16* x_row = a.x + (size_t)token * a.K + k;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    xv[u][n][h] = load_activation16(a.x + (size_t)token * a.K + k + h * 8, token < a.T && k + h * 8 < a.K);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint4 xv = load16(x_row + h * 8, token < a.T && k + h * 8 < a.K);
-                    mma_bf16(acc[n], wl[u][h].x, wh[u][h].x, wl[u][h].y, wh[u][h].y, xv.x, xv.y);
-                    mma_bf16(acc[n], wl[u][h].z, wh[u][h].z, wl[u][h].w, wh[u][h].w, xv.z, xv.w);
+                    mma_bf16(acc[n], wl[u][h].x, wh[u][h].x, wl[u][h].y, wh[u][h].y, xv[u][n][h].x, xv[u][n][h].y);
+                    mma_bf16(acc[n], wl[u][h].z, wh[u][h].z, wl[u][h].w, wh[u][h].w, xv[u][n][h].z, xv[u][n][h].w);
                 }
             }
         }
     }
 
+    if (!waited) pdl_wait();  // a warp whose K range is empty still orders its writes after the predecessor
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) partial[warp][n][lane][e] = acc[n][e];
     __syncthreads();
-    // every thread finishes one (n, lane, e) element per pass: NT * 128 elements, 128 threads
-    for (int i = threadIdx.x; i < NT * 128; i += WARPS_K * 32) {
+    for (int i = threadIdx.x; i < NT * 128; i += WARPS_K * 32) {  // one (n, lane, e) element per thread and pass
         const int n = i / 128, l = (i / 4) % 32, e = i % 4;
         float sum = 0.0f;
 #pragma unroll
@@ -170,9 +200,19 @@ SHISO_API int shiso_gemm_skinny(const void* x, const void* w, const float* bias,
     a.inter = inter;
     a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     const unsigned blocks = inter > 0 ? ceil_div_u(inter, 8) : ceil_div_u(N, 16);
-    const dim3 block(WARPS_K * 32);
-    if (T <= 8) gemm_skinny_kernel<1, 4><<<blocks, block, 0, stream>>>(a);
-    else if (T <= 16) gemm_skinny_kernel<2, 4><<<blocks, block, 0, stream>>>(a);
-    else gemm_skinny_kernel<4, 2><<<blocks, block, 0, stream>>>(a);
+    // enough warps per CTA that one round of loads covers the CTA's whole K range
+    const bool deep = K > 3072;
+#define SHISO_LAUNCH(NT_, WK_, UN_) launch_kernel(gemm_skinny_kernel<NT_, WK_, UN_>, blocks, WK_ * 32, 0, stream, a)
+    if (T <= 8) {
+        if (deep) SHISO_LAUNCH(1, 16, 4);
+        else SHISO_LAUNCH(1, 8, 4);
+    } else if (T <= 16) {
+        if (deep) SHISO_LAUNCH(2, 16, 4);
+        else SHISO_LAUNCH(2, 8, 4);
+    } else {
+        if (deep) SHISO_LAUNCH(4, 16, 2);
+        else SHISO_LAUNCH(4, 8, 2);
+    }
+#undef SHISO_LAUNCH
     return launch_status();
 }

@@ -147,6 +147,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
     int* failed = (int*)(tmem_slot + 1);
 
+    pdl_trigger();  // the successor may be scheduled; it waits for this grid before it reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feature0 = blockIdx.x * BM;
     const int token0 = blockIdx.y * BN;
@@ -188,6 +189,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_expect_tx(&full[s], STAGE_BYTES);
             const int k = (kb_begin + i) * BK;
             tma_load_2d(a, &map_w, k, feature0, &full[s]);
+            if (i == 0) pdl_wait();  // weights depend on no predecessor; the activations do
             tma_load_2d(a + A_BYTES, &map_x, k, token0, &full[s]);
         }
     } else if (warp == 1 && lane == 0) {
@@ -217,6 +219,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncwarp();
 
     // ---- epilogue: every thread owns one feature (TMEM lane), columns are tokens
+    pdl_wait();  // nothing is written before the predecessor has finished
     bool ready = true;
     if (kb_count > 0) ready = mbar_wait(accum_bar, 0);
     if (!ready) *failed = 1;
@@ -374,13 +377,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStrea
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = SPLITS;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = shiso_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, p);
     return (int)e;
 }

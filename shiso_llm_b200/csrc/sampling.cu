@@ -55,6 +55,7 @@ __device__ Best block_best(Best mine, Best* scratch /* 32 */) {
 }
 
 __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    pdl_begin();
     __shared__ Best scratch[32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
     Best mine{-INFINITY, 0x7fffffff};
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
 __global__ void __launch_bounds__(256)
 argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ best_v, int* __restrict__ best_i, int vocab,
                     int chunk_len, int chunks) {
+    pdl_begin();
     __shared__ Best scratch[32];
     const int chunk = blockIdx.x, row_index = blockIdx.y;
     const float* row = logits + (size_t)row_index * vocab;
@@ -90,6 +92,7 @@ argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ best_v
 
 __global__ void argmax_final_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i,
                                     int* __restrict__ out, int chunks) {
+    pdl_begin();
     const int row_index = blockIdx.x;
     Best mine{-INFINITY, 0x7fffffff};
     for (int c = threadIdx.x; c < chunks; c += 32) {
@@ -185,6 +188,7 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p,
               const long long* __restrict__ keys, const int* __restrict__ positions, int* __restrict__ out, int vocab) {
+    pdl_begin();
     __shared__ Best scratch[32];
     __shared__ unsigned long long hist[256];
     __shared__ unsigned shared_u[2];
@@ -251,7 +255,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 SHISO_API int shiso_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0) return SHISO_ERR_SHAPE;
-    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab);
+    launch_kernel(argmax_kernel, rows, THREADS, 0, stream, logits, out, vocab);
     return launch_status();
 }
 
@@ -260,7 +264,7 @@ SHISO_API int shiso_sample(const float* logits, const float* temperature, const 
                            int vocab, cudaStream_t stream) {
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0) return SHISO_ERR_SHAPE;
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, temperature, top_k, top_p, min_p, keys, positions, out, vocab);
+    launch_kernel(sample_kernel, rows, THREADS, 0, stream, logits, temperature, top_k, top_p, min_p, keys, positions, out, vocab);
     return launch_status();
 }
 
@@ -272,7 +276,7 @@ SHISO_API int shiso_argmax_chunked(const float* logits, int* out, float* scratch
     const int chunk_len = (vocab + chunks - 1) / chunks;
     float* best_v = scratch;
     int* best_i = (int*)(scratch + (size_t)rows * chunks);
-    argmax_chunk_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, best_v, best_i, vocab, chunk_len, chunks);
-    argmax_final_kernel<<<rows, 32, 0, stream>>>(best_v, best_i, out, chunks);
+    launch_kernel(argmax_chunk_kernel, dim3(chunks, rows), 256, 0, stream, logits, best_v, best_i, vocab, chunk_len, chunks);
+    launch_kernel(argmax_final_kernel, rows, 32, 0, stream, best_v, best_i, out, chunks);
     return launch_status();
 }

@@ -35,6 +35,7 @@ __global__ void short_conv_out_kernel(const AT* __restrict__ proj, const float* 
                                       long long slot_stride, const int* __restrict__ seq_of_token,
                                       const int* __restrict__ q_start, const int* __restrict__ slots,
                                       AT* __restrict__ y, int hidden, int taps) {
+    pdl_begin();
     const int t = blockIdx.x;
     const int ch = blockIdx.y * blockDim.x + threadIdx.x;
     if (ch >= hidden) return;
@@ -59,6 +60,7 @@ template <typename AT>
 __global__ void short_conv_state_kernel(const AT* __restrict__ proj, float* __restrict__ state,
                                         long long slot_stride, const int* __restrict__ q_start,
                                         const int* __restrict__ slots, int hidden, int taps) {
+    pdl_begin();
     const int s = blockIdx.x;
     const int ch = blockIdx.y * blockDim.x + threadIdx.x;
     if (ch >= hidden) return;
@@ -88,6 +90,7 @@ __global__ void short_conv_serial_kernel(const AT* __restrict__ proj, const floa
                                          const float* __restrict__ bias, float* __restrict__ state,
                                          long long slot_stride, const int* __restrict__ q_start,
                                          const int* __restrict__ slots, AT* __restrict__ y, int hidden, int taps) {
+    pdl_begin();
     const int s = blockIdx.x;
     const int ch = blockIdx.y * blockDim.x + threadIdx.x;
     if (ch >= hidden) return;
@@ -137,10 +140,10 @@ SHISO_API int shiso_short_conv(const void* proj, int act_dtype, const float* w, 
     if (update_state && max_rows_per_seq > 0 && max_rows_per_seq <= 4) {
         dim3 grid(seqs, ceil_div_u(hidden, threads));
         if (act_dtype == SHISO_F32)
-            short_conv_serial_kernel<float><<<grid, threads, 0, stream>>>(
+            launch_kernel(short_conv_serial_kernel<float>, grid, threads, 0, stream, 
                 (const float*)proj, w, bias, state, slot_stride, q_start, slots, (float*)y, hidden, taps);
         else if (act_dtype == SHISO_BF16)
-            short_conv_serial_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+            launch_kernel(short_conv_serial_kernel<__nv_bfloat16>, grid, threads, 0, stream, 
                 (const __nv_bfloat16*)proj, w, bias, state, slot_stride, q_start, slots, (__nv_bfloat16*)y, hidden, taps);
         else
             return SHISO_ERR_DTYPE;
@@ -149,17 +152,17 @@ SHISO_API int shiso_short_conv(const void* proj, int act_dtype, const float* w, 
     dim3 grid_out(tokens, ceil_div_u(hidden, threads));
     dim3 grid_state(seqs, ceil_div_u(hidden, threads));
     if (act_dtype == SHISO_F32) {
-        short_conv_out_kernel<float><<<grid_out, threads, 0, stream>>>(
+        launch_kernel(short_conv_out_kernel<float>, grid_out, threads, 0, stream, 
             (const float*)proj, w, bias, state, slot_stride, seq_of_token, q_start, slots, (float*)y, hidden, taps);
         if (update_state)
-            short_conv_state_kernel<float><<<grid_state, threads, 0, stream>>>(
+            launch_kernel(short_conv_state_kernel<float>, grid_state, threads, 0, stream, 
                 (const float*)proj, state, slot_stride, q_start, slots, hidden, taps);
     } else if (act_dtype == SHISO_BF16) {
-        short_conv_out_kernel<__nv_bfloat16><<<grid_out, threads, 0, stream>>>(
+        launch_kernel(short_conv_out_kernel<__nv_bfloat16>, grid_out, threads, 0, stream, 
             (const __nv_bfloat16*)proj, w, bias, state, slot_stride, seq_of_token, q_start, slots,
             (__nv_bfloat16*)y, hidden, taps);
         if (update_state)
-            short_conv_state_kernel<__nv_bfloat16><<<grid_state, threads, 0, stream>>>(
+            launch_kernel(short_conv_state_kernel<__nv_bfloat16>, grid_state, threads, 0, stream, 
                 (const __nv_bfloat16*)proj, state, slot_stride, q_start, slots, hidden, taps);
     } else {
         return SHISO_ERR_DTYPE;
