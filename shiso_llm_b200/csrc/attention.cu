@@ -88,7 +88,7 @@ paged_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache,
                        const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, AT* __restrict__ out, int tokens, int heads,
                        int kv_heads, int head_dim, int page_size, float scale, int window) {
-    pdl_begin();
+    pdl_wait();
     __shared__ float q_s[WARPS][MAX_HEAD_DIM];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long index = (long long)blockIdx.x * WARPS + warp;
@@ -139,6 +139,7 @@ paged_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache,
             }
         }
     }
+    pdl_trigger();
     AT* o = out + ((size_t)t * heads + h) * head_dim;
     const float inv = run_sum > 0.0f ? 1.0f / run_sum : 0.0f;  // an empty span yields zeros
 #pragma unroll

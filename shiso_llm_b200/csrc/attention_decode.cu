@@ -3,16 +3,15 @@
 // A decode step reads every live request's keys and values once; at batch 64 that is half
 // of the step's bytes, so the kernel is organised around reading the cache once and wide:
 // one CTA per (key range, KV head, sequence) serves all query heads of the group from the
-// same keys and values (the reference reads them once per query head:
-// kernels/cuda/dense/dense_attn.cuh:44-180), and the key range of a sequence is cut into
+// same keys and values, as rows of one tensor-core tile (the reference reads them once per
+// query head with scalar code: kernels/cuda/dense/dense_attn.cuh:44-180), and the key range of a sequence is cut into
 // `splits` parts so that a few long sequences still fill 148 SMs.  Each part leaves an
 // unnormalised output with its running maximum and sum in scratch memory; a second kernel
 // merges the parts in index order.  The number of parts is fixed by the launch (capacity),
 // the cut points are computed on the device from the sequence's own length, so a captured
 // step serves any lengths.
 //
-// Scores: lane-per-key dot products against the float query in shared memory;
-// softmax statistics in float; P*V with one key per iteration, lanes across head columns.
+// Scores, softmax statistics and P*V are float; keys, values and the query are bfloat16.
 #include <stdio.h>
 
 #include "common.cuh"
@@ -34,184 +33,227 @@ struct DecodeArgs {
     float scale;
 };
 
-// D = head size (16, 32, 64, 128 or 256), GMAX = query heads per KV head, rounded up.
-//
-// Memory-level parallelism is what this kernel lives on, so both phases issue all their
-// loads before they use any.  Scores: lane-per-key, the key row read in 16-byte pieces, 8
-// of them in flight per lane.  P*V: the value rows of a 32-key group are read 16 bytes per
-// lane with D/8 lanes across a row, so 8 load instructions fetch the whole group; a lane
-// accumulates 8 columns of the rows it sees and the lanes that share columns are summed
-// once at the end.
-template <int D, int GMAX>
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int TILE_KEYS = 64;  // keys per shared-memory tile; each of the four warps takes 16 of them
+
+// D = head size (a multiple of 16 up to 128).  The query heads of one KV group (at most 16)
+// are the rows of a 16-row MMA tile, so one pass over the keys serves the whole group and the
+// arithmetic per key is a handful of tensor-core instructions instead of hundreds of FMAs -
+// what is left is moving the cache.  Keys and values of 64 positions are gathered through
+// the block table into shared memory with cp.async (16-byte pieces, whole rows, two stages);
+// warp w scores keys 16w .. 16w+15 of a tile (Q K^T, m16n8k16), keeps its own running
+// maximum, sum and output (P V), and the four warps are merged at the end.
+template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(DecodeArgs a) {
-    pdl_begin();
-    constexpr int LANES_PER_ROW = D / 8;                                   // 2 .. 32
-    constexpr int ROWS_PER_LOAD = 32 / LANES_PER_ROW;                      // 16 .. 1
-    constexpr int V_LOADS = 32 / ROWS_PER_LOAD;                            // loads per 32-key group
-    constexpr int K_CHUNK = D < 64 ? D : 64;                               // elements of a key row per batch of loads
+    pdl_wait();
+    constexpr int ROW_BYTES = D * 2 + 16;  // padded rows: ldmatrix without bank conflicts
+    constexpr int CHUNKS = D / 8;
+    constexpr int KSTEPS = D / 16;
+    constexpr int DTILES = D / 8;
 
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) uint8_t smem_bytes[];
+    uint8_t* q_s = smem_bytes;                           // [16][ROW_BYTES]
+    uint8_t* k_s = q_s + 16 * ROW_BYTES;                 // [2][TILE_KEYS][ROW_BYTES]
+    uint8_t* v_s = k_s + 2 * TILE_KEYS * ROW_BYTES;      // [2][TILE_KEYS][ROW_BYTES]
+    float* merge = reinterpret_cast<float*>(k_s);        // after the loop: [WARPS][16][D + 2]
+
     const int group = a.heads / a.kv_heads;
-    float* q_s = smem;                               // [GMAX][D]
-    float* p_s = q_s + GMAX * D;                     // [WARPS][GMAX][32]
-    int* row_s = (int*)(p_s + WARPS * GMAX * 32);    // [WARPS][32]
-    float* merge_ml = (float*)(row_s + WARPS * 32);  // [WARPS][GMAX][2]
-    float* merge_acc = merge_ml + WARPS * GMAX * 2;  // [WARPS][GMAX][D]
-
-    const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int split = blockIdx.x, g_head = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
     const int pos = a.positions[t];
     const int lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
     const int n_keys = pos + 1 - lo;
+    // A part is at least one tile; longer ranges are divided evenly in whole tiles.  Parts past
+    // the sequence's end have nothing to do.
     int chunk = (n_keys + a.splits - 1) / a.splits;
-    chunk = (chunk + 31) & ~31;
+    chunk = max(TILE_KEYS, (chunk + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS);
     const int begin = lo + split * chunk;
     const int end = min(begin + chunk, pos + 1);
     const int* table = a.block_table + (size_t)a.seq_of_token[t] * a.width;
+    const int tiles = end > begin ? (end - begin + TILE_KEYS - 1) / TILE_KEYS : 0;
 
-    for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
-        const int h = i / D, c = i % D;
-        q_s[h * D + c] = __bfloat162float(a.q[((size_t)t * a.heads + g * group + h) * D + c]);
+    // the group's queries as 16 rows (rows past the group are zero)
+    for (int c = tid; c < 16 * CHUNKS; c += WARPS * 32) {
+        const int r = c / CHUNKS, ch = c % CHUNKS;
+        const __nv_bfloat16* src = a.q + ((size_t)t * a.heads + g_head * group + min(r, group - 1)) * D + ch * 8;
+        cp_async16(q_s + r * ROW_BYTES + ch * 16, src, r < group);
     }
-    __syncthreads();
+    auto load_tile = [&](int tile, int stage) {
+        uint8_t* kd = k_s + stage * TILE_KEYS * ROW_BYTES;
+        uint8_t* vd = v_s + stage * TILE_KEYS * ROW_BYTES;
+        for (int c = tid; c < TILE_KEYS * CHUNKS; c += WARPS * 32) {
+            const int r = c / CHUNKS, ch = c % CHUNKS;
+            const int key = begin + tile * TILE_KEYS + r;
+            const bool valid = key < end;
+            size_t row = 0;
+            if (valid) row = (size_t)table[key / a.page_size] * a.page_size + key % a.page_size;
+            const size_t at = (row * a.kv_heads + g_head) * D + ch * 8;
+            cp_async16(kd + r * ROW_BYTES + ch * 16, a.k_cache + at, valid);
+            cp_async16(vd + r * ROW_BYTES + ch * 16, a.v_cache + at, valid);
+        }
+    };
+    if (tiles > 0) load_tile(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
-    const int my_col = (lane % LANES_PER_ROW) * 8;   // the 8 value columns this lane accumulates
-    const int my_sub = lane / LANES_PER_ROW;         // which row of each load this lane sees
-    float acc[GMAX][8];
-    float run_max[GMAX], run_sum[GMAX];
+    float o_acc[DTILES][4];
 #pragma unroll
-    for (int h = 0; h < GMAX; ++h) {
-        run_max[h] = -INFINITY;
-        run_sum[h] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) acc[h][c] = 0.0f;
-    }
+    for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    uint32_t q_frag[KSTEPS][4];
+    const float scale_log2 = a.scale * 1.4426950408889634f;
 
-    for (int p0 = begin + warp * 32; p0 < end; p0 += WARPS * 32) {
-        const int p = p0 + lane;
-        const bool valid = p < end;
-        float score[GMAX];
+    for (int tile = 0; tile < tiles; ++tile) {
+        const int stage = tile & 1;
+        if (tile + 1 < tiles) load_tile(tile + 1, stage ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        if (tile == 0) {
 #pragma unroll
-        for (int h = 0; h < GMAX; ++h) score[h] = 0.0f;
-        int row = 0;
-        if (valid) {
-            row = table[p / a.page_size] * a.page_size + p % a.page_size;
-            const __nv_bfloat16* k_row = a.k_cache + ((size_t)row * a.kv_heads + g) * D;
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int col = kk * 16 + (lane >> 4) * 8;
+                ldmatrix_x4(smem_addr(q_s + r * ROW_BYTES + col * 2), q_frag[kk][0], q_frag[kk][1], q_frag[kk][2], q_frag[kk][3]);
+            }
+        }
+        const uint8_t* kt = k_s + stage * TILE_KEYS * ROW_BYTES + warp * 16 * ROW_BYTES;  // this warp's 16 keys
+        const uint8_t* vt = v_s + stage * TILE_KEYS * ROW_BYTES + warp * 16 * ROW_BYTES;
+        const int key0 = begin + tile * TILE_KEYS + warp * 16;
+        if (key0 < end) {  // warp-uniform: this warp has keys in the tile
+            float s_acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += K_CHUNK) {
-                uint4 raw[K_CHUNK / 8];
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                const int r = (lane & 7) + (lane >> 4) * 8;
+                const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(smem_addr(kt + r * ROW_BYTES + col * 2), b0, b1, b2, b3);
+                mma_bf16(s_acc[0], q_frag[kk], b0, b1);
+                mma_bf16(s_acc[1], q_frag[kk], b2, b3);
+            }
+            float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < K_CHUNK / 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(k_row + c0 + i * 8);
+            for (int j = 0; j < 2; ++j) {
 #pragma unroll
-                for (int i = 0; i < K_CHUNK / 8; ++i) {
-                    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
-                    float kf[8];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __bfloat1622float2(pairs[e]);
-                        kf[2 * e] = f.x;
-                        kf[2 * e + 1] = f.y;
-                    }
-#pragma unroll
-                    for (int h = 0; h < GMAX; ++h) {
-                        if (h < group) {
-                            const float4 q0 = *reinterpret_cast<const float4*>(q_s + h * D + c0 + i * 8);
-                            const float4 q1 = *reinterpret_cast<const float4*>(q_s + h * D + c0 + i * 8 + 4);
-                            score[h] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] +
-                                        q1.x * kf[4] + q1.y * kf[5] + q1.z * kf[6] + q1.w * kf[7];
-                        }
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + t4 * 2 + (e & 1);
+                    const float v = key < end ? s_acc[j][e] * scale_log2 : -INFINITY;
+                    s_acc[j][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
                 }
             }
-        }
-        row_s[warp * 32 + lane] = row;
+            float correction[2], use_max[2];
 #pragma unroll
-        for (int h = 0; h < GMAX; ++h) {
-            if (h < group) {
-                const float s = valid ? score[h] * a.scale : -INFINITY;  // the scale meets the reduced dot
-                const float new_max = fmaxf(run_max[h], warp_max(s));
-                const float weight = valid ? expf(s - new_max) : 0.0f;
-                const float correction = expf(run_max[h] - new_max);
-                run_sum[h] = run_sum[h] * correction + warp_sum(weight);
-                run_max[h] = new_max;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) acc[h][c] *= correction;
-                p_s[(warp * GMAX + h) * 32 + lane] = weight;
+            for (int r = 0; r < 2; ++r) {
+                float m = tile_max[r];
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                const float new_max = fmaxf(row_max[r], m);  // finite: key0 < end
+                use_max[r] = new_max;
+                correction[r] = exp2f(row_max[r] - new_max);
+                row_max[r] = new_max;
             }
-        }
-        __syncwarp();
-        const int count = min(32, end - p0);
-        uint4 vraw[V_LOADS];
+            float tile_sum[2] = {0.0f, 0.0f};
+            uint32_t p_frag[4];
 #pragma unroll
-        for (int i = 0; i < V_LOADS; ++i) {
-            const int j = i * ROWS_PER_LOAD + my_sub;
-            vraw[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (j < count) {
-                const __nv_bfloat16* v_row = a.v_cache + ((size_t)row_s[warp * 32 + j] * a.kv_heads + g) * D;
-                vraw[i] = *reinterpret_cast<const uint4*>(v_row + my_col);
-            }
-        }
+            for (int j = 0; j < 2; ++j) {
+                float p[4];
 #pragma unroll
-        for (int i = 0; i < V_LOADS; ++i) {
-            const int j = i * ROWS_PER_LOAD + my_sub;  // weights of keys past `count` are zero
-            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&vraw[i]);
-            float vf[8];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(pairs[e]);
-                vf[2 * e] = f.x;
-                vf[2 * e + 1] = f.y;
-            }
-#pragma unroll
-            for (int h = 0; h < GMAX; ++h) {
-                if (h < group) {
-                    const float w = p_s[(warp * GMAX + h) * 32 + j];
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) acc[h][c] = fmaf(w, vf[c], acc[h][c]);
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = exp2f(s_acc[j][e] - use_max[e >> 1]);
+                    tile_sum[e >> 1] += p[e];
                 }
+                p_frag[j * 2 + 0] = pack_bf16(p[0], p[1]);
+                p_frag[j * 2 + 1] = pack_bf16(p[2], p[3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * correction[r] + tile_sum[r];
+#pragma unroll
+            for (int i = 0; i < DTILES; ++i) {
+                o_acc[i][0] *= correction[0];
+                o_acc[i][1] *= correction[0];
+                o_acc[i][2] *= correction[1];
+                o_acc[i][3] *= correction[1];
+            }
+#pragma unroll
+            for (int dn = 0; dn < DTILES; dn += 2) {
+                const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int col = (dn + (lane >> 4)) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(smem_addr(vt + r * ROW_BYTES + col * 2), b0, b1, b2, b3);
+                mma_bf16(o_acc[dn], p_frag, b0, b1);
+                mma_bf16(o_acc[dn + 1], p_frag, b2, b3);
             }
         }
-        __syncwarp();
+        __syncthreads();  // the stage is refilled by the next iteration's prefetch
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    pdl_trigger();
+    __syncthreads();
 
-    // lanes that hold the same columns (different rows) are summed, then the four warps merge
+    // ---- merge the four warps (warp order), in log2 units, and write the part's result
 #pragma unroll
-    for (int h = 0; h < GMAX; ++h) {
-        if (h < group) {
+    for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int row = g + r * 8;
+        float* dst = merge + ((size_t)warp * 16 + row) * (D + 2);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                float v = acc[h][c];
-#pragma unroll
-                for (int o = LANES_PER_ROW; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                acc[h][c] = v;
-            }
-            if (lane == 0) {
-                merge_ml[(warp * GMAX + h) * 2] = run_max[h];
-                merge_ml[(warp * GMAX + h) * 2 + 1] = run_sum[h];
-            }
-            if (lane < LANES_PER_ROW) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) merge_acc[(warp * GMAX + h) * D + my_col + c] = acc[h][c];
-            }
+        for (int i = 0; i < DTILES; ++i) {
+            dst[i * 8 + t4 * 2] = o_acc[i][r * 2];
+            dst[i * 8 + t4 * 2 + 1] = o_acc[i][r * 2 + 1];
+        }
+        if (t4 == 0) {
+            dst[D] = row_max[r];
+            dst[D + 1] = sum;
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
+    for (int i = tid; i < group * D; i += WARPS * 32) {
         const int h = i / D, col = i % D;
         float m = -INFINITY;
-        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge_ml[(w * GMAX + h) * 2]);
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge[((size_t)w * 16 + h) * (D + 2) + D]);
         float sum = 0.0f, out = 0.0f;
         for (int w = 0; w < WARPS; ++w) {
-            const float wm = merge_ml[(w * GMAX + h) * 2];
-            const float f = wm == -INFINITY ? 0.0f : expf(wm - m);
-            sum += f * merge_ml[(w * GMAX + h) * 2 + 1];
-            out += f * merge_acc[(w * GMAX + h) * D + col];
+            const float* src = merge + ((size_t)w * 16 + h) * (D + 2);
+            const float f = src[D] == -INFINITY ? 0.0f : exp2f(src[D] - m);
+            sum += f * src[D + 1];
+            out += f * src[col];
         }
-        float* dst = a.partial + (((size_t)t * a.heads + g * group + h) * a.splits + split) * (D + 2);
+        float* dst = a.partial + (((size_t)t * a.heads + g_head * group + h) * a.splits + split) * (D + 2);
         dst[col] = out;
         if (col == 0) {
-            dst[D] = m;
+            dst[D] = m;      // running maximum in log2 units
             dst[D + 1] = sum;
         }
     }
@@ -229,7 +271,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bflo
         float sum = 0.0f, acc = 0.0f;
         for (int s = 0; s < splits; ++s) {
             const float sm = base[s * (d + 2) + d];
-            const float f = sm == -INFINITY ? 0.0f : expf(sm - m);
+            const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);  // maxima are kept in log2 units
             sum += f * base[s * (d + 2) + d + 1];
             acc += f * base[s * (d + 2) + col];
         }
@@ -237,21 +279,23 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bflo
     }
 }
 
-template <int D, int GMAX>
+template <int D>
 int launch_split(const DecodeArgs& a, int tokens, cudaStream_t stream) {
-    const size_t smem = sizeof(float) * ((size_t)GMAX * D + WARPS * GMAX * 32 + WARPS * 32 + WARPS * GMAX * 2 +
-                                         (size_t)WARPS * GMAX * D);
-    auto kernel = decode_split_kernel<D, GMAX>;
-    if (smem > 48 * 1024) {
+    constexpr int ROW_BYTES = D * 2 + 16;
+    constexpr int TILE_BYTES = (16 + 4 * TILE_KEYS) * ROW_BYTES;
+    constexpr int MERGE_BYTES = 16 * ROW_BYTES + WARPS * 16 * (D + 2) * 4;
+    constexpr int SMEM = TILE_BYTES > MERGE_BYTES ? TILE_BYTES : MERGE_BYTES;
+    auto kernel = decode_split_kernel<D>;
+    if (SMEM > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
             if (e != cudaSuccess) return (int)e;
             configured = true;
         }
     }
     dim3 grid(a.splits, a.kv_heads, tokens);
-    launch_kernel(kernel, grid, WARPS * 32, smem, stream, a);
+    launch_kernel(kernel, grid, WARPS * 32, SMEM, stream, a);
     return launch_status();
 }
 
@@ -268,10 +312,9 @@ SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const v
                                      float scale, int window, int splits, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
-    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256)
-        return SHISO_ERR_UNSUPPORTED;  // other head sizes take the general kernel
+    if (head_dim % 16 || head_dim < 16 || head_dim > 128) return SHISO_ERR_UNSUPPORTED;  // these take the general kernel
     const int group = heads / kv_heads;
-    if (group > 8) return SHISO_ERR_UNSUPPORTED;
+    if (group > 16) return SHISO_ERR_UNSUPPORTED;
     DecodeArgs a;
     a.q = (const __nv_bfloat16*)q;
     a.k_cache = (const __nv_bfloat16*)k_cache;
@@ -288,13 +331,18 @@ SHISO_API int shiso_decode_attention(const void* q, const void* k_cache, const v
     a.splits = splits;
     a.window = window;
     a.scale = scale;
-    const int gmax = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
     int status = SHISO_ERR_UNSUPPORTED;
-#define SHISO_CASE(D_, G_) if (head_dim == D_ && gmax == G_) status = launch_split<D_, G_>(a, tokens, stream);
-#define SHISO_CASES(D_) SHISO_CASE(D_, 1) SHISO_CASE(D_, 2) SHISO_CASE(D_, 4) SHISO_CASE(D_, 8)
-    SHISO_CASES(16) SHISO_CASES(32) SHISO_CASES(64) SHISO_CASES(128) SHISO_CASES(256)
-#undef SHISO_CASES
-#undef SHISO_CASE
+    switch (head_dim) {
+        case 16: status = launch_split<16>(a, tokens, stream); break;
+        case 32: status = launch_split<32>(a, tokens, stream); break;
+        case 48: status = launch_split<48>(a, tokens, stream); break;
+        case 64: status = launch_split<64>(a, tokens, stream); break;
+        case 80: status = launch_split<80>(a, tokens, stream); break;
+        case 96: status = launch_split<96>(a, tokens, stream); break;
+        case 112: status = launch_split<112>(a, tokens, stream); break;
+        case 128: status = launch_split<128>(a, tokens, stream); break;
+        default: break;
+    }
     if (status != 0) return status;
     dim3 grid(heads, tokens);
     launch_kernel(decode_merge_kernel, grid, head_dim >= 128 ? 128 : 64, 0, stream, scratch, (__nv_bfloat16*)out, heads, head_dim, splits);

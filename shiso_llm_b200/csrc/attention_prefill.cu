@@ -71,7 +71,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 flash_prefill_kernel(PrefillArgs a) {
-    pdl_begin();
+    pdl_wait();
     constexpr int ROW_BYTES = D * 2 + 16;  // 16 bytes of padding: ldmatrix rows fall on distinct banks
     constexpr int CHUNKS = D / 8;          // 16-byte pieces per row
     constexpr int KSTEPS = D / 16;
@@ -244,6 +244,7 @@ flash_prefill_kernel(PrefillArgs a) {
         __syncthreads();  // the stage is refilled by the next iteration's prefetch
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    pdl_trigger();
 
     // ---- normalise and store
 #pragma unroll

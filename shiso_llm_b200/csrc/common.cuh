@@ -64,12 +64,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 // ---- programmatic dependent launch ---------------------------------------------------------
 // Every kernel is launched so that it may start while its predecessor in the stream is still
-// finishing: it announces at once that its own successor may be scheduled
-// (griddepcontrol.launch_dependents) and waits for the predecessor to complete and flush
-// (griddepcontrol.wait) before it touches anything a predecessor may have written.  Work that
-// depends on no predecessor - address arithmetic, loads of weights - goes before the wait.
-// The wait is a no-op for a kernel launched without the attribute.  SHISO_PDL=0 turns the
-// attribute off.
+// finishing.  It waits for the predecessor to complete and flush (griddepcontrol.wait) before
+// it touches anything a predecessor may have written; work that depends on no predecessor -
+// address arithmetic, loads of weights - goes before the wait.  It says when its own successor
+// may be scheduled (griddepcontrol.launch_dependents): small row kernels say so at once
+// (pdl_begin), kernels that fill the SMs only after their main loop (pdl_trigger), because a
+// successor that is resident early only spins in its wait and takes registers and shared
+// memory from the CTAs that still have work to do.  The wait is a no-op for a kernel launched
+// without the attribute.  SHISO_PDL=0 turns the attribute off.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_begin() {

@@ -91,12 +91,82 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const AT* __restric
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<AT>(row_cache[i] * inv * w[i]);
 }
 
+// Four elements per thread and pass (hidden a multiple of 4): 16-byte accesses of the float
+// residual, 8-byte accesses of bfloat16 rows.  Same arithmetic and the same order of the
+// per-thread sums as the scalar kernel's would be for this thread-to-element map.
+template <typename AT> struct Pack4;
+template <> struct Pack4<float> {
+    using type = float4;
+    __device__ static float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    __device__ static void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    using type = uint2;
+    __device__ static float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    __device__ static void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename AT>
+__global__ void rmsnorm_vec_kernel(float* residual, const AT* delta, const int* rows, const float* w, AT* out,
+                                   int hidden, float eps) {
+    pdl_begin();
+    __shared__ float scratch[33];
+    extern __shared__ float4 row_cache4[];
+    const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = residual + (size_t)src_row * hidden;
+    const AT* d = delta ? delta + (size_t)src_row * hidden : nullptr;
+    AT* o = out + (size_t)blockIdx.x * hidden;
+    const int quads = hidden / 4;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        float4 v = *reinterpret_cast<const float4*>(r + 4 * i);
+        if (d) {
+            const float4 dv = Pack4<AT>::load(d + 4 * i);
+            v.x += dv.x;
+            v.y += dv.y;
+            v.z += dv.z;
+            v.w += dv.w;
+            if (!rows) *reinterpret_cast<float4*>(r + 4 * i) = v;
+        }
+        row_cache4[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const float4 v = row_cache4[i];
+        const float4 wv = *reinterpret_cast<const float4*>(w + 4 * i);
+        Pack4<AT>::store(o + 4 * i, make_float4(v.x * inv * wv.x, v.y * inv * wv.y, v.z * inv * wv.z, v.w * inv * wv.w));
+    }
+}
+
 SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows, const float* w, void* out,
                             int act_dtype, int out_rows, int hidden, float eps, cudaStream_t stream) {
     if (out_rows <= 0) return SHISO_OK;
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return SHISO_ERR_SHAPE;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (hidden % 4 == 0 && aligned && smem <= 48 * 1024) {
+        const int vec_threads = hidden >= 2048 ? 256 : 128;
+        if (act_dtype == SHISO_F32)
+            launch_kernel(rmsnorm_vec_kernel<float>, out_rows, vec_threads, smem, stream, residual, (const float*)delta, rows, w, (float*)out, hidden, eps);
+        else if (act_dtype == SHISO_BF16)
+            launch_kernel(rmsnorm_vec_kernel<__nv_bfloat16>, out_rows, vec_threads, smem, stream, residual, (const __nv_bfloat16*)delta, rows, w, (__nv_bfloat16*)out, hidden, eps);
+        else
+            return SHISO_ERR_DTYPE;
+        return launch_status();
+    }
     if (act_dtype == SHISO_F32) {
         auto k = rmsnorm_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -127,10 +197,38 @@ __global__ void swiglu_kernel(const AT* __restrict__ gate_up, AT* __restrict__ o
     out[i] = from_f32<AT>(silu * u);
 }
 
+// Eight bfloat16 values per thread (inter a multiple of 8).
+__global__ void swiglu_vec_kernel(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int inter, long long total8) {
+    pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const int per_row = inter / 8;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    const __nv_bfloat16* row = gate_up + (size_t)t * 2 * inter;
+    const uint4 graw = *reinterpret_cast<const uint4*>(row + c);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(row + inter + c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 oraw;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+        op[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * inter + c) = oraw;
+}
+
 SHISO_API int shiso_swiglu(const void* gate_up, void* out, int act_dtype, int tokens, int inter, cudaStream_t stream) {
     const long long total = (long long)tokens * inter;
     if (total <= 0) return SHISO_OK;
     const unsigned blocks = ceil_div_u(total, 256);
+    if (act_dtype == SHISO_BF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        launch_kernel(swiglu_vec_kernel, ceil_div_u(total / 8, 256), 256, 0, stream, (const __nv_bfloat16*)gate_up,
+                      (__nv_bfloat16*)out, inter, total / 8);
+        return launch_status();
+    }
     if (act_dtype == SHISO_F32)
         launch_kernel(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total);
     else if (act_dtype == SHISO_BF16)

@@ -17,7 +17,7 @@ template <typename WT, typename XT, typename OT>
 __global__ void __launch_bounds__(256)
 gemm_simple_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ bias,
                    OT* __restrict__ y, int T, int N, int K) {
-    pdl_begin();
+    pdl_wait();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -57,6 +57,7 @@ gemm_simple_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const flo
         }
         __syncthreads();
     }
+    pdl_trigger();
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int gr = row0 + ty * TM + i;

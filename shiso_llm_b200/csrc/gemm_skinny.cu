@@ -63,7 +63,6 @@ template <int NT, int WARPS_K, int UNROLL>
 __global__ void __launch_bounds__(WARPS_K * 32)
 gemm_skinny_kernel(SkinnyArgs a) {
     __shared__ float partial[WARPS_K][NT][32][4];
-    pdl_trigger();  // the successor may be scheduled; it waits for this grid before it reads
     bool waited = false;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
@@ -130,6 +129,7 @@ gemm_skinny_kernel(SkinnyArgs a) {
         }
     }
 
+    pdl_trigger();            // the weights are read: the successor may start fetching its own
     if (!waited) pdl_wait();  // a warp whose K range is empty still orders its writes after the predecessor
 #pragma unroll
     for (int n = 0; n < NT; ++n)

@@ -124,6 +124,7 @@ struct GemmParams {
     int T, N, K;
     int k_blocks_per_split;  // BK-blocks each CTA of a cluster handles
     int out_f32;             // 1: float output, 0: bfloat16
+    int inter;               // GLU kernels: rows of the gate (and of the up) matrix, and of the output
 };
 
 template <typename OT>
@@ -131,13 +132,20 @@ __device__ __forceinline__ void store_out(OT* y, size_t at, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* y, size_t at, float v) { y[at] = v; }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* y, size_t at, float v) { y[at] = __float2bfloat16_rn(v); }
 
-template <int BN, int STAGES, int SPLITS>
+// GLU: the weight is a [2 * inter, K] gate-over-up pair.  A CTA then loads the gate rows and
+// the matching up rows of its 128 features, keeps two accumulators in TMEM (columns 0..BN-1
+// and BN..2BN-1), and its epilogue writes silu(gate) * up - the token tile is read once for
+// 256 weight rows and the [T, 2 * inter] intermediate never exists.
+template <int BN, int STAGES, int SPLITS, bool GLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    static_assert(!GLU || SPLITS == 1, "the fused activation needs the whole sum in one CTA");
     constexpr int A_BYTES = BM * BK * 2;
+    constexpr int A_TILES = GLU ? 2 : 1;
     constexpr int B_BYTES = BN * BK * 2;
-    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two >= 32
+    constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+    constexpr int ACC_COLS = A_TILES * BN;
+    constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;  // a power of two >= 32
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -147,7 +155,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
     int* failed = (int*)(tmem_slot + 1);
 
-    pdl_trigger();  // the successor may be scheduled; it waits for this grid before it reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feature0 = blockIdx.x * BM;
     const int token0 = blockIdx.y * BN;
@@ -189,8 +196,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_expect_tx(&full[s], STAGE_BYTES);
             const int k = (kb_begin + i) * BK;
             tma_load_2d(a, &map_w, k, feature0, &full[s]);
+            if (GLU) tma_load_2d(a + A_BYTES, &map_w, k, p.inter + feature0, &full[s]);
             if (i == 0) pdl_wait();  // weights depend on no predecessor; the activations do
-            tma_load_2d(a + A_BYTES, &map_x, k, token0, &full[s]);
+            tma_load_2d(a + A_TILES * A_BYTES, &map_x, k, token0, &full[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
@@ -205,12 +213,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-            const uint32_t b_addr = a_addr + A_BYTES;
+            const uint32_t b_addr = a_addr + A_TILES * A_BYTES;
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
                 const uint64_t a_desc = umma_desc(a_addr + k * UMMA_K * 2);
                 const uint64_t b_desc = umma_desc(b_addr + k * UMMA_K * 2);
                 umma_bf16(tmem_base, a_desc, b_desc, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                if (GLU) {
+                    const uint64_t up_desc = umma_desc(a_addr + A_BYTES + k * UMMA_K * 2);
+                    umma_bf16(tmem_base + BN, up_desc, b_desc, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
             }
             umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
         }
@@ -223,6 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     bool ready = true;
     if (kb_count > 0) ready = mbar_wait(accum_bar, 0);
     if (!ready) *failed = 1;
+    pdl_trigger();  // the main loop is over: the successor may be scheduled while the epilogue runs
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool bad = *failed != 0;
@@ -231,7 +244,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int feature = feature0 + warp * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
-    if constexpr (SPLITS == 1) {
+    if constexpr (GLU) {
+        if (!bad) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 8) {
+                float gate[8], up[8];  // the loads are warp-wide; rows past `inter` are dropped at the store
+                tmem_ld8(lane_addr + c, gate);
+                tmem_ld8(lane_addr + BN + c, up);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int token = token0 + c + j;
+                    if (token < p.T && feature < p.inter) {
+                        const float v = gate[j] / (1.0f + expf(-gate[j])) * up[j];
+                        const size_t at = (size_t)token * p.inter + feature;
+                        if (p.out_f32) store_out<float>((float*)p.y, at, v);
+                        else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v);
+                    }
+                }
+            }
+        }
+    } else if constexpr (SPLITS == 1) {
         if (!bad) {
             const float b = (p.bias && feature < p.N) ? p.bias[feature] : 0.0f;
 #pragma unroll 1
@@ -359,13 +391,13 @@ bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* 
     return true;
 }
 
-template <int BN, int STAGES, int SPLITS>
+template <int BN, int STAGES, int SPLITS, bool GLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
-    constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    constexpr int STAGE_BYTES = (GLU ? 2 : 1) * BM * BK * 2 + BN * BK * 2;
     constexpr int PARTIAL_BYTES = SPLITS > 1 ? BN * BM * 4 : 0;
     constexpr int TILE_BYTES = STAGES * STAGE_BYTES > PARTIAL_BYTES ? STAGES * STAGE_BYTES : PARTIAL_BYTES;
     constexpr int SMEM = TILE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SPLITS>;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SPLITS, GLU>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -373,7 +405,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStrea
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div_u(p.N, BM), ceil_div_u(p.T, BN), SPLITS);
+    cfg.gridDim = dim3(ceil_div_u(GLU ? p.inter : p.N, BM), ceil_div_u(p.T, BN), SPLITS);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = stream;
@@ -432,6 +464,7 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     p.N = N;
     p.K = K;
     p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    p.inter = 0;
     const int total_kb = (K + BK - 1) / BK;
     p.k_blocks_per_split = total_kb;
 
@@ -459,4 +492,31 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     if (bn == 32) { SHISO_PICK(32) }
     SHISO_PICK(64)
 #undef SHISO_PICK
+}
+
+// silu(x gate^T) * (x up^T) for w = [gate; up] of shape [2 * inter, K]; y [T, inter].
+SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, int y_dtype, int T, int inter, int K,
+                                        cudaStream_t stream) {
+    if (T <= 0 || inter <= 0) return SHISO_OK;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p;
+    p.y = y;
+    p.bias = nullptr;
+    p.status = status_word();
+    p.T = T;
+    p.N = 2 * inter;
+    p.K = K;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    p.inter = inter;
+    p.k_blocks_per_split = (K + BK - 1) / BK;
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    if (!tensor_map(w, 2 * inter, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
+    switch (bn) {
+        case 16: return launch<16, 5, 1, true>(mw, mx, p, stream);
+        case 32: return launch<32, 5, 1, true>(mw, mx, p, stream);
+        case 64: return launch<64, 4, 1, true>(mw, mx, p, stream);
+        case 128: return launch<128, 4, 1, true>(mw, mx, p, stream);
+        default: return launch<256, 3, 1, true>(mw, mx, p, stream);
+    }
 }

@@ -54,6 +54,63 @@ __global__ void short_conv_out_kernel(const AT* __restrict__ proj, const float* 
     y[(size_t)t * hidden + ch] = from_f32<AT>(c * acc);
 }
 
+// bfloat16 rows, eight channels per thread (hidden a multiple of 8): 16-byte loads of b, c and x.
+// Per channel the arithmetic and its order are those of the kernel above.
+__global__ void short_conv_out_vec_kernel(const __nv_bfloat16* proj, const float* w, const float* bias,
+                                          const float* state, long long slot_stride, const int* seq_of_token,
+                                          const int* q_start, const int* slots, __nv_bfloat16* y, int hidden, int taps) {
+    pdl_begin();
+    const int t = blockIdx.x;
+    const int ch = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (ch >= hidden) return;
+    const int s = seq_of_token[t];
+    const int first = q_start[s];
+    const float* state_row = state + (size_t)slots[s] * slot_stride;
+    const int rel_now = t - first;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int rel = rel_now - (taps - 1) + j;
+        float u[8];
+        if (rel >= 0) {
+            const __nv_bfloat16* row = proj + (size_t)(first + rel) * 3 * hidden;
+            const uint4 braw = *reinterpret_cast<const uint4*>(row + ch);
+            const uint4 xraw = *reinterpret_cast<const uint4*>(row + 2 * hidden + ch);
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&braw);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xraw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 b = __bfloat1622float2(bp[e]), x = __bfloat1622float2(xp[e]);
+                u[2 * e] = b.x * x.x;
+                u[2 * e + 1] = b.y * x.y;
+            }
+        } else {
+            const float* sr = state_row + (size_t)(taps - 1 + rel) * hidden + ch;
+            const float4 lo = *reinterpret_cast<const float4*>(sr), hi = *reinterpret_cast<const float4*>(sr + 4);
+            u[0] = lo.x; u[1] = lo.y; u[2] = lo.z; u[3] = lo.w;
+            u[4] = hi.x; u[5] = hi.y; u[6] = hi.z; u[7] = hi.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(size_t)(ch + e) * taps + j], u[e], acc[e]);
+    }
+    const uint4 craw = *reinterpret_cast<const uint4*>(proj + (size_t)t * 3 * hidden + hidden + ch);
+    const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&craw);
+    uint4 oraw;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 c = __bfloat1622float2(cp[e]);
+        float a0 = acc[2 * e], a1 = acc[2 * e + 1];
+        if (bias) {
+            a0 += bias[ch + 2 * e];
+            a1 += bias[ch + 2 * e + 1];
+        }
+        op[e] = __floats2bfloat162_rn(c.x * a0, c.y * a1);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)t * hidden + ch) = oraw;
+}
+
 // New state = the last taps-1 values of (old state ++ this step's u).  One thread owns a
 // (sequence, channel) pair and reads everything it needs before it writes.
 template <typename AT>
@@ -158,6 +215,13 @@ SHISO_API int shiso_short_conv(const void* proj, int act_dtype, const float* w, 
             launch_kernel(short_conv_state_kernel<float>, grid_state, threads, 0, stream, 
                 (const float*)proj, state, slot_stride, q_start, slots, hidden, taps);
     } else if (act_dtype == SHISO_BF16) {
+        const bool vec = hidden % 8 == 0 && slot_stride % 4 == 0 &&
+                         (((uintptr_t)proj | (uintptr_t)y | (uintptr_t)state) & 15) == 0;
+        if (vec) {
+            launch_kernel(short_conv_out_vec_kernel, dim3(tokens, ceil_div_u(hidden / 8, threads)), threads, 0, stream,
+                          (const __nv_bfloat16*)proj, w, bias, (const float*)state, slot_stride, seq_of_token, q_start,
+                          slots, (__nv_bfloat16*)y, hidden, taps);
+        } else
         launch_kernel(short_conv_out_kernel<__nv_bfloat16>, grid_out, threads, 0, stream, 
             (const __nv_bfloat16*)proj, w, bias, state, slot_stride, seq_of_token, q_start, slots,
             (__nv_bfloat16*)y, hidden, taps);

@@ -184,8 +184,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
 
 def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """``silu(x @ gate^T) * (x @ up^T)`` for ``gate_up = [gate; up]`` of shape ``[2I, K]``.
-    For a handful of bfloat16 rows the activation is fused into the product's epilogue;
-    otherwise the product is followed by the activation kernel."""
+    In bfloat16 the activation is applied in the product's epilogue (the skinny kernel for a
+    handful of rows, the tensor-memory kernel with two accumulators otherwise); other types
+    run the product and then the activation kernel."""
     _check(x, "x", None, 2)
     _check(gate_up, "gate_up", None, 2)
     tokens, k = x.shape
@@ -201,6 +202,17 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
             _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2, _stream()
         )
         _done(status, "linear_swiglu (skinny)")
+        return out
+    lib = library()
+    if (
+        x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16
+        and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(gate_up))
+    ):
+        out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
+        status = lib.shiso_gemm_tcgen05_swiglu(
+            _ptr(x), _ptr(gate_up), _ptr(out), _code(out), tokens, two_inter // 2, k, _stream()
+        )
+        _done(status, "linear_swiglu (tcgen05)")
         return out
     return swiglu(linear(x, gate_up, out_dtype))
 
@@ -289,9 +301,17 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
     return q
 
 
-MAX_DECODE_GROUP = 8  # query heads per KV head the decode kernel serves from one read
-DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)  # other head sizes take the general kernel
+MAX_DECODE_GROUP = 16  # query heads per KV head the decode kernel serves from one read (rows of one MMA tile)
+DECODE_HEAD_DIMS = tuple(range(16, 129, 16))  # larger head sizes take the general kernel
 PREFILL_MAX_HEAD_DIM = 128  # the tiled prompt kernel keeps a row's output in registers
+
+
+def decode_splits(tokens: int, kv_heads: int, capacity: int) -> int:
+    """Into how many parts the decode kernel cuts a sequence's keys: enough CTAs (tokens x KV
+    heads x parts) to fill the SMs a few times over, no part shorter than 128 keys of the
+    table's capacity.  It depends on the launch shape only, never on current lengths, so a
+    captured step stays valid."""
+    return max(1, min(16, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
 
 
 def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step,
@@ -317,8 +337,7 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
         q.dtype == torch.bfloat16 and getattr(step, "all_decode", False)
         and heads // kv_heads <= MAX_DECODE_GROUP and head_dim in DECODE_HEAD_DIMS
     ):
-        capacity = block_table.shape[1] * page_size
-        splits = max(1, min(32, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 64)))
+        splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size)
         scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
         status = lib.shiso_decode_attention(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),

@@ -293,7 +293,7 @@ def test_sample_kernel_follows_the_host_rule():
     assert same >= 4 * 6 - 1
 
 
-@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (32, 8, 64, 16), (6, 6, 48, 8), (8, 1, 128, 16), (2, 1, 256, 4), (5, 5, 80, 16)])
+@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (32, 8, 64, 16), (6, 6, 48, 8), (8, 1, 128, 16), (2, 1, 256, 4), (5, 5, 80, 16), (32, 2, 64, 16), (36, 2, 32, 8)])
 def test_decode_attention_split_keys(case):
     """Steps of single tokens in bfloat16 take the split-key kernel: sequences of very
     different lengths in one launch (one key, a page's edge, thousands of keys), windows."""
@@ -418,3 +418,17 @@ def test_short_conv_few_rows_per_sequence_takes_the_serial_kernel(dtype):
     close(one, want, dtype, "serial short conv", rel32=4e-6)
     assert torch.equal(one, two) and torch.equal(s_one, s_two)
     assert torch.allclose(s_one.cpu(), s_ref, rtol=0, atol=1e-7)
+
+
+@pytest.mark.parametrize("shape", [(40, 600, 264), (130, 256, 512), (300, 1000, 96), (513, 2 * 5632, 2048)])
+def test_tensor_core_product_with_fused_swiglu(shape):
+    """More than a handful of bfloat16 rows: gate and up accumulate side by side in tensor
+    memory and the epilogue applies the activation (token tiles of 64, 128 and 256; feature
+    counts that do not fill the last tile)."""
+    T, N, K = shape
+    x, w = rnd((T, K), torch.bfloat16, 110), rnd((N, K), torch.bfloat16, 111, 0.05)
+    got = ops().linear_swiglu(x.cuda(), w.cuda(), torch.bfloat16)
+    ops().check_kernel_status()
+    close(got, ref.linear_swiglu(x, w, torch.bfloat16), torch.bfloat16, f"fused swiglu {shape}")
+    unfused = ops().swiglu(ops().linear(x.cuda(), w.cuda(), torch.bfloat16))
+    close(got, unfused, torch.bfloat16, "fused against product + activation kernel", scale=ref.linear_swiglu(x, w, torch.float32).abs().max().item() * 2)
