@@ -24,98 +24,16 @@
 // plane and a vendor SGEMM in 256-token bands (crates/shiso-engine/src/projection.rs:949-1070,
 // 1297-1304) and its decode products through matvec kernels (projection.rs:972-1069).
 #include <cooperative_groups.h>
-#include <cuda.h>
 
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int BM = 128;       // output features per CTA (MMA M)
-constexpr int BK = 64;        // k per stage: 64 bf16 = 128 bytes = one swizzle row
-constexpr int UMMA_K = 16;    // k per tcgen05.mma of 16-bit operands
+using namespace tc;
+
 constexpr int THREADS = 128;
-constexpr unsigned long long WAIT_LIMIT_CYCLES = 2000000000ull;  // about a second
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Waits for the phase with the given parity; false when the clock limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    const unsigned long long start = clock64();
-    while (true) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major bf16 tile stored as rows of 128 bytes with
-// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading
-// byte offset is unused for swizzled K-major layouts, version 1, layout type 2 (128B swizzle).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;                 // leading byte offset (ignored)
-    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-    d |= (uint64_t)1 << 46;                 // descriptor version
-    d |= (uint64_t)2 << 61;                 // 128-byte swizzle
-    return d;
-}
-
-// kind::f16 instruction descriptor: D float, A and B bfloat16, both K-major, M x N.
-__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 struct GemmParams {
     void* y;
@@ -335,62 +253,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // ---------------------------------------------------------------------------- host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)sym;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr;
-    int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 10007u) ^ (size_t)k.box_rows;
-    }
-};
-
-// A [rows, cols] bf16 row-major matrix seen as tiles of box_rows x 64 with the 128B swizzle.
-bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex lock;
-    MapKey key{ptr, rows, cols, box_rows};
-    std::lock_guard<std::mutex> guard(lock);
-    auto it = cache.find(key);
-    if (it != cache.end()) {
-        *out = it->second;
-        return true;
-    }
-    EncodeTiledFn encode = encode_fn();
-    if (!encode) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMap map;
-    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return false;
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, map);
-    *out = map;
-    return true;
-}
-
 template <int BN, int STAGES, int SPLITS, bool GLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
     constexpr int STAGE_BYTES = (GLU ? 2 : 1) * BM * BK * 2 + BN * BK * 2;
@@ -422,7 +284,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStrea
     return (int)e;
 }
 
-int* status_word() {
+}  // namespace
+
+int* shiso_tc_status_word() {
     static int* word = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
@@ -431,8 +295,6 @@ int* status_word() {
     });
     return word;
 }
-
-}  // namespace
 
 // Whether the tensor-core kernel takes this problem (bfloat16 operands, rows 16-byte aligned).
 SHISO_API int shiso_gemm_tcgen05_supported(int K, const void* x, const void* w) {
@@ -443,7 +305,7 @@ SHISO_API int shiso_gemm_tcgen05_supported(int K, const void* x, const void* w) 
 
 // Reads and clears the status word: non-zero when a bounded wait inside a kernel ran out.
 SHISO_API int shiso_gemm_tcgen05_status() {
-    int* word = status_word();
+    int* word = shiso_tc_status_word();
     if (!word) return -1;
     int host = 0;
     if (cudaMemcpy(&host, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
@@ -459,7 +321,7 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     GemmParams p;
     p.y = y;
     p.bias = bias;
-    p.status = status_word();
+    p.status = shiso_tc_status_word();
     p.T = T;
     p.N = N;
     p.K = K;
@@ -502,7 +364,7 @@ SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, i
     GemmParams p;
     p.y = y;
     p.bias = nullptr;
-    p.status = status_word();
+    p.status = shiso_tc_status_word();
     p.T = T;
     p.N = 2 * inter;
     p.K = K;

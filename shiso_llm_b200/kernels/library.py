@@ -26,6 +26,7 @@ _SIGNATURES = {
     "shiso_gemm_simple": [P, I, P, I, P, P, I, I, I, I, P],
     "shiso_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_swiglu": [P, P, P, I, I, I, I, P],
+    "shiso_gemm_tcgen05_prompt": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
     "shiso_gemm_tcgen05_status": [],
     "shiso_gemm_skinny": [P, P, P, P, I, I, I, I, I, P],

@@ -139,6 +139,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 _SM_COUNT = None
 SKINNY_MAX_TOKENS = 16  # up to here a product is weight streaming and takes the skinny kernel
+PROMPT_MIN_TOKENS = 128  # from here the persistent tensor-memory kernel (tokens as the MMA's M operand)
 
 
 def _sm_count() -> int:
@@ -168,6 +169,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     if both_bf16 and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0:
         status = lib.shiso_gemm_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _stream())
         _done(status, "linear (skinny)")
+        return out
+    if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
+        status = lib.shiso_gemm_tcgen05_prompt(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
+        )
+        _done(status, "linear (tcgen05, persistent)")
         return out
     if both_bf16 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05(
@@ -209,6 +216,13 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(gate_up))
     ):
         out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
+        if tokens >= PROMPT_MIN_TOKENS and (two_inter // 2) % 8 == 0:
+            status = lib.shiso_gemm_tcgen05_prompt(
+                _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter // 2, k, two_inter // 2,
+                _sm_count(), _stream(),
+            )
+            _done(status, "linear_swiglu (tcgen05, persistent)")
+            return out
         status = lib.shiso_gemm_tcgen05_swiglu(
             _ptr(x), _ptr(gate_up), _ptr(out), _code(out), tokens, two_inter // 2, k, _stream()
         )
