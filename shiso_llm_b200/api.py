@@ -96,7 +96,7 @@ class LLM:
         if plan.entries:
             entries, params, positions = [], [], []
             for e in plan.entries:
-                tokens = e.request.tokens[e.start : e.start + e.count]
+                tokens = e.request.token_slice(e.start, e.count)
                 entries.append(StepEntry(e.request.id, tokens, [e.count - 1] if e.samples else []))
                 if e.samples:
                     params.append(e.request.params)

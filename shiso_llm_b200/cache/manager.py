@@ -229,7 +229,7 @@ class CacheManager:
         the window stop first)."""
         out.fill(HOLE)
         for i, request in enumerate(requests):
-            pages = self._held[request].tables[group].pages
+            pages = self._held[request].tables[group].as_array()
             if len(pages) > out.shape[1]:
                 raise RuntimeError(f"request {request!r} holds {len(pages)} blocks, the table has {out.shape[1]} columns")
             out[i, : len(pages)] = pages

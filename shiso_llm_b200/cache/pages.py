@@ -13,6 +13,8 @@ from __future__ import annotations
 
 from collections import deque
 
+import numpy as np
+
 
 class OutOfPages(RuntimeError):
     """A claim needs more pages than the pool has free.  Nothing was taken."""
@@ -87,6 +89,7 @@ class BlockTable:
         self.window = window
         self.pages: list[int] = []
         self.first_live = 0  # entries below this index are holes
+        self._array = np.empty(16, dtype=np.int32)  # the same entries, ready to be copied into a step's table
 
     def pages_for(self, length: int) -> int:
         return -(-length // self.page_size)
@@ -97,7 +100,13 @@ class BlockTable:
     def grow(self, pool: PagePool, length: int) -> None:
         need = self.missing_for(length)
         if need:
+            have = len(self.pages)
             self.pages.extend(pool.take(need))
+            if len(self.pages) > len(self._array):
+                bigger = np.empty(max(2 * len(self._array), len(self.pages)), dtype=np.int32)
+                bigger[:have] = self._array[:have]
+                self._array = bigger
+            self._array[have : len(self.pages)] = self.pages[have:]
 
     def release_passed(self, pool: PagePool, length: int) -> int:
         """Gives back pages that no later position can read: with a window ``w`` the
@@ -110,6 +119,7 @@ class BlockTable:
         while self.first_live < min(keep_from, len(self.pages)):
             pool.give_back(self.pages[self.first_live])
             self.pages[self.first_live] = HOLE
+            self._array[self.first_live] = HOLE
             self.first_live += 1
             released += 1
         return released
@@ -119,6 +129,10 @@ class BlockTable:
             pool.give_back(p)
         self.pages = []
         self.first_live = 0
+
+    def as_array(self) -> np.ndarray:
+        """The entries as int32 (a view; valid until the table grows)."""
+        return self._array[: len(self.pages)]
 
     def live_pages(self) -> list[int]:
         return self.pages[self.first_live :]

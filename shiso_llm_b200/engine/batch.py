@@ -95,6 +95,10 @@ class StepBuilder:
         self._events = [None, None]
         self._turn = 0
         self.device_block = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._arange = np.arange(max_seqs + 2, dtype=np.int32)
+
+    def _iota(self, n: int) -> np.ndarray:
+        return self._arange[:n]
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepMeta:
         """``starts[i]`` = positions the cache held for entry ``i`` before this step."""
@@ -120,14 +124,33 @@ class StepBuilder:
         stage = self._staging[turn]
         host = stage.numpy()
 
-        q_start = np.zeros(num_seqs + 1, dtype=np.int32)
-        np.cumsum(lens, out=q_start[1:])
-        host[lay.q_start : lay.q_start + num_seqs + 1] = q_start
-        host[lay.start_pos : lay.start_pos + num_seqs] = starts
         slots = [self.cache.slot_of(r) for r in requests]
+        host[lay.start_pos : lay.start_pos + num_seqs] = starts
         host[lay.state_slots : lay.state_slots + num_seqs] = slots
+        single = num_tokens == num_seqs  # every sequence brings one token: rows and sequences coincide
+        if single:
+            rows = self._iota(num_seqs + 1)
+            q_start = rows
+            host[lay.q_start : lay.q_start + num_seqs + 1] = rows
+            host[lay.token_ids : lay.token_ids + num_seqs] = [e.tokens[0] for e in entries]
+            host[lay.positions : lay.positions + num_seqs] = starts
+            host[lay.seq_of_token : lay.seq_of_token + num_seqs] = rows[:num_seqs]
+            want_at = lay.want_rows
+            if num_wanted == num_seqs:
+                host[want_at : want_at + num_seqs] = rows[:num_seqs]
+            else:
+                for i, e in enumerate(entries):
+                    for w in e.want:
+                        if w != 0:
+                            raise ValueError(f"request {e.request!r}: wanted place {w} is outside its 1 tokens")
+                        host[want_at] = i
+                        want_at += 1
+        else:
+            q_start = np.zeros(num_seqs + 1, dtype=np.int32)
+            np.cumsum(lens, out=q_start[1:])
+            host[lay.q_start : lay.q_start + num_seqs + 1] = q_start
         want_at = lay.want_rows
-        for i, e in enumerate(entries):
+        for i, e in enumerate(entries if not single else ()):
             a, b = int(q_start[i]), int(q_start[i + 1])
             host[lay.token_ids + a : lay.token_ids + b] = e.tokens
             host[lay.positions + a : lay.positions + b] = np.arange(starts[i], starts[i] + lens[i], dtype=np.int32)

@@ -75,6 +75,15 @@ class Request:
     def tokens(self) -> list:
         return self.prompt + self.output
 
+    def token_slice(self, start: int, count: int) -> list:
+        """``tokens[start : start + count]`` without joining prompt and output."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n : start - n + count]
+        if start + count <= n:
+            return self.prompt[start : start + count]
+        return self.prompt[start:] + self.output[: start + count - n]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed

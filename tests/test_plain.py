@@ -100,3 +100,23 @@ def test_whole_model_prefix_property_and_tied_head():
     logits, hidden = plain.plain_forward(doc, tensors, [1, 2, 3], return_hidden=True)
     nf = plain.plain_rmsnorm(hidden, tensors["model.embedding_norm.weight"].double(), doc["norm_eps"])
     assert torch.allclose(logits, nf @ tensors["model.embed_tokens.weight"].double().T)
+
+
+def test_plain_implementation_has_not_drifted():
+    """tests/golden/plain_tiny.json pins a few logits of this file's functions (it is not an
+    output of the reference, which cannot be run here)."""
+    import importlib.util
+    import json
+    import os
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "golden", "make_golden.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    stored = json.load(open(os.path.join(here, "golden", "plain_tiny.json")))
+    fresh = module.golden()
+    for name in ("A", "B"):
+        assert fresh[name]["tokens"] == stored[name]["tokens"]
+        assert fresh[name]["argmax"] == stored[name]["argmax"] and fresh[name]["greedy"] == stored[name]["greedy"]
+        for a, b in zip(fresh[name]["logits"], stored[name]["logits"]):
+            assert all(abs(x - y) < 1e-9 for x, y in zip(a, b))

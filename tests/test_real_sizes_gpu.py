@@ -1,0 +1,58 @@
+"""The engine at LFM2-1.2B layer sizes (hidden 2048, 32/8 heads of 64, intermediate 5632,
+vocabulary 65536) with random weights, against the plain implementation: the first three
+layers (conv, conv, attention), so that the float64 reference stays within seconds.  Every
+tensor-core and weight-streaming kernel runs at the shapes the benchmark uses: a portion long
+enough for the persistent product and the tiled attention (200 rows), the cluster split-K
+product (40 rows), and single tokens for the skinny product and the decode attention.
+"""
+
+import json
+
+import pytest
+import torch
+
+import helpers
+import plain_lfm2
+import replay
+from shiso_llm_b200.cli import preset_path
+from shiso_llm_b200.config import plan_from_document
+from shiso_llm_b200.engine import Engine, EngineOptions
+from shiso_llm_b200.parts import BuildEnv, Model
+from shiso_llm_b200.weights import random_tensors
+from shiso_llm_b200.weights.loader import target_dtype
+from tolerances import check_logits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def sized():
+    document = json.load(open(preset_path("lfm2-1.2b")))
+    document["layer_types"] = document["layer_types"][:3]
+    document["num_hidden_layers"] = 3
+    _, _, plan = plan_from_document(document)
+    specs = Model(plan, BuildEnv(torch.float32, torch.device("cpu"), None)).tensor_specs()
+    stored = random_tensors(specs, 7, 0.02, "bfloat16", 0.1)
+    tokens = helpers.random_prompt(248, document["vocab_size"], 3)
+    reference = plain_lfm2.plain_forward(document, stored, tokens)
+    return document, plan, specs, stored, tokens, reference
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_sizes_every_kernel_route(sized, dtype):
+    from shiso_llm_b200.kernels import ops
+
+    document, plan, specs, stored, tokens, reference = sized
+    compute = torch.float32 if dtype == "float32" else torch.bfloat16
+    by = {s.name: s for s in specs}
+    tensors = {k: v.to("cuda", target_dtype(by[k], v.dtype, compute)) for k, v in stored.items()}
+    options = EngineOptions(dtype=dtype, ctx=512, page_size=16, kv_cache_tokens=1024, max_num_seqs=2,
+                            max_num_batched_tokens=256)
+    engine = Engine.from_plan(plan, tensors, options, ops)
+    steps = helpers.portions("a", tokens, [200, 40] + [1] * 8)
+    rows = helpers.run_steps(engine, steps)
+    ops.check_kernel_status()
+    got = replay.stack_rows(rows, "a", len(tokens))
+    check_logits(got, reference, dtype, f"1.2B layer sizes, {dtype}")
+    whole = replay.stack_rows(helpers.run_steps(engine, helpers.whole("b", tokens)), "b", len(tokens))
+    check_logits(whole, reference, dtype, f"1.2B layer sizes whole, {dtype}")
