@@ -46,11 +46,23 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
     float* v = staged[warp];
     const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
     float ss = 0.0f;
-    for (int i = lane; i < head_dim; i += 32) {
-        const float x = to_f32(src[i]);
-        v[i] = x;
-        ss += x * x;
+    if (sizeof(AT) == 2 && (head_dim & 1) == 0) {
+        // two values per access (rows start on 4-byte boundaries when head_dim is even)
+        const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
+        for (int i = lane; i < head_dim / 2; i += 32) {
+            const float2 x = __bfloat1622float2(src2[i]);
+            v[2 * i] = x.x;
+            v[2 * i + 1] = x.y;
+            ss += x.x * x.x + x.y * x.y;
+        }
+    } else {
+        for (int i = lane; i < head_dim; i += 32) {
+            const float x = to_f32(src[i]);
+            v[i] = x;
+            ss += x * x;
+        }
     }
+    __syncwarp();
     if (w) {
         const float inv = rsqrtf(warp_sum(ss) / (float)head_dim + eps);
         for (int i = lane; i < head_dim; i += 32) v[i] = v[i] * inv * w[i];
@@ -79,7 +91,12 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
         const int h = is_k ? u - heads : u - heads - kv_heads;
         dst = (is_k ? k_cache : v_cache) + (row * kv_heads + h) * head_dim;
     }
-    for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<AT>(v[i]);
+    if (sizeof(AT) == 2 && (head_dim & 1) == 0) {
+        __nv_bfloat162* dst2 = reinterpret_cast<__nv_bfloat162*>(dst);
+        for (int i = lane; i < head_dim / 2; i += 32) dst2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    } else {
+        for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<AT>(v[i]);
+    }
 }
 
 template <typename AT>

@@ -63,6 +63,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 constexpr int TILE_KEYS = 64;  // keys per shared-memory tile; each of the four warps takes 16 of them
+constexpr int KV_STAGES = 2;   // tiles in flight; more stages cost occupancy and measured slower (4 stages: 20 us against 17 us at batch 8)
 
 // D = head size (a multiple of 16 up to 128).  The query heads of one KV group (at most 16)
 // are the rows of a 16-row MMA tile, so one pass over the keys serves the whole group and the
@@ -82,8 +83,8 @@ decode_split_kernel(DecodeArgs a) {
 
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     uint8_t* q_s = smem_bytes;                           // [16][ROW_BYTES]
-    uint8_t* k_s = q_s + 16 * ROW_BYTES;                 // [2][TILE_KEYS][ROW_BYTES]
-    uint8_t* v_s = k_s + 2 * TILE_KEYS * ROW_BYTES;      // [2][TILE_KEYS][ROW_BYTES]
+    uint8_t* k_s = q_s + 16 * ROW_BYTES;                       // [KV_STAGES][TILE_KEYS][ROW_BYTES]
+    uint8_t* v_s = k_s + KV_STAGES * TILE_KEYS * ROW_BYTES;    // [KV_STAGES][TILE_KEYS][ROW_BYTES]
     float* merge = reinterpret_cast<float*>(k_s);        // after the loop: [WARPS][16][D + 2]
 
     const int group = a.heads / a.kv_heads;
@@ -122,8 +123,11 @@ decode_split_kernel(DecodeArgs a) {
             cp_async16(vd + r * ROW_BYTES + ch * 16, a.v_cache + at, valid);
         }
     };
-    if (tiles > 0) load_tile(0, 0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+    for (int s = 0; s < KV_STAGES - 1; ++s) {
+        if (s < tiles) load_tile(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
 
     float o_acc[DTILES][4];
 #pragma unroll
@@ -133,10 +137,10 @@ decode_split_kernel(DecodeArgs a) {
     const float scale_log2 = a.scale * 1.4426950408889634f;
 
     for (int tile = 0; tile < tiles; ++tile) {
-        const int stage = tile & 1;
-        if (tile + 1 < tiles) load_tile(tile + 1, stage ^ 1);
+        const int stage = tile % KV_STAGES;
+        if (tile + KV_STAGES - 1 < tiles) load_tile(tile + KV_STAGES - 1, (tile + KV_STAGES - 1) % KV_STAGES);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(KV_STAGES - 1) : "memory");  // this tile's group has landed
         __syncthreads();
         if (tile == 0) {
 #pragma unroll
@@ -282,7 +286,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bflo
 template <int D>
 int launch_split(const DecodeArgs& a, int tokens, cudaStream_t stream) {
     constexpr int ROW_BYTES = D * 2 + 16;
-    constexpr int TILE_BYTES = (16 + 4 * TILE_KEYS) * ROW_BYTES;
+    constexpr int TILE_BYTES = (16 + 2 * KV_STAGES * TILE_KEYS) * ROW_BYTES;
     constexpr int MERGE_BYTES = 16 * ROW_BYTES + WARPS * 16 * (D + 2) * 4;
     constexpr int SMEM = TILE_BYTES > MERGE_BYTES ? TILE_BYTES : MERGE_BYTES;
     auto kernel = decode_split_kernel<D>;

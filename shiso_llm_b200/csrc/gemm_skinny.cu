@@ -1,4 +1,4 @@
-// Y[T, N] = X[T, K] * W[N, K]^T for a handful of rows (T <= 32), bfloat16: the decode step's
+// Y[T, N] = X[T, K] * W[N, K]^T for a handful of rows (T <= 64), bfloat16: the decode step's
 // matrix products, which are weight streaming.
 //
 // At these sizes a product is over in a few microseconds, so what counts is how soon the
@@ -11,8 +11,16 @@
 // set of products.  The partial tiles are summed through shared memory in warp order,
 // so the result does not depend on timing.
 //
-// With `inter > 0` the weight is a [2 * inter, K] gate-over-up pair and the epilogue writes
-// silu(gate) * up (kernels/cuda/generic/glu.cuh:35-57) - the activation never leaves the chip.
+// What follows the product is folded into the epilogue, because at these sizes every extra
+// kernel costs more than its arithmetic:
+//   GLU       the weight is a [2 * inter, K] gate-over-up pair; a CTA takes 8 gate rows and
+//             their 8 up rows and writes silu(gate) * up (kernels/cuda/generic/glu.cuh:35-57);
+// (Two more fusions were built, measured inside a captured step and dropped.  Folding in the
+// residual add and the next RMS norm - the CTA that finishes last normalising all rows - cost
+// 10.5 us against 6.1 us for product + row kernel: fence, ticket and a single-CTA tail.  Running
+// the gated short convolution in the input projection's epilogue won 0.9 us in isolation and
+// lost 3 us per layer in the whole step, because its thin tail delays the grid's completion,
+// which is what the next product's activations wait for.)
 //
 // The reference's decode products are matvec kernels that re-read the weights per row block
 // (crates/shiso-engine/src/projection.rs:972-1069).
@@ -49,15 +57,17 @@ __device__ __forceinline__ uint4 load_activation16(const __nv_bfloat16* p, bool 
     return v;
 }
 
+enum { MODE_PLAIN = 0, MODE_GLU = 1 };
+
 struct SkinnyArgs {
     const __nv_bfloat16* x;  // [T, K]
-    const __nv_bfloat16* w;  // [N, K] (N = 2 * inter for a gate/up pair)
+    const __nv_bfloat16* w;  // [N, K]
     const float* bias;       // [N] or null (plain products only)
-    void* y;                 // [T, N] or [T, inter]
-    int T, N, K, inter, out_f32;
+    void* y;                 // plain [T, N]; GLU [T, inter]
+    int T, N, K, inter, out_f32, mode;
 };
 
-// NT = 8-token tiles (1, 2 or 4); WARPS_K = warps that split K; UNROLL = 64-wide k blocks per
+// NT = 8-token tiles (1, 2, 4 or 8); WARPS_K = warps that split K; UNROLL = 64-wide k blocks per
 // warp whose loads (weights and activations) are all issued before the first MMA.
 template <int NT, int WARPS_K, int UNROLL>
 __global__ void __launch_bounds__(WARPS_K * 32)
@@ -66,21 +76,23 @@ gemm_skinny_kernel(SkinnyArgs a) {
     bool waited = false;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
-    const bool glu = a.inter > 0;
-    // rows of the 16 x K weight tile: g and g + 8
-    int row_lo, row_hi;
-    if (glu) {
-        row_lo = blockIdx.x * 8 + g;            // gate row
-        row_hi = a.inter + blockIdx.x * 8 + g;  // its up row
-    } else {
-        row_lo = blockIdx.x * 16 + g;
-        row_hi = row_lo + 8;
+    const int mode = a.mode;
+    // the two rows of the 16 x K weight tile this lane streams: tile rows g and g + 8
+    int rows[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + 8 * h;
+        if (mode == MODE_GLU) {
+            rows[h] = (h ? a.inter : 0) + blockIdx.x * 8 + g;  // gate row, and its up row
+            row_ok[h] = blockIdx.x * 8 + g < a.inter;
+        } else {
+            rows[h] = blockIdx.x * 16 + r;
+            row_ok[h] = rows[h] < a.N;
+        }
     }
-    const int limit = glu ? a.inter : a.N;
-    const bool lo_ok = glu ? (blockIdx.x * 8 + g < limit) : (row_lo < limit);
-    const bool hi_ok = glu ? lo_ok : (row_hi < limit);
-    const __nv_bfloat16* w_lo = a.w + (size_t)row_lo * a.K;
-    const __nv_bfloat16* w_hi = a.w + (size_t)row_hi * a.K;
+    const __nv_bfloat16* w_lo = a.w + (size_t)(row_ok[0] ? rows[0] : 0) * a.K;
+    const __nv_bfloat16* w_hi = a.w + (size_t)(row_ok[1] ? rows[1] : 0) * a.K;
 
     float acc[NT][4];
 #pragma unroll
@@ -95,8 +107,8 @@ gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const bool in = k + h * 8 < a.K;
-                wl[u][h] = load_weight16(w_lo + k + h * 8, in && lo_ok);
-                wh[u][h] = load_weight16(w_hi + k + h * 8, in && hi_ok);
+                wl[u][h] = load_weight16(w_lo + k + h * 8, in && row_ok[0]);
+                wh[u][h] = load_weight16(w_hi + k + h * 8, in && row_ok[1]);
             }
         }
         if (!waited) {
@@ -144,7 +156,7 @@ gemm_skinny_kernel(SkinnyArgs a) {
         partial[0][n][l][e] = sum;  // only this thread touches this element
     }
     __syncthreads();
-    // c0: (row g, token 2t), c1: (row g, token 2t+1), c2: (row g+8, token 2t), c3: (row g+8, token 2t+1)
+    // In a lane's registers: c0: (row g, token 2t), c1: (row g, token 2t+1), c2/c3: row g + 8.
     if (warp == 0) {
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
@@ -153,23 +165,23 @@ gemm_skinny_kernel(SkinnyArgs a) {
                 const int token = n * 8 + t4 * 2 + e;
                 if (token >= a.T) continue;
                 const float lo = partial[0][n][lane][e], hi = partial[0][n][lane][2 + e];
-                if (glu) {
-                    if (lo_ok) {
+                if (mode == MODE_GLU) {
+                    if (row_ok[0]) {
                         const float v = lo / (1.0f + expf(-lo)) * hi;
                         const size_t at = (size_t)token * a.inter + blockIdx.x * 8 + g;
                         if (a.out_f32) ((float*)a.y)[at] = v;
                         else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
                     }
                 } else {
-                    if (lo_ok) {
-                        const float v = lo + (a.bias ? a.bias[row_lo] : 0.0f);
-                        const size_t at = (size_t)token * a.N + row_lo;
+                    if (row_ok[0]) {
+                        const float v = lo + (a.bias ? a.bias[rows[0]] : 0.0f);
+                        const size_t at = (size_t)token * a.N + rows[0];
                         if (a.out_f32) ((float*)a.y)[at] = v;
                         else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
                     }
-                    if (hi_ok) {
-                        const float v = hi + (a.bias ? a.bias[row_hi] : 0.0f);
-                        const size_t at = (size_t)token * a.N + row_hi;
+                    if (row_ok[1]) {
+                        const float v = hi + (a.bias ? a.bias[rows[1]] : 0.0f);
+                        const size_t at = (size_t)token * a.N + rows[1];
                         if (a.out_f32) ((float*)a.y)[at] = v;
                         else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
                     }
@@ -179,17 +191,37 @@ gemm_skinny_kernel(SkinnyArgs a) {
     }
 }
 
+int launch_skinny(const SkinnyArgs& a, unsigned blocks, cudaStream_t stream) {
+    // enough warps per CTA that one round of loads covers the CTA's whole K range
+    const bool deep = a.K > 3072;
+#define SHISO_LAUNCH(NT_, WK_, UN_) launch_kernel(gemm_skinny_kernel<NT_, WK_, UN_>, blocks, WK_ * 32, 0, stream, a)
+    if (a.T <= 8) {
+        if (deep) SHISO_LAUNCH(1, 16, 4);
+        else SHISO_LAUNCH(1, 8, 4);
+    } else if (a.T <= 16) {
+        if (deep) SHISO_LAUNCH(2, 16, 4);
+        else SHISO_LAUNCH(2, 8, 4);
+    } else if (a.T <= 32) {
+        if (deep) SHISO_LAUNCH(4, 16, 2);
+        else SHISO_LAUNCH(4, 8, 2);
+    } else {
+        SHISO_LAUNCH(8, 8, 1);  // 16 warps would need more static shared memory than a CTA may have
+    }
+#undef SHISO_LAUNCH
+    return launch_status();
+}
+
 }  // namespace
 
-// x [T, K] bf16 (T <= 32), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
+// x [T, K] bf16 (T <= 64), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
 // inter == 0: y[T, N] = x w^T (+ bias).  inter > 0: N == 2 * inter, y[T, inter] = silu(x gate^T) * (x up^T).
 SHISO_API int shiso_gemm_skinny(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
                                 int K, int inter, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > 32 || K % 8 != 0 || K <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (T > 64 || K % 8 != 0 || K <= 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
     if (inter > 0 && (N != 2 * inter || bias)) return SHISO_ERR_SHAPE;
-    SkinnyArgs a;
+    SkinnyArgs a = {};
     a.x = (const __nv_bfloat16*)x;
     a.w = (const __nv_bfloat16*)w;
     a.bias = bias;
@@ -199,20 +231,6 @@ SHISO_API int shiso_gemm_skinny(const void* x, const void* w, const float* bias,
     a.K = K;
     a.inter = inter;
     a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
-    const unsigned blocks = inter > 0 ? ceil_div_u(inter, 8) : ceil_div_u(N, 16);
-    // enough warps per CTA that one round of loads covers the CTA's whole K range
-    const bool deep = K > 3072;
-#define SHISO_LAUNCH(NT_, WK_, UN_) launch_kernel(gemm_skinny_kernel<NT_, WK_, UN_>, blocks, WK_ * 32, 0, stream, a)
-    if (T <= 8) {
-        if (deep) SHISO_LAUNCH(1, 16, 4);
-        else SHISO_LAUNCH(1, 8, 4);
-    } else if (T <= 16) {
-        if (deep) SHISO_LAUNCH(2, 16, 4);
-        else SHISO_LAUNCH(2, 8, 4);
-    } else {
-        if (deep) SHISO_LAUNCH(4, 16, 2);
-        else SHISO_LAUNCH(4, 8, 2);
-    }
-#undef SHISO_LAUNCH
-    return launch_status();
+    a.mode = inter > 0 ? MODE_GLU : MODE_PLAIN;
+    return launch_skinny(a, inter > 0 ? ceil_div_u(inter, 8) : ceil_div_u(N, 16), stream);
 }

@@ -51,6 +51,7 @@ class StepMeta:
     max_q_len: int
     max_context: int  # most positions any sequence can see after this step
     all_decode: bool  # every sequence brings exactly one token
+    wants_every_row: bool = False  # want_rows is 0, 1, .. T-1: logits of all rows, in order
     h_q_start: list = field(default_factory=list)
     h_start_pos: list = field(default_factory=list)
     h_state_slots: list = field(default_factory=list)
@@ -128,6 +129,7 @@ class StepBuilder:
         host[lay.start_pos : lay.start_pos + num_seqs] = starts
         host[lay.state_slots : lay.state_slots + num_seqs] = slots
         single = num_tokens == num_seqs  # every sequence brings one token: rows and sequences coincide
+        every_row = False
         if single:
             rows = self._iota(num_seqs + 1)
             q_start = rows
@@ -136,7 +138,8 @@ class StepBuilder:
             host[lay.positions : lay.positions + num_seqs] = starts
             host[lay.seq_of_token : lay.seq_of_token + num_seqs] = rows[:num_seqs]
             want_at = lay.want_rows
-            if num_wanted == num_seqs:
+            every_row = num_wanted == num_seqs and all(len(e.want) == 1 and e.want[0] == 0 for e in entries)
+            if every_row:
                 host[want_at : want_at + num_seqs] = rows[:num_seqs]
             else:
                 for i, e in enumerate(entries):
@@ -192,6 +195,7 @@ class StepBuilder:
             max_q_len=max(lens),
             max_context=max(s + n for s, n in zip(starts, lens)),
             all_decode=all(n == 1 for n in lens),
+            wants_every_row=single and every_row,
             h_q_start=q_start.tolist(),
             h_start_pos=list(starts),
             h_state_slots=slots,

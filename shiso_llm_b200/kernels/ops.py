@@ -149,6 +149,17 @@ def _sm_count() -> int:
     return _SM_COUNT
 
 
+def _takes_skinny(tokens: int, n: int) -> bool:
+    """Which plain products the weight-streaming kernel runs (measured inside captured steps
+    against the tensor-memory kernel): up to 8 rows always; up to 16 rows unless the matrix is
+    as tall as a vocabulary; up to 32 rows for matrices of at most 8192 rows."""
+    if tokens <= 8:
+        return True
+    if tokens <= SKINNY_MAX_TOKENS:
+        return n < 32768
+    return tokens <= 32 and n <= 8192
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x[T, K] @ w[N, K]^T`` with float accumulation.
 
@@ -166,7 +177,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
     lib = library()
     both_bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    if both_bf16 and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0:
+    if both_bf16 and k % 8 == 0 and _takes_skinny(tokens, n):
         status = lib.shiso_gemm_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _stream())
         _done(status, "linear (skinny)")
         return out
@@ -229,6 +240,22 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         _done(status, "linear_swiglu (tcgen05)")
         return out
     return swiglu(linear(x, gate_up, out_dtype))
+
+
+def linear_add_rmsnorm(x, w, residual, norm_w, eps, out_dtype):
+    """A block's output projection, the residual add and the next RMS norm:
+    ``residual += x @ w^T`` (float32, in place) and returns ``rmsnorm(residual) * norm_w``.
+    Two launches: the product, then the fused add + norm row kernel.  (One launch, with the
+    CTA that finishes last normalising, was measured at 10.5 us against 6.1 us for the pair
+    in a dependent-launch chain and was dropped.)"""
+    return add_rmsnorm(residual, linear(x, w, out_dtype), norm_w, eps, out_dtype)
+
+
+def linear_short_conv(x, in_proj, taps, bias, state, step):
+    """The short conv's input projection followed by the gated convolution.  Two launches (a
+    single one, with the convolution in the product's epilogue, was measured and lost 3 us per
+    layer inside a captured step)."""
+    return short_conv(linear(x, in_proj, x.dtype), taps, bias, state, step)
 
 
 def linear_simple(x, w, out_dtype, bias=None):

@@ -3,7 +3,7 @@
 from .plan import LayerSpec, ModelPlan, PartSpec, RunEntry, sequential_order
 from .base import (
     BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
-    Block, BuildEnv, Embedding, FeedForward, FixedState, Head, Mixer, Norm, PagedKV,
+    Block, BuildEnv, DeferredLinear, Embedding, FeedForward, FixedState, Head, Mixer, Norm, PagedKV,
     Part, PositionEncoding, Registry, Stream,
 )
 from . import norm, position, attention, short_conv, feed_forward, block, embedding  # register built-ins
@@ -11,7 +11,7 @@ from .model import Model
 
 __all__ = [
     "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS",
-    "Block", "BuildEnv", "Embedding", "FeedForward", "FixedState", "Head", "LayerSpec", "Mixer",
+    "Block", "BuildEnv", "DeferredLinear", "Embedding", "FeedForward", "FixedState", "Head", "LayerSpec", "Mixer",
     "Model", "ModelPlan", "Norm", "PagedKV", "Part", "PartSpec", "PositionEncoding", "Registry",
     "RunEntry", "Stream", "sequential_order",
 ]

@@ -25,7 +25,7 @@ import torch
 
 from ..config.errors import UnsupportedShape
 from ..weights.spec import TensorSpec
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, Mixer, PagedKV
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, DeferredLinear, Mixer, PagedKV
 
 MAX_HEAD_DIM = 256
 HEAD_DIM_STEP = 16
@@ -130,4 +130,4 @@ class GqaAttention(Mixer):
             self.window or 0,
             step,
         )
-        return ops.linear(attn, self.out, self.env.dtype)
+        return DeferredLinear(ops, attn, self.out, self.env.dtype)

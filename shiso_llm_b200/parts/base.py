@@ -7,10 +7,10 @@ rows of one step.  No part knows which model it is in.
 
 Kinds of part and what each must provide:
 
-``Norm``             ``apply(x)``, ``add_apply(residual, delta, rows=None)``
+``Norm``             ``apply(x)``, ``add_apply(residual, delta, rows=None)``, optional ``add_apply_linear``
 ``PositionEncoding`` ``rotary()`` - the per-pair frequencies the fused kernel rotates by
-``Mixer``            ``cache_spec()``, ``forward(x, step, cache)``
-``FeedForward``      ``forward(x, step)``
+``Mixer``            ``cache_spec()``, ``forward(x, step, cache)`` -> tensor or ``DeferredLinear``
+``FeedForward``      ``forward(x, step)`` -> tensor or ``DeferredLinear``
 ``Block``            ``forward(stream, step, cache)`` - the arrangement of the above
 ``Embedding``        ``forward(step)`` -> float32 residual rows
 ``Head``             ``forward(x)`` -> float32 logits
@@ -149,6 +149,21 @@ class Head(Part):
         raise NotImplementedError
 
 
+class DeferredLinear:
+    """A block's output projection that has not run yet: ``x @ w^T``.
+
+    A mixer or feed-forward may return this instead of a tensor; the stream then runs the
+    product together with the residual add and the next norm when the norm can
+    (``Norm.add_apply_linear``), which for decode-sized steps is one launch instead of two.
+    ``materialize()`` runs it on its own."""
+
+    def __init__(self, ops, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype):
+        self.ops, self.x, self.w, self.out_dtype = ops, x, w, out_dtype
+
+    def materialize(self) -> torch.Tensor:
+        return self.ops.linear(self.x, self.w, self.out_dtype)
+
+
 class Stream:
     """The residual stream between blocks.
 
@@ -164,9 +179,21 @@ class Stream:
         if self.pending is None:
             return norm.apply(self.residual)
         delta, self.pending = self.pending, None
+        if isinstance(delta, DeferredLinear):
+            fused = getattr(norm, "add_apply_linear", None)
+            if fused is not None:
+                return fused(self.residual, delta)
+            delta = delta.materialize()
         return norm.add_apply(self.residual, delta)
 
-    def add(self, delta: torch.Tensor) -> None:
+    def take_pending(self) -> Optional[torch.Tensor]:
+        """The block output still waiting to be added, as a tensor (or None)."""
+        delta, self.pending = self.pending, None
+        if isinstance(delta, DeferredLinear):
+            delta = delta.materialize()
+        return delta
+
+    def add(self, delta) -> None:
         if self.pending is not None:
             raise RuntimeError("a block output is already waiting to be added to the residual")
         self.pending = delta

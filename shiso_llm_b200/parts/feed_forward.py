@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.spec import TensorSpec
-from .base import FEED_FORWARDS, FeedForward
+from .base import FEED_FORWARDS, DeferredLinear, FeedForward
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -45,4 +45,4 @@ class SwiGLU(FeedForward):
     def forward(self, x, step):
         ops = self.env.ops
         mid = ops.linear_swiglu(x, self.gate_up, self.env.dtype)
-        return ops.linear(mid, self.down, self.env.dtype)
+        return DeferredLinear(ops, mid, self.down, self.env.dtype)

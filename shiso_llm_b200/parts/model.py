@@ -80,9 +80,12 @@ class Model:
             self.blocks[entry.layer].forward(stream, step, view)
         if step.num_wanted == 0:
             return None
+        if getattr(step, "wants_every_row", False):
+            # every row in order (a decode step): the norm that closes the last block is the final norm
+            return self.head.forward(stream.normed(self.final_norm))
         rows = step.want_rows
-        if stream.pending is not None:
-            delta, stream.pending = stream.pending, None
+        delta = stream.take_pending()
+        if delta is not None:
             normed = self.final_norm.add_apply(stream.residual, delta, rows)
         else:
             normed = self.final_norm.apply(self.env.ops.gather_rows(stream.residual, rows))

@@ -32,3 +32,8 @@ class RMSNorm(Norm):
 
     def add_apply(self, residual, delta, rows=None):
         return self.env.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, rows)
+
+    def add_apply_linear(self, residual, deferred):
+        """``residual += deferred.x @ deferred.w^T`` and the norm of the sum, fused where the
+        kernel table can (decode-sized bfloat16 steps)."""
+        return self.env.ops.linear_add_rmsnorm(deferred.x, deferred.w, residual, self.weight, self.eps, self.env.dtype)

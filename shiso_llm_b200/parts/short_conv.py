@@ -16,7 +16,7 @@ from __future__ import annotations
 
 from ..config.errors import UnsupportedShape
 from ..weights.spec import VECTOR, ZEROS, TensorSpec
-from .base import MIXERS, FixedState, Mixer
+from .base import MIXERS, DeferredLinear, FixedState, Mixer
 
 MAX_TAPS = 8
 
@@ -57,6 +57,5 @@ class ShortConv(Mixer):
 
     def forward(self, x, step, cache):
         ops = self.env.ops
-        proj = ops.linear(x, self.in_proj, self.env.dtype)
-        y = ops.short_conv(proj, self.conv, self.bias, cache.state, step)
-        return ops.linear(y, self.out_proj, self.env.dtype)
+        y = ops.linear_short_conv(x, self.in_proj, self.conv, self.bias, cache.state, step)
+        return DeferredLinear(ops, y, self.out_proj, self.env.dtype)

@@ -68,6 +68,14 @@ def linear_swiglu(x, gate_up, out_dtype):
     return (g / (1.0 + torch.exp(-g)) * u).to(out_dtype)
 
 
+def linear_add_rmsnorm(x, w, residual, norm_w, eps, out_dtype):
+    return add_rmsnorm(residual, linear(x, w, out_dtype), norm_w, eps, out_dtype)
+
+
+def linear_short_conv(x, in_proj, taps, bias, state, step):
+    return short_conv(linear(x, in_proj, x.dtype), taps, bias, state, step)
+
+
 def short_conv(proj, taps, bias, state, step):
     """y[t] = c[t] * (sum_j taps[:, j] * u[t - (L-1) + j] + bias); u = b * x; the state of
     each sequence's slot holds the last L-1 values of u (float32) and is updated."""

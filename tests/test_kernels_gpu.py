@@ -432,3 +432,47 @@ def test_tensor_core_product_with_fused_swiglu(shape):
     close(got, ref.linear_swiglu(x, w, torch.bfloat16), torch.bfloat16, f"fused swiglu {shape}")
     unfused = ops().swiglu(ops().linear(x.cuda(), w.cuda(), torch.bfloat16))
     close(got, unfused, torch.bfloat16, "fused against product + activation kernel", scale=ref.linear_swiglu(x, w, torch.float32).abs().max().item() * 2)
+
+
+@pytest.mark.parametrize("taps,hidden,bias", [(3, 2048, False), (4, 96, True), (2, 203 * 8, True)])
+def test_fused_projection_and_short_conv(taps, hidden, bias):
+    """The conv's input projection followed by the gated convolution through the one kernel-table
+    entry the mixer uses for them."""
+    k = 264
+    q_lens, starts = [1, 1, 3, 2, 1, 4], [0, 9, 2, 0, 77, 5]
+    cpu, gpu, _ = make_step(q_lens, starts, 4, 64, 120, num_slots=8)
+    gpu.max_q_len = cpu.max_q_len = 4
+    x = rnd((sum(q_lens), k), torch.bfloat16, 121)
+    w_in = rnd((3 * hidden, k), torch.bfloat16, 122, 0.1)
+    w = rnd((hidden, taps), torch.float32, 123)
+    b = rnd((hidden,), torch.float32, 124) if bias else None
+    start = rnd((8, taps - 1, hidden), torch.float32, 125)
+    s_ref, s_fused, s_two = start.clone(), start.clone().cuda(), start.clone().cuda()
+    want = ref.short_conv(ref.linear(x, w_in, torch.bfloat16), w, b, s_ref, cpu)
+    fused = ops().linear_short_conv(x.cuda(), w_in.cuda(), w.cuda(), b.cuda() if bias else None, s_fused, gpu)
+    close(fused, want, torch.bfloat16, "fused projection + conv")
+    two = ops().short_conv(ops().linear(x.cuda(), w_in.cuda(), torch.bfloat16), w.cuda(), b.cuda() if bias else None, s_two, gpu)
+    close(fused, two, torch.bfloat16, "fused against two kernels")
+    assert torch.allclose(s_fused.cpu(), s_ref, rtol=0, atol=2.0 ** -7 * s_ref.abs().max().item())
+    untouched = torch.ones(8, dtype=torch.bool)
+    untouched[cpu.state_slots.long()] = False
+    assert torch.equal(s_fused.cpu()[untouched], start[untouched])
+
+
+@pytest.mark.parametrize("shape", [(8, 2048, 2048), (1, 96, 64), (13, 1000, 264), (16, 2048, 5632)])
+def test_fused_projection_residual_add_and_norm(shape):
+    """A block's output projection, the residual add and the next RMS norm through the one
+    kernel-table entry the stream uses for them."""
+    T, N, K = shape
+    x, w = rnd((T, K), torch.bfloat16, 130), rnd((N, K), torch.bfloat16, 131, 0.05)
+    res = rnd((T, N), torch.float32, 132, 2.0)
+    nw = 1.0 + 0.2 * rnd((N,), torch.float32, 133)
+    for round_ in range(3):
+        res_ref, res_gpu = res.clone(), res.clone().cuda()
+        want = ref.linear_add_rmsnorm(x, w, res_ref, nw, 1e-5, torch.bfloat16)
+        got = ops().linear_add_rmsnorm(x.cuda(), w.cuda(), res_gpu, nw.cuda(), 1e-5, torch.bfloat16)
+        close(got, want, torch.bfloat16, f"fused add + norm {shape} round {round_}")
+        # the product is rounded to bfloat16 before it is added (as the two-kernel route stores
+        # it), so the sums may differ by one unit in the last place of the product
+        delta_scale = ref.linear(x, w, torch.float32).abs().max().item()
+        assert (res_gpu.cpu() - res_ref).abs().max().item() <= 2.0 ** -7 * delta_scale
