@@ -241,6 +241,7 @@ def main() -> int:
         t0 = time.perf_counter()
         for _ in range(steps):
             llm.step()
+        llm.drain()  # the last step's tokens reach the host inside the timed region too
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
         assert len(llm.scheduler.running) == batch, "a request ended inside the timed region"

@@ -46,9 +46,15 @@ class LLM:
         cuda_graphs: bool = True,
         device: str = "cuda:0",
         ops=None,
+        lookahead: bool = True,
     ):
         """``model`` is a model folder (config.json + *.safetensors), or an ``Engine`` that is
-        already built (then the engine's own options stand for dtype and cache sizes)."""
+        already built (then the engine's own options stand for dtype and cache sizes).
+
+        With ``lookahead`` a step is planned and launched while the tokens of the step before
+        it are still on their way to the host: a decoding request's next row takes its token
+        on the device, and the host reads each step's tokens one step late.  The tokens are the
+        same; a request that ends on a stop token has one more row computed, which is dropped."""
         if isinstance(model, Engine):
             self.engine = model
             opts = model.options
@@ -71,6 +77,12 @@ class LLM:
         )
         self.sampler = DeviceSampler(self.engine.env.ops, self.engine.device)
         self._next_id = 0
+        self.lookahead = bool(lookahead)
+        self._in_flight = None  # (plan, host buffer, count, event) of the step whose tokens are on their way
+        self._turn = 0
+        pin = self.engine.device.type == "cuda"
+        rows = self.engine.fed_tokens.shape[0]
+        self._host_picks = [torch.zeros(rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
 
     # ------------------------------------------------------------------ low level
 
@@ -87,25 +99,60 @@ class LLM:
         return self.scheduler.abort(request_id)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._in_flight is not None
 
     def step(self) -> list:
         """One scheduler decision and one engine step; returns the outputs that finished."""
         plan: StepPlan = self.scheduler.plan()
-        sampled = []
+        launched = None
         if plan.entries:
             entries, params, positions = [], [], []
             for e in plan.entries:
-                tokens = e.request.token_slice(e.start, e.count)
-                entries.append(StepEntry(e.request.id, tokens, [e.count - 1] if e.samples else []))
+                if e.feed is not None:
+                    tokens = [0]  # a placeholder: the device reads the token a sampler left it
+                else:
+                    tokens = e.request.token_slice(e.start, e.count)
+                entries.append(StepEntry(e.request.id, tokens, [e.count - 1] if e.samples else [], e.feed))
                 if e.samples:
                     params.append(e.request.params)
                     positions.append(e.start + e.count)
             logits = self.engine.step(entries)
+            launched = (plan, None, 0, None)
             if logits is not None:
-                sampled = self.sampler.sample(logits, params, positions)
-        self.scheduler.step_done(plan, sampled)
+                count = logits.shape[0]
+                picks = self.engine.fed_tokens[:count]
+                self.sampler.sample_into(logits, params, positions, picks)
+                host = self._host_picks[self._turn]
+                self._turn ^= 1
+                host[:count].copy_(picks, non_blocking=True)
+                event = None
+                if picks.is_cuda:
+                    event = torch.cuda.Event()
+                    event.record()
+                launched = (plan, host, count, event)
+        self.scheduler.launched(plan)
+        if self.lookahead:
+            self._collect(self._in_flight)
+            self._in_flight = launched
+        else:
+            self._collect(launched)
         return [self._output(r) for r in self.scheduler.take_finished()]
+
+    def drain(self) -> list:
+        """Waits for the step that is still on its way (lookahead), so that every token the
+        device has picked is known to the host; returns the outputs that finished with it."""
+        self._collect(self._in_flight)
+        self._in_flight = None
+        return [self._output(r) for r in self.scheduler.take_finished()]
+
+    def _collect(self, launched) -> None:
+        """Waits for a launched step's tokens and hands them to the scheduler."""
+        if launched is None:
+            return
+        plan, host, count, event = launched
+        if event is not None:
+            event.synchronize()
+        self.scheduler.arrived(plan, host[:count].tolist() if count else [])
 
     @staticmethod
     def _output(req) -> Output:

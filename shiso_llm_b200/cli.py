@@ -96,6 +96,7 @@ def cmd_generate(args) -> int:
         kv_cache_tokens=args.kv_cache_tokens, max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk=args.prefill_chunk,
         on_exhaustion=args.on_exhaustion, cuda_graphs=not args.no_cuda_graphs, device=args.device,
+        lookahead=not args.no_lookahead,
     )
     prompts = parse_prompts(args, llm.engine.vocab_size)
     params = SamplingParams(
@@ -140,6 +141,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prefill-chunk", type=int, default=None)
     g.add_argument("--on-exhaustion", choices=["preempt", "fail"], default="preempt")
     g.add_argument("--no-cuda-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    g.add_argument("--no-lookahead", action="store_true",
+                   help="wait for each step's tokens on the host before planning the next step")
     g.add_argument("--device", default="cuda:0")
     g.set_defaults(func=cmd_generate)
 

@@ -14,6 +14,8 @@
 // result depends only on the row's own position and cache, not on the batch.  This is the
 // kernel of the 32-bit path and of any head size; faster kernels for bfloat16 live in
 // their own files.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -21,81 +23,124 @@ namespace {
 constexpr int MAX_HEAD_DIM = 256;
 constexpr int WARPS = 4;
 
-template <typename AT>
+// A unit is one head of one token: a query head, a key head or a value head.  A warp owns
+// `per_warp` consecutive units of one token and keeps a unit in registers: lane l holds the
+// rotation pairs (p, p + rotary_dim/2) for p = l, l + 32, .. and the elements past rotary_dim
+// in the same stride.  The angle's sine and cosine are computed once per warp and serve all its
+// units (the angle depends on the token and the pair, not on the head).  A unit is a few hundred
+// bytes, so its time is the latency of its loads: the next unit's values are asked for before
+// the current one is worked on, and HD_MAX (the head size rounded up to 64, 128 or 256) sizes the
+// registers so that small heads leave room for many warps.  The lane layout, and with it every
+// sum's order, is the same whatever per_warp and HD_MAX are.
+template <int HD_MAX>
+struct UnitRegs {
+    float a[HD_MAX / 64], b[HD_MAX / 64], tl[HD_MAX / 32];
+};
+
+template <typename AT, int HD_MAX>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
                           const float* __restrict__ inv_freq, const int* __restrict__ positions,
                           const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                           int table_width, AT* __restrict__ k_cache, AT* __restrict__ v_cache,
                           AT* __restrict__ q_out, int tokens, int heads, int kv_heads, int head_dim,
-                          int rotary_dim, int page_size, float eps, int store) {
+                          int rotary_dim, int page_size, float eps, int store, int per_warp) {
     pdl_begin();
-    __shared__ float staged[WARPS][MAX_HEAD_DIM];
+    constexpr int PAIRS = HD_MAX / 64;  // rotation pairs a lane can hold
+    constexpr int TAIL = HD_MAX / 32;   // unrotated elements a lane can hold
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int units = heads + 2 * kv_heads;
-    const long long unit_index = (long long)blockIdx.x * WARPS + warp;
-    if (unit_index >= (long long)tokens * units) return;
-    const int t = (int)(unit_index / units);
-    const int u = (int)(unit_index % units);
-    const int row_width = units * head_dim;
-    const AT* src = qkv + (size_t)t * row_width + (size_t)u * head_dim;
-    const bool is_q = u < heads;
-    const bool is_k = !is_q && u < heads + kv_heads;
-    if (!is_q && !store) return;
+    const int warps_per_token = (units + per_warp - 1) / per_warp;
+    const long long warp_index = (long long)blockIdx.x * WARPS + warp;
+    if (warp_index >= (long long)tokens * warps_per_token) return;
+    const int t = (int)(warp_index / warps_per_token);
+    const int u_first = (int)(warp_index % warps_per_token) * per_warp;
+    const int u_last = min(store ? units : heads, u_first + per_warp);
+    if (u_first >= u_last) return;
+    const int half = rotary_dim / 2;
+    const AT* token_row = qkv + (size_t)t * units * head_dim;
 
-    float* v = staged[warp];
-    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
-    float ss = 0.0f;
-    if (sizeof(AT) == 2 && (head_dim & 1) == 0) {
-        // two values per access (rows start on 4-byte boundaries when head_dim is even)
-        const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
-        for (int i = lane; i < head_dim / 2; i += 32) {
-            const float2 x = __bfloat1622float2(src2[i]);
-            v[2 * i] = x.x;
-            v[2 * i + 1] = x.y;
-            ss += x.x * x.x + x.y * x.y;
+    auto load_unit = [&](int u, UnitRegs<HD_MAX>& r) {
+        const AT* src = token_row + (size_t)u * head_dim;
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            const int p = lane + 32 * j;
+            r.a[j] = p < half ? to_f32(src[p]) : 0.0f;
+            r.b[j] = p < half ? to_f32(src[p + half]) : 0.0f;
         }
-    } else {
-        for (int i = lane; i < head_dim; i += 32) {
-            const float x = to_f32(src[i]);
-            v[i] = x;
-            ss += x * x;
+#pragma unroll
+        for (int j = 0; j < TAIL; ++j) {
+            const int e = rotary_dim + lane + 32 * j;
+            r.tl[j] = e < head_dim ? to_f32(src[e]) : 0.0f;
         }
+    };
+
+    UnitRegs<HD_MAX> cur, nxt;
+    load_unit(u_first, cur);
+    const int pos_i = positions[t];
+    size_t cache_row = 0;
+    if (u_last > heads) {
+        const int page = block_table[(size_t)seq_of_token[t] * table_width + pos_i / page_size];
+        cache_row = (size_t)page * page_size + pos_i % page_size;
     }
-    __syncwarp();
-    if (w) {
-        const float inv = rsqrtf(warp_sum(ss) / (float)head_dim + eps);
-        for (int i = lane; i < head_dim; i += 32) v[i] = v[i] * inv * w[i];
+    float cs[PAIRS], sn[PAIRS];
+#pragma unroll
+    for (int j = 0; j < PAIRS; ++j) {
+        const int p = lane + 32 * j;
+        cs[j] = 1.0f;
+        sn[j] = 0.0f;
+        if (p < half && u_first < heads + kv_heads) sincosf((float)pos_i * inv_freq[p], &sn[j], &cs[j]);
     }
-    __syncwarp();
-    if ((is_q || is_k) && rotary_dim > 0) {
-        const int half = rotary_dim / 2;
-        const float pos = (float)positions[t];
-        for (int i = lane; i < half; i += 32) {
-            const float angle = pos * inv_freq[i];
-            float s, c;
-            sincosf(angle, &s, &c);
-            const float a = v[i], b = v[i + half];
-            v[i] = a * c - b * s;
-            v[i + half] = a * s + b * c;
+
+    for (int u = u_first; u < u_last; ++u) {
+        if (u + 1 < u_last) load_unit(u + 1, nxt);
+        const bool is_q = u < heads;
+        const bool is_k = !is_q && u < heads + kv_heads;
+        AT* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * heads + u) * head_dim;
+        } else {
+            const int h = is_k ? u - heads : u - heads - kv_heads;
+            dst = (is_k ? k_cache : v_cache) + (cache_row * kv_heads + h) * head_dim;
         }
-        __syncwarp();
-    }
-    AT* dst;
-    if (is_q) {
-        dst = q_out + (size_t)t * heads * head_dim + (size_t)u * head_dim;
-    } else {
-        const int pos = positions[t];
-        const int page = block_table[(size_t)seq_of_token[t] * table_width + pos / page_size];
-        const size_t row = (size_t)page * page_size + pos % page_size;
-        const int h = is_k ? u - heads : u - heads - kv_heads;
-        dst = (is_k ? k_cache : v_cache) + (row * kv_heads + h) * head_dim;
-    }
-    if (sizeof(AT) == 2 && (head_dim & 1) == 0) {
-        __nv_bfloat162* dst2 = reinterpret_cast<__nv_bfloat162*>(dst);
-        for (int i = lane; i < head_dim / 2; i += 32) dst2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    } else {
-        for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<AT>(v[i]);
+        if (is_q || is_k) {
+            const float* w = is_q ? q_w : k_w;
+            float ss = 0.0f;  // summed in the order pairs, then tail, whatever HD_MAX is
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) ss += cur.a[j] * cur.a[j] + cur.b[j] * cur.b[j];
+#pragma unroll
+            for (int j = 0; j < TAIL; ++j) ss += cur.tl[j] * cur.tl[j];
+            const float inv = rsqrtf(warp_sum(ss) / (float)head_dim + eps);
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int p = lane + 32 * j;
+                if (p < half) {
+                    const float x = cur.a[j] * inv * w[p], y = cur.b[j] * inv * w[p + half];
+                    dst[p] = from_f32<AT>(x * cs[j] - y * sn[j]);
+                    dst[p + half] = from_f32<AT>(x * sn[j] + y * cs[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < TAIL; ++j) {
+                const int e = rotary_dim + lane + 32 * j;
+                if (e < head_dim) dst[e] = from_f32<AT>(cur.tl[j] * inv * w[e]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int p = lane + 32 * j;
+                if (p < half) {
+                    dst[p] = from_f32<AT>(cur.a[j]);
+                    dst[p + half] = from_f32<AT>(cur.b[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < TAIL; ++j) {
+                const int e = rotary_dim + lane + 32 * j;
+                if (e < head_dim) dst[e] = from_f32<AT>(cur.tl[j]);
+            }
+        }
+        cur = nxt;
     }
 }
 
@@ -177,20 +222,32 @@ SHISO_API int shiso_qk_norm_rope_store(const void* qkv, int act_dtype, const flo
     if (head_dim <= 0 || head_dim > MAX_HEAD_DIM || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
         return SHISO_ERR_SHAPE;
     if (rotary_dim > 0 && !inv_freq) return SHISO_ERR_SHAPE;
-    const long long units = (long long)tokens * (heads + 2 * kv_heads);
-    const unsigned blocks = ceil_div_u(units, WARPS);
-    if (act_dtype == SHISO_F32)
-        launch_kernel(qk_norm_rope_store_kernel<float>, blocks, WARPS * 32, 0, stream, 
-            (const float*)qkv, q_w, k_w, inv_freq, positions, seq_of_token, block_table, table_width,
-            (float*)k_cache, (float*)v_cache, (float*)q_out, tokens, heads, kv_heads, head_dim, rotary_dim,
-            page_size, eps, store);
-    else if (act_dtype == SHISO_BF16)
-        launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
-            (const __nv_bfloat16*)qkv, q_w, k_w, inv_freq, positions, seq_of_token, block_table, table_width,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (__nv_bfloat16*)q_out, tokens, heads, kv_heads,
-            head_dim, rotary_dim, page_size, eps, store);
-    else
+    // Few units: one per warp, for the shortest chain.  Many: up to eight per warp, which share
+    // the angle's sine and cosine.
+    const int units = heads + 2 * kv_heads;
+    const long long all_units = (long long)tokens * units;
+    int per_warp = (int)((all_units + 16383) / 16384);
+    per_warp = per_warp < 1 ? 1 : (per_warp > 8 ? 8 : per_warp);
+    const unsigned blocks = ceil_div_u((long long)tokens * ((units + per_warp - 1) / per_warp), WARPS);
+    auto go = [&](auto kernel, auto* typed) {
+        using T = std::remove_pointer_t<decltype(typed)>;
+        launch_kernel(kernel, blocks, WARPS * 32, 0, stream, (const T*)qkv, q_w, k_w, inv_freq, positions, seq_of_token,
+                      block_table, table_width, (T*)k_cache, (T*)v_cache, (T*)q_out, tokens, heads, kv_heads, head_dim,
+                      rotary_dim, page_size, eps, store, per_warp);
+    };
+    if (act_dtype == SHISO_F32) {
+        float* tag = nullptr;
+        if (head_dim <= 64) go(qk_norm_rope_store_kernel<float, 64>, tag);
+        else if (head_dim <= 128) go(qk_norm_rope_store_kernel<float, 128>, tag);
+        else go(qk_norm_rope_store_kernel<float, 256>, tag);
+    } else if (act_dtype == SHISO_BF16) {
+        __nv_bfloat16* tag = nullptr;
+        if (head_dim <= 64) go(qk_norm_rope_store_kernel<__nv_bfloat16, 64>, tag);
+        else if (head_dim <= 128) go(qk_norm_rope_store_kernel<__nv_bfloat16, 128>, tag);
+        else go(qk_norm_rope_store_kernel<__nv_bfloat16, 256>, tag);
+    } else {
         return SHISO_ERR_DTYPE;
+    }
     return launch_status();
 }
 

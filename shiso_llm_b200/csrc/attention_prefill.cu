@@ -1,8 +1,9 @@
 // Paged GQA attention for steps that hold prompt portions (bfloat16): a tiled, online-softmax
 // kernel on the tensor cores.
 //
-// One CTA owns 64 consecutive query rows of one sequence and one query head; its four warps
-// own 16 rows each.  Key and value tiles of 64 positions are gathered from the paged cache
+// One CTA owns 64 consecutive query rows of one sequence and up to four query heads of one KV
+// group (HG of them): four warps per head, 16 rows per warp.  The heads of a group read the
+// same keys and values, so a tile brought to shared memory serves all of them.  Key and value tiles of 64 positions are gathered from the paged cache
 // through the block table into shared memory with cp.async (two stages), scores are
 // Q K^T with mma.sync m16n8k16 (bfloat16 in, float out), the softmax statistics are kept in
 // float per row, and P V accumulates in float registers.  A row at position p sees keys
@@ -25,7 +26,6 @@ namespace {
 
 constexpr int BM = 64;   // query rows per CTA
 constexpr int BN = 64;   // keys per tile
-constexpr int THREADS = 128;
 
 struct PrefillArgs {
     const __nv_bfloat16* q;        // [T, heads * D]
@@ -68,9 +68,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D>
-__global__ void __launch_bounds__(THREADS)
+template <int D, int HG>
+__global__ void __launch_bounds__(HG * 128)
 flash_prefill_kernel(PrefillArgs a) {
+    constexpr int THREADS = HG * 128;
     pdl_wait();
     constexpr int ROW_BYTES = D * 2 + 16;  // 16 bytes of padding: ldmatrix rows fall on distinct banks
     constexpr int CHUNKS = D / 8;          // 16-byte pieces per row
@@ -78,14 +79,16 @@ flash_prefill_kernel(PrefillArgs a) {
     constexpr int DTILES = D / 8;
 
     extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t* q_s = smem;                               // [BM][ROW_BYTES]
-    uint8_t* k_s = q_s + BM * ROW_BYTES;               // [2][BN][ROW_BYTES]
+    uint8_t* q_s = smem;                               // [HG][BM][ROW_BYTES]
+    uint8_t* k_s = q_s + HG * BM * ROW_BYTES;          // [2][BN][ROW_BYTES]
     uint8_t* v_s = k_s + 2 * BN * ROW_BYTES;           // [2][BN][ROW_BYTES]
     __shared__ int tile_seq, tile_row0;
 
     // ---- which (sequence, tile) is this CTA?
     if (threadIdx.x == 0) {
-        int left = blockIdx.x, found = -1, row0 = 0;
+        // the last tiles of a portion have the most keys: they take the first CTAs, so that the
+        // grid's tail is made of short ones
+        int left = gridDim.x - 1 - blockIdx.x, found = -1, row0 = 0;
         for (int s = 0; s < a.num_seqs; ++s) {
             const int tiles = (a.q_start[s + 1] - a.q_start[s] + BM - 1) / BM;
             if (left < tiles) {
@@ -106,20 +109,29 @@ flash_prefill_kernel(PrefillArgs a) {
     const int rows = min(BM, a.q_start[seq + 1] - first_token);
     const int first_pos = a.start_pos[seq] + row0;
     const int last_pos = first_pos + rows - 1;
-    const int head = blockIdx.y;
-    const int kv_head = head / (a.heads / a.kv_heads);
+    const int group = a.heads / a.kv_heads;
+    const int chunks = (group + HG - 1) / HG;          // head chunks per KV head
+    const int kv_head = blockIdx.y / chunks;
+    const int head0 = kv_head * group + (blockIdx.y % chunks) * HG;
+    const int heads_here = min(HG, kv_head * group + group - head0);
     const int* table = a.block_table + (size_t)seq * a.width;
     const int key_lo = a.window > 0 ? max(0, first_pos + 1 - a.window) : 0;  // the smallest key any row sees
     const int tile_first = key_lo / BN, tile_last = last_pos / BN;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
+    const int head_sel = warp >> 2;            // which of the CTA's heads this warp serves
+    const int row_block = (warp & 3) * 16;     // its 16 query rows inside the tile
+    const int head = head0 + head_sel;
+    const bool active = head_sel < heads_here;  // warp-uniform
 
-    // ---- Q tile -> shared (rows past the portion are zero)
-    for (int c = tid; c < BM * CHUNKS; c += THREADS) {
-        const int r = c / CHUNKS, ch = c % CHUNKS;
-        const __nv_bfloat16* src = a.q + ((size_t)(first_token + min(r, rows - 1)) * a.heads + head) * D + ch * 8;
-        cp_async16(q_s + r * ROW_BYTES + ch * 16, src, r < rows);
+    // ---- Q tiles -> shared (rows past the portion, and heads past the group, are zero)
+    for (int c = tid; c < HG * BM * CHUNKS; c += THREADS) {
+        const int hr = c / CHUNKS, ch = c % CHUNKS;
+        const int hs = hr / BM, r = hr % BM;
+        const bool valid = r < rows && hs < heads_here;
+        const __nv_bfloat16* src = a.q + ((size_t)(first_token + min(r, rows - 1)) * a.heads + head0 + min(hs, heads_here - 1)) * D + ch * 8;
+        cp_async16(q_s + hr * ROW_BYTES + ch * 16, src, valid);
     }
     auto load_kv = [&](int tile, int stage) {
         uint8_t* kd = k_s + stage * BN * ROW_BYTES;
@@ -143,7 +155,7 @@ flash_prefill_kernel(PrefillArgs a) {
     for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
     uint32_t q_frag[KSTEPS][4];
-    const int my_pos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
+    const int my_pos[2] = {first_pos + row_block + g, first_pos + row_block + g + 8};
 
     for (int tile = tile_first; tile <= tile_last; ++tile) {
         const int stage = (tile - tile_first) & 1;
@@ -154,7 +166,7 @@ flash_prefill_kernel(PrefillArgs a) {
         if (tile == tile_first) {
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; ++kk) {
-                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int r = head_sel * BM + row_block + (lane & 7) + ((lane >> 3) & 1) * 8;
                 const int col = kk * 16 + (lane >> 4) * 8;
                 ldmatrix_x4(smem_addr(q_s + r * ROW_BYTES + col * 2), q_frag[kk][0], q_frag[kk][1], q_frag[kk][2], q_frag[kk][3]);
             }
@@ -162,6 +174,11 @@ flash_prefill_kernel(PrefillArgs a) {
         const uint8_t* kt = k_s + stage * BN * ROW_BYTES;
         const uint8_t* vt = v_s + stage * BN * ROW_BYTES;
 
+        // a warp whose rows all lie before this tile's first key, or whose windows all start after
+        // its last, has nothing to add: every score would be masked
+        const bool warp_has_keys = active && tile * BN <= first_pos + row_block + 15 &&
+                                   (a.window <= 0 || tile * BN + BN - 1 > first_pos + row_block - a.window);
+        if (warp_has_keys) {
         // ---- S = Q K^T for this warp's 16 rows x 64 keys
         float s_acc[BN / 8][4];
 #pragma unroll
@@ -182,16 +199,31 @@ flash_prefill_kernel(PrefillArgs a) {
         // ---- mask, online softmax (base 2)
         const int key0 = tile * BN;
         float tile_max[2] = {-INFINITY, -INFINITY};
+        // every key of the tile is seen by every row of this warp: no mask to evaluate
+        const bool all_seen = key0 + BN - 1 <= first_pos + row_block &&
+                              (a.window <= 0 || key0 > first_pos + row_block + 15 - a.window);
+        if (all_seen) {
 #pragma unroll
-        for (int j = 0; j < BN / 8; ++j) {
+            for (int j = 0; j < BN / 8; ++j) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = key0 + j * 8 + t4 * 2 + (e & 1);
-                const int pos = my_pos[e >> 1];
-                const bool seen = key <= pos && (a.window <= 0 || key > pos - a.window);
-                const float v = seen ? s_acc[j][e] * a.scale_log2 : -INFINITY;
-                s_acc[j][e] = v;
-                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                for (int e = 0; e < 4; ++e) {
+                    const float v = s_acc[j][e] * a.scale_log2;
+                    s_acc[j][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + t4 * 2 + (e & 1);
+                    const int pos = my_pos[e >> 1];
+                    const bool seen = key <= pos && (a.window <= 0 || key > pos - a.window);
+                    const float v = seen ? s_acc[j][e] * a.scale_log2 : -INFINITY;
+                    s_acc[j][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
             }
         }
         float correction[2], use_max[2];
@@ -241,6 +273,7 @@ flash_prefill_kernel(PrefillArgs a) {
                 mma_bf16(o_acc[dn + 1], p_frag[ks], b2, b3);
             }
         }
+        }  // warp_has_keys
         __syncthreads();  // the stage is refilled by the next iteration's prefetch
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -256,8 +289,8 @@ flash_prefill_kernel(PrefillArgs a) {
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + g + r * 8;
-        if (row < rows) {
+        const int row = row_block + g + r * 8;
+        if (active && row < rows) {
             __nv_bfloat16* dst = a.out + ((size_t)(first_token + row) * a.heads + head) * D;
 #pragma unroll
             for (int i = 0; i < DTILES; ++i) {
@@ -268,10 +301,10 @@ flash_prefill_kernel(PrefillArgs a) {
     }
 }
 
-template <int D>
-int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
-    constexpr int SMEM = (BM + 4 * BN) * (D * 2 + 16);
-    auto kernel = flash_prefill_kernel<D>;
+template <int D, int HG>
+int launch_heads(const PrefillArgs& a, int tiles, cudaStream_t stream) {
+    constexpr int SMEM = (HG * BM + 4 * BN) * (D * 2 + 16);
+    auto kernel = flash_prefill_kernel<D, HG>;
     if (SMEM > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -280,9 +313,23 @@ int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
             configured = true;
         }
     }
-    dim3 grid(tiles, a.heads);
-    launch_kernel(kernel, grid, THREADS, SMEM, stream, a);
+    const int group = a.heads / a.kv_heads;
+    dim3 grid(tiles, a.kv_heads * ((group + HG - 1) / HG));
+    launch_kernel(kernel, grid, HG * 128, SMEM, stream, a);
     return launch_status();
+}
+
+// heads of a KV group served by one CTA: as many as the group has, up to 4 (2 for wide heads,
+// whose output accumulators need the registers)
+template <int D>
+int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
+    const int group = a.heads / a.kv_heads;
+    constexpr int MAX_HG = D <= 64 ? 4 : 2;
+    if constexpr (MAX_HG >= 4) {
+        if (group >= 3) return launch_heads<D, 4>(a, tiles, stream);
+    }
+    if (group >= 2) return launch_heads<D, 2>(a, tiles, stream);
+    return launch_heads<D, 1>(a, tiles, stream);
 }
 
 }  // namespace

@@ -18,26 +18,35 @@ bool shiso_pdl_enabled() {
 
 // --------------------------------------------------------------------------- embedding
 
+// A row's token id comes from `ids`, or - where feed_index[t] >= 0 - from fed_tokens at that
+// index: the token a sampling kernel picked on the device a step earlier, which the host has
+// not seen yet.
 template <typename WT>
-__global__ void embed_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ feed_index,
+                             const int* fed_tokens, const WT* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab) {
     pdl_begin();
     const int t = blockIdx.x;
     int id = ids[t];
+    if (feed_index) {
+        const int from = feed_index[t];
+        if (from >= 0) id = fed_tokens[from];
+    }
     const bool valid = id >= 0 && id < vocab;  // the host refuses such ids; never read outside
     const WT* row = table + (size_t)(valid ? id : 0) * hidden;
     float* dst = out + (size_t)t * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? to_f32(row[i]) : 0.0f;
 }
 
-SHISO_API int shiso_embed(const int* ids, const void* table, int table_dtype, float* out,
-                          int tokens, int hidden, int vocab, cudaStream_t stream) {
+SHISO_API int shiso_embed(const int* ids, const int* feed_index, const int* fed_tokens, const void* table,
+                          int table_dtype, float* out, int tokens, int hidden, int vocab, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
+    if ((feed_index == nullptr) != (fed_tokens == nullptr)) return SHISO_ERR_SHAPE;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == SHISO_F32)
-        launch_kernel(embed_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab);
+        launch_kernel(embed_kernel<float>, tokens, threads, 0, stream, ids, feed_index, fed_tokens, (const float*)table, out, hidden, vocab);
     else if (table_dtype == SHISO_BF16)
-        launch_kernel(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        launch_kernel(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, feed_index, fed_tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();

@@ -187,21 +187,40 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int token = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TILE_N;
+            // Four TMEM loads are in flight before the one wait: 64 columns a round (32 gate and
+            // 32 up for the pair), so the round trip to TMEM is paid 4 times a tile, not 16.
+            constexpr int ROUND = GLU ? 32 : 64;
 #pragma unroll 1
-            for (int c = 0; c < out_per_tile; c += 16) {
-                float v[16];
-                tmem_ld16(taddr + c, v);
+            for (int c = 0; c < out_per_tile; c += ROUND) {
+                uint32_t r[4][16];
                 if (GLU) {
-                    float up[16];
-                    tmem_ld16(taddr + TILE_N / 2 + c, up);
+                    tmem_ld16_issue(taddr + c, r[0]);
+                    tmem_ld16_issue(taddr + c + 16, r[1]);
+                    tmem_ld16_issue(taddr + TILE_N / 2 + c, r[2]);
+                    tmem_ld16_issue(taddr + TILE_N / 2 + c + 16, r[3]);
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * up[i];
-                } else if (p.bias) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (n0 + c + i < p.N) v[i] += p.bias[n0 + c + i];
+                    for (int q = 0; q < 4; ++q) tmem_ld16_issue(taddr + c + 16 * q, r[q]);
                 }
-                if (token < p.T && n0 + c < p.N) store16(p, token, n0 + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tmem_ld_pin(r[q]);
+#pragma unroll
+                for (int q = 0; q < (GLU ? 2 : 4); ++q) {
+                    float v[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[q][i]);
+                    const int feature = n0 + c + 16 * q;
+                    if (GLU) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * __uint_as_float(r[q + 2][i]);
+                    } else if (p.bias) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (feature + i < p.N) v[i] += p.bias[feature + i];
+                    }
+                    if (token < p.T && feature < p.N) store16(p, token, feature, v);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

@@ -111,6 +111,110 @@ __global__ void short_conv_out_vec_kernel(const __nv_bfloat16* proj, const float
     *reinterpret_cast<uint4*>(y + (size_t)t * hidden + ch) = oraw;
 }
 
+// For long portions: a thread owns eight channels and walks RUN consecutive rows with the
+// window of gated inputs in registers, so every row of b, c and x is read once (the kernel
+// above reads b and x once per tap) and the weights once per thread.  When the walk crosses
+// into another sequence, or starts, the window is refilled from the rows or the state behind
+// it.  Per channel the sum is the same fused multiply-adds in the same order as above.
+constexpr int RUN = 16;
+
+__device__ __forceinline__ void gated8(const uint4& braw, const uint4& xraw, float* u) {
+    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&braw);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xraw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 b = __bfloat1622float2(bp[e]), x = __bfloat1622float2(xp[e]);
+        u[2 * e] = b.x * x.x;
+        u[2 * e + 1] = b.y * x.y;
+    }
+}
+
+template <int TAPS>
+__global__ void __launch_bounds__(128)
+short_conv_run_kernel(const __nv_bfloat16* proj, const float* __restrict__ w, const float* __restrict__ bias,
+                      const float* state, long long slot_stride, const int* __restrict__ seq_of_token,
+                      const int* __restrict__ q_start, const int* __restrict__ slots, __nv_bfloat16* y,
+                      int hidden, int tokens) {
+    pdl_begin();
+    const int ch = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (ch >= hidden) return;
+    const int t0 = blockIdx.x * RUN, t1 = min(tokens, t0 + RUN);
+    float wr[TAPS][8], br[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[j][e] = w[(size_t)(ch + e) * TAPS + j];
+        br[e] = bias ? bias[ch + e] : 0.0f;
+    }
+    float win[TAPS - 1][8];
+    int cur_seq = -1;
+    constexpr int AHEAD = 4;  // rows whose loads are in flight together
+    for (int tb = t0; tb < t1; tb += AHEAD) {
+        uint4 braw[AHEAD], craw[AHEAD], xraw[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const int t = min(tb + i, t1 - 1);
+            const __nv_bfloat16* row = proj + (size_t)t * 3 * hidden + ch;
+            braw[i] = *reinterpret_cast<const uint4*>(row);
+            craw[i] = *reinterpret_cast<const uint4*>(row + hidden);
+            xraw[i] = *reinterpret_cast<const uint4*>(row + 2 * hidden);
+        }
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const int t = tb + i;
+            if (t >= t1) break;
+            const int s = seq_of_token[t];
+            if (s != cur_seq) {
+                cur_seq = s;
+                const int first = q_start[s];
+                const float* state_row = state + (size_t)slots[s] * slot_stride;
+#pragma unroll
+                for (int j = 0; j < TAPS - 1; ++j) {
+                    const int rel = t - first - (TAPS - 1) + j;
+                    if (rel >= 0) {
+                        const __nv_bfloat16* row = proj + (size_t)(first + rel) * 3 * hidden + ch;
+                        gated8(*reinterpret_cast<const uint4*>(row), *reinterpret_cast<const uint4*>(row + 2 * hidden), win[j]);
+                    } else {
+                        const float* sr = state_row + (size_t)(TAPS - 1 + rel) * hidden + ch;
+                        const float4 lo = *reinterpret_cast<const float4*>(sr), hi = *reinterpret_cast<const float4*>(sr + 4);
+                        win[j][0] = lo.x; win[j][1] = lo.y; win[j][2] = lo.z; win[j][3] = lo.w;
+                        win[j][4] = hi.x; win[j][5] = hi.y; win[j][6] = hi.z; win[j][7] = hi.w;
+                    }
+                }
+            }
+            float u[8], acc[8];
+            gated8(braw[i], xraw[i], u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                acc[e] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < TAPS - 1; ++j) acc[e] = fmaf(wr[j][e], win[j][e], acc[e]);
+                acc[e] = fmaf(wr[TAPS - 1][e], u[e], acc[e]);
+            }
+            const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&craw[i]);
+            uint4 oraw;
+            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 c = __bfloat1622float2(cp[e]);
+                float a0 = acc[2 * e], a1 = acc[2 * e + 1];
+                if (bias) {
+                    a0 += br[2 * e];
+                    a1 += br[2 * e + 1];
+                }
+                op[e] = __floats2bfloat162_rn(c.x * a0, c.y * a1);
+            }
+            *reinterpret_cast<uint4*>(y + (size_t)t * hidden + ch) = oraw;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+#pragma unroll
+                for (int j = 0; j < TAPS - 2; ++j) win[j][e] = win[j + 1][e];
+                win[TAPS - 2][e] = u[e];
+            }
+        }
+    }
+}
+
 // New state = the last taps-1 values of (old state ++ this step's u).  One thread owns a
 // (sequence, channel) pair and reads everything it needs before it writes.
 template <typename AT>
@@ -217,7 +321,17 @@ SHISO_API int shiso_short_conv(const void* proj, int act_dtype, const float* w, 
     } else if (act_dtype == SHISO_BF16) {
         const bool vec = hidden % 8 == 0 && slot_stride % 4 == 0 &&
                          (((uintptr_t)proj | (uintptr_t)y | (uintptr_t)state) & 15) == 0;
-        if (vec) {
+        const bool runs = vec && tokens >= 512 && taps >= 2 && taps <= 4;
+        if (runs) {
+            dim3 grid_run(ceil_div_u(tokens, RUN), ceil_div_u(hidden / 8, threads));
+            auto launch_run = [&](auto kernel) {
+                launch_kernel(kernel, grid_run, threads, 0, stream, (const __nv_bfloat16*)proj, w, bias,
+                              (const float*)state, slot_stride, seq_of_token, q_start, slots, (__nv_bfloat16*)y, hidden, tokens);
+            };
+            if (taps == 2) launch_run(short_conv_run_kernel<2>);
+            else if (taps == 3) launch_run(short_conv_run_kernel<3>);
+            else launch_run(short_conv_run_kernel<4>);
+        } else if (vec) {
             launch_kernel(short_conv_out_vec_kernel, dim3(tokens, ceil_div_u(hidden / 8, threads)), threads, 0, stream,
                           (const __nv_bfloat16*)proj, w, bias, (const float*)state, slot_stride, seq_of_token, q_start,
                           slots, (__nv_bfloat16*)y, hidden, taps);

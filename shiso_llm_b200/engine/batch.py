@@ -31,6 +31,10 @@ class StepEntry:
     request: object
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # The entry's one token is not known on the host: the device reads it from this index of the
+    # engine's ``fed_tokens`` buffer (where a sampler left it a step earlier); ``tokens`` then
+    # holds a placeholder.
+    feed: Optional[int] = None
 
 
 @dataclass
@@ -52,6 +56,8 @@ class StepMeta:
     max_context: int  # most positions any sequence can see after this step
     all_decode: bool  # every sequence brings exactly one token
     wants_every_row: bool = False  # want_rows is 0, 1, .. T-1: logits of all rows, in order
+    feed_index: Optional[torch.Tensor] = None  # [T] index into fed_tokens, or -1: the id in token_ids stands
+    fed_tokens: Optional[torch.Tensor] = None  # the engine's buffer of tokens picked on the device
     h_q_start: list = field(default_factory=list)
     h_start_pos: list = field(default_factory=list)
     h_state_slots: list = field(default_factory=list)
@@ -70,7 +76,8 @@ class MetaLayout:
         self.token_ids = 0
         self.positions = t
         self.seq_of_token = 2 * t
-        self.q_start = 3 * t
+        self.feed_index = 3 * t
+        self.q_start = 4 * t
         self.start_pos = self.q_start + _align(num_seqs + 1)
         self.state_slots = self.start_pos + s
         self.want_rows = self.state_slots + s
@@ -97,6 +104,7 @@ class StepBuilder:
         self._turn = 0
         self.device_block = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._arange = np.arange(max_seqs + 2, dtype=np.int32)
+        self.fed_tokens: Optional[torch.Tensor] = None  # set by the engine; None: steps carry no feed arrays
 
     def _iota(self, n: int) -> np.ndarray:
         return self._arange[:n]
@@ -137,6 +145,7 @@ class StepBuilder:
             host[lay.token_ids : lay.token_ids + num_seqs] = [e.tokens[0] for e in entries]
             host[lay.positions : lay.positions + num_seqs] = starts
             host[lay.seq_of_token : lay.seq_of_token + num_seqs] = rows[:num_seqs]
+            host[lay.feed_index : lay.feed_index + num_seqs] = [-1 if e.feed is None else e.feed for e in entries]
             want_at = lay.want_rows
             every_row = num_wanted == num_seqs and all(len(e.want) == 1 and e.want[0] == 0 for e in entries)
             if every_row:
@@ -158,6 +167,11 @@ class StepBuilder:
             host[lay.token_ids + a : lay.token_ids + b] = e.tokens
             host[lay.positions + a : lay.positions + b] = np.arange(starts[i], starts[i] + lens[i], dtype=np.int32)
             host[lay.seq_of_token + a : lay.seq_of_token + b] = i
+            host[lay.feed_index + a : lay.feed_index + b] = -1
+            if e.feed is not None:
+                if lens[i] != 1:
+                    raise ValueError(f"request {e.request!r}: only a single token can be fed from the device")
+                host[lay.feed_index + a] = e.feed
             for w in e.want:
                 if not 0 <= w < lens[i]:
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {lens[i]} tokens")
@@ -196,6 +210,8 @@ class StepBuilder:
             max_context=max(s + n for s, n in zip(starts, lens)),
             all_decode=all(n == 1 for n in lens),
             wants_every_row=single and every_row,
+            feed_index=part(lay.feed_index, num_tokens) if self.fed_tokens is not None else None,
+            fed_tokens=self.fed_tokens,
             h_q_start=q_start.tolist(),
             h_start_pos=list(starts),
             h_state_slots=slots,

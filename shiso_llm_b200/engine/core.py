@@ -87,6 +87,10 @@ class Engine:
         self.builder = StepBuilder(
             cache, self.device, options.max_num_batched_tokens, options.max_num_seqs
         )
+        # Tokens picked on the device from the last step's logits, one per sampling row; an entry
+        # with ``feed = j`` takes its token from index j without the host having seen it.
+        self.fed_tokens = torch.zeros(max(1, options.max_num_seqs), dtype=torch.int32, device=self.device)
+        self.builder.fed_tokens = self.fed_tokens
         self.steps_run = 0
         self.graphs = None
         if options.cuda_graphs and self.device.type == "cuda" and model.graph_safe:
@@ -95,6 +99,7 @@ class Engine:
             decode_builder = StepBuilder(
                 cache, self.device, options.max_num_seqs, options.max_num_seqs, fixed_table_width=cache.max_blocks
             )
+            decode_builder.fed_tokens = self.fed_tokens
             self.graphs = DecodeGraphs(model, cache, decode_builder)
 
     def warm_up(self) -> None:
@@ -167,6 +172,8 @@ class Engine:
                 raise ValueError(f"request {e.request!r}: a step brings at least one token")
             if min(e.tokens) < 0 or max(e.tokens) >= self.vocab_size:
                 raise ValueError(f"request {e.request!r}: a token id lies outside the vocabulary of {self.vocab_size}")
+            if e.feed is not None and (len(e.tokens) != 1 or not 0 <= e.feed < self.fed_tokens.shape[0]):
+                raise ValueError(f"request {e.request!r}: a fed token is one token from index 0..{self.fed_tokens.shape[0] - 1}")
         # Admission check for the whole step before anything is claimed.
         self._check_room(entries)
         starts = []

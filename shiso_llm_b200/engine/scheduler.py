@@ -21,6 +21,14 @@ One decision per step (``plan``), pure host bookkeeping over the cache manager's
    never evicted there, scheduler/config.rs:276-283).  A request that cannot get a page
    although nothing else is left to preempt ends with an error in both modes.
 
+A step's bookkeeping comes in two halves, so that the host need not wait for a step's tokens
+before it plans the next one.  ``launched(plan)`` counts the step's tokens as computed and
+puts a placeholder where each sampled token will go; a request that stands on a placeholder
+can be planned again (its decode row then takes the token on the device, ``PlannedEntry.feed``);
+one whose length budget the placeholder fills stops being planned (state ``draining``).
+``arrived(plan, tokens)`` puts the values in: a stop token ends the request there, and what a
+later step computed for it by then is dropped.  ``step_done`` is both at once.
+
 Finishing (crates/shiso-runtime/src/scheduler/lifecycle.rs:1136-1208): a stop token ends the
 request with reason ``stop`` (the token is counted, not emitted); ``max_new_tokens`` or the
 context limit ends it with ``length``; ``abort`` ends it at once.  The budget at admission is
@@ -36,7 +44,8 @@ from typing import Optional, Sequence
 
 from ..sampling.params import SamplingParams
 
-WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+WAITING, RUNNING, DRAINING, FINISHED = "waiting", "running", "draining", "finished"
+PENDING = -1  # stands in ``Request.output`` for a token that was sampled but has not reached the host
 
 
 @dataclass
@@ -70,6 +79,7 @@ class Request:
     error: Optional[str] = None
     preemptions: int = 0
     arrival: int = 0
+    pending_row: Optional[int] = None  # which of the last step's sampling rows holds its pending token
 
     @property
     def tokens(self) -> list:
@@ -99,6 +109,8 @@ class PlannedEntry:
     start: int  # index of the first token in request.tokens
     count: int
     samples: bool  # the portion reaches the request's last token: its logits are wanted
+    feed: Optional[int] = None  # the one token is pending: the device takes it from this sampling row of the last step
+    output_index: int = -1  # set by ``launched``: where in request.output the sampled token goes
 
 
 @dataclass
@@ -214,12 +226,14 @@ class Scheduler:
             if req.state != RUNNING:
                 continue
             claim(need)
-            plan.entries.append(PlannedEntry(req, req.computed, 1, True))
+            feed = req.pending_row if req.output[-1] == PENDING else None
+            plan.entries.append(PlannedEntry(req, req.computed, 1, True, feed))
             budget -= 1
 
         # 2. prompt portions of running requests, oldest first
         for req in self.running:
-            if req.decoding or req.remaining <= 0 or budget <= 0 or any(e.request is req for e in plan.entries):
+            if (req.state != RUNNING or req.decoding or req.remaining <= 0 or budget <= 0
+                    or any(e.request is req for e in plan.entries)):
                 continue
             count = self._portion(req, min(req.remaining, budget, chunk), free)
             if count <= 0:
@@ -247,13 +261,15 @@ class Scheduler:
             plan.entries.append(PlannedEntry(req, req.computed, count, count == req.remaining))
             budget -= count
 
-        if not plan.entries and self.running and not plan.preempted and not plan.failed:
+        residents = [r for r in self.running if r.state == RUNNING]
+        draining = len(residents) < len(self.running)  # those give their pages back by themselves
+        if not plan.entries and residents and not draining and not plan.preempted and not plan.failed:
             # Residents but no work: nothing can ever free a page for them.  Fail the
             # youngest rather than spin (crates/shiso-runtime/src/scheduler/mod.rs:2148-2159).
-            if len(self.running) > 1 and cfg.on_exhaustion == "preempt":
-                self._preempt(self.running[-1], plan)
+            if len(residents) > 1 and cfg.on_exhaustion == "preempt":
+                self._preempt(residents[-1], plan)
             else:
-                self._fail(self.running[-1], "kv pool: no request can make progress", plan)
+                self._fail(residents[-1], "kv pool: no request can make progress", plan)
         return plan
 
     def _portion(self, req: Request, want: int, free) -> int:
@@ -279,7 +295,7 @@ class Scheduler:
         if self.cache.has(req.id):
             self.cache.release(req.id)
         self.running.remove(req)
-        req.state, req.computed = WAITING, 0
+        req.state, req.computed, req.pending_row = WAITING, 0, None
         req.preemptions += 1
         self.waiting.appendleft(req)
         plan.preempted.append(req)
@@ -297,18 +313,19 @@ class Scheduler:
             self.cache.release(req.id)
         if req in self.running:
             self.running.remove(req)
+        if req in self.waiting:
+            self.waiting.remove(req)
         req.state, req.finish_reason = FINISHED, reason
         self.finished.append(req)
         self.stats["finished"] += 1
 
     # ------------------------------------------------------------------ after the step
 
-    def step_done(self, plan: StepPlan, sampled: Sequence[int]) -> list:
-        """``sampled[i]`` is the token picked for the i-th entry of the plan that samples.
-        Returns the requests that finished with this step."""
-        done = []
-        at = 0
+    def launched(self, plan: StepPlan) -> None:
+        """The step is on its way: its tokens count as computed, and a placeholder stands where
+        each sampled token will go."""
         self.stats["steps"] += 1
+        row = 0
         for entry in plan.entries:
             req = entry.request
             req.computed += entry.count
@@ -318,19 +335,48 @@ class Scheduler:
                 self.stats["prefill_tokens"] += entry.count
             if not entry.samples:
                 continue
+            if req.state == RUNNING:
+                assert req.remaining == 0, "a request is either reading its prompt or standing on a sampled token"
+                entry.output_index = len(req.output)
+                req.output.append(PENDING)
+                req.pending_row = row
+                if len(req.output) >= req.budget:
+                    req.state = DRAINING  # nothing more to compute; it ends when the token arrives
+            row += 1
+
+    def arrived(self, plan: StepPlan, sampled: Sequence[int]) -> list:
+        """``sampled[i]`` is the token picked for the i-th entry of the plan that samples.
+        Returns the requests that finished with it."""
+        done = []
+        at = 0
+        for entry in plan.entries:
+            if not entry.samples:
+                continue
             token = int(sampled[at])
             at += 1
-            if req.state != RUNNING:
+            req, idx = entry.request, entry.output_index
+            # a request that ended meanwhile (a stop token a step earlier, an abort, an error)
+            # has no use for the token; one that was preempted still takes it
+            if req.state == FINISHED or idx < 0 or idx >= len(req.output) or req.output[idx] != PENDING:
                 continue
-            assert req.remaining == 0, "a request is either reading its prompt or standing on a sampled token"
+            if idx == len(req.output) - 1:
+                req.pending_row = None
             if token in req.stop_ids:
+                extra = len(req.output) - idx - 1  # computed past the stop before it was known
+                del req.output[idx:]
+                req.computed -= extra
                 self._retire(req, "stop")
                 done.append(req)
                 continue
-            req.output.append(token)
-            if len(req.output) >= req.budget:
+            req.output[idx] = token
+            if req.state == DRAINING and idx == len(req.output) - 1:
                 self._retire(req, "length")
                 done.append(req)
         if at != len(sampled):
             raise ValueError(f"{len(sampled)} sampled tokens for {at} sampling entries")
         return done
+
+    def step_done(self, plan: StepPlan, sampled: Sequence[int]) -> list:
+        """Both halves at once, for a caller that waits for each step's tokens."""
+        self.launched(plan)
+        return self.arrived(plan, sampled)

@@ -19,7 +19,7 @@ F = c_float
 LL = c_longlong
 
 _SIGNATURES = {
-    "shiso_embed": [P, P, I, P, I, I, I, P],
+    "shiso_embed": [P, P, P, P, I, P, I, I, I, P],
     "shiso_gather_rows": [P, P, P, I, I, P],
     "shiso_rmsnorm": [P, P, P, P, P, I, I, I, F, P],
     "shiso_swiglu": [P, P, I, I, I, P],
@@ -27,6 +27,7 @@ _SIGNATURES = {
     "shiso_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_swiglu": [P, P, P, I, I, I, I, P],
     "shiso_gemm_tcgen05_prompt": [P, P, P, P, I, I, I, I, I, I, P],
+    "shiso_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
     "shiso_gemm_tcgen05_status": [],
     "shiso_gemm_skinny": [P, P, P, P, I, I, I, I, I, P],

@@ -79,12 +79,25 @@ def _done(status: int, what: str, launches: int = 1) -> None:
 # --------------------------------------------------------------------------- rows
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=None) -> torch.Tensor:
+    """Rows of ``table`` for ``ids``.  Where ``feed_index[t] >= 0`` the id is read on the device
+    from ``fed_tokens[feed_index[t]]`` instead (a token picked a step earlier that the host has
+    not seen)."""
     _check(ids, "ids", torch.int32, 1)
     _check(table, "embedding table", None, 2)
     tokens, (vocab, hidden) = ids.shape[0], table.shape
+    if (feed_index is None) != (fed_tokens is None):
+        raise KernelError("embed: feed_index and fed_tokens come together")
+    if feed_index is not None:
+        _check(feed_index, "feed_index", torch.int32, 1)
+        _check(fed_tokens, "fed_tokens", torch.int32, 1)
+        if feed_index.shape[0] != tokens:
+            raise KernelError(f"feed_index has {feed_index.shape[0]} entries for {tokens} rows")
     out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
-    _done(library().shiso_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), tokens, hidden, vocab, _stream()), "embed")
+    status = library().shiso_embed(
+        _ptr(ids), _ptr(feed_index), _ptr(fed_tokens), _ptr(table), _code(table), _ptr(out), tokens, hidden, vocab, _stream()
+    )
+    _done(status, "embed")
     return out
 
 
@@ -140,6 +153,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 _SM_COUNT = None
 SKINNY_MAX_TOKENS = 16  # up to here a product is weight streaming and takes the skinny kernel
 PROMPT_MIN_TOKENS = 128  # from here the persistent tensor-memory kernel (tokens as the MMA's M operand)
+PAIR_MIN_TOKENS = 512  # from here the same kernel on pairs of SMs (256-token tiles, half the operand traffic per SM)
 
 
 def _sm_count() -> int:
@@ -182,9 +196,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         _done(status, "linear (skinny)")
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
-        status = lib.shiso_gemm_tcgen05_prompt(
-            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
-        )
+        product = lib.shiso_gemm_tcgen05_pair if tokens >= PAIR_MIN_TOKENS else lib.shiso_gemm_tcgen05_prompt
+        status = product(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream())
         _done(status, "linear (tcgen05, persistent)")
         return out
     if both_bf16 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
@@ -228,7 +241,8 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
     ):
         out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
         if tokens >= PROMPT_MIN_TOKENS and (two_inter // 2) % 8 == 0:
-            status = lib.shiso_gemm_tcgen05_prompt(
+            product = lib.shiso_gemm_tcgen05_pair if tokens >= PAIR_MIN_TOKENS else lib.shiso_gemm_tcgen05_prompt
+            status = product(
                 _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter // 2, k, two_inter // 2,
                 _sm_count(), _stream(),
             )
@@ -412,10 +426,21 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
 # --------------------------------------------------------------------------- sampling
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def _picks(out, rows, device):
+    if out is None:
+        return torch.empty((rows,), dtype=torch.int32, device=device)
+    _check(out, "out", torch.int32, 1)
+    if out.shape[0] != rows:
+        raise KernelError(f"out has {out.shape[0]} entries for {rows} rows")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The index of each row's largest value (the smallest index among equals), int32, written
+    to ``out`` when one is given."""
     _check(logits, "logits", torch.float32, 2)
     rows, vocab = logits.shape
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    out = _picks(out, rows, logits.device)
     if vocab >= 8192:
         chunks = min(128, -(-vocab // 1024))
         scratch = torch.empty((2 * rows * chunks,), dtype=torch.float32, device=logits.device)
@@ -426,7 +451,7 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def sample(logits, temperature, top_k, top_p, min_p, keys, positions) -> torch.Tensor:
+def sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None) -> torch.Tensor:
     """Keyed sampling, one row per request: float32 ``temperature``/``top_p``/``min_p``,
     int32 ``top_k`` (0 = off) and ``positions``, int64 ``keys``, all of length rows."""
     _check(logits, "logits", torch.float32, 2)
@@ -439,7 +464,7 @@ def sample(logits, temperature, top_k, top_p, min_p, keys, positions) -> torch.T
         _check(t, name, dt, 1)
         if t.shape[0] != rows:
             raise KernelError(f"{name} has {t.shape[0]} entries for {rows} rows")
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    out = _picks(out, rows, logits.device)
     status = library().shiso_sample(
         _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(keys), _ptr(positions),
         _ptr(out), rows, logits.shape[1], _stream(),

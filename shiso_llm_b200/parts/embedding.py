@@ -32,7 +32,10 @@ class TokenEmbedding(Embedding):
         return self.weight
 
     def forward(self, step):
-        return self.env.ops.embed(step.token_ids, self.weight)
+        feed = getattr(step, "feed_index", None)
+        if feed is None:
+            return self.env.ops.embed(step.token_ids, self.weight)
+        return self.env.ops.embed(step.token_ids, self.weight, feed, step.fed_tokens)
 
 
 @HEADS.register("linear_head")

@@ -20,10 +20,15 @@ class DeviceSampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]) -> list[int]:
         """``logits[R, V]`` float32 on the device; ``positions[r]`` is the position the
         sampled token will occupy in its sequence.  Returns host ints."""
+        return self.sample_into(logits, params, positions, None).tolist()
+
+    def sample_into(self, logits, params: Sequence[SamplingParams], positions: Sequence[int], out) -> torch.Tensor:
+        """The same, leaving the picks on the device: in ``out`` (int32 ``[R]``) when one is
+        given.  Nothing waits for the device."""
         if logits.shape[0] != len(params):
             raise ValueError(f"{logits.shape[0]} rows of logits for {len(params)} requests")
         if all(p.greedy for p in params):
-            return self.ops.argmax(logits).tolist()
+            return self.ops.argmax(logits, out)
         clamped = [p.clamped() for p in params]
         host = torch.tensor(
             [[c[0] if not p.greedy else 0.0, c[2], c[3]] for c, p in zip(clamped, params)], dtype=torch.float32
@@ -41,8 +46,9 @@ class DeviceSampler:
             floats[:, 2].contiguous(),
             keys.to(dev, non_blocking=True),
             ints[:, 1].contiguous(),
+            out,
         )
-        return picks.tolist()
+        return picks
 
 
 def _as_signed(seed: int) -> int:

@@ -24,8 +24,12 @@ def require():
     return None
 
 
-def embed(ids, table):
-    return table[ids.long()].to(torch.float32)
+def embed(ids, table, feed_index=None, fed_tokens=None):
+    ids = ids.long()
+    if feed_index is not None:
+        fed = fed_tokens.long()[feed_index.long().clamp(min=0)]
+        ids = torch.where(feed_index.long() >= 0, fed, ids)
+    return table[ids].to(torch.float32)
 
 
 def gather_rows(x, rows):
@@ -169,6 +173,10 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
     return out.reshape(T, heads * d).to(q.dtype)
 
 
-def argmax(logits):
+def argmax(logits, out=None):
     """Lowest id among the maxima (crates/shiso-engine/src/sampling.rs:91-154)."""
-    return torch.argmax(logits, dim=-1).to(torch.int32)
+    picks = torch.argmax(logits, dim=-1).to(torch.int32)
+    if out is None:
+        return picks
+    out.copy_(picks)
+    return out

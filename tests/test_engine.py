@@ -20,12 +20,16 @@ from shiso_llm_b200.weights import random_tensors
 from tolerances import check_logits
 
 
-def _fake_sample(logits, temperature, top_k, top_p, min_p, keys, positions):
-    out = []
+def _fake_sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None):
+    picks = []
     for r in range(logits.shape[0]):
         p = SamplingParams(temperature=float(temperature[r]), top_k=int(top_k[r]), top_p=float(top_p[r]), min_p=float(min_p[r]))
-        out.append(host_sampling.keyed_sample(logits[r].numpy(), p, int(keys[r]), int(positions[r])))
-    return torch.tensor(out, dtype=torch.int32)
+        picks.append(host_sampling.keyed_sample(logits[r].numpy(), p, int(keys[r]), int(positions[r])))
+    picks = torch.tensor(picks, dtype=torch.int32)
+    if out is None:
+        return picks
+    out.copy_(picks)
+    return out
 
 
 fake_kernels.sample = _fake_sample
@@ -114,7 +118,7 @@ def test_sampling_is_the_same_under_every_cut_and_after_preemption(tmp_path, bac
     prompts = [helpers.random_prompt(n, doc["vocab_size"], 30 + n) for n in (1, 7, 40, 64, 100)]
     params = SamplingParams(temperature=0.8, seed=1, max_new_tokens=24, top_k=200, top_p=0.95)
     roomy = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, max_num_seqs=5, max_num_batched_tokens=256,
-                **backend_args(backend))
+                lookahead=False, **backend_args(backend))
     base = roomy.generate(prompts, params)
     assert all(len(o.token_ids) == 24 and o.preemptions == 0 for o in base)
     assert len({tuple(o.token_ids) for o in base}) == 5
@@ -135,6 +139,42 @@ def test_sampling_is_the_same_under_every_cut_and_after_preemption(tmp_path, bac
         if o.finish_reason == "length":
             assert o.token_ids == b.token_ids
     assert failing.engine.cache.free_pages() == [13]
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_lookahead_gives_the_same_tokens_and_stops(tmp_path, backend):
+    """Planning a step before the last one's tokens have reached the host changes no token: greedy
+    and sampled requests side by side, one of which ends on a stop token (found in the output of
+    a first run), through a pool small enough to preempt."""
+    doc, seed = helpers.TINY["A"]
+    helpers.make_folder(tmp_path, doc, seed)
+    prompts = [helpers.random_prompt(n, doc["vocab_size"], 60 + n) for n in (3, 21, 50, 9)]
+
+    def run(lookahead, stop, **kw):
+        params = [
+            SamplingParams(temperature=1.0, seed=6, top_k=50, max_new_tokens=20, stop_token_ids=stop),
+            SamplingParams(temperature=0.7, seed=5, max_new_tokens=12),
+            SamplingParams(temperature=0.0, max_new_tokens=1),
+            SamplingParams(temperature=0.0, max_new_tokens=20),
+        ]
+        llm = LLM(str(tmp_path), dtype="float32", ctx=128, page_size=16, max_num_seqs=4, max_num_batched_tokens=24,
+                  prefill_chunk=11, lookahead=lookahead, **kw, **backend_args(backend))
+        outs = llm.generate(prompts, params)
+        llm.engine.cache.check()
+        assert llm.engine.cache.slots.free_slots == 4 and not llm.has_unfinished()
+        return [(o.token_ids, o.finish_reason) for o in outs], llm
+
+    free_run, _ = run(False, ())
+    first = free_run[0][0]
+    cut = next((i for i in range(3, len(first)) if first[i] not in first[:i]), None)
+    assert cut is not None, "the tiny model repeats itself too early for this test"
+    stop = (first[cut],)  # a token the first request reaches after a few steps ends it from now on
+    waited, _ = run(False, stop)
+    ahead, llm = run(True, stop)
+    assert waited == ahead
+    assert ahead[0] == (first[:cut], "stop") and ahead[1:] == free_run[1:]
+    # one row was computed past the stop before the host knew of it
+    assert llm.scheduler.stats["decode_tokens"] == run(False, stop)[1].scheduler.stats["decode_tokens"] + 1
 
 
 @pytest.mark.parametrize("backend", BACKENDS)

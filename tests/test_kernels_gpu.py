@@ -121,6 +121,26 @@ def test_linear(shape, xw):
         close(got, ref.linear(x, w, out_dtype), out_dtype, f"linear {shape} {xw} -> {out_dtype}", rel32=1e-5)
 
 
+@pytest.mark.parametrize("shape", [(512, 256, 64), (700, 1000, 264), (1030, 2048, 2048), (2048, 6144, 512), (515, 520, 5632)])
+def test_linear_on_sm_pairs(shape):
+    """From 512 bfloat16 rows a product runs on pairs of SMs (one 256-row tile per pair, each CTA
+    loading half of both operands): row counts that leave the second CTA of the last pair with
+    few or no rows, feature counts that leave its weight half partly or wholly outside the
+    matrix, one and many k steps, more tiles than pairs; bfloat16 and float32 results, a bias."""
+    T, N, K = shape
+    x, w = rnd((T, K), torch.bfloat16, 140), rnd((N, K), torch.bfloat16, 141, 0.05)
+    bias = rnd((N,), torch.float32, 142)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = ops().linear(x.cuda(), w.cuda(), out_dtype)
+        ops().check_kernel_status()
+        close(got, ref.linear(x, w, out_dtype), out_dtype, f"pair linear {shape} -> {out_dtype}", rel32=1e-5)
+    got = ops().linear(x.cuda(), w.cuda(), torch.float32, bias.cuda())
+    close(got, ref.linear(x, w, torch.float32, bias), torch.float32, f"pair linear {shape} with bias", rel32=1e-5)
+    # the rows of a long step are those of a short one (other kernel, same sums up to rounding)
+    short = ops().linear(x[:130].contiguous().cuda(), w.cuda(), torch.float32, bias.cuda())
+    close(got[:130], short, torch.float32, "pair against single-SM kernel", rel32=1e-5)
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     x, w = rnd((70, 200), torch.float32, 8), rnd((150, 200), torch.float32, 9)
     full = ops().linear(x.cuda(), w.cuda(), torch.float32)
@@ -151,6 +171,33 @@ def test_short_conv(dtype, taps, hidden, bias):
     untouched[cpu.state_slots.long()] = False
     assert torch.equal(buf_gpu.cpu()[untouched], buf[untouched]), "slots of other requests must not change"
     assert torch.equal(buf_gpu.cpu()[:, :50], buf[:, :50]) and torch.equal(buf_gpu.cpu()[:, -9:], buf[:, -9:])
+
+
+@pytest.mark.parametrize("taps,hidden,bias", [(3, 304, False), (4, 96, True), (2, 136, True), (5, 64, True)])
+def test_short_conv_long_portions(taps, hidden, bias):
+    """Steps of 512 rows and more in bfloat16 walk runs of rows with the window in registers:
+    sequences that start and end inside a run, one with history in its state, single rows, and
+    a tap count the run kernel leaves to the per-row kernel.  Both give the same bits."""
+    q_lens, starts = [7, 300, 1, 40, 250, 1, 21], [0, 5, 9, 0, 64, 3, 0]
+    cpu, gpu, _ = make_step(q_lens, starts, 16, 64, 130, num_slots=9)
+    T = cpu.num_tokens
+    assert T >= 512
+    proj = rnd((T, 3 * hidden), torch.bfloat16, 131)
+    w = rnd((hidden, taps), torch.float32, 132)
+    b = rnd((hidden,), torch.float32, 133) if bias else None
+    start = rnd((9, taps - 1, hidden), torch.float32, 134)
+    s_ref, s_gpu = start.clone(), start.clone().cuda()
+    want = ref.short_conv(proj, w, b, s_ref, cpu)
+    got = ops().short_conv(proj.cuda(), w.cuda(), b.cuda() if bias else None, s_gpu, gpu)
+    close(got, want, torch.bfloat16, "short conv over runs")
+    assert torch.allclose(s_gpu.cpu(), s_ref, rtol=0, atol=1e-7)
+    # the same rows through the per-row kernel (a step of fewer than 512 rows): identical bits
+    cut = q_lens[0] + q_lens[1]
+    cpu2, gpu2, _ = make_step(q_lens[:2], starts[:2], 16, 64, 130, num_slots=9)
+    gpu2.state_slots = gpu.state_slots[:2]
+    s_two = start.clone().cuda()
+    two = ops().short_conv(proj[:cut].contiguous().cuda(), w.cuda(), b.cuda() if bias else None, s_two, gpu2)
+    assert torch.equal(two, got[:cut])
 
 
 def test_short_conv_portions_match_whole():
@@ -317,7 +364,8 @@ def test_decode_attention_split_keys(case):
         close(got, general, dtype, "decode kernel against the general kernel")
 
 
-@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (8, 2, 64, 16), (6, 3, 48, 8), (5, 5, 80, 16), (4, 1, 128, 16), (2, 2, 112, 4)])
+@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (8, 2, 64, 16), (6, 3, 48, 8), (5, 5, 80, 16), (4, 1, 128, 16), (2, 2, 112, 4),
+                                  (10, 2, 64, 16), (12, 2, 96, 8)])
 def test_prefill_attention_tiles(case):
     """Prompt portions in bfloat16 take the tiled tensor-core kernel: portions that span several
     query tiles and many key tiles, portions that start deep in a sequence, single rows beside
@@ -420,7 +468,7 @@ def test_short_conv_few_rows_per_sequence_takes_the_serial_kernel(dtype):
     assert torch.allclose(s_one.cpu(), s_ref, rtol=0, atol=1e-7)
 
 
-@pytest.mark.parametrize("shape", [(40, 600, 264), (130, 256, 512), (300, 1000, 96), (513, 2 * 5632, 2048)])
+@pytest.mark.parametrize("shape", [(40, 600, 264), (130, 256, 512), (300, 1000, 96), (513, 2 * 5632, 2048), (777, 2 * 1000, 96), (2048, 2 * 264, 520)])
 def test_tensor_core_product_with_fused_swiglu(shape):
     """More than a handful of bfloat16 rows: gate and up accumulate side by side in tensor
     memory and the epilogue applies the activation (token tiles of 64, 128 and 256; feature

@@ -179,3 +179,97 @@ def test_invariant_prefilling_or_standing_on_a_token():
         for r in s.running:
             assert r.remaining >= 1 and (r.decoding or r.remaining >= 1)
     assert all(r.finish_reason == "length" and len(r.output) == 3 for r in reqs)
+
+
+# --------------------------------------------------------------------------- tokens that arrive a step late
+
+
+def drive_late(s, cache, token_of, max_steps=200):
+    """The lookahead loop without a model: each step's tokens arrive after the next step was
+    planned and launched.  ``token_of(request, output_index)`` is the token the "model" picks.
+    Returns the plans, in order."""
+    plans, in_flight = [], None
+    for _ in range(max_steps):
+        if not s.has_work() and in_flight is None:
+            break
+        plan = s.plan()
+        for e in plan.entries:
+            assert cache.append(e.request.id, e.count) == e.start
+        for e in plan.entries:
+            cache.commit(e.request.id)
+        s.launched(plan)
+        tokens = [token_of(e.request, e.output_index) for e in plan.entries if e.samples]
+        if in_flight is not None:
+            s.arrived(*in_flight)
+        in_flight = (plan, tokens) if plan.entries else None
+        cache.check()
+        plans.append(plan)
+    assert not s.has_work()
+    return plans
+
+
+def test_late_tokens_give_the_same_outputs_as_waiting_for_each_step():
+    def pick(req, idx):
+        return 100 + 10 * req.id + idx
+
+    outputs = []
+    for late in (False, True):
+        s, cache = make(num_pages=64, max_num_batched_tokens=6, prefill_chunk=4)
+        reqs = [s.add(i, [1] * n, SamplingParams(max_new_tokens=m)) for i, (n, m) in enumerate([(9, 5), (2, 1), (6, 3), (4, 7)])]
+        if late:
+            plans = drive_late(s, cache, pick)
+            # a request standing on a token the host has not seen is planned again, fed from the device
+            assert any(e.feed is not None for p in plans for e in p.entries)
+        else:
+            while s.has_work():
+                p = s.plan()
+                for e in p.entries:
+                    cache.append(e.request.id, e.count)
+                    cache.commit(e.request.id)
+                s.launched(p)
+                s.arrived(p, [pick(e.request, e.output_index) for e in p.entries if e.samples])
+        outputs.append([(r.output, r.finish_reason) for r in reqs])
+        assert cache.free_pages() == [64] and cache.slots.free_slots == 4
+    assert outputs[0] == outputs[1]
+    assert [len(o) for o, _ in outputs[0]] == [5, 1, 3, 7] and all(why == "length" for _, why in outputs[0])
+
+
+def test_a_stop_token_that_arrives_late_drops_the_row_computed_past_it():
+    s, cache = make(num_pages=32, eos=(9,))
+    a = s.add("a", [1] * 5, SamplingParams(max_new_tokens=10))
+    b = s.add("b", [1] * 3, SamplingParams(max_new_tokens=10, ignore_eos=True))
+
+    def pick(req, idx):
+        return 9 if idx == 2 else 50 + idx  # the third token is the stop token
+
+    plans = drive_late(s, cache, pick)
+    assert a.finish_reason == "stop" and a.output == [50, 51]
+    assert b.finish_reason == "length" and b.output == [50, 51, 9] + [50 + i for i in range(3, 10)]
+    # "a" was planned once more before its stop token was known
+    rows_a = [e for p in plans for e in p.entries if e.request is a]
+    assert len(rows_a) == 1 + 3  # the prompt, two decode rows, and the one past the stop
+    assert cache.free_pages() == [32] and cache.slots.free_slots == 4 and not s.running and not s.waiting
+
+
+def test_preemption_and_abort_while_a_token_is_on_its_way():
+    """With 6 pages of 4, two requests of 8 tokens each outgrow the pool while decoding: the
+    younger is preempted standing on a token the host has not seen, takes it when it arrives,
+    and recomputes with it; an abort in the same situation frees everything at once."""
+    s, cache = make(num_pages=6, page=4, max_num_batched_tokens=16)
+    a = s.add("a", [1] * 8, SamplingParams(max_new_tokens=8))
+    b = s.add("b", [2] * 8, SamplingParams(max_new_tokens=8))
+    drive_late(s, cache, lambda req, idx: 30 + idx)
+    assert a.output == b.output == [30 + i for i in range(8)]
+    assert s.stats["preempted"] > 0 and b.preemptions > 0
+    assert cache.free_pages() == [6] and cache.slots.free_slots == 4
+
+    s, cache = make(num_pages=16)
+    c = s.add("c", [1] * 4, SamplingParams(max_new_tokens=8))
+    p1 = s.plan()
+    for e in p1.entries:
+        cache.append(e.request.id, e.count)
+        cache.commit(e.request.id)
+    s.launched(p1)
+    assert c.output == [-1] and c.decoding
+    assert s.abort("c") and cache.free_pages() == [16]
+    assert s.arrived(p1, [5]) == [] and c.finish_reason == "abort" and not s.has_work()
