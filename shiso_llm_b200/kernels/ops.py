@@ -163,6 +163,27 @@ def _sm_count() -> int:
     return _SM_COUNT
 
 
+PREFETCH_MAX_BYTES = 48 << 20  # of the next matrix; L2 holds 126 MB and this one is passing through it too
+
+
+def link_matrices(matrices) -> None:
+    """``matrices``: the large matrices one step reads, in the order it reads them.  Each gets
+    its successor as the attribute ``read_next`` (the last one the first: the next step starts
+    there), and a weight-streaming product asks for that successor to be brought into L2 while
+    it streams its own rows."""
+    matrices = [m for m in matrices if m is not None]
+    for m, nxt in zip(matrices, matrices[1:] + matrices[:1]):
+        if nxt is not m:
+            m.read_next = nxt
+
+
+def _next_matrix(w):
+    nxt = getattr(w, "read_next", None)
+    if nxt is None or not nxt.is_cuda or not nxt.is_contiguous():
+        return 0, 0
+    return nxt.data_ptr(), min(nxt.numel() * nxt.element_size(), PREFETCH_MAX_BYTES)
+
+
 def _takes_skinny(tokens: int, n: int) -> bool:
     """Which plain products the weight-streaming kernel runs (measured inside captured steps
     against the tensor-memory kernel): up to 8 rows always; up to 16 rows unless the matrix is
@@ -192,7 +213,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     lib = library()
     both_bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     if both_bf16 and k % 8 == 0 and _takes_skinny(tokens, n):
-        status = lib.shiso_gemm_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _stream())
+        next_ptr, next_bytes = _next_matrix(w)
+        status = lib.shiso_gemm_skinny(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, next_ptr, next_bytes, _stream()
+        )
         _done(status, "linear (skinny)")
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
@@ -229,8 +253,10 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0
     ):
         out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
+        next_ptr, next_bytes = _next_matrix(gate_up)
         status = library().shiso_gemm_skinny(
-            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2, _stream()
+            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
+            next_ptr, next_bytes, _stream(),
         )
         _done(status, "linear_swiglu (skinny)")
         return out
@@ -254,6 +280,71 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         _done(status, "linear_swiglu (tcgen05)")
         return out
     return swiglu(linear(x, gate_up, out_dtype))
+
+
+STREAM_MAX_TOKENS = 8  # rows the product-into-stream / scaled-product pair takes (the kernel itself takes 16, spilling)
+
+
+class ScaledRows:
+    """Rows that still lack their RMS scale: ``x`` is bfloat16 ``(residual * norm weight)`` and
+    ``partials[c, t]`` are sums of squares of token ``t`` whose total over ``c`` gives the mean
+    square.  ``linear_scaled`` applies the scale after its product."""
+
+    def __init__(self, x, partials, eps):
+        self.x, self.partials, self.eps = x, partials, float(eps)
+
+
+def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
+    """A block's output projection, the residual add and the first half of the next RMS norm in
+    one launch, for a handful of bfloat16 rows: returns ``(residual + x @ w^T, ScaledRows)`` -
+    ``residual`` (float32 ``[T, N]``) itself is not changed - or None when sizes or types are
+    not the ones the kernel takes."""
+    tokens, k = x.shape
+    n = w.shape[0]
+    if (
+        x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or residual.dtype != torch.float32
+        or tokens > STREAM_MAX_TOKENS or k % 8 or w.shape[1] != k or n % 8
+    ):
+        return None
+    _check(x, "x", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(residual, "residual", torch.float32, 2)
+    _check(next_norm_w, "norm weight", torch.float32, 1)
+    if residual.shape != (tokens, n) or next_norm_w.shape[0] != n:
+        raise KernelError(f"a residual of shape {tuple(residual.shape)} beside a product of {tokens} x {n}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    summed = torch.empty_like(residual)
+    rows = torch.empty((tokens, n), dtype=torch.bfloat16, device=x.device)
+    partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
+    next_ptr, next_bytes = _next_matrix(w)
+    status = library().shiso_gemm_skinny_stream(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
+        tokens, n, k, next_ptr, next_bytes, _stream(),
+    )
+    _done(status, "linear_into_stream")
+    return summed, ScaledRows(rows, partials, eps)
+
+
+def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
+    """``rmsnorm(..) @ w^T`` (SwiGLU over the gate/up pair ``w`` when ``glu``) for rows that
+    ``linear_into_stream`` left: the row scale is applied to the accumulators."""
+    x = rows.x
+    _check(x, "x", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    tokens, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or (glu and n % 2):
+        raise KernelError(f"a matrix of shape {tuple(w.shape)} for rows of {k}")
+    inter = n // 2 if glu else 0
+    out = torch.empty((tokens, inter if glu else n), dtype=out_dtype, device=x.device)
+    next_ptr, next_bytes = _next_matrix(w)
+    status = library().shiso_gemm_skinny_scaled(
+        _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.eps, _ptr(w), _ptr(out), _code(out),
+        tokens, n, k, inter, next_ptr, next_bytes, _stream(),
+    )
+    _done(status, "linear_scaled")
+    return out
 
 
 def linear_add_rmsnorm(x, w, residual, norm_w, eps, out_dtype):

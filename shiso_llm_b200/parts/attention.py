@@ -25,7 +25,7 @@ import torch
 
 from ..config.errors import UnsupportedShape
 from ..weights.spec import TensorSpec
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, DeferredLinear, Mixer, PagedKV
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, DeferredLinear, Mixer, PagedKV, project
 
 MAX_HEAD_DIM = 256
 HEAD_DIM_STEP = 16
@@ -33,6 +33,8 @@ HEAD_DIM_STEP = 16
 
 @MIXERS.register("gqa_attention")
 class GqaAttention(Mixer):
+    takes_deferred_norm = True
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         p = spec.params
@@ -90,6 +92,9 @@ class GqaAttention(Mixer):
         for part in self.sub_parts():
             part.bind(tensors)
 
+    def matrices(self):
+        return [self.qkv, self.out]
+
     def cache_spec(self):
         if self.borrows_cache:
             return None
@@ -98,7 +103,7 @@ class GqaAttention(Mixer):
     def forward(self, x, step, cache):
         ops = self.env.ops
         store = cache.owner and not self.borrows_cache
-        qkv = ops.linear(x, self.qkv, self.env.dtype)
+        qkv = project(ops, x, self.qkv, self.env.dtype)
         inv_freq, rotary_dim = self.position.rotary()
         q = ops.qk_norm_rope_store(
             qkv,

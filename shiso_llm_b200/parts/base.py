@@ -11,6 +11,7 @@ Kinds of part and what each must provide:
 ``PositionEncoding`` ``rotary()`` - the per-pair frequencies the fused kernel rotates by
 ``Mixer``            ``cache_spec()``, ``forward(x, step, cache)`` -> tensor or ``DeferredLinear``
 ``FeedForward``      ``forward(x, step)`` -> tensor or ``DeferredLinear``
+                     (both: ``takes_deferred_norm = True`` to get ``x`` as a ``DeferredNorm``)
 ``Block``            ``forward(stream, step, cache)`` - the arrangement of the above
 ``Embedding``        ``forward(step)`` -> float32 residual rows
 ``Head``             ``forward(x)`` -> float32 logits
@@ -92,6 +93,16 @@ class Part:
     def sub_parts(self) -> list["Part"]:
         return []
 
+    def matrices(self) -> list[torch.Tensor]:
+        """After ``bind``: the large matrices the part reads in one step, in the order it reads
+        them.  The model strings the lists of all parts together so that a kernel streaming one
+        matrix can have the next one fetched meanwhile; a part that lists nothing just takes no
+        part in that."""
+        out = []
+        for sub in self.sub_parts():
+            out += sub.matrices()
+        return out
+
 
 class Norm(Part):
     def apply(self, x: torch.Tensor) -> torch.Tensor:
@@ -164,6 +175,50 @@ class DeferredLinear:
         return self.ops.linear(self.x, self.w, self.out_dtype)
 
 
+class DeferredNorm:
+    """The normed rows a mixer or feed-forward is about to read, not computed yet:
+    ``norm(residual + pending)`` of a stream.
+
+    A part that sets ``takes_deferred_norm = True`` is handed this instead of a tensor and
+    starts with ``project(ops, x, w, ...)``.  Where the block output waiting to be added is a
+    product (``DeferredLinear``), the norm is an RMS norm and the kernel table has the pair
+    ``linear_into_stream`` / ``linear_scaled`` (a handful of rows), the two products run with
+    nothing between them: the first adds into the stream and leaves unscaled rows, the second
+    applies the row scale.  Else the norm runs first, as it always did.  ``materialize()``
+    gives the rows themselves."""
+
+    def __init__(self, stream: "Stream", norm: Norm):
+        self.stream, self.norm = stream, norm
+
+    def materialize(self) -> torch.Tensor:
+        return self.stream.normed(self.norm)
+
+    def linear(self, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+        stream, norm = self.stream, self.norm
+        ops = norm.env.ops
+        waiting = stream.pending
+        into_stream = getattr(ops, "linear_into_stream", None)
+        params = norm.rms_params() if hasattr(norm, "rms_params") else None
+        if isinstance(waiting, DeferredLinear) and into_stream is not None and params is not None:
+            # the block output waiting to be added is a product: it goes straight into the
+            # stream and leaves rows that this product scales by itself
+            result = into_stream(waiting.x, waiting.w, stream.residual, params[0], params[1])
+            if result is not None:
+                stream.residual, rows = result
+                stream.pending = None
+                return ops.linear_scaled(rows, w, out_dtype, glu)
+        x = stream.normed(norm)
+        return ops.linear_swiglu(x, w, out_dtype) if glu else ops.linear(x, w, out_dtype)
+
+
+def project(ops, x, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+    """``x @ w^T`` (or SwiGLU over the gate/up pair ``w``) for rows ``x`` that are a tensor or a
+    ``DeferredNorm``."""
+    if isinstance(x, DeferredNorm):
+        return x.linear(w, out_dtype, glu)
+    return ops.linear_swiglu(x, w, out_dtype) if glu else ops.linear(x, w, out_dtype)
+
+
 class Stream:
     """The residual stream between blocks.
 
@@ -175,7 +230,11 @@ class Stream:
         self.residual = residual
         self.pending: Optional[torch.Tensor] = None
 
-    def normed(self, norm: Norm) -> torch.Tensor:
+    def normed(self, norm: Norm, deferred: bool = False):
+        """The normed rows; with ``deferred`` a ``DeferredNorm`` that computes them when (and how)
+        its reader wants."""
+        if deferred:
+            return DeferredNorm(self, norm)
         if self.pending is None:
             return norm.apply(self.residual)
         delta, self.pending = self.pending, None

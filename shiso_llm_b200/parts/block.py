@@ -41,6 +41,8 @@ class PreNormBlock(Block):
         return self.mixer
 
     def forward(self, stream, step, cache):
-        stream.add(self.mixer.forward(stream.normed(self.mixer_norm), step, cache))
+        x = stream.normed(self.mixer_norm, getattr(self.mixer, "takes_deferred_norm", False))
+        stream.add(self.mixer.forward(x, step, cache))
         if self.feed_forward is not None:
-            stream.add(self.feed_forward.forward(stream.normed(self.ff_norm), step))
+            x = stream.normed(self.ff_norm, getattr(self.feed_forward, "takes_deferred_norm", False))
+            stream.add(self.feed_forward.forward(x, step))

@@ -12,11 +12,13 @@ from __future__ import annotations
 import torch
 
 from ..weights.spec import TensorSpec
-from .base import FEED_FORWARDS, DeferredLinear, FeedForward
+from .base import FEED_FORWARDS, DeferredLinear, FeedForward, project
 
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    takes_deferred_norm = True
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         p = spec.params
@@ -42,7 +44,10 @@ class SwiGLU(FeedForward):
         self.gate_up = torch.cat([g, u], dim=0).contiguous()
         self.down = tensors[down]
 
+    def matrices(self):
+        return [self.gate_up, self.down]
+
     def forward(self, x, step):
         ops = self.env.ops
-        mid = ops.linear_swiglu(x, self.gate_up, self.env.dtype)
+        mid = project(ops, x, self.gate_up, self.env.dtype, glu=True)
         return DeferredLinear(ops, mid, self.down, self.env.dtype)

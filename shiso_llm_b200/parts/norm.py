@@ -27,6 +27,10 @@ class RMSNorm(Norm):
     def bind(self, tensors):
         self.weight = tensors[self.tensor_name]
 
+    def rms_params(self):
+        """``(weight, eps)``: what a kernel that normalises inside a product needs."""
+        return self.weight, self.eps
+
     def apply(self, x):
         return self.env.ops.rmsnorm(x, self.weight, self.eps, self.env.dtype)
 

@@ -16,13 +16,15 @@ from __future__ import annotations
 
 from ..config.errors import UnsupportedShape
 from ..weights.spec import VECTOR, ZEROS, TensorSpec
-from .base import MIXERS, DeferredLinear, FixedState, Mixer
+from .base import MIXERS, DeferredLinear, DeferredNorm, FixedState, Mixer
 
 MAX_TAPS = 8
 
 
 @MIXERS.register("short_conv")
 class ShortConv(Mixer):
+    takes_deferred_norm = True
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         p = spec.params
@@ -52,10 +54,16 @@ class ShortConv(Mixer):
         self.out_proj = tensors[self.names["out_proj"]]
         self.bias = tensors[self.bias_name] if self.has_bias else None
 
+    def matrices(self):
+        return [self.in_proj, self.out_proj]
+
     def cache_spec(self):
         return FixedState((self.taps - 1, self.hidden))
 
     def forward(self, x, step, cache):
         ops = self.env.ops
-        y = ops.linear_short_conv(x, self.in_proj, self.conv, self.bias, cache.state, step)
+        if isinstance(x, DeferredNorm):
+            y = ops.short_conv(x.linear(self.in_proj, self.env.dtype), self.conv, self.bias, cache.state, step)
+        else:
+            y = ops.linear_short_conv(x, self.in_proj, self.conv, self.bias, cache.state, step)
         return DeferredLinear(ops, y, self.out_proj, self.env.dtype)

@@ -72,6 +72,32 @@ def linear_swiglu(x, gate_up, out_dtype):
     return (g / (1.0 + torch.exp(-g)) * u).to(out_dtype)
 
 
+class ScaledRows:
+    def __init__(self, x, partials, eps):
+        self.x, self.partials, self.eps = x, partials, eps
+
+
+def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
+    """The pair the CUDA table offers for a few bfloat16 rows; here for any type and up to 16
+    rows, so that the parts' handling of it runs on the CPU too."""
+    if x.shape[0] > 16:
+        return None
+    summed = residual + linear(x, w, torch.float32, bias)
+    rows = (summed.to(F64) * next_norm_w.to(F64)).to(x.dtype)
+    return summed, ScaledRows(rows, (summed.to(F64) ** 2).sum(-1, keepdim=True).T.contiguous(), eps)
+
+
+def linear_scaled(rows, w, out_dtype, glu=False):
+    k = rows.x.shape[1]
+    inv = 1.0 / torch.sqrt(rows.partials.sum(0) / k + rows.eps)
+    y = (rows.x.to(F64) @ w.to(F64).T) * inv[:, None]
+    if glu:
+        inter = y.shape[1] // 2
+        g, u = y[:, :inter], y[:, inter:]
+        y = g / (1.0 + torch.exp(-g)) * u
+    return y.to(out_dtype)
+
+
 def linear_add_rmsnorm(x, w, residual, norm_w, eps, out_dtype):
     return add_rmsnorm(residual, linear(x, w, out_dtype), norm_w, eps, out_dtype)
 

@@ -524,3 +524,46 @@ def test_fused_projection_residual_add_and_norm(shape):
         # it), so the sums may differ by one unit in the last place of the product
         delta_scale = ref.linear(x, w, torch.float32).abs().max().item()
         assert (res_gpu.cpu() - res_ref).abs().max().item() <= 2.0 ** -7 * delta_scale
+
+
+@pytest.mark.parametrize("shape", [(8, 2048, 2048, 6144), (1, 96, 64, 200), (3, 264, 1000, 520), (13, 4096, 512, 64), (16, 2048, 5632, 2048), (5, 8, 24, 40)])
+@pytest.mark.parametrize("glu", [False, True])
+@pytest.mark.parametrize("bias", [False, True])
+def test_product_into_the_stream_then_scaled_product(shape, glu, bias):
+    """A handful of bfloat16 rows: a block's output projection adds into the residual stream and
+    leaves norm-weighted rows and partial sums of squares; the next product applies the row
+    scale to its accumulators.  Against product, add + RMS norm, product (or SwiGLU pair), one
+    after the other; the old residual must stay as it was (other CTAs still read it)."""
+    T, H, K1, N2 = shape  # stream width H; the first product reads K1, the second gives N2
+    x1 = rnd((T, K1), torch.bfloat16, 150)
+    w1 = rnd((H, K1), torch.bfloat16, 151, 0.05)
+    b1 = rnd((H,), torch.float32, 154) if bias else None
+    residual = rnd((T, H), torch.float32, 152, 2.0)
+    norm_w = 1.0 + 0.2 * rnd((H,), torch.float32, 153)
+    w2 = rnd((2 * N2 if glu else N2, H), torch.bfloat16, 155, 0.05)
+    eps = 1e-5
+    res_gpu = residual.clone().cuda()
+    got = ops().linear_into_stream(x1.cuda(), w1.cuda(), res_gpu, norm_w.cuda(), eps, b1.cuda() if bias else None)
+    assert got is not None
+    summed, rows = got
+    assert torch.equal(res_gpu.cpu(), residual)
+    want_sum = residual + ref.linear(x1, w1, torch.float32, b1)
+    close(summed, want_sum, torch.float32, "stream after the product", rel32=1e-5)
+    assert rows.partials.shape == (-(-H // 16), 16)
+    mean_square = rows.partials.cpu()[:, :T].sum(0) / H
+    assert torch.allclose(mean_square, (want_sum.double() ** 2).mean(-1).float(), rtol=1e-5)
+    y = ops().linear_scaled(rows, w2.cuda(), torch.bfloat16, glu)
+    x = ref.rmsnorm(want_sum, norm_w, eps, torch.bfloat16)
+    want = ref.linear_swiglu(x, w2, torch.bfloat16) if glu else ref.linear(x, w2, torch.bfloat16)
+    # x is rounded to bfloat16 on both sides but at different points (before and after the row
+    # scale): single inputs differ by one unit in the last place, which the product averages out
+    scale = (ref.linear_swiglu(x, w2, torch.float32) if glu else ref.linear(x, w2, torch.float32)).abs().max().item()
+    close(y, want, torch.bfloat16, f"scaled product {shape} glu={glu}", scale=2 * scale)
+
+
+def test_product_into_the_stream_declines_what_it_cannot_take():
+    w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
+    nw = torch.ones(32, device="cuda")
+    x = torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops().linear_into_stream(x, w, torch.zeros(17, 32, device="cuda"), nw, 1e-5) is None  # too many rows
+    assert ops().linear_into_stream(x[:4].float(), w.float(), torch.zeros(4, 32, device="cuda"), nw, 1e-5) is None
