@@ -1,5 +1,6 @@
 // Y[T, N] = X[T, K] * W[N, K]^T for a handful of rows (T <= 64), bfloat16: the decode step's
-// matrix products, which are weight streaming.
+// matrix products, which are weight streaming.  (Up to 16 rows the persistent kernel of
+// gemm_stream.cu runs them; this one-shot kernel takes 17 to 64.)
 //
 // At these sizes a product is over in a few microseconds, so what counts is how soon the
 // weight bytes are in flight and how little else happens: no tensor map, no tensor memory,
@@ -15,24 +16,12 @@
 // kernel costs more than its arithmetic:
 //   GLU       the weight is a [2 * inter, K] gate-over-up pair; a CTA takes 8 gate rows and
 //             their 8 up rows and writes silu(gate) * up (kernels/cuda/generic/glu.cuh:35-57);
-//   STREAM    (a block's output projection) the CTA adds its 16 features to the float32 residual
-//             stream (into a second buffer), writes them times the next RMS norm's weight as
-//             bfloat16 rows - the next product's input but for the row scale - and leaves the
-//             sum of their squares per token in a table of partials, one row per CTA;
-//   SCALED    (the product after it) sums the partials of each token in a fixed order, and
-//             scales its accumulators by rsqrt(mean square + eps) before the activation or the
-//             store: x W^T is linear in the row scale, so the norm needs no pass of its own.
-//             Together the two stand for product, residual add, RMS norm, product with no row
-//             kernel between them.  The rows are rounded to bfloat16 before the scale instead
-//             of after it, which is the same relative rounding.
 // (Two more fusions were built, measured inside a captured step and dropped.  Folding in the
 // residual add and the next RMS norm - the CTA that finishes last normalising all rows - cost
 // 10.5 us against 6.1 us for product + row kernel: fence, ticket and a single-CTA tail.  Running
 // the gated short convolution in the input projection's epilogue won 0.9 us in isolation and
 // lost 3 us per layer in the whole step, because its thin tail delays the grid's completion,
-// which is what the next product's activations wait for.  A third, the norm as a prologue that
-// every CTA repeats for itself over residual + delta, took 14 us more per product: two passes
-// of loads that wait for one another.)
+// which is what the next product's activations wait for.)
 //
 // The reference's decode products are matvec kernels that re-read the weights per row block
 // (crates/shiso-engine/src/projection.rs:972-1069).
@@ -77,43 +66,14 @@ struct SkinnyArgs {
     const float* bias;       // [N] or null (plain products only)
     void* y;                 // plain [T, N]; GLU [T, inter]
     int T, N, K, inter, out_f32, mode;
-    // The matrix the step reads after this one (or null): every CTA asks for a slice of it to be
-    // brought into L2 while it streams its own rows, so that memory keeps working through the
-    // small kernels and launch gaps that follow, and the next product finds its matrix on chip.
-    const char* next_w;
-    long long next_bytes;
-    // STREAM epilogue (plain products): y is not written.
-    const float* res_in;        // [T, N] float32 residual stream
-    float* res_out;             // [T, N] res_in + product
-    const float* next_norm_w;   // [N]
-    __nv_bfloat16* x_out;       // [T, N] bf16((res_in + product) * next_norm_w)
-    float* partials_out;        // [CTAs, PARTIAL_STRIDE] sums of squares of the CTA's features per token
-    // SCALED epilogue: accumulators times rsqrt(sum of partials / norm_k + eps) per token.
-    const float* partials_in;   // [partial_count, PARTIAL_STRIDE] or null
-    int partial_count, norm_k;
-    float eps;
 };
-
-constexpr int PARTIAL_STRIDE = 16;  // tokens per row of the partials table (the most these epilogues take)
-
-__device__ __forceinline__ void prefetch_slice(const SkinnyArgs& a, int lane) {
-    const long long units = a.next_bytes >> 4;  // 16-byte units
-    const long long lanes = (long long)gridDim.x * 32;
-    const long long per_lane = (units + lanes - 1) / lanes;
-    const long long first = ((long long)blockIdx.x * 32 + lane) * per_lane;
-    if (first < units) {
-        const long long n = min(per_lane, units - first);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.next_w + first * 16), "r"((uint32_t)(n * 16)) : "memory");
-    }
-}
 
 // NT = 8-token tiles (1, 2, 4 or 8); WARPS_K = warps that split K; UNROLL = 64-wide k blocks per
 // warp whose loads (weights and activations) are all issued before the first MMA.
 template <int NT, int WARPS_K, int UNROLL>
-__global__ void __launch_bounds__(WARPS_K * 32, WARPS_K <= 8 ? 2 : 1)
+__global__ void __launch_bounds__(WARPS_K * 32)
 gemm_skinny_kernel(SkinnyArgs a) {
     __shared__ float partial[WARPS_K][NT][32][4];
-    __shared__ float square_parts[16][PARTIAL_STRIDE];
     bool waited = false;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t4 = lane & 3;
@@ -139,47 +99,6 @@ gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
     for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
 
-    // What the STREAM and SCALED epilogues read from global memory is asked for as soon as the
-    // predecessor is known to be done (first trip, after the activations), not when it is
-    // needed: the epilogue is the tail of a chain of dependent kernels.
-    constexpr bool FUSED = NT <= 2;                      // STREAM and SCALED take up to 16 rows
-    constexpr int EARLY_PARTIALS = 8;                    // covers 128 CTAs of the producer
-    float early_part[EARLY_PARTIALS];
-    float early_res[NT][2][2], early_nw[2] = {0.0f, 0.0f}, early_bias[2] = {0.0f, 0.0f};
-    bool early_done = false;
-    auto early_loads = [&]() {
-        early_done = true;
-        if (!FUSED) return;
-        if (a.partials_in) {
-            const int chunk = threadIdx.x / PARTIAL_STRIDE, token = threadIdx.x % PARTIAL_STRIDE;
-#pragma unroll
-            for (int j = 0; j < EARLY_PARTIALS; ++j) {
-                const int c = chunk + 16 * j;
-                early_part[j] = 0.0f;
-                if (threadIdx.x < 16 * PARTIAL_STRIDE && c < a.partial_count)
-                    asm volatile("ld.global.f32 %0, [%1];" : "=f"(early_part[j]) : "l"(a.partials_in + (size_t)c * PARTIAL_STRIDE + token) : "memory");
-            }
-        }
-        if (a.res_in && warp == 0) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (row_ok[h]) {
-                    early_nw[h] = a.next_norm_w[rows[h]];
-                    if (a.bias) early_bias[h] = a.bias[rows[h]];
-                }
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int token = n * 8 + t4 * 2 + e;
-                        early_res[n][e][h] = 0.0f;
-                        if (row_ok[h] && token < a.T)
-                            asm volatile("ld.global.f32 %0, [%1];" : "=f"(early_res[n][e][h]) : "l"(a.res_in + (size_t)token * a.N + rows[h]) : "memory");
-                    }
-            }
-        }
-    };
-
     // warp w takes the 64-wide k blocks w, w + WARPS_K, ...; a lane owns 16 consecutive k of a block
     for (int k0 = warp * 64; k0 < a.K; k0 += WARPS_K * 64 * UNROLL) {
         uint4 wl[UNROLL][2], wh[UNROLL][2], xv[UNROLL][NT][2];
@@ -196,7 +115,6 @@ gemm_skinny_kernel(SkinnyArgs a) {
         if (!waited) {
             // The weights above depend on no predecessor and are already on their way; the
             // activations below were written by one.
-            if (warp == 0 && a.next_bytes > 0) prefetch_slice(a, lane);
             pdl_wait();
             waited = true;
         }
@@ -211,7 +129,6 @@ gemm_skinny_kernel(SkinnyArgs a) {
                     xv[u][n][h] = load_activation16(a.x + (size_t)token * a.K + k + h * 8, token < a.T && k + h * 8 < a.K);
             }
         }
-        if (!early_done) early_loads();
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
@@ -227,20 +144,6 @@ gemm_skinny_kernel(SkinnyArgs a) {
 
     pdl_trigger();            // the weights are read: the successor may start fetching its own
     if (!waited) pdl_wait();  // a warp whose K range is empty still orders its writes after the predecessor
-    if (!early_done) early_loads();  // a warp whose K range is empty
-    if (FUSED && a.partials_in && threadIdx.x < 16 * PARTIAL_STRIDE) {
-        // SCALED: thread (chunk, token) sums every 16th row of the partials table for its token
-        const int chunk = threadIdx.x / PARTIAL_STRIDE, token = threadIdx.x % PARTIAL_STRIDE;
-        float sum = 0.0f;
-#pragma unroll
-        for (int j = 0; j < EARLY_PARTIALS; ++j) sum += early_part[j];
-        for (int c = chunk + 16 * EARLY_PARTIALS; c < a.partial_count; c += 16) {
-            float v;
-            asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(a.partials_in + (size_t)c * PARTIAL_STRIDE + token) : "memory");
-            sum += v;
-        }
-        square_parts[chunk][token] = sum;
-    }
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -256,49 +159,13 @@ gemm_skinny_kernel(SkinnyArgs a) {
     __syncthreads();
     // In a lane's registers: c0: (row g, token 2t), c1: (row g, token 2t+1), c2/c3: row g + 8.
     if (warp == 0) {
-        if (FUSED && a.res_in) {
-            // STREAM: residual + product -> new residual, norm-weighted bf16 rows, partial squares
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int token = n * 8 + t4 * 2 + e;
-                    float squares = 0.0f;
-                    if (token < a.T) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            if (!row_ok[h]) continue;
-                            const size_t at = (size_t)token * a.N + rows[h];
-                            const float v = early_res[n][e][h] + partial[0][n][lane][2 * h + e] + early_bias[h];
-                            a.res_out[at] = v;
-                            a.x_out[at] = __float2bfloat16_rn(v * early_nw[h]);
-                            squares += v * v;
-                        }
-                    }
-                    // over the 8 lanes that hold this token (g = 0..7), in a fixed order
-                    squares += __shfl_xor_sync(0xffffffffu, squares, 4);
-                    squares += __shfl_xor_sync(0xffffffffu, squares, 8);
-                    squares += __shfl_xor_sync(0xffffffffu, squares, 16);
-                    if (g == 0 && token < PARTIAL_STRIDE) a.partials_out[(size_t)blockIdx.x * PARTIAL_STRIDE + token] = squares;
-                }
-            }
-            return;
-        }
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int token = n * 8 + t4 * 2 + e;
                 if (token >= a.T) continue;
-                float lo = partial[0][n][lane][e], hi = partial[0][n][lane][2 + e];
-                if (FUSED && a.partials_in) {
-                    float total = 0.0f;
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) total += square_parts[c][token];
-                    const float inv = rsqrtf(total / (float)a.norm_k + a.eps);
-                    lo *= inv;
-                    hi *= inv;
-                }
+                const float lo = partial[0][n][lane][e], hi = partial[0][n][lane][2 + e];
                 if (mode == MODE_GLU) {
                     if (row_ok[0]) {
                         const float v = lo / (1.0f + expf(-lo)) * hi;
@@ -349,9 +216,8 @@ int launch_skinny(const SkinnyArgs& a, unsigned blocks, cudaStream_t stream) {
 
 // x [T, K] bf16 (T <= 64), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
 // inter == 0: y[T, N] = x w^T (+ bias).  inter > 0: N == 2 * inter, y[T, inter] = silu(x gate^T) * (x up^T).
-// next_w / next_bytes: a matrix to bring into L2 meanwhile (16-byte aligned; 0 bytes: none).
 SHISO_API int shiso_gemm_skinny(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
-                                int K, int inter, const void* next_w, long long next_bytes, cudaStream_t stream) {
+                                int K, int inter, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
     if (T > 64 || K % 8 != 0 || K <= 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
@@ -367,70 +233,5 @@ SHISO_API int shiso_gemm_skinny(const void* x, const void* w, const float* bias,
     a.inter = inter;
     a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     a.mode = inter > 0 ? MODE_GLU : MODE_PLAIN;
-    if (next_w && next_bytes >= 16 && ((uintptr_t)next_w & 15) == 0) {
-        a.next_w = (const char*)next_w;
-        a.next_bytes = next_bytes;
-    }
-    return launch_skinny(a, inter > 0 ? ceil_div_u(inter, 8) : ceil_div_u(N, 16), stream);
-}
-
-// A block's output projection into the residual stream (T <= 16): res_out = res_in + x w^T (+ bias),
-// x_out = bf16(res_out * next_norm_w), partials_out[cta][token] = sum over the CTA's 16 features of
-// res_out^2 (ceil(N / 16) rows of 16 floats; tokens >= T hold zeros).
-SHISO_API int shiso_gemm_skinny_stream(const void* x, const void* w, const float* bias, const float* res_in,
-                                       float* res_out, const float* next_norm_w, void* x_out, float* partials_out,
-                                       int T, int N, int K, const void* next_w, long long next_bytes,
-                                       cudaStream_t stream) {
-    if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > PARTIAL_STRIDE || K % 8 != 0 || K <= 0) return SHISO_ERR_UNSUPPORTED;
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
-    if (!res_in || !res_out || res_in == res_out || !next_norm_w || !x_out || !partials_out) return SHISO_ERR_SHAPE;
-    SkinnyArgs a = {};
-    a.x = (const __nv_bfloat16*)x;
-    a.w = (const __nv_bfloat16*)w;
-    a.bias = bias;
-    a.T = T;
-    a.N = N;
-    a.K = K;
-    a.mode = MODE_PLAIN;
-    a.res_in = res_in;
-    a.res_out = res_out;
-    a.next_norm_w = next_norm_w;
-    a.x_out = (__nv_bfloat16*)x_out;
-    a.partials_out = partials_out;
-    if (next_w && next_bytes >= 16 && ((uintptr_t)next_w & 15) == 0) {
-        a.next_w = (const char*)next_w;
-        a.next_bytes = next_bytes;
-    }
-    return launch_skinny(a, ceil_div_u(N, 16), stream);
-}
-
-// The product after it: y = (x w^T) * rsqrt(sum_c partials[c][token] / K + eps) per token (then
-// SwiGLU when inter > 0), x being the x_out rows above (T <= 16).
-SHISO_API int shiso_gemm_skinny_scaled(const void* x, const float* partials, int partial_count, float eps,
-                                       const void* w, void* y, int y_dtype, int T, int N, int K, int inter,
-                                       const void* next_w, long long next_bytes, cudaStream_t stream) {
-    if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > PARTIAL_STRIDE || K % 8 != 0 || K <= 0 || !partials || partial_count <= 0) return SHISO_ERR_UNSUPPORTED;
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
-    if (inter > 0 && N != 2 * inter) return SHISO_ERR_SHAPE;
-    SkinnyArgs a = {};
-    a.x = (const __nv_bfloat16*)x;
-    a.w = (const __nv_bfloat16*)w;
-    a.y = y;
-    a.T = T;
-    a.N = N;
-    a.K = K;
-    a.inter = inter;
-    a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
-    a.mode = inter > 0 ? MODE_GLU : MODE_PLAIN;
-    a.partials_in = partials;
-    a.partial_count = partial_count;
-    a.norm_k = K;
-    a.eps = eps;
-    if (next_w && next_bytes >= 16 && ((uintptr_t)next_w & 15) == 0) {
-        a.next_w = (const char*)next_w;
-        a.next_bytes = next_bytes;
-    }
     return launch_skinny(a, inter > 0 ? ceil_div_u(inter, 8) : ceil_div_u(N, 16), stream);
 }

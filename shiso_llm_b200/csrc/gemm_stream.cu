@@ -1,0 +1,508 @@
+// Y[T, N] = X[T, K] * W[N, K]^T for up to 16 rows, bfloat16: the decode step's matrix products as
+// a persistent weight-streaming kernel.
+//
+// The one-shot kernel of gemm_skinny.cu gives a CTA 16 weight rows and lets it ask for all of
+// them at once; a matrix of more than two CTAs per SM then runs in waves, and every wave pays the
+// memory latency again.  Here one CTA per SM walks its share of the 16-row tiles, and a producer
+// warp keeps a ring of shared-memory stages full with bulk copies (cp.async.bulk, one per weight
+// row and 1,024-column chunk, completion counted on an mbarrier), up to three stages = 96 KB
+// ahead of the four consumer warps and independent of them: the weights stream from the first
+// cycle of the kernel - before its predecessor in the dependent-launch chain has finished - to
+// the last tile without a gap (a CTA takes less than half an SM's shared memory and registers, so
+// the successor's CTA can move in beside it and start its own stream).  The consumers split the chunk's columns (256 each), read their
+// 16-byte pieces of the two weight rows a lane owns from shared memory (rows are padded by 16
+// bytes, which spreads them over the banks) and feed mma.sync m16n8k16 exactly as the one-shot
+// kernel does, activations in registers with the same k permutation.  A tile's partial sums
+// meet in shared memory in warp order; warp 0 writes the result while the others go on.
+//
+// What follows the product is folded into the epilogue, because at these sizes every extra kernel
+// costs more than its arithmetic:
+//   GLU     the weight is a [2 * inter, K] gate-over-up pair; a tile is 8 gate rows and their 8 up
+//           rows, and the epilogue writes silu(gate) * up (kernels/cuda/generic/glu.cuh:35-57);
+//   STREAM  (a block's output projection) the tile's 16 features are added to the float32 residual
+//           stream (into a second buffer), written once more times the next RMS norm's weight as
+//           bfloat16 rows - the next product's input but for the row scale - and the sum of their
+//           squares per token goes to a table of partials, one row per tile;
+//   SCALED  (the product after it) sums the partials of each token in a fixed order and scales
+//           its accumulators by rsqrt(mean square + eps) before the activation or the store:
+//           x W^T is linear in the row scale, so the norm needs no pass of its own.  The rows are
+//           rounded to bfloat16 before the scale instead of after it, which is the same relative
+//           rounding.
+// What the STREAM and SCALED epilogues read from global memory is asked for at the start of a
+// tile, not when it is needed: the epilogue is the tail of a chain of dependent kernels.
+// (Asking, from inside this kernel, for the matrix the step reads next to be brought into L2 was
+// measured too - cp.async.bulk.prefetch.L2 over a slice per CTA - and made the whole step slower:
+// the stream already keeps memory busy, and the extra requests only delay its own rows.)
+//
+// Every mbarrier wait is bounded; a wait that runs out sets the status word and the kernel
+// carries on (its result is then wrong, and the host raises when it reads the word).
+#include "tcgen05.cuh"
+
+namespace {
+
+using tc::mbar_arrive;
+using tc::mbar_expect_tx;
+using tc::mbar_init;
+using tc::mbar_wait;
+using tc::smem_u32;
+
+constexpr int KC = 1024;                       // columns per stage
+constexpr int ROWS = 16;                       // weight rows per tile
+constexpr int ROW_BYTES = KC * 2 + 16;         // padded row of a stage
+constexpr int STAGE_BYTES = ROWS * ROW_BYTES;  // 33,024
+constexpr int STAGES = 3;                      // two CTAs (this kernel's and its successor's) must fit an SM
+constexpr int CONSUMERS = 4;                   // warps; each takes 256 columns of a chunk
+constexpr int KB = KC / CONSUMERS / 64;        // 64-wide k blocks per warp and chunk
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int PARTIAL_STRIDE = 16;             // tokens per row of the partials table
+constexpr int EARLY_PARTIALS = 8;
+
+enum { MODE_PLAIN = 0, MODE_GLU = 1 };
+
+struct StreamArgs {
+    const __nv_bfloat16* x;  // [T, K]
+    const __nv_bfloat16* w;  // [N, K]
+    const float* bias;       // [N] or null (plain products only)
+    void* y;                 // plain [T, N]; GLU [T, inter]
+    int T, N, K, inter, out_f32, mode;
+    int tiles;               // 16-row tiles (GLU: 8 gate + 8 up rows)
+    int* status;
+    // STREAM epilogue
+    const float* res_in;
+    float* res_out;
+    const float* next_norm_w;
+    __nv_bfloat16* x_out;
+    float* partials_out;     // [tiles, PARTIAL_STRIDE]
+    // SCALED epilogue
+    const float* partials_in;
+    int partial_count, norm_k;
+    float eps;
+};
+
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Activations were written by a predecessor grid: coherent loads, after the dependency wait.
+__device__ __forceinline__ uint4 load_activation16(const __nv_bfloat16* p, bool valid) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) {
+        asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    }
+    return v;
+}
+
+__device__ __forceinline__ float load_stream1(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void consumer_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+}
+
+// Row of W behind row r (0..15) of a tile, or -1.
+__device__ __forceinline__ int tile_row(const StreamArgs& a, int tile, int r) {
+    if (a.mode == MODE_GLU) {
+        const int f = tile * 8 + (r & 7);
+        return f < a.inter ? (r < 8 ? f : a.inter + f) : -1;
+    }
+    const int row = tile * ROWS + r;
+    return row < a.N ? row : -1;
+}
+
+// HELD: the chunks of K whose activations a lane keeps in registers for the whole kernel (K <= HELD *
+// KC); they are the same for every tile, and a reload per chunk would put an L2 round trip into
+// every stage.  HELD = 0: K is longer than that and the activations of the next chunk are fetched
+// while the current one is worked on.
+template <int NT, int HELD>
+__global__ void __launch_bounds__(THREADS, NT * HELD > 2 ? 1 : 2)
+gemm_stream_kernel(StreamArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    uint64_t* full = (uint64_t*)(ring + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    float* partial = (float*)(empty + STAGES);                      // [2][CONSUMERS][NT][32][4]
+    float* square_parts = partial + 2 * CONSUMERS * NT * 128;       // [16][PARTIAL_STRIDE]
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunks = (a.K + KC - 1) / KC;
+    bool timed_out = false;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMERS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == CONSUMERS) {
+        // ---- producer: weights depend on no predecessor, so nothing here waits for one.  Lane r
+        // copies row r of each stage: one thread issuing all sixteen copies took longer per stage
+        // than the memory system needs to deliver it.
+        int unit = 0;
+        for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x) {
+            const int row = lane < ROWS ? tile_row(a, tile, lane) : -1;
+            const int present = __popc(__ballot_sync(0xffffffffu, row >= 0));
+            const __nv_bfloat16* src = a.w + (size_t)(row >= 0 ? row : 0) * a.K;
+            for (int c = 0; c < chunks; ++c, ++unit) {
+                const int s = unit % STAGES;
+                if (unit >= STAGES && !mbar_wait(&empty[s], ((unit / STAGES) - 1) & 1)) timed_out = true;
+                const int cols = min(KC, a.K - c * KC);
+                if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)(present * cols * 2));
+                __syncwarp();
+                if (row >= 0)
+                    bulk_load(smem_u32(ring + s * STAGE_BYTES) + lane * ROW_BYTES, src + (size_t)c * KC, (uint32_t)(cols * 2), &full[s]);
+            }
+        }
+        if (timed_out && lane == 0 && a.status) atomicExch(a.status, 1);
+        pdl_trigger();
+        return;
+    }
+
+    // ---- consumers
+    const int g = lane >> 2, t4 = lane & 3;
+    pdl_wait();
+
+    // the activations of chunk c this warp needs: KB k blocks of 64, a lane 16 consecutive k of each
+    auto load_x = [&](int c, uint4 (&xv)[KB][NT][2]) {
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+            const int k = c * KC + warp * (KC / CONSUMERS) + kb * 64 + t4 * 16;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int token = n * 8 + g;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    xv[kb][n][h] = load_activation16(a.x + (size_t)token * a.K + k + h * 8, token < a.T && k + h * 8 < a.K);
+            }
+        }
+    };
+
+    // SCALED: the partial squares, asked for now and summed at the first epilogue.  Slot i of
+    // 256 is (group i / 16, token i % 16); a group sums every 16th row of the table.
+    constexpr int SLOTS = 16 * PARTIAL_STRIDE / (CONSUMERS * 32);
+    float early_part[SLOTS][EARLY_PARTIALS];
+    if (a.partials_in) {
+#pragma unroll
+        for (int q = 0; q < SLOTS; ++q) {
+            const int i = threadIdx.x + q * CONSUMERS * 32;
+            const int group = i / PARTIAL_STRIDE, token = i % PARTIAL_STRIDE;
+#pragma unroll
+            for (int j = 0; j < EARLY_PARTIALS; ++j) {
+                const int c = group + 16 * j;
+                early_part[q][j] = c < a.partial_count ? load_stream1(a.partials_in + (size_t)c * PARTIAL_STRIDE + token) : 0.0f;
+            }
+        }
+    }
+
+    constexpr int SLOTS_X = HELD > 0 ? HELD : 2;  // rolling: the current chunk and the next
+    uint4 xs[SLOTS_X][KB][NT][2];
+    if (HELD > 0) {
+#pragma unroll
+        for (int c = 0; c < HELD; ++c) load_x(c, xs[c]);
+    } else {
+        load_x(0, xs[0]);
+    }
+    bool scale_ready = false;
+    int unit = 0, local = 0;
+    for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x, ++local) {
+        // STREAM: what the epilogue reads, asked for before the tile's products
+        float early_res[NT][2][2], early_nw[2] = {0.0f, 0.0f}, early_bias[2] = {0.0f, 0.0f};
+        int rows[2];
+        rows[0] = tile_row(a, tile, g);
+        rows[1] = tile_row(a, tile, g + 8);
+        if (warp == 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (rows[h] >= 0 && a.mode == MODE_PLAIN) {
+                    if (a.bias) early_bias[h] = a.bias[rows[h]];
+                    if (a.res_in) early_nw[h] = a.next_norm_w[rows[h]];
+                }
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int token = n * 8 + t4 * 2 + e;
+                        early_res[n][e][h] = 0.0f;
+                        if (a.res_in && rows[h] >= 0 && token < a.T) early_res[n][e][h] = load_stream1(a.res_in + (size_t)token * a.N + rows[h]);
+                    }
+            }
+        }
+
+        float acc[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+
+        // one stage: wait for it, multiply this warp's columns, give it back
+        auto work = [&](int c, uint4 (&xv)[KB][NT][2]) {
+            const int s = unit % STAGES;
+            if (!mbar_wait(&full[s], (unit / STAGES) & 1)) timed_out = true;
+            const uint32_t base = smem_u32(ring + s * STAGE_BYTES);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const int col = warp * (KC / CONSUMERS) + kb * 64 + t4 * 16;  // within the chunk
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint4 wl = make_uint4(0u, 0u, 0u, 0u), wh = wl;
+                    if (c * KC + col + h * 8 < a.K) {  // past K the stage holds what an earlier chunk left
+                        wl = lds16(base + g * ROW_BYTES + (col + h * 8) * 2);
+                        wh = lds16(base + (g + 8) * ROW_BYTES + (col + h * 8) * 2);
+                    }
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+                        mma_bf16(acc[n], wl.x, wh.x, wl.y, wh.y, xv[kb][n][h].x, xv[kb][n][h].y);
+                        mma_bf16(acc[n], wl.z, wh.z, wl.w, wh.w, xv[kb][n][h].z, xv[kb][n][h].w);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            ++unit;
+        };
+        if constexpr (HELD > 0) {
+#pragma unroll
+            for (int c = 0; c < HELD; ++c) work(c, xs[c]);
+        } else {
+            for (int c = 0; c < chunks; ++c) {
+                // the next unit's activations travel while this one is worked on
+                const int next_c = c + 1 < chunks ? c + 1 : 0;
+                const bool more = c + 1 < chunks || tile + (int)gridDim.x < a.tiles;
+                if (more) load_x(next_c, xs[1]);
+                work(c, xs[0]);
+                if (more) {
+#pragma unroll
+                    for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                        for (int n = 0; n < NT; ++n)
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) xs[0][kb][n][h] = xs[1][kb][n][h];
+                }
+            }
+        }
+
+        // ---- the tile's partial sums meet in shared memory, in warp order
+        float* mine = partial + (size_t)(local & 1) * CONSUMERS * NT * 128;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mine[((warp * NT + n) * 32 + lane) * 4 + e] = acc[n][e];
+        if (!scale_ready && a.partials_in) {
+#pragma unroll
+            for (int q = 0; q < SLOTS; ++q) {
+                const int i = threadIdx.x + q * CONSUMERS * 32;
+                const int group = i / PARTIAL_STRIDE, token = i % PARTIAL_STRIDE;
+                float sum = 0.0f;
+#pragma unroll
+                for (int j = 0; j < EARLY_PARTIALS; ++j) sum += early_part[q][j];
+                for (int c = group + 16 * EARLY_PARTIALS; c < a.partial_count; c += 16)
+                    sum += load_stream1(a.partials_in + (size_t)c * PARTIAL_STRIDE + token);
+                square_parts[group * PARTIAL_STRIDE + token] = sum;
+            }
+            scale_ready = true;
+        }
+        consumer_barrier();
+        for (int i = threadIdx.x; i < NT * 128; i += CONSUMERS * 32) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < CONSUMERS; ++w) sum += mine[w * NT * 128 + i];
+            mine[i] = sum;  // only this thread touches this element
+        }
+        consumer_barrier();
+        if (warp != 0) continue;
+
+        // ---- epilogue (warp 0).  In a lane: c0: (row g, token 2t), c1: (row g, token 2t+1), c2/c3: row g + 8.
+        if (a.res_in) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int token = n * 8 + t4 * 2 + e;
+                    float squares = 0.0f;
+                    if (token < a.T) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (rows[h] < 0) continue;
+                            const size_t at = (size_t)token * a.N + rows[h];
+                            const float v = early_res[n][e][h] + mine[(n * 32 + lane) * 4 + 2 * h + e] + early_bias[h];
+                            a.res_out[at] = v;
+                            a.x_out[at] = __float2bfloat16_rn(v * early_nw[h]);
+                            squares += v * v;
+                        }
+                    }
+                    squares += __shfl_xor_sync(0xffffffffu, squares, 4);
+                    squares += __shfl_xor_sync(0xffffffffu, squares, 8);
+                    squares += __shfl_xor_sync(0xffffffffu, squares, 16);
+                    if (g == 0) a.partials_out[(size_t)tile * PARTIAL_STRIDE + token] = squares;
+                }
+            }
+            continue;
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int token = n * 8 + t4 * 2 + e;
+                if (token >= a.T) continue;
+                float lo = mine[(n * 32 + lane) * 4 + e], hi = mine[(n * 32 + lane) * 4 + 2 + e];
+                if (a.partials_in) {
+                    float total = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) total += square_parts[c * PARTIAL_STRIDE + token];
+                    const float inv = rsqrtf(total / (float)a.norm_k + a.eps);
+                    lo *= inv;
+                    hi *= inv;
+                }
+                if (a.mode == MODE_GLU) {
+                    if (rows[0] >= 0) {
+                        const float v = lo / (1.0f + expf(-lo)) * hi;
+                        const size_t at = (size_t)token * a.inter + rows[0];
+                        if (a.out_f32) ((float*)a.y)[at] = v;
+                        else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
+                    }
+                } else {
+                    if (rows[0] >= 0) {
+                        const float v = lo + early_bias[0];
+                        const size_t at = (size_t)token * a.N + rows[0];
+                        if (a.out_f32) ((float*)a.y)[at] = v;
+                        else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
+                    }
+                    if (rows[1] >= 0) {
+                        const float v = hi + early_bias[1];
+                        const size_t at = (size_t)token * a.N + rows[1];
+                        if (a.out_f32) ((float*)a.y)[at] = v;
+                        else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+    pdl_trigger();
+    if (timed_out && lane == 0 && a.status) atomicExch(a.status, 1);
+}
+
+template <int NT, int HELD>
+int launch_as(const StreamArgs& a, int sm_count, cudaStream_t stream) {
+    constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + (2 * CONSUMERS * NT * 128 + 16 * PARTIAL_STRIDE) * 4 + 128;
+    auto kernel = gemm_stream_kernel<NT, HELD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int grid = a.tiles < sm_count ? a.tiles : sm_count;
+    launch_kernel(kernel, grid, THREADS, SMEM, stream, a);
+    return launch_status();
+}
+
+int launch_stream(StreamArgs& a, int sm_count, cudaStream_t stream) {
+    a.tiles = a.mode == MODE_GLU ? (a.inter + 7) / 8 : (a.N + ROWS - 1) / ROWS;
+    a.status = shiso_tc_status_word();
+    const int chunks = (a.K + KC - 1) / KC;
+    if (a.T <= 8) {
+        if (chunks == 1) return launch_as<1, 1>(a, sm_count, stream);
+        if (chunks == 2) return launch_as<1, 2>(a, sm_count, stream);
+        return launch_as<1, 0>(a, sm_count, stream);
+    }
+    if (chunks == 1) return launch_as<2, 1>(a, sm_count, stream);
+    if (chunks == 2) return launch_as<2, 2>(a, sm_count, stream);  // many registers: no successor beside it
+    return launch_as<2, 0>(a, sm_count, stream);
+}
+
+}  // namespace
+
+// x [T, K] bf16 (T <= 16), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
+// inter == 0: y[T, N] = x w^T (+ bias).  inter > 0: N == 2 * inter, y[T, inter] = silu(x gate^T) * (x up^T).
+// In the GLU layout a tile's row r < 8 is gate row 8 * tile + r and row r >= 8 its up row.
+SHISO_API int shiso_gemm_stream(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
+                                int K, int inter, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (T > 16 || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
+    if (inter > 0 && (N != 2 * inter || bias)) return SHISO_ERR_SHAPE;
+    StreamArgs a = {};
+    a.x = (const __nv_bfloat16*)x;
+    a.w = (const __nv_bfloat16*)w;
+    a.bias = bias;
+    a.y = y;
+    a.T = T;
+    a.N = N;
+    a.K = K;
+    a.inter = inter;
+    a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    a.mode = inter > 0 ? MODE_GLU : MODE_PLAIN;
+    return launch_stream(a, sm_count, stream);
+}
+
+// A block's output projection into the residual stream: res_out = res_in + x w^T (+ bias),
+// x_out = bf16(res_out * next_norm_w), partials_out[tile][token] = sum over the tile's 16 features
+// of res_out^2 (ceil(N / 16) rows of 16 floats).
+SHISO_API int shiso_gemm_stream_into(const void* x, const void* w, const float* bias, const float* res_in,
+                                     float* res_out, const float* next_norm_w, void* x_out, float* partials_out,
+                                     int T, int N, int K, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (T > 16 || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
+    if (!res_in || !res_out || res_in == res_out || !next_norm_w || !x_out || !partials_out) return SHISO_ERR_SHAPE;
+    StreamArgs a = {};
+    a.x = (const __nv_bfloat16*)x;
+    a.w = (const __nv_bfloat16*)w;
+    a.bias = bias;
+    a.T = T;
+    a.N = N;
+    a.K = K;
+    a.mode = MODE_PLAIN;
+    a.res_in = res_in;
+    a.res_out = res_out;
+    a.next_norm_w = next_norm_w;
+    a.x_out = (__nv_bfloat16*)x_out;
+    a.partials_out = partials_out;
+    return launch_stream(a, sm_count, stream);
+}
+
+// The product after it: y = (x w^T) * rsqrt(sum_c partials[c][token] / K + eps) per token (then
+// SwiGLU when inter > 0).
+SHISO_API int shiso_gemm_stream_scaled(const void* x, const float* partials, int partial_count, float eps,
+                                       const void* w, void* y, int y_dtype, int T, int N, int K, int inter,
+                                       int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (T > 16 || K % 8 != 0 || K <= 0 || !partials || partial_count <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
+    if (inter > 0 && N != 2 * inter) return SHISO_ERR_SHAPE;
+    StreamArgs a = {};
+    a.x = (const __nv_bfloat16*)x;
+    a.w = (const __nv_bfloat16*)w;
+    a.y = y;
+    a.T = T;
+    a.N = N;
+    a.K = K;
+    a.inter = inter;
+    a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    a.mode = inter > 0 ? MODE_GLU : MODE_PLAIN;
+    a.partials_in = partials;
+    a.partial_count = partial_count;
+    a.norm_k = K;
+    a.eps = eps;
+    return launch_stream(a, sm_count, stream);
+}

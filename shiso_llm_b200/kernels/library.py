@@ -30,9 +30,10 @@ _SIGNATURES = {
     "shiso_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
     "shiso_gemm_tcgen05_status": [],
-    "shiso_gemm_skinny": [P, P, P, P, I, I, I, I, I, P, LL, P],
-    "shiso_gemm_skinny_stream": [P, P, P, P, P, P, P, P, I, I, I, P, LL, P],
-    "shiso_gemm_skinny_scaled": [P, P, I, F, P, P, I, I, I, I, I, P, LL, P],
+    "shiso_gemm_skinny": [P, P, P, P, I, I, I, I, I, P],
+    "shiso_gemm_stream": [P, P, P, P, I, I, I, I, I, I, P],
+    "shiso_gemm_stream_into": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "shiso_gemm_stream_scaled": [P, P, I, F, P, P, I, I, I, I, I, I, P],
     "shiso_short_conv": [P, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, I, P],
     "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],

@@ -163,35 +163,15 @@ def _sm_count() -> int:
     return _SM_COUNT
 
 
-PREFETCH_MAX_BYTES = 48 << 20  # of the next matrix; L2 holds 126 MB and this one is passing through it too
-
-
-def link_matrices(matrices) -> None:
-    """``matrices``: the large matrices one step reads, in the order it reads them.  Each gets
-    its successor as the attribute ``read_next`` (the last one the first: the next step starts
-    there), and a weight-streaming product asks for that successor to be brought into L2 while
-    it streams its own rows."""
-    matrices = [m for m in matrices if m is not None]
-    for m, nxt in zip(matrices, matrices[1:] + matrices[:1]):
-        if nxt is not m:
-            m.read_next = nxt
-
-
-def _next_matrix(w):
-    nxt = getattr(w, "read_next", None)
-    if nxt is None or not nxt.is_cuda or not nxt.is_contiguous():
-        return 0, 0
-    return nxt.data_ptr(), min(nxt.numel() * nxt.element_size(), PREFETCH_MAX_BYTES)
+STREAM_KERNEL_MAX_TOKENS = 16  # up to here the persistent weight-streaming kernel runs the product
 
 
 def _takes_skinny(tokens: int, n: int) -> bool:
-    """Which plain products the weight-streaming kernel runs (measured inside captured steps
-    against the tensor-memory kernel): up to 8 rows always; up to 16 rows unless the matrix is
-    as tall as a vocabulary; up to 32 rows for matrices of at most 8192 rows."""
-    if tokens <= 8:
+    """Which plain products a weight-streaming kernel runs rather than the tensor-memory kernel
+    (measured inside captured steps): up to 16 rows always (the persistent kernel); up to 32 rows
+    for matrices of at most 8192 rows (the one-shot kernel)."""
+    if tokens <= STREAM_KERNEL_MAX_TOKENS:
         return True
-    if tokens <= SKINNY_MAX_TOKENS:
-        return n < 32768
     return tokens <= 32 and n <= 8192
 
 
@@ -213,10 +193,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     lib = library()
     both_bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     if both_bf16 and k % 8 == 0 and _takes_skinny(tokens, n):
-        next_ptr, next_bytes = _next_matrix(w)
-        status = lib.shiso_gemm_skinny(
-            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, next_ptr, next_bytes, _stream()
-        )
+        if tokens <= STREAM_KERNEL_MAX_TOKENS:
+            status = lib.shiso_gemm_stream(
+                _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
+            )
+            _done(status, "linear (streaming)")
+            return out
+        status = lib.shiso_gemm_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _stream())
         _done(status, "linear (skinny)")
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
@@ -253,10 +236,15 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0
     ):
         out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
-        next_ptr, next_bytes = _next_matrix(gate_up)
+        if tokens <= STREAM_KERNEL_MAX_TOKENS:
+            status = library().shiso_gemm_stream(
+                _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
+                _sm_count(), _stream(),
+            )
+            _done(status, "linear_swiglu (streaming)")
+            return out
         status = library().shiso_gemm_skinny(
-            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
-            next_ptr, next_bytes, _stream(),
+            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2, _stream()
         )
         _done(status, "linear_swiglu (skinny)")
         return out
@@ -282,7 +270,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
     return swiglu(linear(x, gate_up, out_dtype))
 
 
-STREAM_MAX_TOKENS = 8  # rows the product-into-stream / scaled-product pair takes (the kernel itself takes 16, spilling)
+STREAM_MAX_TOKENS = 16  # rows the product-into-stream / scaled-product pair takes (those of the streaming kernel)
 
 
 class ScaledRows:
@@ -303,7 +291,7 @@ def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
     n = w.shape[0]
     if (
         x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or residual.dtype != torch.float32
-        or tokens > STREAM_MAX_TOKENS or k % 8 or w.shape[1] != k or n % 8
+        or tokens > min(STREAM_MAX_TOKENS, STREAM_KERNEL_MAX_TOKENS) or k % 8 or w.shape[1] != k or n % 8
     ):
         return None
     _check(x, "x", torch.bfloat16, 2)
@@ -317,10 +305,9 @@ def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
     summed = torch.empty_like(residual)
     rows = torch.empty((tokens, n), dtype=torch.bfloat16, device=x.device)
     partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
-    next_ptr, next_bytes = _next_matrix(w)
-    status = library().shiso_gemm_skinny_stream(
+    status = library().shiso_gemm_stream_into(
         _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
-        tokens, n, k, next_ptr, next_bytes, _stream(),
+        tokens, n, k, _sm_count(), _stream(),
     )
     _done(status, "linear_into_stream")
     return summed, ScaledRows(rows, partials, eps)
@@ -338,10 +325,9 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
         raise KernelError(f"a matrix of shape {tuple(w.shape)} for rows of {k}")
     inter = n // 2 if glu else 0
     out = torch.empty((tokens, inter if glu else n), dtype=out_dtype, device=x.device)
-    next_ptr, next_bytes = _next_matrix(w)
-    status = library().shiso_gemm_skinny_scaled(
+    status = library().shiso_gemm_stream_scaled(
         _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.eps, _ptr(w), _ptr(out), _code(out),
-        tokens, n, k, inter, next_ptr, next_bytes, _stream(),
+        tokens, n, k, inter, _sm_count(), _stream(),
     )
     _done(status, "linear_scaled")
     return out

@@ -92,9 +92,6 @@ class GqaAttention(Mixer):
         for part in self.sub_parts():
             part.bind(tensors)
 
-    def matrices(self):
-        return [self.qkv, self.out]
-
     def cache_spec(self):
         if self.borrows_cache:
             return None

@@ -93,16 +93,6 @@ class Part:
     def sub_parts(self) -> list["Part"]:
         return []
 
-    def matrices(self) -> list[torch.Tensor]:
-        """After ``bind``: the large matrices the part reads in one step, in the order it reads
-        them.  The model strings the lists of all parts together so that a kernel streaming one
-        matrix can have the next one fetched meanwhile; a part that lists nothing just takes no
-        part in that."""
-        out = []
-        for sub in self.sub_parts():
-            out += sub.matrices()
-        return out
-
 
 class Norm(Part):
     def apply(self, x: torch.Tensor) -> torch.Tensor:

@@ -59,8 +59,5 @@ class LinearHead(Head):
     def bind(self, tensors):
         self.weight = tensors[self.tied_to if self.tied_to is not None else self.tensor_name]
 
-    def matrices(self):
-        return [self.weight]
-
     def forward(self, x):
         return self.env.ops.linear(x, self.weight, torch.float32)

@@ -44,9 +44,6 @@ class SwiGLU(FeedForward):
         self.gate_up = torch.cat([g, u], dim=0).contiguous()
         self.down = tensors[down]
 
-    def matrices(self):
-        return [self.gate_up, self.down]
-
     def forward(self, x, step):
         ops = self.env.ops
         mid = project(ops, x, self.gate_up, self.env.dtype, glu=True)

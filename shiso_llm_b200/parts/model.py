@@ -42,16 +42,6 @@ class Model:
         for part in self.parts():
             part.bind(tensors)
         self.bound = True
-        link = getattr(self.env.ops, "link_matrices", None)
-        if link is not None:
-            link(self.matrix_order())
-
-    def matrix_order(self) -> list:
-        """The large matrices of one step in the order the step reads them."""
-        order = []
-        for entry in self.plan.order:
-            order += self.blocks[entry.layer].matrices()
-        return order + self.head.matrices()
 
     @property
     def graph_safe(self) -> bool:

@@ -54,9 +54,6 @@ class ShortConv(Mixer):
         self.out_proj = tensors[self.names["out_proj"]]
         self.bias = tensors[self.bias_name] if self.has_bias else None
 
-    def matrices(self):
-        return [self.in_proj, self.out_proj]
-
     def cache_spec(self):
         return FixedState((self.taps - 1, self.hidden))
 
