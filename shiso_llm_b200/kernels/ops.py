@@ -286,7 +286,9 @@ def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
     """A block's output projection, the residual add and the first half of the next RMS norm in
     one launch, for a handful of bfloat16 rows: returns ``(residual + x @ w^T, ScaledRows)`` -
     ``residual`` (float32 ``[T, N]``) itself is not changed - or None when sizes or types are
-    not the ones the kernel takes."""
+    not the ones the kernel takes.  (The same pair of epilogues in the tensor-memory kernel for
+    long prompts was measured slower than product + row kernel: there a thread owns a row, and
+    its strided reads and writes of the stream cost more than the row kernel they replace.)"""
     tokens, k = x.shape
     n = w.shape[0]
     if (
