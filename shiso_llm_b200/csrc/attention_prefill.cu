@@ -17,9 +17,9 @@
 // rows outside the tile's range are zero-filled, never read (a window group's table has
 // holes there).
 //
-// The tensor-memory path (tcgen05) is used for the matrix products of the model, which are
-// 97 % of a prompt step's arithmetic; this kernel keeps the register-resident mma.sync form
-// because the softmax between its two products lives in registers.
+// Long portions of head size 64 take the tensor-memory kernel of attention_prefill_tc.cu; this
+// one, with the softmax between its two products in registers, takes every other head size
+// (multiples of 16 up to 128), short portions, and steps that mix a few prompt rows with decode rows.
 #include "common.cuh"
 
 namespace {

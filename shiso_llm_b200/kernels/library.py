@@ -27,6 +27,8 @@ _SIGNATURES = {
     "shiso_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_swiglu": [P, P, P, I, I, I, I, P],
     "shiso_gemm_tcgen05_prompt": [P, P, P, P, I, I, I, I, I, I, P],
+    "shiso_prefill_attention_tc_supported": [I, I],
+    "shiso_prefill_attention_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, LL, F, I, P],
     "shiso_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
     "shiso_gemm_tcgen05_status": [],

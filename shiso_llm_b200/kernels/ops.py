@@ -438,6 +438,8 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
 MAX_DECODE_GROUP = 16  # query heads per KV head the decode kernel serves from one read (rows of one MMA tile)
 DECODE_HEAD_DIMS = tuple(range(16, 129, 16))  # larger head sizes take the general kernel
 PREFILL_MAX_HEAD_DIM = 128  # the tiled prompt kernel keeps a row's output in registers
+TC_ATTENTION_MIN_TOKENS = 256  # steps from here on, with a portion of at least ...
+TC_ATTENTION_MIN_PORTION = 128  # ... this many rows, take the tensor-memory attention kernel (head size 64)
 
 
 def decode_splits(tokens: int, kv_heads: int, capacity: int) -> int:
@@ -479,6 +481,24 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
             float(scale), int(window), splits, _stream(),
         )
         _done(status, "decode_attention", 2)
+        return out
+    elif (
+        q.dtype == torch.bfloat16 and tokens >= TC_ATTENTION_MIN_TOKENS
+        and getattr(step, "max_q_len", tokens) >= TC_ATTENTION_MIN_PORTION
+        and lib.shiso_prefill_attention_tc_supported(head_dim, page_size)
+    ):
+        # long portions: products in tensor memory, 128 query rows per CTA
+        starts = getattr(step, "h_q_start", None)
+        if starts:
+            tiles = sum(-(-(b - a) // 128) for a, b in zip(starts[:-1], starts[1:]))
+        else:
+            tiles = tokens // 128 + step.num_seqs
+        status = lib.shiso_prefill_attention_tc(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
+            _ptr(step.start_pos), _ptr(out), tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
+            k_cache.shape[0], float(scale), int(window), _stream(),
+        )
+        _done(status, "prefill_attention (tcgen05)")
         return out
     elif q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= PREFILL_MAX_HEAD_DIM:
         starts = getattr(step, "h_q_start", None)

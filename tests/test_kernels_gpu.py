@@ -386,6 +386,48 @@ def test_prefill_attention_tiles(case):
         close(got, want, dtype, f"tiled attention {case} window {window}")
 
 
+@pytest.mark.parametrize("case", [(4, 2, 16), (8, 2, 8), (3, 1, 64), (6, 6, 128), (32, 8, 16)])
+def test_prefill_attention_in_tensor_memory(case):
+    """Long portions of head size 64 in bfloat16 take the tcgen05 kernel (128 query rows per CTA,
+    key tiles of 128 through one TMA box per page): portions of several tiles beside short ones
+    and single rows, portions that start deep in a sequence, windows that cut inside and between
+    tiles and leave holes in the table; cache rows outside every range hold NaN."""
+    heads, kv_heads, page = case
+    d = 64
+    q_lens, starts = [300, 1, 130, 128, 5, 257], [0, 37, 300, 70, 333, 1000]
+    if heads >= 32:
+        q_lens, starts = [300, 130, 1], [200, 0, 5]
+    need = [-(-(s + n) // page) for s, n in zip(starts, q_lens)]
+    num_pages = sum(need) + 3
+    cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 170)
+    cpu.h_q_start = gpu.h_q_start = cpu.q_start.tolist()
+    cpu.max_q_len = gpu.max_q_len = max(q_lens)
+    dtype = torch.bfloat16
+    k = rnd((num_pages, page, kv_heads, d), dtype, 171)
+    v = rnd((num_pages, page, kv_heads, d), dtype, 172)
+    q = rnd((sum(q_lens), heads * d), dtype, 173)
+    scale = 1.0 / math.sqrt(d)
+    for window in (0, 200, 9):
+        want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, scale, window, cpu)
+        kn, vn, holes = k.clone(), v.clone(), table.clone()
+        used = set()
+        for s, (start, n) in enumerate(zip(starts, q_lens)):
+            lo = max(0, start + 1 - window) if window > 0 else 0
+            for p in range(lo, start + n):
+                used.add((table[s, p // page].item(), p % page))
+            for b in range(lo // page):
+                holes[s, b] = -1  # pages before every row's window
+        for pg in range(num_pages):
+            for r in range(page):
+                if (pg, r) not in used:
+                    kn[pg, r] = float("nan")
+                    vn[pg, r] = float("nan")
+        got = ops().paged_attention(q.cuda(), heads, kv_heads, d, kn.cuda(), vn.cuda(), holes.cuda(), page, scale, window, gpu)
+        ops().check_kernel_status()
+        assert torch.isfinite(got).all(), f"window {window}: something outside the range reached the result"
+        close(got, want, dtype, f"tensor-memory attention {case} window {window}")
+
+
 def test_prefill_attention_never_reads_outside_its_range():
     """Cache rows the portion must not see hold NaN: pages of other requests, positions after
     the portion, pages a window has passed (holes in the table)."""
