@@ -154,6 +154,98 @@ def prefill_flops(costs, config, tokens):
     return gemm + attention
 
 
+def run_workload(args, config, plan, full_layers) -> int:
+    """The two serving workloads beside the headline: whole requests through the scheduler and the
+    Python entry point, host token ids in and out, wall-clock time."""
+    import torch
+
+    from shiso_llm_b200 import LLM, SamplingParams
+    from shiso_llm_b200.engine import Engine, EngineOptions
+    from shiso_llm_b200.kernels import ops
+    from shiso_llm_b200.parts import BuildEnv, Model
+    from shiso_llm_b200.weights import random_device_tensors
+
+    device = torch.device("cuda:0")
+    ops.require()
+    probe = Model(plan, BuildEnv(dtype=torch.bfloat16, device=device, ops=ops))
+    tensors = random_device_tensors(probe.tensor_specs(), 0, torch.bfloat16, device)
+    del probe
+    gen = torch.Generator().manual_seed(4321)
+
+    def prompt(n):
+        return torch.randint(0, config.vocab_size, (n,), generator=gen).tolist()
+
+    def drive(llm, until=None):
+        """Steps until nothing is left (or ``until()`` holds); returns (steps, seconds)."""
+        torch.cuda.synchronize()
+        t0, steps = time.perf_counter(), 0
+        while llm.has_unfinished() and not (until and until()):
+            llm.step()
+            steps += 1
+        llm.drain()
+        torch.cuda.synchronize()
+        return steps, time.perf_counter() - t0
+
+    base = {
+        "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "unit": "tok/s", "higher_is_better": True,
+        "config": {"model": f"{args.preset} (random weights)", "layers_run": config.num_hidden_layers,
+                   "layers_full": full_layers, "hidden_size": config.hidden_size,
+                   "intermediate_size": config.intermediate_size, "page_size": 16},
+    }
+    if args.workload == "serve":
+        count, new_tokens, chunk = 64, 128, 512
+        lengths = torch.randint(16, 2049, (count,), generator=gen).tolist()
+        options = EngineOptions(dtype="bfloat16", ctx=4096, page_size=16, kv_cache_tokens=count * (2048 + new_tokens + 64),
+                                max_num_seqs=count, max_num_batched_tokens=chunk + count)
+        llm = LLM(Engine.from_plan(plan, tensors, options), prefill_chunk=chunk)
+        params = SamplingParams(temperature=0.0, max_new_tokens=new_tokens, ignore_eos=True)
+        for rep in range(2):  # the first pass warms up (graph captures, tensor maps); the second is timed
+            for n in lengths:
+                llm.add_request(prompt(n), params)
+            steps, seconds = drive(llm)
+            llm.scheduler.take_finished()
+        produced = count * new_tokens
+        print(json.dumps({**base, "metric": "generated tok/s, 64 concurrent requests, prompts 16..2048, 512-token portions, "
+                          "128 new tokens each (continuous batching through LLM.step)",
+                          "value": produced / seconds, "seconds": seconds, "steps": steps,
+                          "prompt_tokens": sum(lengths), "prompt_tok_s": sum(lengths) / seconds,
+                          "generated_tokens": produced, "preempted": llm.scheduler.stats["preempted"]}))
+        return 0
+    # mixed: 32 streams decode while one long prompt is read in portions; then 64 streams decode
+    streams, long_prompt, chunk, new_tokens = 32, 8192, 1024, 256
+    options = EngineOptions(dtype="bfloat16", ctx=8192 + 512, page_size=16,
+                            kv_cache_tokens=long_prompt + 512 + 64 * (1024 + new_tokens + 64),
+                            max_num_seqs=64, max_num_batched_tokens=chunk + 64)
+    llm = LLM(Engine.from_plan(plan, tensors, options), prefill_chunk=chunk)
+    params = SamplingParams(temperature=0.0, max_new_tokens=4096, ignore_eos=True)
+    results = {}
+    for rep in range(2):
+        ids = [llm.add_request(prompt(1024), params).id for _ in range(streams)]
+        drive(llm, until=lambda: all(r.decoding for r in llm.scheduler.running) and not llm.scheduler.waiting)
+        long_request = llm.add_request(prompt(long_prompt), SamplingParams(temperature=0.0, max_new_tokens=1, ignore_eos=True))
+        steps, seconds = drive(llm, until=lambda: long_request.state == "finished")
+        results["mixed"] = {"steps": steps, "seconds": seconds, "ms_per_step": seconds / max(steps, 1) * 1e3,
+                            "prompt_tok_s": long_prompt / seconds, "decode_tok_s_beside": streams * steps / seconds}
+        more = [llm.add_request(prompt(1024), params).id for _ in range(64 - streams)]
+        drive(llm, until=lambda: all(r.decoding for r in llm.scheduler.running) and not llm.scheduler.waiting)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(new_tokens):
+            llm.step()
+        llm.drain()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        results["decode_b64"] = {"tok_s": 64 * new_tokens / seconds, "ms_per_step": seconds / new_tokens * 1e3}
+        for rid in ids + more:
+            llm.abort(rid)
+        llm.drain()
+        llm.scheduler.take_finished()
+    print(json.dumps({**base, "metric": "prompt tok/s of one 8,192-token prompt read in 1,024-token portions beside 32 "
+                      "decoding streams; then decode tok/s at batch 64 (through LLM.step)",
+                      "value": results["mixed"]["prompt_tok_s"], **results}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -166,6 +258,11 @@ def main() -> int:
     parser.add_argument("--points", default="1,64", help="other decode batch sizes to report")
     parser.add_argument("--no-cuda-graphs", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--workload", choices=["decode", "serve", "mixed"], default="decode",
+                        help="decode: the contract's line (default).  serve: 64 concurrent requests with prompts of "
+                             "16..2048 tokens, 512-token portions, 128 new tokens each, through LLM.generate (use with "
+                             "--preset lfm2-350m).  mixed: one 8,192-token prompt in 1,024-token portions beside 32 "
+                             "decoding streams, then batch-64 decode of 256 tokens (use with --preset lfm2-2.6b).")
     parser.add_argument("--profiler-range", choices=["decode", "prefill"], default=None,
                         help="bracket the device-timed decode steps (or the prefill steps) with cudaProfilerStart/Stop, "
                              "for `ncu --profile-from-start off`")
@@ -204,6 +301,8 @@ def main() -> int:
     _, config, plan = plan_from_document(document)
 
     device = torch.device("cuda:0")
+    if args.workload != "decode":
+        return run_workload(args, config, plan, full_layers)
     batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip() and b.strip().lower() != "none"]
     max_batch = max(batches)
     budget = PROMPT_LEN + NEW_TOKENS + 64
@@ -353,7 +452,7 @@ def main() -> int:
             "prompt_len": PROMPT_LEN,
             "mean_context": main_point["context"],
             "page_size": 16,
-            "cuda_graphs": not args.no_cuda_graphs,
+            "step_launch": ("cuda graph" if not args.no_cuda_graphs else "kernel by kernel") + ", lookahead 1 in e2e",
             "l2": "inputs larger than L2 (1.8 GB of weights read per step)",
             "peaks": peak_source,
         },
