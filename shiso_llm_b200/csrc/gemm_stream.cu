@@ -1,19 +1,23 @@
 // Y[T, N] = X[T, K] * W[N, K]^T for up to 16 rows, bfloat16: the decode step's matrix products as
 // a persistent weight-streaming kernel.
 //
-// The one-shot kernel of gemm_skinny.cu gives a CTA 16 weight rows and lets it ask for all of
-// them at once; a matrix of more than two CTAs per SM then runs in waves, and every wave pays the
-// memory latency again.  Here one CTA per SM walks its share of the 16-row tiles, and a producer
-// warp keeps a ring of shared-memory stages full with bulk copies (cp.async.bulk, one per weight
-// row and 1,024-column chunk, completion counted on an mbarrier), up to three stages = 96 KB
-// ahead of the four consumer warps and independent of them: the weights stream from the first
-// cycle of the kernel - before its predecessor in the dependent-launch chain has finished - to
-// the last tile without a gap (a CTA takes less than half an SM's shared memory and registers, so
-// the successor's CTA can move in beside it and start its own stream).  The consumers split the chunk's columns (256 each), read their
-// 16-byte pieces of the two weight rows a lane owns from shared memory (rows are padded by 16
-// bytes, which spreads them over the banks) and feed mma.sync m16n8k16 exactly as the one-shot
-// kernel does, activations in registers with the same k permutation.  A tile's partial sums
-// meet in shared memory in warp order; warp 0 writes the result while the others go on.
+// At these sizes a product is over in a few microseconds and is bound by reading W once, so what
+// counts is that the weight bytes are in flight from the kernel's first cycle to its last.  (The
+// first version gave a CTA 16 weight rows and let it ask for all of them at once; a matrix of
+// more than two such CTAs per SM then runs in waves, and every wave pays the memory latency
+// again.)  One CTA per SM walks its share of the 16-row tiles.  A producer warp - lane r copies
+// weight row r - keeps a ring of three shared-memory stages full with bulk copies
+// (cp.async.bulk, 1,024 columns of a row each, completion counted on an mbarrier), up to 96 KB
+// ahead of the consumers and independent of them; it starts before the predecessor in the
+// dependent-launch chain has finished, and because a CTA takes less than half of an SM's shared
+// memory and registers, the successor's CTA moves in beside it and starts its own stream under
+// this one's tail.  Four consumer warps split a chunk's columns (256 each), read their 16-byte
+// pieces of the two weight rows a lane owns from shared memory (rows are padded by 16 bytes,
+// which spreads them over the banks) and feed mma.sync m16n8k16: weights are the M operand, tokens
+// the N operand; a lane's 8 consecutive k values feed two MMAs as (k0..k3 | k4..k7) and the
+// activation fragment, kept in registers, is loaded with the same permutation, so the sum over k
+// is the same set of products.  A tile's partial sums meet in shared memory in warp order; warp 0
+// writes the result while the others go on.
 //
 // What follows the product is folded into the epilogue, because at these sizes every extra kernel
 // costs more than its arithmetic:

@@ -13,9 +13,17 @@
 // 32q .. 32q+31, i.e. features).  Stages are handed back and forth with mbarriers: `full`
 // (TMA bytes landed) and `empty` (tcgen05.commit: the MMAs that read the stage are done).
 //
-// Small token counts leave too few feature tiles to fill 148 SMs, so the K dimension can be
-// split over a thread-block cluster (up to 8 CTAs); the partial tiles are summed through
-// distributed shared memory in a fixed order, so the result does not depend on timing.
+// Small token counts leave too few feature tiles to fill 148 SMs, so the K dimension is split
+// over a thread-block cluster of 2 to 8 CTAs, chosen so that the grid is one wave (48 feature
+// tiles: 3 CTAs each).  Token j of the tile is summed by the CTA of rank j % size: every CTA
+// pushes its partial values into that CTA's shared memory (remote stores into an inbox behind
+// the stages), the cluster meets once, and each CTA adds up what it was sent in rank order, so
+// the result does not depend on timing.  With a gate/up pair both accumulators travel and the
+// summing CTA applies the activation.  (Clock stamps showed where the first version's 18 us for
+// 64 tokens x 6144 x 2048 went: 4.7 us in the main loop, 3.6 us in a reduction that pulled its
+// terms with remote loads between two cluster barriers, and 9 us outside the CTA's own timeline -
+// a 176 KB CTA leaves no room for the next kernel's CTAs to start under its tail.  Three stages
+// and the push took it to 9.3 us.)
 //
 // Every wait is bounded by a clock limit; a wait that runs out sets a status word that the
 // host reads, frees the TMEM it holds and returns.
@@ -54,10 +62,11 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 // the matching up rows of its 128 features, keeps two accumulators in TMEM (columns 0..BN-1
 // and BN..2BN-1), and its epilogue writes silu(gate) * up - the token tile is read once for
 // 256 weight rows and the [T, 2 * inter] intermediate never exists.
+// (up to 64 tokens a CTA takes under half of an SM's shared memory, so that the CTAs of the next
+// product in a chain of dependent launches can move in and start their loads under this one's tail)
 template <int BN, int STAGES, int SPLITS, bool GLU>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, (BN <= 64 && !GLU) ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
-    static_assert(!GLU || SPLITS == 1, "the fused activation needs the whole sum in one CTA");
     constexpr int A_BYTES = BM * BK * 2;
     constexpr int A_TILES = GLU ? 2 : 1;
     constexpr int B_BYTES = BN * BK * 2;
@@ -67,7 +76,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    // with K split over a cluster, an inbox for the partial sums the other CTAs push stands behind
+    // the stages (not over them: a peer may push while this CTA's own loads are still landing)
+    constexpr int INBOX_BYTES = SPLITS > 1 ? A_TILES * SPLITS * ((BN + SPLITS - 1) / SPLITS) * BM * 4 : 0;
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES + INBOX_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* accum_bar = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
@@ -162,7 +174,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int feature = feature0 + warp * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
-    if constexpr (GLU) {
+    if constexpr (GLU && SPLITS == 1) {
         if (!bad) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 8) {
@@ -207,41 +219,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
     } else {
-        // Partial tiles go to this CTA's shared memory (token-major), the cluster meets, and
-        // CTA r sums tokens r, r + SPLITS, ... over the CTAs in rank order.
+        // Token j is summed by the CTA of rank j % SPLITS.  Every CTA pushes its partial values
+        // into the shared memory of the CTA that sums them (remote stores), the cluster meets
+        // once, and each CTA adds up what it was sent in rank order: no remote loads, and nobody
+        // reads a CTA's memory after the meeting, so a CTA may leave as soon as it is done.
         cg::cluster_group cluster = cg::this_cluster();
-        float* partial = (float*)smem;  // [BN][BM]; the stages are no longer in use
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 8) {
-            float v[8];
-            if (kb_count > 0 && !bad) {
-                tmem_ld8(lane_addr + c, v);
-            } else {
+        // With a gate/up pair both accumulators travel, and the CTA that has the sums applies
+        // the activation.
+        constexpr int OWN = (BN + SPLITS - 1) / SPLITS;  // tokens a CTA sums
+        float* inbox = (float*)(smem + STAGES * STAGE_BYTES);  // [A_TILES][SPLITS][OWN][BM]
+        const unsigned rank = cluster.block_rank();
+        float* target[SPLITS];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        for (int r = 0; r < SPLITS; ++r) target[r] = cluster.map_shared_rank(inbox, r) + (size_t)rank * OWN * BM;
+#pragma unroll
+        for (int t = 0; t < A_TILES; ++t) {
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) {
+                float v[16];
+                if (kb_count > 0 && !bad) {
+                    tmem_ld16(lane_addr + t * BN + c, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    target[(c + j) % SPLITS][(size_t)t * SPLITS * OWN * BM + ((c + j) / SPLITS) * BM + warp * 32 + lane] = v[j];
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) partial[(c + j) * BM + warp * 32 + lane] = v[j];
         }
         cluster.sync();
-        const unsigned rank = cluster.block_rank();
-        if (feature < p.N) {
-            const float b = p.bias ? p.bias[feature] : 0.0f;
-            for (int j = (int)rank; j < BN; j += SPLITS) {
-                const int token = token0 + j;
-                if (token >= p.T) break;
-                float sum = 0.0f;
+        const int out_rows = GLU ? p.inter : p.N;
+        if (feature < out_rows) {
+            const float b = (!GLU && p.bias) ? p.bias[feature] : 0.0f;
+#pragma unroll 4
+            for (int i = 0; i < OWN; ++i) {
+                const int j = i * SPLITS + (int)rank;
+                if (j >= BN || token0 + j >= p.T) break;
+                float sum[A_TILES];
 #pragma unroll
-                for (int r = 0; r < SPLITS; ++r) {
-                    const float* remote = cluster.map_shared_rank(partial, r);
-                    sum += remote[j * BM + warp * 32 + lane];
+                for (int t = 0; t < A_TILES; ++t) {
+                    sum[t] = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < SPLITS; ++r)  // rank order
+                        sum[t] += inbox[(((size_t)t * SPLITS + r) * OWN + i) * BM + warp * 32 + lane];
                 }
-                const size_t at = (size_t)token * p.N + feature;
-                if (p.out_f32) store_out<float>((float*)p.y, at, sum + b);
-                else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, sum + b);
+                float v = sum[0] + b;
+                if (GLU) v = sum[0] / (1.0f + expf(-sum[0])) * sum[A_TILES - 1];
+                const size_t at = (size_t)(token0 + j) * out_rows + feature;
+                if (p.out_f32) store_out<float>((float*)p.y, at, v);
+                else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v);
             }
         }
-        cluster.sync();  // nobody leaves while its shared memory may still be read
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -256,8 +285,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 template <int BN, int STAGES, int SPLITS, bool GLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
     constexpr int STAGE_BYTES = (GLU ? 2 : 1) * BM * BK * 2 + BN * BK * 2;
-    constexpr int PARTIAL_BYTES = SPLITS > 1 ? BN * BM * 4 : 0;
-    constexpr int TILE_BYTES = STAGES * STAGE_BYTES > PARTIAL_BYTES ? STAGES * STAGE_BYTES : PARTIAL_BYTES;
+    constexpr int PARTIAL_BYTES = SPLITS > 1 ? (GLU ? 2 : 1) * SPLITS * ((BN + SPLITS - 1) / SPLITS) * BM * 4 : 0;
+    constexpr int TILE_BYTES = STAGES * STAGE_BYTES + PARTIAL_BYTES;
     constexpr int SMEM = TILE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SPLITS, GLU>;
     static bool configured = false;
@@ -334,25 +363,30 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     CUtensorMap mw, mx;
     if (!tensor_map(w, N, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
 
-    if (bn >= 128) {
-        if (bn == 128) return launch<128, 5, 1>(mw, mx, p, stream);
-        return launch<256, 4, 1>(mw, mx, p, stream);
-    }
-    // Few tokens: split K over a cluster until the grid covers the SMs (each CTA keeps >= 2 k blocks).
+    if (bn == 256) return launch<256, 4, 1>(mw, mx, p, stream);
+    // Few tokens: split K over a cluster so that the grid is one wave that covers the SMs (one CTA
+    // per SM; each CTA keeps >= 2 k blocks).  Any cluster size up to 8 will do: 48 feature tiles
+    // take 3 CTAs each (144 CTAs), not 4 (192: a second wave for a quarter of the work).
     const int tiles = (int)ceil_div_u(N, BM) * (int)ceil_div_u(T, bn);
-    int splits = 1;
-    while (splits < 8 && tiles * splits * 2 <= sm_count + sm_count / 2 && total_kb / (splits * 2) >= 2) splits *= 2;
+    int splits = sm_count / (tiles > 0 ? tiles : 1);
+    splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+    while (splits > 1 && total_kb / splits < 2) --splits;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
 #define SHISO_PICK(BN_)                                                        \
     switch (splits) {                                                          \
-        case 1: return launch<BN_, 6, 1>(mw, mx, p, stream);                   \
-        case 2: return launch<BN_, 6, 2>(mw, mx, p, stream);                   \
-        case 4: return launch<BN_, 6, 4>(mw, mx, p, stream);                   \
-        default: return launch<BN_, 6, 8>(mw, mx, p, stream);                  \
+        case 1: return launch<BN_, 4, 1>(mw, mx, p, stream);                   \
+        case 2: return launch<BN_, 3, 2>(mw, mx, p, stream);                   \
+        case 3: return launch<BN_, 3, 3>(mw, mx, p, stream);                   \
+        case 4: return launch<BN_, 3, 4>(mw, mx, p, stream);                   \
+        case 5: return launch<BN_, 3, 5>(mw, mx, p, stream);                   \
+        case 6: return launch<BN_, 3, 6>(mw, mx, p, stream);                   \
+        case 7: return launch<BN_, 3, 7>(mw, mx, p, stream);                   \
+        default: return launch<BN_, 3, 8>(mw, mx, p, stream);                  \
     }
     if (bn == 16) { SHISO_PICK(16) }
     if (bn == 32) { SHISO_PICK(32) }
-    SHISO_PICK(64)
+    if (bn == 64) { SHISO_PICK(64) }
+    SHISO_PICK(128)
 #undef SHISO_PICK
 }
 
@@ -374,11 +408,32 @@ SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, i
     const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     CUtensorMap mw, mx;
     if (!tensor_map(w, 2 * inter, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
-    switch (bn) {
-        case 16: return launch<16, 5, 1, true>(mw, mx, p, stream);
-        case 32: return launch<32, 5, 1, true>(mw, mx, p, stream);
-        case 64: return launch<64, 4, 1, true>(mw, mx, p, stream);
-        case 128: return launch<128, 4, 1, true>(mw, mx, p, stream);
-        default: return launch<256, 3, 1, true>(mw, mx, p, stream);
+    if (bn >= 128) {
+        if (bn == 128) return launch<128, 4, 1, true>(mw, mx, p, stream);
+        return launch<256, 3, 1, true>(mw, mx, p, stream);
     }
+    // Few tokens: K split over a cluster of up to 4 CTAs, as for plain products (one wave over the SMs).
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    }
+    const int total_kb = (K + BK - 1) / BK;
+    const int tiles = (int)ceil_div_u(inter, BM) * (int)ceil_div_u(T, bn);
+    int splits = sm_count / (tiles > 0 ? tiles : 1);
+    splits = splits < 1 ? 1 : (splits > 4 ? 4 : splits);
+    while (splits > 1 && total_kb / splits < 2) --splits;
+    p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+#define SHISO_PICK_GLU(BN_)                                                          \
+    switch (splits) {                                                                \
+        case 1: return launch<BN_, 4, 1, true>(mw, mx, p, stream);                   \
+        case 2: return launch<BN_, 3, 2, true>(mw, mx, p, stream);                   \
+        case 3: return launch<BN_, 3, 3, true>(mw, mx, p, stream);                   \
+        default: return launch<BN_, 3, 4, true>(mw, mx, p, stream);                  \
+    }
+    if (bn == 16) { SHISO_PICK_GLU(16) }
+    if (bn == 32) { SHISO_PICK_GLU(32) }
+    SHISO_PICK_GLU(64)
+#undef SHISO_PICK_GLU
 }

@@ -32,7 +32,6 @@ _SIGNATURES = {
     "shiso_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
     "shiso_gemm_tcgen05_status": [],
-    "shiso_gemm_skinny": [P, P, P, P, I, I, I, I, I, P],
     "shiso_gemm_stream": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_stream_into": [P, P, P, P, P, P, P, P, I, I, I, I, P],
     "shiso_gemm_stream_scaled": [P, P, I, F, P, P, I, I, I, I, I, I, P],

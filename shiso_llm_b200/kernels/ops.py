@@ -151,8 +151,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 _SM_COUNT = None
-SKINNY_MAX_TOKENS = 16  # up to here a product is weight streaming and takes the skinny kernel
-PROMPT_MIN_TOKENS = 128  # from here the persistent tensor-memory kernel (tokens as the MMA's M operand)
+PROMPT_MIN_TOKENS = 129  # from here the persistent tensor-memory kernel (tokens as the MMA's M operand)
 PAIR_MIN_TOKENS = 512  # from here the same kernel on pairs of SMs (256-token tiles, half the operand traffic per SM)
 
 
@@ -164,15 +163,6 @@ def _sm_count() -> int:
 
 
 STREAM_KERNEL_MAX_TOKENS = 16  # up to here the persistent weight-streaming kernel runs the product
-
-
-def _takes_skinny(tokens: int, n: int) -> bool:
-    """Which plain products a weight-streaming kernel runs rather than the tensor-memory kernel
-    (measured inside captured steps): up to 16 rows always (the persistent kernel); up to 32 rows
-    for matrices of at most 8192 rows (the one-shot kernel)."""
-    if tokens <= STREAM_KERNEL_MAX_TOKENS:
-        return True
-    return tokens <= 32 and n <= 8192
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -192,15 +182,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
     out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
     lib = library()
     both_bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    if both_bf16 and k % 8 == 0 and _takes_skinny(tokens, n):
-        if tokens <= STREAM_KERNEL_MAX_TOKENS:
-            status = lib.shiso_gemm_stream(
-                _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
-            )
-            _done(status, "linear (streaming)")
-            return out
-        status = lib.shiso_gemm_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _stream())
-        _done(status, "linear (skinny)")
+    if both_bf16 and k % 8 == 0 and tokens <= STREAM_KERNEL_MAX_TOKENS:
+        status = lib.shiso_gemm_stream(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
+        )
+        _done(status, "linear (streaming)")
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         product = lib.shiso_gemm_tcgen05_pair if tokens >= PAIR_MIN_TOKENS else lib.shiso_gemm_tcgen05_prompt
@@ -222,7 +208,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
 
 def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """``silu(x @ gate^T) * (x @ up^T)`` for ``gate_up = [gate; up]`` of shape ``[2I, K]``.
-    In bfloat16 the activation is applied in the product's epilogue (the skinny kernel for a
+    In bfloat16 the activation is applied in the product's epilogue (the streaming kernel for a
     handful of rows, the tensor-memory kernel with two accumulators otherwise); other types
     run the product and then the activation kernel."""
     _check(x, "x", None, 2)
@@ -233,20 +219,14 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         raise KernelError(f"gate/up matrix of shape {tuple(gate_up.shape)} does not fit rows of {k}")
     if (
         x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
-        and tokens <= SKINNY_MAX_TOKENS and k % 8 == 0
+        and tokens <= STREAM_KERNEL_MAX_TOKENS and k % 8 == 0
     ):
         out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
-        if tokens <= STREAM_KERNEL_MAX_TOKENS:
-            status = library().shiso_gemm_stream(
-                _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
-                _sm_count(), _stream(),
-            )
-            _done(status, "linear_swiglu (streaming)")
-            return out
-        status = library().shiso_gemm_skinny(
-            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2, _stream()
+        status = library().shiso_gemm_stream(
+            _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
+            _sm_count(), _stream(),
         )
-        _done(status, "linear_swiglu (skinny)")
+        _done(status, "linear_swiglu (streaming)")
         return out
     lib = library()
     if (

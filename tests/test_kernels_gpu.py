@@ -459,7 +459,8 @@ def test_prefill_attention_never_reads_outside_its_range():
 
 
 @pytest.mark.parametrize("shape", [(1, 96, 64), (8, 2048, 2048), (5, 1000, 96), (8, 300, 200), (16, 2048, 5632), (13, 48, 264), (3, 16, 8),
-                                   (8, 4800, 1032), (2, 24, 3080), (24, 2048, 2048), (32, 1000, 264), (17, 40, 5632)])
+                                   (8, 4800, 1032), (2, 24, 3080), (24, 2048, 2048), (32, 1000, 264), (17, 40, 5632),
+                                   (64, 6144, 2048), (33, 2048, 5632), (50, 776, 264), (64, 48, 8), (40, 11264, 2048)])
 def test_skinny_linear_and_fused_swiglu(shape):
     """A handful of bfloat16 rows take the weight-streaming kernel; with a gate/up pair the
     activation is applied in its epilogue."""
