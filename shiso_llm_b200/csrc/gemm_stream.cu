@@ -34,6 +34,10 @@
 //           rounding.
 // What the STREAM and SCALED epilogues read from global memory is asked for at the start of a
 // tile, not when it is needed: the epilogue is the tail of a chain of dependent kernels.
+// (Measured and left out: filling a stage with four TMA boxes of 256 columns x 16 rows instead of
+// sixteen row copies.  The boxes are asked for faster - a copy costs its issuing lane some 35 ns
+// whatever its size - but their 512-byte row pieces use memory less well than 2 KB pieces of a
+// row: 30.0 against 26.7 us for the four products of a layer in a captured chain.)
 // (Asking, from inside this kernel, for the matrix the step reads next to be brought into L2 was
 // measured too - cp.async.bulk.prefetch.L2 over a slice per CTA - and made the whole step slower:
 // the stream already keeps memory busy, and the extra requests only delay its own rows.)
