@@ -56,3 +56,47 @@ def test_real_layer_sizes_every_kernel_route(sized, dtype):
     check_logits(got, reference, dtype, f"1.2B layer sizes, {dtype}")
     whole = replay.stack_rows(helpers.run_steps(engine, helpers.whole("b", tokens)), "b", len(tokens))
     check_logits(whole, reference, dtype, f"1.2B layer sizes whole, {dtype}")
+
+
+@pytest.fixture(scope="module")
+def sized_long(sized):
+    document, plan, specs, stored, _, _ = sized
+    a = helpers.random_prompt(640, document["vocab_size"], 5)
+    b = helpers.random_prompt(290, document["vocab_size"], 6)
+    return a, b, plain_lfm2.plain_forward(document, stored, a), plain_lfm2.plain_forward(document, stored, b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_sizes_long_portions_and_mixed_steps(sized, sized_long, dtype):
+    """Two requests at the same layer sizes through the routes only long steps take: a 600-row
+    portion (products on SM pairs, attention in tensor memory, the short conv over runs of rows),
+    a mixed step of a 20-row portion deep in one sequence beside the first 260 rows of another,
+    decode steps of two rows (the weight-streaming products with the row scale applied to their
+    accumulators) with one request further along than the other, and a 12-row portion."""
+    from shiso_llm_b200.kernels import ops
+
+    document, plan, specs, stored, _, _ = sized
+    a, b, ref_a, ref_b = sized_long
+    compute = torch.float32 if dtype == "float32" else torch.bfloat16
+    by = {s.name: s for s in specs}
+    tensors = {k: v.to("cuda", target_dtype(by[k], v.dtype, compute)) for k, v in stored.items()}
+    options = EngineOptions(dtype=dtype, ctx=1024, page_size=16, kv_cache_tokens=1024, max_num_seqs=2,
+                            max_num_batched_tokens=640)
+    engine = Engine.from_plan(plan, tensors, options, ops)
+
+    def every(n):
+        return list(range(n))
+
+    steps = [
+        ([("a", a[:600], every(600))], []),
+        ([("a", a[600:620], every(20)), ("b", b[:260], every(260))], []),
+    ]
+    for i in range(8):
+        steps.append(([("b", [b[260 + i]], [0]), ("a", [a[620 + i]], [0])], []))
+    steps.append(([("a", a[628:640], every(12))], ["a"]))
+    steps.append(([("b", b[268:290], every(22))], ["b"]))
+    rows = helpers.run_steps(engine, steps)
+    ops.check_kernel_status()
+    check_logits(replay.stack_rows(rows, "a", len(a)), ref_a, dtype, f"long request, {dtype}")
+    check_logits(replay.stack_rows(rows, "b", len(b)), ref_b, dtype, f"second request, {dtype}")
+    engine.cache.check()
