@@ -163,8 +163,8 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 _SM_COUNT = None
-PROMPT_MIN_TOKENS = 129  # from here the persistent tensor-memory kernel (tokens as the MMA's M operand)
-PAIR_MIN_TOKENS = 512  # from here the same kernel on pairs of SMs (256-token tiles, half the operand traffic per SM)
+PROMPT_MIN_TOKENS = 129  # from here the persistent tensor-memory kernels (tokens as the MMA's M operand): plain products on pairs of SMs
+PAIR_MIN_TOKENS_GLU = 512  # gate/up pairs below this stay on single SMs: the pairs' 256-token tiles would leave a second, nearly empty wave
 
 
 def _sm_count() -> int:
@@ -201,8 +201,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         _done(status, "linear (streaming)")
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
-        product = lib.shiso_gemm_tcgen05_pair if tokens >= PAIR_MIN_TOKENS else lib.shiso_gemm_tcgen05_prompt
-        status = product(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream())
+        status = lib.shiso_gemm_tcgen05_pair(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
+        )
         _done(status, "linear (tcgen05, persistent)")
         return out
     if both_bf16 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
@@ -247,7 +248,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
     ):
         out = torch.empty((tokens, two_inter // 2), dtype=out_dtype, device=x.device)
         if tokens >= PROMPT_MIN_TOKENS and (two_inter // 2) % 8 == 0:
-            product = lib.shiso_gemm_tcgen05_pair if tokens >= PAIR_MIN_TOKENS else lib.shiso_gemm_tcgen05_prompt
+            product = lib.shiso_gemm_tcgen05_pair if tokens >= PAIR_MIN_TOKENS_GLU else lib.shiso_gemm_tcgen05_prompt
             status = product(
                 _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter // 2, k, two_inter // 2,
                 _sm_count(), _stream(),
