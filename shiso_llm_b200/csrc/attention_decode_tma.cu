@@ -1,0 +1,394 @@
+// Paged GQA attention for decode steps (one token per sequence), bfloat16, head size 64:
+// the keys and values come in by TMA and the parts of a sequence are merged in the same kernel.
+//
+// The work is cut as in attention_decode.cu: one CTA per (part of the keys, KV head, sequence)
+// serves the query heads of the group from one read of the cache (the reference reads it once
+// per query head: kernels/cuda/dense/dense_attn.cuh:44-180).  What differs is how the bytes
+// move.  A producer warp brings every page of a 64-key tile with one 3-D TMA box (page rows x
+// one head x 64 values, 128-byte swizzle), each lane looking its own page up in the block
+// table, into a ring of four tiles with full/empty mbarriers: a CTA with four tiles or fewer
+// has all of its keys and values in flight at once, and a long part streams without a
+// CTA-wide barrier per tile.  Four consumer warps take 16 keys of a tile each (Q K^T and P V
+// as m16n8k16 MMAs, float softmax statistics) and are merged at the end.
+//
+// The parts of one (sequence, KV head) count themselves off on a counter; the CTA that
+// arrives last adds the parts up in index order and writes the output, so there is no second
+// launch, and the result does not depend on which CTA came last.  The counter is back at
+// zero when the kernel ends.
+//
+// Every wait is bounded by a clock limit and reports through the status word.
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int HEAD = 64;
+constexpr int TILE = 64;           // keys per tile
+constexpr int ROW = HEAD * 2;      // bytes per key or value row
+constexpr int TILE_BYTES = TILE * ROW;
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // keys, then values
+constexpr int STAGES = 4;
+constexpr int CONSUMERS = 4;
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int KSTEPS = HEAD / 16;
+constexpr int DTILES = HEAD / 8;
+constexpr int MERGE_ROW = HEAD + 2;  // floats: output, running maximum (log2 units), sum
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 128;
+static_assert(CONSUMERS * 16 * MERGE_ROW * 4 <= STAGES * STAGE_BYTES, "the merge area lies over the ring");
+
+struct DecodeTmaArgs {
+    const __nv_bfloat16* q;   // [T, heads * 64]
+    const int* block_table;   // [S, width]
+    const int* positions;     // [T]
+    const int* seq_of_token;  // [T]
+    float* partial;           // [T, heads, splits, 66]
+    int* counters;            // [T, kv_heads], zero between launches
+    __nv_bfloat16* out;       // [T, heads * 64]
+    int* status;
+    int width, heads, kv_heads, page_size, splits, window;
+    int cache_rows;           // pages * page size: a row coordinate from here on reads zeros
+    float scale_log2;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
+
+// (five warps take the registers of eight: the bound of 256 threads x 3 CTAs caps them at 85 a thread)
+__global__ void __launch_bounds__(256, 3)
+decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeTmaArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // [STAGES][keys | values]
+    uint64_t* full = (uint64_t*)(ring + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    int* shared_ints = (int*)(empty + STAGES);  // [0] failed, [1] this CTA merges the parts
+    float* merge = (float*)ring;                // after the loop: [CONSUMERS][16][MERGE_ROW]
+
+    const int split = blockIdx.x, g_head = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pages_per_tile = TILE / a.page_size;
+
+    // Step data (positions, tables) was uploaded before the chain of kernels began: it may be
+    // read before the predecessor has finished.  Tiles are counted on the absolute 64-key grid,
+    // so that a tile is whole pages whatever the window's edge.
+    const int pos = a.positions[t];
+    const int lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
+    const int first_tile = lo / TILE, last_tile = pos / TILE;
+    const int n_tiles = last_tile - first_tile + 1;
+    const int per_part = (n_tiles + a.splits - 1) / a.splits;
+    const int parts = (n_tiles + per_part - 1) / per_part;  // parts that have keys
+    const int tile0 = first_tile + split * per_part;
+    const int my_tiles = min(per_part, last_tile + 1 - tile0);
+    if (my_tiles <= 0) return;  // uniform: a part past the sequence's end
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 2 * pages_per_tile);  // one arrival (with its bytes) per box
+            mbar_init(&empty[s], CONSUMERS);
+        }
+        shared_ints[0] = 0;
+        shared_ints[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    bool failed = false;
+
+    const int group = a.heads / a.kv_heads;
+    const int g = lane >> 2, t4 = lane & 3;
+    float o_acc[DTILES][4];
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+
+    if (warp == CONSUMERS) {
+        // ---- producer: a lane owns one box (a page of keys or of values) of one of the tiles
+        // of a round; it waits for the stage, announces its bytes and issues the copy
+        const int boxes = 2 * pages_per_tile;
+        const int tiles_per_round = min(STAGES, 32 / boxes);
+        const int sub = lane / boxes, rest = lane % boxes, kv = rest & 1, pg = rest >> 1;
+        const int* table = a.block_table + (size_t)a.seq_of_token[t] * a.width;
+        const uint32_t box_bytes = a.page_size * ROW;
+        for (int base = 0; base < my_tiles && !failed; base += tiles_per_round) {
+            const int i = base + sub;
+            const bool on = sub < tiles_per_round && i < my_tiles;
+            int row = a.cache_rows;  // a page wholly outside the keys this token sees: zeros
+            if (on) {
+                const int key = (tile0 + i) * TILE + pg * a.page_size;
+                if (key <= pos && key + a.page_size > lo) row = table[key / a.page_size] * a.page_size;
+            }
+            if (base == 0) pdl_wait();  // the cache rows of this step were written by the kernel before
+            if (on) {
+                const int stage = i % STAGES, use = i / STAGES;
+                if (use > 0 && !mbar_wait(&empty[stage], (use - 1) & 1)) {
+                    failed = true;
+                } else {
+                    mbar_expect_tx(&full[stage], box_bytes);
+                    tma_load_3d(ring + stage * STAGE_BYTES + kv * TILE_BYTES + pg * box_bytes, kv ? &map_v : &map_k, 0, g_head,
+                                row, &full[stage]);
+                }
+            }
+            failed = __any_sync(0xffffffffu, failed);
+        }
+    } else {
+        // ---- consumers: warp w scores keys 16w .. 16w+15 of every tile
+        pdl_wait();
+        uint32_t q_frag[KSTEPS][4];
+        {
+            // the group's queries as the 16 rows of the MMA's A operand (rows past the group are zero)
+            const uint32_t* q_lo = reinterpret_cast<const uint32_t*>(a.q + ((size_t)t * a.heads + g_head * group + min(g, group - 1)) * HEAD);
+            const uint32_t* q_hi = reinterpret_cast<const uint32_t*>(a.q + ((size_t)t * a.heads + g_head * group + min(g + 8, group - 1)) * HEAD);
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                q_frag[kk][0] = g < group ? q_lo[kk * 8 + t4] : 0u;
+                q_frag[kk][1] = g + 8 < group ? q_hi[kk * 8 + t4] : 0u;
+                q_frag[kk][2] = g < group ? q_lo[kk * 8 + 4 + t4] : 0u;
+                q_frag[kk][3] = g + 8 < group ? q_hi[kk * 8 + 4 + t4] : 0u;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.0f;
+        const uint32_t swz = lane & 7;  // a row's 16-byte pieces are stored at piece ^ (row & 7)
+        for (int i = 0; i < my_tiles; ++i) {
+            const int stage = i % STAGES, use = i / STAGES;
+            if (!mbar_wait(&full[stage], use & 1)) {
+                failed = true;
+                break;
+            }
+            const uint32_t kt = smem_u32(ring + stage * STAGE_BYTES) + warp * 16 * ROW;
+            const uint32_t vt = kt + TILE_BYTES;
+            const int key0 = (tile0 + i) * TILE + warp * 16;
+            if (key0 <= pos && key0 + 16 > lo) {  // warp-uniform: some of this warp's keys are seen
+                float s_acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    const uint32_t r = (lane & 7) + (lane >> 4) * 8;
+                    const uint32_t piece = kk * 2 + ((lane >> 3) & 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(kt + r * ROW + ((piece ^ swz) << 4), b0, b1, b2, b3);
+                    mma16816(s_acc[0], q_frag[kk], b0, b1);
+                    mma16816(s_acc[1], q_frag[kk], b2, b3);
+                }
+                float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + t4 * 2 + (e & 1);
+                        const float v = (key >= lo && key <= pos) ? s_acc[j][e] * a.scale_log2 : -INFINITY;
+                        s_acc[j][e] = v;
+                        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                    }
+                }
+                float correction[2], use_max[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float m = tile_max[r];
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                    const float new_max = fmaxf(row_max[r], m);  // finite: one of the 16 keys is seen
+                    use_max[r] = new_max;
+                    correction[r] = exp2f(row_max[r] - new_max);
+                    row_max[r] = new_max;
+                }
+                float tile_sum[2] = {0.0f, 0.0f};
+                uint32_t p_frag[4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    float p[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        p[e] = exp2f(s_acc[j][e] - use_max[e >> 1]);
+                        tile_sum[e >> 1] += p[e];
+                    }
+                    p_frag[j * 2 + 0] = pack2(p[0], p[1]);
+                    p_frag[j * 2 + 1] = pack2(p[2], p[3]);
+                }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * correction[r] + tile_sum[r];
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d) {
+                    o_acc[d][0] *= correction[0];
+                    o_acc[d][1] *= correction[0];
+                    o_acc[d][2] *= correction[1];
+                    o_acc[d][3] *= correction[1];
+                }
+#pragma unroll
+                for (int dn = 0; dn < DTILES; dn += 2) {
+                    const uint32_t r = (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const uint32_t piece = dn + (lane >> 4);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_trans(vt + r * ROW + ((piece ^ swz) << 4), b0, b1, b2, b3);
+                    mma16816(o_acc[dn], p_frag, b0, b1);
+                    mma16816(o_acc[dn + 1], p_frag, b2, b3);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);  // the producer may refill the stage
+        }
+    }
+    pdl_trigger();
+    if (failed) shared_ints[0] = 1;
+    if (warp == CONSUMERS) return;
+
+    // ---- the four warps' results side by side (over the ring: every tile has been consumed)
+    consumer_sync();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        float* dst = merge + ((size_t)warp * 16 + g + r * 8) * MERGE_ROW;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            dst[d * 8 + t4 * 2] = o_acc[d][r * 2];
+            dst[d * 8 + t4 * 2 + 1] = o_acc[d][r * 2 + 1];
+        }
+        if (t4 == 0) {
+            dst[HEAD] = row_max[r];
+            dst[HEAD + 1] = sum;
+        }
+    }
+    consumer_sync();
+    const bool alone = parts == 1;  // nothing to merge with: the output is written here
+    for (int i = tid; i < group * HEAD; i += CONSUMERS * 32) {
+        const int h = i / HEAD, col = i % HEAD;
+        float m = -INFINITY;
+        for (int w = 0; w < CONSUMERS; ++w) m = fmaxf(m, merge[((size_t)w * 16 + h) * MERGE_ROW + HEAD]);
+        float sum = 0.0f, o = 0.0f;
+        for (int w = 0; w < CONSUMERS; ++w) {
+            const float* src = merge + ((size_t)w * 16 + h) * MERGE_ROW;
+            const float f = src[HEAD] == -INFINITY ? 0.0f : exp2f(src[HEAD] - m);
+            sum += f * src[HEAD + 1];
+            o += f * src[col];
+        }
+        const size_t head = (size_t)t * a.heads + g_head * group + h;
+        if (alone) {
+            a.out[head * HEAD + col] = __float2bfloat16_rn(sum > 0.0f ? o / sum : 0.0f);
+        } else {
+            float* dst = a.partial + (head * a.splits + split) * MERGE_ROW;
+            dst[col] = o;
+            if (col == 0) {
+                dst[HEAD] = m;
+                dst[HEAD + 1] = sum;
+            }
+        }
+    }
+    if (!alone) {
+        // count this part off; the last one of the (sequence, KV head) adds the parts up
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) {
+            int* counter = a.counters + (size_t)t * a.kv_heads + g_head;
+            const int before = atomicAdd(counter, 1);
+            if (before == parts - 1) {
+                *counter = 0;  // no other part touches it any more in this launch
+                shared_ints[1] = 1;
+            }
+        }
+        consumer_sync();
+        if (shared_ints[1] != 0) {
+            __threadfence();
+            for (int i = tid; i < group * HEAD; i += CONSUMERS * 32) {
+                const int h = i / HEAD, col = i % HEAD;
+                const size_t head = (size_t)t * a.heads + g_head * group + h;
+                const float* base = a.partial + head * a.splits * MERGE_ROW;
+                float m = -INFINITY;
+                for (int s = 0; s < parts; ++s) m = fmaxf(m, __ldcg(base + s * MERGE_ROW + HEAD));
+                float sum = 0.0f, acc = 0.0f;
+                for (int s = 0; s < parts; ++s) {
+                    const float sm = __ldcg(base + s * MERGE_ROW + HEAD);
+                    const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
+                    sum += f * __ldcg(base + s * MERGE_ROW + HEAD + 1);
+                    acc += f * __ldcg(base + s * MERGE_ROW + col);
+                }
+                a.out[head * HEAD + col] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+            }
+        }
+    } else {
+        consumer_sync();
+    }
+    if (tid == 0 && shared_ints[0] != 0 && a.status) atomicExch(a.status, 1);
+}
+
+}  // namespace
+
+// Whether the TMA decode kernel takes this shape (others take shiso_decode_attention).
+SHISO_API int shiso_decode_attention_fused_supported(int heads, int kv_heads, int head_dim, int page_size) {
+    return head_dim == HEAD && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= 16 && page_size >= 8 &&
+           page_size <= TILE && page_size % 8 == 0 && TILE % page_size == 0 && tc::encode_fn() != nullptr;
+}
+
+// As shiso_decode_attention, with `counters` (tokens * kv_heads ints that are zero between
+// launches; the kernel leaves them zero) and the number of pages of the caches.
+SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                           int table_width, const int* positions, const int* seq_of_token, float* scratch,
+                                           int* counters, void* out, int tokens, int heads, int kv_heads, int head_dim,
+                                           int page_size, long long num_pages, float scale, int window, int splits,
+                                           cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
+    if (!shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size)) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SHISO_ERR_ALIGN;
+    if (tokens > 65535 || kv_heads > 65535) return SHISO_ERR_UNSUPPORTED;  // grid limits
+    const long long cache_rows = num_pages * page_size;
+    if (cache_rows + page_size > 0x7fffffffLL) return SHISO_ERR_UNSUPPORTED;
+    CUtensorMap mk, mv;
+    if (!tc::tensor_map_paged(k_cache, cache_rows, kv_heads, page_size, &mk) ||
+        !tc::tensor_map_paged(v_cache, cache_rows, kv_heads, page_size, &mv))
+        return SHISO_ERR_UNSUPPORTED;
+    DecodeTmaArgs a;
+    a.q = (const __nv_bfloat16*)q;
+    a.block_table = block_table;
+    a.positions = positions;
+    a.seq_of_token = seq_of_token;
+    a.partial = scratch;
+    a.counters = counters;
+    a.out = (__nv_bfloat16*)out;
+    a.status = shiso_tc_status_word();
+    a.width = table_width;
+    a.heads = heads;
+    a.kv_heads = kv_heads;
+    a.page_size = page_size;
+    a.splits = splits;
+    a.window = window;
+    a.cache_rows = (int)cache_rows;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, kv_heads, tokens);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = shiso_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, decode_tma_kernel, mk, mv, a);
+}

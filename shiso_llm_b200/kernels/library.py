@@ -39,6 +39,8 @@ _SIGNATURES = {
     "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "shiso_decode_attention": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
+    "shiso_decode_attention_fused_supported": [I, I, I, I],
+    "shiso_decode_attention_fused": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, LL, F, I, I, P],
     "shiso_prefill_attention": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "shiso_argmax": [P, P, I, I, P],
     "shiso_argmax_chunked": [P, P, P, I, I, I, P],

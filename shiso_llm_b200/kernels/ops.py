@@ -435,12 +435,30 @@ TC_ATTENTION_MIN_TOKENS = 256  # steps from here on, with a portion of at least 
 TC_ATTENTION_MIN_PORTION = 128  # ... this many rows, take the tensor-memory attention kernel (head size 64)
 
 
-def decode_splits(tokens: int, kv_heads: int, capacity: int) -> int:
-    """Into how many parts the decode kernel cuts a sequence's keys: enough CTAs (tokens x KV
-    heads x parts) to fill the SMs a few times over, no part shorter than 128 keys of the
-    table's capacity.  It depends on the launch shape only, never on current lengths, so a
-    captured step stays valid."""
+def decode_splits(tokens: int, kv_heads: int, capacity: int, fused: bool = False) -> int:
+    """Into how many parts a decode kernel cuts a sequence's keys.  It depends on the launch
+    shape only, never on current lengths, so a captured step stays valid.  The two-launch
+    kernel wants enough CTAs (tokens x KV heads x parts) to fill the SMs a few times over, no
+    part shorter than 128 keys of the table's capacity.  The fused kernel streams a long part
+    at full rate through its ring, and every CTA costs it a start and a hand-over at the end:
+    it wants one wave of about two CTAs per SM (measured: batch 8 x 8 KV heads x 2,190 keys
+    takes 14.8 us in 4 parts, 16.5 in 6, 21 in 10; batch 32 takes 30 us whole, 43 in 2)."""
+    if fused:
+        return max(1, min(16, 2 * _sm_count() // (tokens * kv_heads), -(-capacity // 128)))
     return max(1, min(16, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
+
+
+_DECODE_COUNTERS: dict = {}  # device -> arrays of int32 zeros; the fused decode kernel leaves them zero
+
+
+def _decode_counters(device: torch.device, count: int) -> torch.Tensor:
+    """Counters on which the parts of a (sequence, KV head) count themselves off.  They live as
+    long as the process (captured steps hold their address); a larger step gets a larger array
+    and the old one stays alive for the steps that were captured with it."""
+    held = _DECODE_COUNTERS.setdefault(device, [])
+    if not held or held[-1].numel() < count:
+        held.append(torch.zeros((max(count, 4096),), dtype=torch.int32, device=device))
+    return held[-1]
 
 
 def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step,
@@ -466,8 +484,19 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
         q.dtype == torch.bfloat16 and getattr(step, "all_decode", False)
         and heads // kv_heads <= MAX_DECODE_GROUP and head_dim in DECODE_HEAD_DIMS
     ):
-        splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size)
+        fused = bool(lib.shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size))
+        splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size, fused)
         scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
+        if fused:
+            # keys and values by TMA, the parts merged by the CTA that finishes last: one launch
+            counters = _decode_counters(q.device, tokens * kv_heads)
+            status = lib.shiso_decode_attention_fused(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
+                _ptr(step.seq_of_token), _ptr(scratch), _ptr(counters), _ptr(out), tokens, heads, kv_heads, head_dim,
+                page_size, k_cache.shape[0], float(scale), int(window), splits, _stream(),
+            )
+            _done(status, "decode_attention (fused)")
+            return out
         status = lib.shiso_decode_attention(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
             _ptr(step.seq_of_token), _ptr(scratch), _ptr(out), tokens, heads, kv_heads, head_dim, page_size,

@@ -341,7 +341,8 @@ def test_sample_kernel_follows_the_host_rule():
     assert same >= 4 * 6 - 1
 
 
-@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (32, 8, 64, 16), (6, 6, 48, 8), (8, 1, 128, 16), (2, 1, 256, 4), (5, 5, 80, 16), (32, 2, 64, 16), (36, 2, 32, 8)])
+@pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (32, 8, 64, 16), (6, 6, 48, 8), (8, 1, 128, 16), (2, 1, 256, 4), (5, 5, 80, 16), (32, 2, 64, 16), (36, 2, 32, 8),
+                                  (6, 2, 64, 8), (5, 1, 64, 32), (12, 4, 64, 64), (7, 7, 64, 16), (4, 2, 64, 4)])
 def test_decode_attention_split_keys(case):
     """Steps of single tokens in bfloat16 take the split-key kernel: sequences of very
     different lengths in one launch (one key, a page's edge, thousands of keys), windows."""
@@ -363,6 +364,31 @@ def test_decode_attention_split_keys(case):
         general = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu,
                                         general=True)
         close(got, general, dtype, "decode kernel against the general kernel")
+
+
+@pytest.mark.parametrize("page", [16, 64, 8])
+@pytest.mark.parametrize("parts", [1, 2, 16])
+def test_decode_attention_long_parts(page, parts, monkeypatch):
+    """Head size 64 takes the kernel that brings pages in by TMA and merges the parts itself:
+    parts of many tiles (the ring of four is refilled dozens of times), one part alone (no
+    merge), more parts than a short sequence has tiles, a window whose edge lies inside a
+    page, and the same launch repeated (the parts' counters are back at zero)."""
+    from shiso_llm_b200.kernels import ops as ops_module
+    heads, kv_heads, d = 12, 3, 64
+    starts = [9000, 5003, 63, 64, 65, 0]
+    num_pages = sum(-(-(s + 1) // page) for s in starts) + 2
+    cpu, gpu, table = make_step([1] * len(starts), starts, page, num_pages, 64)
+    cpu.all_decode = gpu.all_decode = True
+    dtype = torch.bfloat16
+    k = rnd((num_pages, page, kv_heads, d), dtype, 65)
+    v = rnd((num_pages, page, kv_heads, d), dtype, 66)
+    q = rnd((len(starts), heads * d), dtype, 67)
+    monkeypatch.setattr(ops_module, "decode_splits", lambda tokens, kv, capacity, fused=False: parts)
+    for window in (0, 3001, 0):
+        want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, 0.125, window, cpu)
+        got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, 0.125, window, gpu)
+        ops().check_kernel_status()
+        close(got, want, dtype, f"decode attention by TMA, pages of {page}, {parts} parts, window {window}")
 
 
 @pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (8, 2, 64, 16), (6, 3, 48, 8), (5, 5, 80, 16), (4, 1, 128, 16), (2, 2, 112, 4),
