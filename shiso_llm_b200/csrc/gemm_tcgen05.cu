@@ -343,6 +343,14 @@ SHISO_API int shiso_gemm_tcgen05_status() {
 }
 
 // x [T, K] bf16, w [N, K] bf16, y [T, N] bf16 (y_dtype 1) or float (y_dtype 0).
+// Tokens per CTA (the MMA's N operand).  Up to 192 tokens run as tiles of at most 64: such a
+// CTA is under half an SM, two are resident together and the next product's CTAs start under
+// this one's tail, and K is split over fewer CTAs.  Measured on a chain of the four products of
+// a 2048-wide layer: 128 tokens as one tile of 128 took 87 us a layer, as two tiles of 64 60 us;
+// 192 tokens as three tiles 64 us against 98 us in the kernels for long portions; from four
+// token tiles on the grid is more than one wave and those kernels are faster.
+static inline int token_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 192 ? 64 : 256; }
+
 SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
                                  int K, int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
@@ -359,7 +367,7 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     const int total_kb = (K + BK - 1) / BK;
     p.k_blocks_per_split = total_kb;
 
-    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    const int bn = token_tile(T);
     CUtensorMap mw, mx;
     if (!tensor_map(w, N, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
 
@@ -385,8 +393,7 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     }
     if (bn == 16) { SHISO_PICK(16) }
     if (bn == 32) { SHISO_PICK(32) }
-    if (bn == 64) { SHISO_PICK(64) }
-    SHISO_PICK(128)
+    SHISO_PICK(64)
 #undef SHISO_PICK
 }
 
@@ -405,13 +412,10 @@ SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, i
     p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     p.inter = inter;
     p.k_blocks_per_split = (K + BK - 1) / BK;
-    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    const int bn = token_tile(T);
     CUtensorMap mw, mx;
     if (!tensor_map(w, 2 * inter, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
-    if (bn >= 128) {
-        if (bn == 128) return launch<128, 4, 1, true>(mw, mx, p, stream);
-        return launch<256, 3, 1, true>(mw, mx, p, stream);
-    }
+    if (bn == 256) return launch<256, 3, 1, true>(mw, mx, p, stream);
     // Few tokens: K split over a cluster of up to 4 CTAs, as for plain products (one wave over the SMs).
     static int sm_count = 0;
     if (sm_count == 0) {

@@ -163,7 +163,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 _SM_COUNT = None
-PROMPT_MIN_TOKENS = 129  # from here the persistent tensor-memory kernels (tokens as the MMA's M operand): plain products on pairs of SMs
+PROMPT_MIN_TOKENS = 193  # from here the persistent tensor-memory kernels (tokens as the MMA's M operand): plain products on pairs of SMs; below, 64-token tiles with K split over a cluster are faster
 PAIR_MIN_TOKENS_GLU = 512  # gate/up pairs below this stay on single SMs: the pairs' 256-token tiles would leave a second, nearly empty wave
 
 

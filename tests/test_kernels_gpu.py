@@ -122,9 +122,9 @@ def test_linear(shape, xw):
 
 
 @pytest.mark.parametrize("shape", [(512, 256, 64), (700, 1000, 264), (1030, 2048, 2048), (2048, 6144, 512), (515, 520, 5632),
-                                   (129, 2048, 2048), (300, 776, 520)])
+                                   (193, 2048, 2048), (300, 776, 520)])
 def test_linear_on_sm_pairs(shape):
-    """From 129 bfloat16 rows a plain product runs on pairs of SMs (one 256-row tile per pair, each CTA
+    """From 193 bfloat16 rows a plain product runs on pairs of SMs (one 256-row tile per pair, each CTA
     loading half of both operands): row counts that leave the second CTA of the last pair with
     few or no rows, feature counts that leave its weight half partly or wholly outside the
     matrix, one and many k steps, more tiles than pairs; bfloat16 and float32 results, a bias."""
@@ -487,10 +487,12 @@ def test_prefill_attention_never_reads_outside_its_range():
 
 @pytest.mark.parametrize("shape", [(1, 96, 64), (8, 2048, 2048), (5, 1000, 96), (8, 300, 200), (16, 2048, 5632), (13, 48, 264), (3, 16, 8),
                                    (8, 4800, 1032), (2, 24, 3080), (24, 2048, 2048), (32, 1000, 264), (17, 40, 5632),
-                                   (64, 6144, 2048), (33, 2048, 5632), (50, 776, 264), (64, 48, 8), (40, 11264, 2048)])
+                                   (64, 6144, 2048), (33, 2048, 5632), (50, 776, 264), (64, 48, 8), (40, 11264, 2048),
+                                   (65, 2048, 2048), (100, 776, 264), (128, 6144, 2048), (129, 2048, 5632), (192, 11264, 2048), (177, 40, 72)])
 def test_skinny_linear_and_fused_swiglu(shape):
-    """A handful of bfloat16 rows take the weight-streaming kernel; with a gate/up pair the
-    activation is applied in its epilogue."""
+    """A handful of bfloat16 rows take the weight-streaming kernel, up to 192 the tensor-memory
+    kernel with tokens as the MMA's N operand (tiles of at most 64 tokens, K split over a
+    cluster); with a gate/up pair the activation is applied in the epilogue."""
     T, N, K = shape
     x, w = rnd((T, K), torch.bfloat16, 90), rnd((N, K), torch.bfloat16, 91, 0.05)
     bias = rnd((N,), torch.float32, 92)
