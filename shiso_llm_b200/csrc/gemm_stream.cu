@@ -1,4 +1,4 @@
-// Y[T, N] = X[T, K] * W[N, K]^T for up to 16 rows, bfloat16: the decode step's matrix products as
+// Y[T, N] = X[T, K] * W[N, K]^T for up to 8 rows, bfloat16: the decode step's matrix products as
 // a persistent weight-streaming kernel.
 //
 // At these sizes a product is over in a few microseconds and is bound by reading W once, so what
@@ -140,6 +140,8 @@ __device__ __forceinline__ int tile_row(const StreamArgs& a, int tile, int r) {
 // KC); they are the same for every tile, and a reload per chunk would put an L2 round trip into
 // every stage.  HELD = 0: K is longer than that and the activations of the next chunk are fetched
 // while the current one is worked on.
+constexpr int MAX_ROWS = 8;  // rows of x the built variants take (NT = 1)
+
 template <int NT, int HELD>
 __global__ void __launch_bounds__(THREADS, NT * HELD > 2 ? 1 : 2)
 gemm_stream_kernel(StreamArgs a) {
@@ -428,25 +430,24 @@ int launch_stream(StreamArgs& a, int sm_count, cudaStream_t stream) {
     a.tiles = a.mode == MODE_GLU ? (a.inter + 7) / 8 : (a.N + ROWS - 1) / ROWS;
     a.status = shiso_tc_status_word();
     const int chunks = (a.K + KC - 1) / KC;
-    if (a.T <= 8) {
-        if (chunks == 1) return launch_as<1, 1>(a, sm_count, stream);
-        if (chunks == 2) return launch_as<1, 2>(a, sm_count, stream);
-        return launch_as<1, 0>(a, sm_count, stream);
-    }
-    if (chunks == 1) return launch_as<2, 1>(a, sm_count, stream);
-    if (chunks == 2) return launch_as<2, 2>(a, sm_count, stream);  // many registers: no successor beside it
-    return launch_as<2, 0>(a, sm_count, stream);
+    // NT = 1: one 8-token tile per weight fragment.  With two (9..16 rows) the held activations
+    // took the registers of a second CTA per SM, and a decode step at batch 16 ran at 17.9k
+    // tokens/s against 19.8k with the tensor-memory kernel and separate norm kernels; reading
+    // the activations from L2 every stage instead fell to 11.5k.  Those rows are not built.
+    if (chunks == 1) return launch_as<1, 1>(a, sm_count, stream);
+    if (chunks == 2) return launch_as<1, 2>(a, sm_count, stream);
+    return launch_as<1, 0>(a, sm_count, stream);
 }
 
 }  // namespace
 
-// x [T, K] bf16 (T <= 16), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
+// x [T, K] bf16 (T <= 8), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
 // inter == 0: y[T, N] = x w^T (+ bias).  inter > 0: N == 2 * inter, y[T, inter] = silu(x gate^T) * (x up^T).
 // In the GLU layout a tile's row r < 8 is gate row 8 * tile + r and row r >= 8 its up row.
 SHISO_API int shiso_gemm_stream(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
                                 int K, int inter, int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > 16 || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (T > MAX_ROWS || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
     if (inter > 0 && (N != 2 * inter || bias)) return SHISO_ERR_SHAPE;
     StreamArgs a = {};
@@ -470,7 +471,7 @@ SHISO_API int shiso_gemm_stream_into(const void* x, const void* w, const float* 
                                      float* res_out, const float* next_norm_w, void* x_out, float* partials_out,
                                      int T, int N, int K, int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > 16 || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (T > MAX_ROWS || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
     if (!res_in || !res_out || res_in == res_out || !next_norm_w || !x_out || !partials_out) return SHISO_ERR_SHAPE;
     StreamArgs a = {};
@@ -495,7 +496,7 @@ SHISO_API int shiso_gemm_stream_scaled(const void* x, const float* partials, int
                                        const void* w, void* y, int y_dtype, int T, int N, int K, int inter,
                                        int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > 16 || K % 8 != 0 || K <= 0 || !partials || partial_count <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (T > MAX_ROWS || K % 8 != 0 || K <= 0 || !partials || partial_count <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
     if (inter > 0 && N != 2 * inter) return SHISO_ERR_SHAPE;
     StreamArgs a = {};

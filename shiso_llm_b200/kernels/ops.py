@@ -174,7 +174,7 @@ def _sm_count() -> int:
     return _SM_COUNT
 
 
-STREAM_KERNEL_MAX_TOKENS = 16  # up to here the persistent weight-streaming kernel runs the product
+STREAM_KERNEL_MAX_TOKENS = 8  # up to here the persistent weight-streaming kernel runs the product (9..16 rows measured slower there than in the tensor-memory kernel)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -263,7 +263,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
     return swiglu(linear(x, gate_up, out_dtype))
 
 
-STREAM_MAX_TOKENS = 16  # rows the product-into-stream / scaled-product pair takes (those of the streaming kernel)
+STREAM_MAX_TOKENS = 8  # rows the product-into-stream / scaled-product pair takes (those of the streaming kernel)
 
 
 class ScaledRows:

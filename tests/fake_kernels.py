@@ -80,7 +80,7 @@ class ScaledRows:
 def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
     """The pair the CUDA table offers for a handful of bfloat16 rows; here for any type, so that
     the parts' handling of it runs on the CPU too."""
-    if x.shape[0] > 16:
+    if x.shape[0] > 8:
         return None  # as the CUDA table: only a handful of rows
     summed = residual + linear(x, w, torch.float32, bias)
     rows = (summed.to(F64) * next_norm_w.to(F64)).to(x.dtype)

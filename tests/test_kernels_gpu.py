@@ -599,7 +599,7 @@ def test_fused_projection_residual_add_and_norm(shape):
         assert (res_gpu.cpu() - res_ref).abs().max().item() <= 2.0 ** -7 * delta_scale
 
 
-@pytest.mark.parametrize("shape", [(8, 2048, 2048, 6144), (1, 96, 64, 200), (3, 264, 1000, 520), (13, 4096, 512, 64), (16, 2048, 5632, 2048), (5, 8, 24, 40)])
+@pytest.mark.parametrize("shape", [(8, 2048, 2048, 6144), (1, 96, 64, 200), (3, 264, 1000, 520), (7, 4096, 512, 64), (8, 2048, 5632, 2048), (5, 8, 24, 40)])
 @pytest.mark.parametrize("glu", [False, True])
 @pytest.mark.parametrize("bias", [False, True])
 def test_product_into_the_stream_then_scaled_product(shape, glu, bias):
@@ -637,6 +637,6 @@ def test_product_into_the_stream_then_scaled_product(shape, glu, bias):
 def test_product_into_the_stream_declines_what_it_cannot_take():
     w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
     nw = torch.ones(32, device="cuda")
-    x = torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16)
-    assert ops().linear_into_stream(x, w, torch.zeros(17, 32, device="cuda"), nw, 1e-5) is None  # too many rows
+    x = torch.zeros(9, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops().linear_into_stream(x, w, torch.zeros(9, 32, device="cuda"), nw, 1e-5) is None  # too many rows
     assert ops().linear_into_stream(x[:4].float(), w.float(), torch.zeros(4, 32, device="cuda"), nw, 1e-5) is None
