@@ -51,7 +51,29 @@ struct GemmParams {
     int k_blocks_per_split;  // BK-blocks each CTA of a cluster handles
     int out_f32;             // 1: float output, 0: bfloat16
     int inter;               // GLU kernels: rows of the gate (and of the up) matrix, and of the output
+    // SCALED (scale_partials != null): the rows of x lack their RMS scale; token t's is
+    // rsqrt(sum over c < scale_count of scale_partials[c * scale_stride + t] / K + scale_eps) and
+    // multiplies the accumulators of its column.
+    const float* scale_partials;
+    int scale_count, scale_stride;
+    float scale_eps;
+    // INTO (res_in != null; plain products): res_out = res_in + product (+ bias), x_out =
+    // bf16(res_out * norm_w) and into_partials[feature tile * T + t] = the sum of res_out^2 over
+    // the tile's 128 features - the input of a SCALED product; y is not written.
+    const float* res_in;
+    float* res_out;
+    const float* norm_w;
+    __nv_bfloat16* x_out;
+    float* into_partials;
 };
+
+constexpr int MAX_FUSED_BN = 64;  // token tiles of the SCALED / INTO modes (their scales lie in shared memory)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
 
 template <typename OT>
 __device__ __forceinline__ void store_out(OT* y, size_t at, float v);
@@ -84,6 +106,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint64_t* accum_bar = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
     int* failed = (int*)(tmem_slot + 1);
+    float* scale_s = (float*)(failed + 1);  // [min(BN, MAX_FUSED_BN)] row scales of the SCALED mode
+    float* square_s = scale_s + MAX_FUSED_BN;  // [4 warps][MAX_FUSED_BN] sums of squares of the INTO mode
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feature0 = blockIdx.x * BM;
@@ -114,6 +138,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    const int feature = feature0 + warp * 32 + lane;
+    const bool scaled = p.scale_partials != nullptr;
+    const bool into = !GLU && p.res_in != nullptr;
+    // INTO: what the epilogue needs from global memory is asked for under the main loop - the
+    // norm weight and the stream's values of this CTA's first tokens (tokens first_own,
+    // first_own + own_stride, ... of the tile).  The two lanes that run the main loop ask when
+    // it suits them: the producer after its last load, the MMA issuer before its first MMA
+    // (its operands cannot land before the predecessor is done either).
+    constexpr int EARLY = 8;
+    const int own_stride = SPLITS > 1 ? SPLITS : 1;
+    int first_own = 0;
+    if constexpr (SPLITS > 1) first_own = (int)cg::this_cluster().block_rank();
+    float norm_weight = 0.0f;
+    float early[EARLY];
+    auto stream_value = [&](int token) {
+        return (feature < p.N && token < p.T) ? p.res_in[(size_t)token * p.N + feature] : 0.0f;
+    };
+    auto ask_early = [&]() {
+        if (!into) return;
+        pdl_wait();  // the stream is the predecessor's
+        norm_weight = feature < p.N ? p.norm_w[feature] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < EARLY; ++u) early[u] = stream_value(token0 + first_own + u * own_stride);
+    };
+
     if (warp == 0 && lane == 0) {
         // ---- producer: TMA loads, one stage per 64-wide k block
         for (int i = 0; i < kb_count; ++i) {
@@ -130,8 +179,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (i == 0) pdl_wait();  // weights depend on no predecessor; the activations do
             tma_load_2d(a + A_TILES * A_BYTES, &map_x, k, token0, &full[s]);
         }
+        ask_early();
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
+        ask_early();
         const uint32_t idesc = umma_idesc(BM, BN);
         bool ok = true;
         for (int i = 0; i < kb_count && ok; ++i) {
@@ -157,6 +208,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
         }
         umma_commit(accum_bar);      // the accumulator is complete once every MMA is done
+    } else {
+        ask_early();
+    }
+    if (warp >= 2 && scaled) {
+        // ---- the row scales, while the main loop runs (the sums of squares are the predecessor's)
+        pdl_wait();
+        for (int j = threadIdx.x - 64; j < BN && j < MAX_FUSED_BN; j += 64) {
+            float sum = 0.0f;
+            if (token0 + j < p.T) {
+                const float* mine = p.scale_partials + token0 + j;
+                int c = 0;
+                for (; c + 8 <= p.scale_count; c += 8) {  // eight loads in flight, added in index order
+                    float part[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) part[u] = mine[(size_t)(c + u) * p.scale_stride];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) sum += part[u];
+                }
+                for (; c < p.scale_count; ++c) sum += mine[(size_t)c * p.scale_stride];
+            }
+            scale_s[j] = rsqrtf(sum / (float)p.K + p.scale_eps);
+        }
     }
     __syncwarp();
 
@@ -171,8 +244,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const bool bad = *failed != 0;
     if (bad && threadIdx.x == 0 && p.status) atomicExch(p.status, 1);
 
-    const int feature = feature0 + warp * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    // INTO: one token's value of this thread's feature joins the stream; all lanes of the warp
+    // call it together (the sum of squares is taken over the warp's 32 features)
+    auto join_stream = [&](int token, float v, float before) {
+        float r = 0.0f;
+        if (feature < p.N && token < p.T) {
+            const size_t at = (size_t)token * p.N + feature;
+            r = before + v;
+            p.res_out[at] = r;
+            p.x_out[at] = __float2bfloat16_rn(r * norm_weight);
+        }
+        const float square = warp_sum(r * r);
+        if (lane == 0) square_s[warp * MAX_FUSED_BN + (token - token0) % MAX_FUSED_BN] = square;
+    };
+    // after the tokens of this CTA have joined: the four warps' sums of squares, added in warp order
+    auto leave_squares = [&](int stride, int first) {  // this CTA's tokens of the tile: first, first + stride, ...
+        __syncthreads();
+        for (int j = first + (int)threadIdx.x * stride; j < BN && j < MAX_FUSED_BN; j += THREADS * stride) {
+            if (token0 + j >= p.T) break;
+            const float sum = square_s[j] + square_s[MAX_FUSED_BN + j] + square_s[2 * MAX_FUSED_BN + j] + square_s[3 * MAX_FUSED_BN + j];
+            p.into_partials[(size_t)blockIdx.x * p.T + token0 + j] = sum;
+        }
+    };
 
     if constexpr (GLU && SPLITS == 1) {
         if (!bad) {
@@ -185,6 +279,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int j = 0; j < 8; ++j) {
                     const int token = token0 + c + j;
                     if (token < p.T && feature < p.inter) {
+                        if (scaled) {
+                            const float sc = scale_s[(c + j) % MAX_FUSED_BN];
+                            gate[j] *= sc;
+                            up[j] *= sc;
+                        }
                         const float v = gate[j] / (1.0f + expf(-gate[j])) * up[j];
                         const size_t at = (size_t)token * p.inter + feature;
                         if (p.out_f32) store_out<float>((float*)p.y, at, v);
@@ -205,7 +304,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 8; ++j) v[j] = 0.0f;
                 }
-                if (feature < p.N) {
+                if (scaled) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] *= scale_s[(c + j) % MAX_FUSED_BN];
+                }
+                if (into) {
+                    float before[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) before[j] = c == 0 ? early[j] : stream_value(token0 + c + j);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) join_stream(token0 + c + j, v[j] + b, before[j]);
+                } else if (feature < p.N) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int token = token0 + c + j;
@@ -217,6 +326,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
             }
+            if (into) leave_squares(1, 0);  // `bad` and `into` are the same in every thread
         }
     } else {
         // Token j is summed by the CTA of rank j % SPLITS.  Every CTA pushes its partial values
@@ -250,27 +360,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         cluster.sync();
         const int out_rows = GLU ? p.inter : p.N;
-        if (feature < out_rows) {
-            const float b = (!GLU && p.bias) ? p.bias[feature] : 0.0f;
-#pragma unroll 4
-            for (int i = 0; i < OWN; ++i) {
-                const int j = i * SPLITS + (int)rank;
-                if (j >= BN || token0 + j >= p.T) break;
-                float sum[A_TILES];
+        const bool live = feature < out_rows;
+        const float b = (!GLU && p.bias && live) ? p.bias[feature] : 0.0f;
+        // token i of this CTA's share; false past the tile or the step (the same in every thread)
+        auto finish = [&](int i, float before) {
+            const int j = i * SPLITS + (int)rank;
+            if (j >= BN || token0 + j >= p.T) return false;
+            float sum[A_TILES];
 #pragma unroll
-                for (int t = 0; t < A_TILES; ++t) {
-                    sum[t] = 0.0f;
+            for (int t = 0; t < A_TILES; ++t) {
+                sum[t] = 0.0f;
 #pragma unroll
-                    for (int r = 0; r < SPLITS; ++r)  // rank order
-                        sum[t] += inbox[(((size_t)t * SPLITS + r) * OWN + i) * BM + warp * 32 + lane];
-                }
-                float v = sum[0] + b;
-                if (GLU) v = sum[0] / (1.0f + expf(-sum[0])) * sum[A_TILES - 1];
+                for (int r = 0; r < SPLITS; ++r)  // rank order
+                    sum[t] += inbox[(((size_t)t * SPLITS + r) * OWN + i) * BM + warp * 32 + lane];
+                if (scaled) sum[t] *= scale_s[j % MAX_FUSED_BN];
+            }
+            float v = sum[0] + b;
+            if (GLU) v = sum[0] / (1.0f + expf(-sum[0])) * sum[A_TILES - 1];
+            if (into) {
+                join_stream(token0 + j, v, before);
+            } else if (live) {
                 const size_t at = (size_t)(token0 + j) * out_rows + feature;
                 if (p.out_f32) store_out<float>((float*)p.y, at, v);
                 else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v);
             }
+            return true;
+        };
+        constexpr int FIRST = OWN < EARLY ? OWN : EARLY;  // tokens whose stream values are here already
+        bool more = true;
+#pragma unroll
+        for (int i = 0; i < FIRST; ++i) more = more && finish(i, early[i]);
+        if (OWN > EARLY && more) {
+            constexpr int AHEAD = 4;  // further stream values are asked for four tokens at a time
+            for (int i0 = EARLY; i0 < OWN && more; i0 += AHEAD) {
+                float before[AHEAD];
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) before[u] = into ? stream_value(token0 + (i0 + u) * SPLITS + (int)rank) : 0.0f;
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) more = more && i0 + u < OWN && finish(i0 + u, before[u]);
+            }
         }
+        if (into) leave_squares(SPLITS, (int)rank);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -287,7 +417,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStrea
     constexpr int STAGE_BYTES = (GLU ? 2 : 1) * BM * BK * 2 + BN * BK * 2;
     constexpr int PARTIAL_BYTES = SPLITS > 1 ? (GLU ? 2 : 1) * SPLITS * ((BN + SPLITS - 1) / SPLITS) * BM * 4 : 0;
     constexpr int TILE_BYTES = STAGES * STAGE_BYTES + PARTIAL_BYTES;
-    constexpr int SMEM = TILE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+    constexpr int SMEM = TILE_BYTES + 1024 /* alignment */ + 1536 /* barriers, flags, row scales, sums of squares */;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SPLITS, GLU>;
     static bool configured = false;
     if (!configured) {
@@ -342,7 +472,6 @@ SHISO_API int shiso_gemm_tcgen05_status() {
     return host;
 }
 
-// x [T, K] bf16, w [N, K] bf16, y [T, N] bf16 (y_dtype 1) or float (y_dtype 0).
 // Tokens per CTA (the MMA's N operand).  Up to 192 tokens run as tiles of at most 64: such a
 // CTA is under half an SM, two are resident together and the next product's CTAs start under
 // this one's tail, and K is split over fewer CTAs.  Measured on a chain of the four products of
@@ -351,22 +480,32 @@ SHISO_API int shiso_gemm_tcgen05_status() {
 // token tiles on the grid is more than one wave and those kernels are faster.
 static inline int token_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 192 ? 64 : 256; }
 
-SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
-                                 int K, int sm_count, cudaStream_t stream) {
-    if (T <= 0 || N <= 0) return SHISO_OK;
-    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
-    GemmParams p;
-    p.y = y;
-    p.bias = bias;
+namespace {
+
+GemmParams blank_params(int T, int N, int K) {
+    GemmParams p = {};
     p.status = shiso_tc_status_word();
     p.T = T;
     p.N = N;
     p.K = K;
-    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
-    p.inter = 0;
-    const int total_kb = (K + BK - 1) / BK;
-    p.k_blocks_per_split = total_kb;
+    p.k_blocks_per_split = (K + BK - 1) / BK;
+    return p;
+}
 
+int sm_count_of_device() {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    }
+    return sm_count;
+}
+
+// A plain product (p.inter == 0), with whatever epilogue mode p carries.
+int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStream_t stream) {
+    const int T = p.T, N = p.N, K = p.K;
+    const int total_kb = (K + BK - 1) / BK;
     const int bn = token_tile(T);
     CUtensorMap mw, mx;
     if (!tensor_map(w, N, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
@@ -397,32 +536,15 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
 #undef SHISO_PICK
 }
 
-// silu(x gate^T) * (x up^T) for w = [gate; up] of shape [2 * inter, K]; y [T, inter].
-SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, int y_dtype, int T, int inter, int K,
-                                        cudaStream_t stream) {
-    if (T <= 0 || inter <= 0) return SHISO_OK;
-    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
-    GemmParams p;
-    p.y = y;
-    p.bias = nullptr;
-    p.status = shiso_tc_status_word();
-    p.T = T;
-    p.N = 2 * inter;
-    p.K = K;
-    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
-    p.inter = inter;
-    p.k_blocks_per_split = (K + BK - 1) / BK;
+// silu(x gate^T) * (x up^T) for w = [gate; up] of shape [2 * p.inter, K], p.N == 2 * p.inter.
+int run_glu(GemmParams p, const void* x, const void* w, cudaStream_t stream) {
+    const int T = p.T, K = p.K, inter = p.inter;
     const int bn = token_tile(T);
     CUtensorMap mw, mx;
     if (!tensor_map(w, 2 * inter, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
     if (bn == 256) return launch<256, 3, 1, true>(mw, mx, p, stream);
     // Few tokens: K split over a cluster of up to 4 CTAs, as for plain products (one wave over the SMs).
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    }
+    const int sm_count = sm_count_of_device();
     const int total_kb = (K + BK - 1) / BK;
     const int tiles = (int)ceil_div_u(inter, BM) * (int)ceil_div_u(T, bn);
     int splits = sm_count / (tiles > 0 ? tiles : 1);
@@ -440,4 +562,79 @@ SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, i
     if (bn == 32) { SHISO_PICK_GLU(32) }
     SHISO_PICK_GLU(64)
 #undef SHISO_PICK_GLU
+}
+
+}  // namespace
+
+// x [T, K] bf16, w [N, K] bf16, y [T, N] bf16 (y_dtype 1) or float (y_dtype 0).
+SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N,
+                                 int K, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p = blank_params(T, N, K);
+    p.y = y;
+    p.bias = bias;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    return run_plain(p, x, w, sm_count, stream);
+}
+
+// silu(x gate^T) * (x up^T) for w = [gate; up] of shape [2 * inter, K]; y [T, inter].
+SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, int y_dtype, int T, int inter, int K,
+                                        cudaStream_t stream) {
+    if (T <= 0 || inter <= 0) return SHISO_OK;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p = blank_params(T, 2 * inter, K);
+    p.y = y;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    p.inter = inter;
+    return run_glu(p, x, w, stream);
+}
+
+// Rows of the fused-norm pair below: token tiles of at most 64.
+SHISO_API int shiso_gemm_tcgen05_fused_max_tokens(void) { return 192; }
+
+// Rows of T floats of `partials_out` that shiso_gemm_tcgen05_into writes for N features.
+SHISO_API int shiso_gemm_tcgen05_into_partial_rows(int N) { return (N + BM - 1) / BM; }
+
+// A block's output projection into the residual stream, for 1..192 rows: res_out = res_in +
+// x w^T (+ bias) (float [T, N]; res_in is not changed), x_out = bf16(res_out * next_norm_w)
+// [T, N], and partials_out[c * T + t] (c < ceil(N / 128)) whose sum over c is the sum of
+// squares of res_out's row t: what shiso_gemm_tcgen05_scaled takes in place of normed rows.
+SHISO_API int shiso_gemm_tcgen05_into(const void* x, const void* w, const float* bias, const float* res_in,
+                                      float* res_out, const float* next_norm_w, void* x_out, float* partials_out, int T,
+                                      int N, int K, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (T > shiso_gemm_tcgen05_fused_max_tokens() || !res_in || !res_out || !next_norm_w || !x_out || !partials_out)
+        return SHISO_ERR_UNSUPPORTED;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p = blank_params(T, N, K);
+    p.bias = bias;
+    p.res_in = res_in;
+    p.res_out = res_out;
+    p.norm_w = next_norm_w;
+    p.x_out = (__nv_bfloat16*)x_out;
+    p.into_partials = partials_out;
+    return run_plain(p, x, w, sm_count, stream);
+}
+
+// y = (x * rsqrt(mean square + eps)) w^T for rows x [T, K] that lack their RMS scale (x_out of
+// the call above; mean square of row t = sum over c < partial_count of partials[c * stride + t]
+// / K), 1..192 rows; with inter > 0 the gate/up pair and SwiGLU as in shiso_gemm_tcgen05_swiglu.
+SHISO_API int shiso_gemm_tcgen05_scaled(const void* x, const float* partials, int partial_count, int partial_stride,
+                                        float eps, const void* w, void* y, int y_dtype, int T, int N, int K, int inter,
+                                        int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (T > shiso_gemm_tcgen05_fused_max_tokens() || !partials || partial_count <= 0 || partial_stride < T)
+        return SHISO_ERR_UNSUPPORTED;
+    if (inter > 0 && N != 2 * inter) return SHISO_ERR_SHAPE;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p = blank_params(T, N, K);
+    p.y = y;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    p.inter = inter;
+    p.scale_partials = partials;
+    p.scale_count = partial_count;
+    p.scale_stride = partial_stride;
+    p.scale_eps = eps;
+    return inter > 0 ? run_glu(p, x, w, stream) : run_plain(p, x, w, sm_count, stream);
 }

@@ -31,6 +31,10 @@ _SIGNATURES = {
     "shiso_prefill_attention_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, LL, F, I, P],
     "shiso_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_supported": [I, P, P],
+    "shiso_gemm_tcgen05_fused_max_tokens": [],
+    "shiso_gemm_tcgen05_into_partial_rows": [I],
+    "shiso_gemm_tcgen05_into": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "shiso_gemm_tcgen05_scaled": [P, P, I, I, F, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_status": [],
     "shiso_gemm_stream": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_stream_into": [P, P, P, P, P, P, P, P, I, I, I, I, P],

@@ -263,7 +263,8 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
     return swiglu(linear(x, gate_up, out_dtype))
 
 
-STREAM_MAX_TOKENS = 8  # rows the product-into-stream / scaled-product pair takes (those of the streaming kernel)
+STREAM_MAX_TOKENS = 8  # rows for which the weight-streaming kernel runs the product-into-stream / scaled-product pair
+FUSED_NORM_MAX_TOKENS = 64  # up to here the tensor-memory kernel (tokens as the MMA's N operand) runs the pair: decode at batch 9 / 16 / 32 / 64 gains 11 / 10 / 4 / 1 % over product + norm kernel, batch 128 loses 2 % (the kernel takes up to 192 rows)
 
 
 class ScaledRows:
@@ -277,17 +278,24 @@ class ScaledRows:
 
 def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
     """A block's output projection, the residual add and the first half of the next RMS norm in
-    one launch, for a handful of bfloat16 rows: returns ``(residual + x @ w^T, ScaledRows)`` -
+    one launch, for up to 64 bfloat16 rows: returns ``(residual + x @ w^T, ScaledRows)`` -
     ``residual`` (float32 ``[T, N]``) itself is not changed - or None when sizes or types are
-    not the ones the kernel takes.  (The same pair of epilogues in the tensor-memory kernel for
-    long prompts was measured slower than product + row kernel: there a thread owns a row, and
-    its strided reads and writes of the stream cost more than the row kernel they replace.)"""
+    not the ones the kernels take.  A handful of rows run in the weight-streaming kernel, more
+    in the tensor-memory kernel whose threads own a feature each, so that a warp reads and
+    writes 32 neighbouring values of a token's row.  (The same pair of epilogues in the
+    tensor-memory kernels for long prompts was measured slower than product + row kernel:
+    there a thread owns a row, and its strided reads and writes of the stream cost more than
+    the row kernel they replace.)"""
     tokens, k = x.shape
     n = w.shape[0]
     if (
         x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or residual.dtype != torch.float32
-        or tokens > min(STREAM_MAX_TOKENS, STREAM_KERNEL_MAX_TOKENS) or k % 8 or w.shape[1] != k or n % 8
+        or tokens > FUSED_NORM_MAX_TOKENS or k % 8 or w.shape[1] != k or n % 8
     ):
+        return None
+    lib = library()
+    streaming = tokens <= min(STREAM_MAX_TOKENS, STREAM_KERNEL_MAX_TOKENS)
+    if not streaming and not lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         return None
     _check(x, "x", torch.bfloat16, 2)
     _check(w, "w", torch.bfloat16, 2)
@@ -299,11 +307,18 @@ def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
         _check(bias, "bias", torch.float32, 1)
     summed = torch.empty_like(residual)
     rows = torch.empty((tokens, n), dtype=torch.bfloat16, device=x.device)
-    partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
-    status = library().shiso_gemm_stream_into(
-        _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
-        tokens, n, k, _sm_count(), _stream(),
-    )
+    if streaming:
+        partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
+        status = lib.shiso_gemm_stream_into(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
+            tokens, n, k, _sm_count(), _stream(),
+        )
+    else:
+        partials = torch.empty((lib.shiso_gemm_tcgen05_into_partial_rows(n), tokens), dtype=torch.float32, device=x.device)
+        status = lib.shiso_gemm_tcgen05_into(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
+            tokens, n, k, _sm_count(), _stream(),
+        )
     _done(status, "linear_into_stream")
     return summed, ScaledRows(rows, partials, eps)
 
@@ -320,10 +335,17 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
         raise KernelError(f"a matrix of shape {tuple(w.shape)} for rows of {k}")
     inter = n // 2 if glu else 0
     out = torch.empty((tokens, inter if glu else n), dtype=out_dtype, device=x.device)
-    status = library().shiso_gemm_stream_scaled(
-        _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.eps, _ptr(w), _ptr(out), _code(out),
-        tokens, n, k, inter, _sm_count(), _stream(),
-    )
+    lib = library()
+    if tokens <= min(STREAM_MAX_TOKENS, STREAM_KERNEL_MAX_TOKENS):
+        status = lib.shiso_gemm_stream_scaled(
+            _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.eps, _ptr(w), _ptr(out), _code(out),
+            tokens, n, k, inter, _sm_count(), _stream(),
+        )
+    else:
+        status = lib.shiso_gemm_tcgen05_scaled(
+            _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.partials.shape[1], rows.eps, _ptr(w), _ptr(out),
+            _code(out), tokens, n, k, inter, _sm_count(), _stream(),
+        )
     _done(status, "linear_scaled")
     return out
 

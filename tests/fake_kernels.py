@@ -78,10 +78,10 @@ class ScaledRows:
 
 
 def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
-    """The pair the CUDA table offers for a handful of bfloat16 rows; here for any type, so that
+    """The pair the CUDA table offers for up to 64 bfloat16 rows; here for any type, so that
     the parts' handling of it runs on the CPU too."""
-    if x.shape[0] > 8:
-        return None  # as the CUDA table: only a handful of rows
+    if x.shape[0] > 64:
+        return None  # as the CUDA table: short steps only
     summed = residual + linear(x, w, torch.float32, bias)
     rows = (summed.to(F64) * next_norm_w.to(F64)).to(x.dtype)
     return summed, ScaledRows(rows, (summed.to(F64) ** 2).sum(-1, keepdim=True).T.contiguous(), eps)

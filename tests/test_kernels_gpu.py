@@ -599,14 +599,19 @@ def test_fused_projection_residual_add_and_norm(shape):
         assert (res_gpu.cpu() - res_ref).abs().max().item() <= 2.0 ** -7 * delta_scale
 
 
-@pytest.mark.parametrize("shape", [(8, 2048, 2048, 6144), (1, 96, 64, 200), (3, 264, 1000, 520), (7, 4096, 512, 64), (8, 2048, 5632, 2048), (5, 8, 24, 40)])
+@pytest.mark.parametrize("shape", [(8, 2048, 2048, 6144), (1, 96, 64, 200), (3, 264, 1000, 520), (7, 4096, 512, 64), (8, 2048, 5632, 2048), (5, 8, 24, 40),
+                                   (9, 2048, 2048, 6144), (16, 264, 1000, 520), (33, 2048, 5632, 2048), (64, 2048, 2048, 3072), (100, 776, 264, 200),
+                                   (192, 2048, 5632, 11264), (130, 40, 72, 24)])
 @pytest.mark.parametrize("glu", [False, True])
 @pytest.mark.parametrize("bias", [False, True])
-def test_product_into_the_stream_then_scaled_product(shape, glu, bias):
-    """A handful of bfloat16 rows: a block's output projection adds into the residual stream and
-    leaves norm-weighted rows and partial sums of squares; the next product applies the row
-    scale to its accumulators.  Against product, add + RMS norm, product (or SwiGLU pair), one
+def test_product_into_the_stream_then_scaled_product(shape, glu, bias, monkeypatch):
+    """Up to 192 bfloat16 rows (the weight-streaming kernel up to 8, the tensor-memory kernel
+    with one, two or three token tiles and K split over 1 to 8 CTAs above): a block's output
+    projection adds into the residual stream and leaves norm-weighted rows and partial sums of
+    squares; the next product applies the row scale to its accumulators.  Against product, add + RMS norm, product (or SwiGLU pair), one
     after the other; the old residual must stay as it was (other CTAs still read it)."""
+    from shiso_llm_b200.kernels import ops as ops_module
+    monkeypatch.setattr(ops_module, "FUSED_NORM_MAX_TOKENS", 192)  # all the rows the kernel takes, not only those the engine gives it
     T, H, K1, N2 = shape  # stream width H; the first product reads K1, the second gives N2
     x1 = rnd((T, K1), torch.bfloat16, 150)
     w1 = rnd((H, K1), torch.bfloat16, 151, 0.05)
@@ -622,7 +627,7 @@ def test_product_into_the_stream_then_scaled_product(shape, glu, bias):
     assert torch.equal(res_gpu.cpu(), residual)
     want_sum = residual + ref.linear(x1, w1, torch.float32, b1)
     close(summed, want_sum, torch.float32, "stream after the product", rel32=1e-5)
-    assert rows.partials.shape == (-(-H // 16), 16)
+    assert rows.partials.shape == ((-(-H // 16), 16) if T <= 8 else (-(-H // 128), T))
     mean_square = rows.partials.cpu()[:, :T].sum(0) / H
     assert torch.allclose(mean_square, (want_sum.double() ** 2).mean(-1).float(), rtol=1e-5)
     y = ops().linear_scaled(rows, w2.cuda(), torch.bfloat16, glu)
@@ -637,6 +642,6 @@ def test_product_into_the_stream_then_scaled_product(shape, glu, bias):
 def test_product_into_the_stream_declines_what_it_cannot_take():
     w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
     nw = torch.ones(32, device="cuda")
-    x = torch.zeros(9, 64, device="cuda", dtype=torch.bfloat16)
-    assert ops().linear_into_stream(x, w, torch.zeros(9, 32, device="cuda"), nw, 1e-5) is None  # too many rows
+    x = torch.zeros(65, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops().linear_into_stream(x, w, torch.zeros(65, 32, device="cuda"), nw, 1e-5) is None  # too many rows
     assert ops().linear_into_stream(x[:4].float(), w.float(), torch.zeros(4, 32, device="cuda"), nw, 1e-5) is None
