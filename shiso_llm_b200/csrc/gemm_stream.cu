@@ -65,7 +65,9 @@ constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int PARTIAL_STRIDE = 16;             // tokens per row of the partials table
 constexpr int EARLY_PARTIALS = 8;
 
-enum { MODE_PLAIN = 0, MODE_GLU = 1 };
+enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_CONV = 2 };
+constexpr int CONV_CHANNELS = 5;  // channels of a CONV tile: their B, C and x rows are 15 of its 16 rows
+constexpr int CONV_MAX_TAPS = 4;
 
 struct StreamArgs {
     const __nv_bfloat16* x;  // [T, K]
@@ -85,6 +87,18 @@ struct StreamArgs {
     const float* partials_in;
     int partial_count, norm_k;
     float eps;
+    // CONV epilogue: w is a short convolution's input projection [3 * hidden, K] (rows B, C, x) and
+    // every sequence brings one row; y[t, ch] = C * (sum_j conv_w[ch][j] * window_j + conv_bias[ch])
+    // where the window is the sequence's last taps - 1 gated inputs B * x followed by this row's,
+    // and the state moves on by one row.  B, C and x are rounded to bfloat16 first, as a product
+    // that stores them would.
+    const float* conv_w;        // [hidden, conv_taps]
+    const float* conv_bias;     // [hidden] or null
+    float* conv_state;          // [slots][conv_taps - 1][hidden], conv_slot_stride floats between slots
+    long long conv_slot_stride;
+    const int* conv_seq_of_token;  // [T]
+    const int* conv_slots;         // [sequences]
+    int conv_taps, hidden;
 };
 
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -127,7 +141,12 @@ __device__ __forceinline__ void consumer_barrier() {
 }
 
 // Row of W behind row r (0..15) of a tile, or -1.
+template <bool CONV>
 __device__ __forceinline__ int tile_row(const StreamArgs& a, int tile, int r) {
+    if constexpr (CONV) {
+        const int ch = tile * CONV_CHANNELS + r % CONV_CHANNELS;
+        return (r < 3 * CONV_CHANNELS && ch < a.hidden) ? (r / CONV_CHANNELS) * a.hidden + ch : -1;
+    }
     if (a.mode == MODE_GLU) {
         const int f = tile * 8 + (r & 7);
         return f < a.inter ? (r < 8 ? f : a.inter + f) : -1;
@@ -142,7 +161,10 @@ __device__ __forceinline__ int tile_row(const StreamArgs& a, int tile, int r) {
 // while the current one is worked on.
 constexpr int MAX_ROWS = 8;  // rows of x the built variants take (NT = 1)
 
-template <int NT, int HELD>
+// CONV: the kernel with the short convolution's epilogue; a variant of its own, because what that
+// epilogue holds across a tile's products (state, taps, bias) would cost the other modes their
+// registers (measured when it was a run-time mode: 0.667 -> 0.735 ms per decode step).
+template <int NT, int HELD, bool CONV>
 __global__ void __launch_bounds__(THREADS, NT * HELD > 2 ? 1 : 2)
 gemm_stream_kernel(StreamArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -172,7 +194,7 @@ gemm_stream_kernel(StreamArgs a) {
         // than the memory system needs to deliver it.
         int unit = 0;
         for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x) {
-            const int row = lane < ROWS ? tile_row(a, tile, lane) : -1;
+            const int row = lane < ROWS ? tile_row<CONV>(a, tile, lane) : -1;
             const int present = __popc(__ballot_sync(0xffffffffu, row >= 0));
             const __nv_bfloat16* src = a.w + (size_t)(row >= 0 ? row : 0) * a.K;
             for (int c = 0; c < chunks; ++c, ++unit) {
@@ -226,6 +248,13 @@ gemm_stream_kernel(StreamArgs a) {
         }
     }
 
+    // CONV: lane l of warp 0 finishes channel l / 8 of a tile for token l % 8, lanes 0..7 also the
+    // fifth channel; the token's state slot is looked up once
+    const int conv_token = lane & 7;
+    long long conv_slot = -1;
+    if (CONV && warp == 0 && conv_token < a.T)
+        conv_slot = a.conv_slots[a.conv_seq_of_token[conv_token]];
+
     constexpr int SLOTS_X = HELD > 0 ? HELD : 2;  // rolling: the current chunk and the next
     uint4 xs[SLOTS_X][KB][NT][2];
     if (HELD > 0) {
@@ -240,8 +269,8 @@ gemm_stream_kernel(StreamArgs a) {
         // STREAM: what the epilogue reads, asked for before the tile's products
         float early_res[NT][2][2], early_nw[2] = {0.0f, 0.0f}, early_bias[2] = {0.0f, 0.0f};
         int rows[2];
-        rows[0] = tile_row(a, tile, g);
-        rows[1] = tile_row(a, tile, g + 8);
+        rows[0] = tile_row<CONV>(a, tile, g);
+        rows[1] = tile_row<CONV>(a, tile, g + 8);
         if (warp == 0) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -257,6 +286,24 @@ gemm_stream_kernel(StreamArgs a) {
                         early_res[n][e][h] = 0.0f;
                         if (a.res_in && rows[h] >= 0 && token < a.T) early_res[n][e][h] = load_stream1(a.res_in + (size_t)token * a.N + rows[h]);
                     }
+            }
+        }
+
+        // CONV: the state, the taps and the bias of this lane's one or two (channel, token) pairs
+        float conv_window[2][CONV_MAX_TAPS - 1], conv_tap[2][CONV_MAX_TAPS], conv_b[2] = {0.0f, 0.0f};
+        if (CONV && warp == 0) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int ch = tile * CONV_CHANNELS + (i == 0 ? lane >> 3 : 4);
+                const bool on = conv_slot >= 0 && ch < a.hidden && (i == 0 || lane < 8);
+#pragma unroll
+                for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+                    conv_tap[i][j] = (on && j < a.conv_taps) ? a.conv_w[(size_t)ch * a.conv_taps + j] : 0.0f;
+                    if (j < CONV_MAX_TAPS - 1)
+                        conv_window[i][j] = (on && j < a.conv_taps - 1)
+                            ? load_stream1(a.conv_state + conv_slot * a.conv_slot_stride + (size_t)j * a.hidden + ch) : 0.0f;
+                }
+                if (on && a.conv_bias) conv_b[i] = a.conv_bias[ch];
             }
         }
 
@@ -342,6 +389,45 @@ gemm_stream_kernel(StreamArgs a) {
         if (warp != 0) continue;
 
         // ---- epilogue (warp 0).  In a lane: c0: (row g, token 2t), c1: (row g, token 2t+1), c2/c3: row g + 8.
+        if constexpr (CONV) {
+            if constexpr (NT == 1) {
+                float inv = 1.0f;
+                if (a.partials_in) {
+                    float total = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) total += square_parts[c * PARTIAL_STRIDE + conv_token];
+                    inv = rsqrtf(total / (float)a.norm_k + a.eps);
+                }
+                // the tile's value of (row r, this lane's token), rounded as a stored product would be
+                auto value = [&](int r) {
+                    const float v = mine[(((r & 7) * 4 + (conv_token >> 1)) * 4) + (r >> 3) * 2 + (conv_token & 1)] * inv;
+                    return __bfloat162float(__float2bfloat16_rn(v));
+                };
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int j = i == 0 ? lane >> 3 : 4;
+                    const int ch = tile * CONV_CHANNELS + j;
+                    if (conv_slot < 0 || ch >= a.hidden || (i == 1 && lane >= 8)) continue;
+                    const float u = value(j) * value(2 * CONV_CHANNELS + j);
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < CONV_MAX_TAPS; ++k) {
+                        if (k < a.conv_taps) sum = fmaf(conv_tap[i][k], k == a.conv_taps - 1 ? u : conv_window[i][k < CONV_MAX_TAPS - 1 ? k : 0], sum);
+                    }
+                    const float out = value(CONV_CHANNELS + j) * (sum + conv_b[i]);
+                    const size_t at = (size_t)conv_token * a.hidden + ch;
+                    if (a.out_f32) ((float*)a.y)[at] = out;
+                    else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(out);
+                    float* state_row = a.conv_state + conv_slot * a.conv_slot_stride + ch;
+#pragma unroll
+                    for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) {
+                        if (k < a.conv_taps - 1)
+                            state_row[(size_t)k * a.hidden] = k == a.conv_taps - 2 ? u : conv_window[i][k + 1 < CONV_MAX_TAPS - 1 ? k + 1 : 0];
+                    }
+                }
+            }
+            continue;
+        }
         if (a.res_in) {
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
@@ -411,10 +497,10 @@ gemm_stream_kernel(StreamArgs a) {
     if (timed_out && lane == 0 && a.status) atomicExch(a.status, 1);
 }
 
-template <int NT, int HELD>
+template <int NT, int HELD, bool CONV>
 int launch_as(const StreamArgs& a, int sm_count, cudaStream_t stream) {
     constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + (2 * CONSUMERS * NT * 128 + 16 * PARTIAL_STRIDE) * 4 + 128;
-    auto kernel = gemm_stream_kernel<NT, HELD>;
+    auto kernel = gemm_stream_kernel<NT, HELD, CONV>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -427,16 +513,21 @@ int launch_as(const StreamArgs& a, int sm_count, cudaStream_t stream) {
 }
 
 int launch_stream(StreamArgs& a, int sm_count, cudaStream_t stream) {
-    a.tiles = a.mode == MODE_GLU ? (a.inter + 7) / 8 : (a.N + ROWS - 1) / ROWS;
+    a.tiles = a.mode == MODE_GLU ? (a.inter + 7) / 8 : a.mode == MODE_CONV ? (a.hidden + CONV_CHANNELS - 1) / CONV_CHANNELS : (a.N + ROWS - 1) / ROWS;
     a.status = shiso_tc_status_word();
     const int chunks = (a.K + KC - 1) / KC;
     // NT = 1: one 8-token tile per weight fragment.  With two (9..16 rows) the held activations
     // took the registers of a second CTA per SM, and a decode step at batch 16 ran at 17.9k
     // tokens/s against 19.8k with the tensor-memory kernel and separate norm kernels; reading
     // the activations from L2 every stage instead fell to 11.5k.  Those rows are not built.
-    if (chunks == 1) return launch_as<1, 1>(a, sm_count, stream);
-    if (chunks == 2) return launch_as<1, 2>(a, sm_count, stream);
-    return launch_as<1, 0>(a, sm_count, stream);
+    if (a.mode == MODE_CONV) {
+        if (chunks == 1) return launch_as<1, 1, true>(a, sm_count, stream);
+        if (chunks == 2) return launch_as<1, 2, true>(a, sm_count, stream);
+        return launch_as<1, 0, true>(a, sm_count, stream);
+    }
+    if (chunks == 1) return launch_as<1, 1, false>(a, sm_count, stream);
+    if (chunks == 2) return launch_as<1, 2, false>(a, sm_count, stream);
+    return launch_as<1, 0, false>(a, sm_count, stream);
 }
 
 }  // namespace
@@ -513,5 +604,43 @@ SHISO_API int shiso_gemm_stream_scaled(const void* x, const float* partials, int
     a.partial_count = partial_count;
     a.norm_k = K;
     a.eps = eps;
+    return launch_stream(a, sm_count, stream);
+}
+
+// A short convolution's input projection and the gated convolution behind it in one launch, for
+// steps in which every sequence brings one row (T <= 8 rows): w [3 * hidden, K] bf16 (rows B, C,
+// x), conv_w [hidden, taps] (2..4 taps), state [slots][taps - 1][hidden] float with slot_stride
+// floats between slots, slots[seq_of_token[t]] the slot of row t; y [T, hidden].  With `partials`
+// the rows of x lack their RMS scale, as in shiso_gemm_stream_scaled; null: x is taken as it is.
+SHISO_API int shiso_gemm_stream_conv(const void* x, const float* partials, int partial_count, float eps, const void* w,
+                                     const float* conv_w, const float* conv_bias, float* state, long long slot_stride,
+                                     const int* seq_of_token, const int* slots, void* y, int y_dtype, int T, int hidden,
+                                     int K, int taps, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || hidden <= 0) return SHISO_OK;
+    if (T > MAX_ROWS || K % 8 != 0 || K <= 0 || sm_count <= 0 || taps < 2 || taps > CONV_MAX_TAPS) return SHISO_ERR_UNSUPPORTED;
+    if (partials && partial_count <= 0) return SHISO_ERR_SHAPE;
+    if (!conv_w || !state || !seq_of_token || !slots) return SHISO_ERR_SHAPE;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
+    StreamArgs a = {};
+    a.x = (const __nv_bfloat16*)x;
+    a.w = (const __nv_bfloat16*)w;
+    a.y = y;
+    a.T = T;
+    a.N = 3 * hidden;
+    a.K = K;
+    a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    a.mode = MODE_CONV;
+    a.partials_in = partials;
+    a.partial_count = partial_count;
+    a.norm_k = K;
+    a.eps = eps;
+    a.conv_w = conv_w;
+    a.conv_bias = conv_bias;
+    a.conv_state = state;
+    a.conv_slot_stride = slot_stride;
+    a.conv_seq_of_token = seq_of_token;
+    a.conv_slots = slots;
+    a.conv_taps = taps;
+    a.hidden = hidden;
     return launch_stream(a, sm_count, stream);
 }

@@ -359,11 +359,44 @@ def linear_add_rmsnorm(x, w, residual, norm_w, eps, out_dtype):
     return add_rmsnorm(residual, linear(x, w, out_dtype), norm_w, eps, out_dtype)
 
 
+CONV_FUSED_MAX_TAPS = 4  # taps the weight-streaming kernel's convolution epilogue takes
+
+
 def linear_short_conv(x, in_proj, taps, bias, state, step):
-    """The short conv's input projection followed by the gated convolution.  Two launches (a
-    single one, with the convolution in the product's epilogue, was measured and lost 3 us per
-    layer inside a captured step)."""
-    return short_conv(linear(x, in_proj, x.dtype), taps, bias, state, step)
+    """The short conv's input projection followed by the gated convolution; ``x`` is a tensor or
+    ``ScaledRows``.  For a handful of bfloat16 rows, one per sequence, the convolution runs in
+    the product's epilogue (a tile of the weight-streaming kernel is then the B, C and x rows of
+    five channels); else the product and the convolution kernel run one after the other."""
+    rows = x if isinstance(x, ScaledRows) else None
+    xt = rows.x if rows is not None else x
+    tokens, k = xt.shape
+    hidden, n_taps = taps.shape
+    if (
+        xt.dtype == torch.bfloat16 and in_proj.dtype == torch.bfloat16 and tokens <= STREAM_KERNEL_MAX_TOKENS
+        and getattr(step, "all_decode", False) and 2 <= n_taps <= CONV_FUSED_MAX_TAPS and k % 8 == 0
+    ):
+        _check(xt, "x", torch.bfloat16, 2)
+        _check(in_proj, "in_proj", torch.bfloat16, 2)
+        _check(taps, "conv taps", torch.float32, 2)
+        if in_proj.shape != (3 * hidden, k):
+            raise KernelError(f"an input projection of shape {tuple(in_proj.shape)} for {hidden} channels of rows of {k}")
+        if state.dtype != torch.float32 or not state.is_cuda or state.dim() != 3:
+            raise KernelError("conv state: expected a float32 CUDA tensor [slots, taps-1, hidden]")
+        if state.shape[1:] != (n_taps - 1, hidden) or state.stride(2) != 1 or state.stride(1) != hidden:
+            raise KernelError(f"conv state of shape {tuple(state.shape)} / strides {state.stride()} does not fit {n_taps} taps x {hidden}")
+        if bias is not None:
+            _check(bias, "conv bias", torch.float32, 1)
+        y = torch.empty((tokens, hidden), dtype=xt.dtype, device=xt.device)
+        status = library().shiso_gemm_stream_conv(
+            _ptr(xt), _ptr(rows.partials) if rows is not None else 0, rows.partials.shape[0] if rows is not None else 0,
+            rows.eps if rows is not None else 0.0, _ptr(in_proj), _ptr(taps), _ptr(bias), state.data_ptr(), state.stride(0),
+            _ptr(step.seq_of_token), _ptr(step.state_slots), _ptr(y), _code(y), tokens, hidden, k, n_taps,
+            _sm_count(), _stream(),
+        )
+        _done(status, "linear_short_conv")
+        return y
+    proj = linear_scaled(rows, in_proj, xt.dtype) if rows is not None else linear(xt, in_proj, xt.dtype)
+    return short_conv(proj, taps, bias, state, step)
 
 
 def linear_simple(x, w, out_dtype, bias=None):

@@ -183,22 +183,37 @@ class DeferredNorm:
     def materialize(self) -> torch.Tensor:
         return self.stream.normed(self.norm)
 
-    def linear(self, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+    def _scaled_rows(self):
+        """The rows without their scale (``ScaledRows`` of the kernel table) when the block output
+        waiting to be added is a product that the table can send straight into the stream;
+        else None, and nothing has happened."""
         stream, norm = self.stream, self.norm
         ops = norm.env.ops
         waiting = stream.pending
         into_stream = getattr(ops, "linear_into_stream", None)
         params = norm.rms_params() if hasattr(norm, "rms_params") else None
         if isinstance(waiting, DeferredLinear) and into_stream is not None and params is not None:
-            # the block output waiting to be added is a product: it goes straight into the
-            # stream and leaves rows that this product scales by itself
             result = into_stream(waiting.x, waiting.w, stream.residual, params[0], params[1])
             if result is not None:
                 stream.residual, rows = result
                 stream.pending = None
-                return ops.linear_scaled(rows, w, out_dtype, glu)
-        x = stream.normed(norm)
+                return rows
+        return None
+
+    def linear(self, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+        ops = self.norm.env.ops
+        rows = self._scaled_rows()
+        if rows is not None:
+            return ops.linear_scaled(rows, w, out_dtype, glu)  # this product scales the rows by itself
+        x = self.stream.normed(self.norm)
         return ops.linear_swiglu(x, w, out_dtype) if glu else ops.linear(x, w, out_dtype)
+
+    def linear_short_conv(self, in_proj: torch.Tensor, taps, bias, state, step) -> torch.Tensor:
+        """``ops.linear_short_conv`` of these rows (the input projection of a gated short
+        convolution and the convolution behind it)."""
+        ops = self.norm.env.ops
+        rows = self._scaled_rows()
+        return ops.linear_short_conv(rows if rows is not None else self.stream.normed(self.norm), in_proj, taps, bias, state, step)
 
 
 def project(ops, x, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:

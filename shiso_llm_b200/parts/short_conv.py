@@ -60,7 +60,7 @@ class ShortConv(Mixer):
     def forward(self, x, step, cache):
         ops = self.env.ops
         if isinstance(x, DeferredNorm):
-            y = ops.short_conv(x.linear(self.in_proj, self.env.dtype), self.conv, self.bias, cache.state, step)
+            y = x.linear_short_conv(self.in_proj, self.conv, self.bias, cache.state, step)
         else:
             y = ops.linear_short_conv(x, self.in_proj, self.conv, self.bias, cache.state, step)
         return DeferredLinear(ops, y, self.out_proj, self.env.dtype)

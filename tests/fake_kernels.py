@@ -103,6 +103,9 @@ def linear_add_rmsnorm(x, w, residual, norm_w, eps, out_dtype):
 
 
 def linear_short_conv(x, in_proj, taps, bias, state, step):
+    """``x`` is a tensor or ``ScaledRows``, as in the CUDA table."""
+    if isinstance(x, ScaledRows):
+        return short_conv(linear_scaled(x, in_proj, x.x.dtype), taps, bias, state, step)
     return short_conv(linear(x, in_proj, x.dtype), taps, bias, state, step)
 
 

@@ -541,6 +541,53 @@ def test_short_conv_few_rows_per_sequence_takes_the_serial_kernel(dtype):
     assert torch.allclose(s_one.cpu(), s_ref, rtol=0, atol=1e-7)
 
 
+@pytest.mark.parametrize("case", [(8, 2048, 2048, 3, True), (1, 96, 64, 2, False), (5, 1001, 264, 4, True), (8, 7, 1032, 3, False), (3, 300, 5632, 3, True)])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_input_projection_with_the_convolution_in_its_epilogue(case, scaled):
+    """A handful of bfloat16 rows, one per sequence: the short conv's input projection and the
+    gated convolution run as one launch (a tile of the product is the B, C and x rows of five
+    channels).  It must give, bit for bit, what the product kernel and the convolution kernel
+    give one after the other - output and state - and leave other slots alone; channel counts
+    that are no multiple of five, one to eight rows, 2..4 taps, rows with and without their
+    RMS scale pending."""
+    T, hidden, K, taps, bias = case
+    cpu, gpu, _ = make_step([1] * T, [3 + i for i in range(T)], 4, 64, 160, num_slots=11)
+    cpu.all_decode = gpu.all_decode = True
+    cpu.max_q_len = gpu.max_q_len = 1
+    x = rnd((T, K), torch.bfloat16, 161)
+    in_proj = rnd((3 * hidden, K), torch.bfloat16, 162, 0.05)
+    w = rnd((hidden, taps), torch.float32, 163)
+    b = rnd((hidden,), torch.float32, 164) if bias else None
+    start = rnd((11, taps - 1, hidden), torch.float32, 165)
+    rows = None
+    if scaled:
+        squares = (0.5 + torch.rand((-(-K // 16), 16), generator=torch.Generator().manual_seed(166))) * K / 16
+        rows = ops().ScaledRows(x.cuda(), squares.cuda().contiguous(), 1e-5)
+        proj = ops().linear_scaled(rows, in_proj.cuda(), torch.bfloat16)
+    else:
+        proj = ops().linear(x.cuda(), in_proj.cuda(), torch.bfloat16)
+    s_two, s_one, s_ref = start.clone().cuda(), start.clone().cuda(), start.clone()
+    two = ops().short_conv(proj, w.cuda(), b.cuda() if bias else None, s_two, gpu)
+    one = ops().linear_short_conv(rows if scaled else x.cuda(), in_proj.cuda(), w.cuda(), b.cuda() if bias else None, s_one, gpu)
+    ops().check_kernel_status()
+    assert torch.equal(one, two), f"fused and two-launch outputs differ by {(one.float() - two.float()).abs().max().item()}"
+    assert torch.equal(s_one, s_two)
+    # the plain convolution of the same projected rows (the products have their own tests)
+    want = ref.short_conv(proj.cpu(), w, b, s_ref, cpu)
+    close(one, want, torch.bfloat16, f"projection + convolution {case}")
+    assert torch.allclose(s_one.cpu(), s_ref, rtol=0, atol=1e-7)
+    untouched = torch.ones(11, dtype=torch.bool)
+    untouched[cpu.state_slots.long()] = False
+    assert torch.equal(s_one.cpu()[untouched], start[untouched]), "slots of other requests must not change"
+    # a step with two rows of one sequence is not taken by the fused route: same result through the two kernels
+    cpu2, gpu2, _ = make_step([2], [5], 4, 64, 167, num_slots=11)
+    s_a, s_b = start.clone().cuda(), start.clone().cuda()
+    xa = x[:1].repeat(2, 1).cuda()
+    ya = ops().linear_short_conv(xa, in_proj.cuda(), w.cuda(), b.cuda() if bias else None, s_a, gpu2)
+    yb = ops().short_conv(ops().linear(xa, in_proj.cuda(), torch.bfloat16), w.cuda(), b.cuda() if bias else None, s_b, gpu2)
+    assert torch.equal(ya, yb) and torch.equal(s_a, s_b)
+
+
 @pytest.mark.parametrize("shape", [(40, 600, 264), (130, 256, 512), (300, 1000, 96), (513, 2 * 5632, 2048), (777, 2 * 1000, 96), (2048, 2 * 264, 520)])
 def test_tensor_core_product_with_fused_swiglu(shape):
     """More than a handful of bfloat16 rows: gate and up accumulate side by side in tensor
