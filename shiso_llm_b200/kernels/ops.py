@@ -509,7 +509,8 @@ _DECODE_COUNTERS: dict = {}  # device -> arrays of int32 zeros; the fused decode
 def _decode_counters(device: torch.device, count: int) -> torch.Tensor:
     """Counters on which the parts of a (sequence, KV head) count themselves off.  They live as
     long as the process (captured steps hold their address); a larger step gets a larger array
-    and the old one stays alive for the steps that were captured with it."""
+    and the old one stays alive for the steps that were captured with it.  Launches that share
+    an array must not overlap on the device: the engine issues its steps on one stream."""
     held = _DECODE_COUNTERS.setdefault(device, [])
     if not held or held[-1].numel() < count:
         held.append(torch.zeros((max(count, 4096),), dtype=torch.int32, device=device))
