@@ -227,6 +227,10 @@ CASES = [  # heads, kv_heads, head_dim, page_size, rotary_dim
     (5, 5, 80, 16, 80),
     (8, 2, 64, 16, 64),
     (2, 1, 256, 4, 128),
+    (6, 3, 64, 8, 64),  # heads of 64 rotated whole (in bfloat16 the kernel of eight lanes per head): groups of four heads that mix kinds
+    (5, 1, 64, 16, 64),
+    (32, 8, 64, 16, 64),
+    (4, 4, 64, 4, 32),  # heads of 64 rotated in part: the general kernel
 ]
 
 
