@@ -55,6 +55,17 @@ struct DecodeTmaArgs {
     int width, heads, kv_heads, page_size, splits, window;
     int cache_rows;           // pages * page size: a row coordinate from here on reads zeros
     float scale_log2;
+    // FROM_QKV: the step's rows come straight from the qkv product, [T, (heads + 2 * kv_heads) * 64]
+    // (q unused): per-head RMS norm and rotation of q and of the new key happen here, and with
+    // `store` the new key and value are written to the caches (else another layer has written them)
+    const __nv_bfloat16* qkv;
+    const float* q_w;         // [64] norm weights
+    const float* k_w;
+    const float* inv_freq;    // [32]
+    __nv_bfloat16* k_cache;   // [pages, page, kv_heads, 64]
+    __nv_bfloat16* v_cache;
+    float eps;
+    int store;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -81,7 +92,22 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
 
+__device__ __forceinline__ void unpack4(uint2 raw, float* v) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+__device__ __forceinline__ uint2 pack4(const float* v) {
+    uint2 raw;
+    raw.x = pack2(v[0], v[1]);
+    raw.y = pack2(v[2], v[3]);
+    return raw;
+}
+
+// FROM_QKV: a variant of its own (what it holds would cost the plain kernel registers).
 // (five warps take the registers of eight: the bound of 256 threads x 3 CTAs caps them at 85 a thread)
+template <bool FROM_QKV>
 __global__ void __launch_bounds__(256, 3)
 decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeTmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -143,7 +169,10 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 const int key = (tile0 + i) * TILE + pg * a.page_size;
                 if (key <= pos && key + a.page_size > lo) row = table[key / a.page_size] * a.page_size;
             }
-            if (base == 0) pdl_wait();  // the cache rows of this step were written by the kernel before
+            // the cache rows of this step were written by the kernel before - unless this kernel
+            // writes them itself: then the caches hold nothing of this step yet, the kernel
+            // before only made the qkv rows, and the keys and values may start to move at once
+            if (base == 0 && !FROM_QKV) pdl_wait();
             if (on) {
                 const int stage = i % STAGES, use = i / STAGES;
                 if (use > 0 && !mbar_wait(&empty[stage], (use - 1) & 1)) {
@@ -158,18 +187,75 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
     } else {
         // ---- consumers: warp w scores keys 16w .. 16w+15 of every tile
+        // FROM_QKV: what depends on no predecessor comes first - lane p's sine and cosine of pair
+        // p's angle (passed round by shuffles later) and this thread's norm weights
+        float cs_lane = 1.0f, sn_lane = 0.0f, wq_lo[8], wq_hi[8];
+        if constexpr (FROM_QKV) {
+            sincosf((float)pos * a.inv_freq[lane], &sn_lane, &cs_lane);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // i = 4 kk + 2 h + e: column 16 kk + 8 h + 2 t4 + e and its partner 32 on
+                const int c = (i >> 2) * 16 + ((i >> 1) & 1) * 8 + t4 * 2 + (i & 1);
+                wq_lo[i] = a.q_w[c];
+                wq_hi[i] = a.q_w[c + 32];
+            }
+        }
         pdl_wait();
         uint32_t q_frag[KSTEPS][4];
         {
             // the group's queries as the 16 rows of the MMA's A operand (rows past the group are zero)
-            const uint32_t* q_lo = reinterpret_cast<const uint32_t*>(a.q + ((size_t)t * a.heads + g_head * group + min(g, group - 1)) * HEAD);
-            const uint32_t* q_hi = reinterpret_cast<const uint32_t*>(a.q + ((size_t)t * a.heads + g_head * group + min(g + 8, group - 1)) * HEAD);
+            const int units = a.heads + 2 * a.kv_heads;
+            const __nv_bfloat16* q_rows = FROM_QKV ? a.qkv + (size_t)t * units * HEAD : a.q + (size_t)t * a.heads * HEAD;
+            const uint32_t* q_lo = reinterpret_cast<const uint32_t*>(q_rows + (size_t)(g_head * group + min(g, group - 1)) * HEAD);
+            const uint32_t* q_hi = reinterpret_cast<const uint32_t*>(q_rows + (size_t)(g_head * group + min(g + 8, group - 1)) * HEAD);
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; ++kk) {
                 q_frag[kk][0] = g < group ? q_lo[kk * 8 + t4] : 0u;
                 q_frag[kk][1] = g + 8 < group ? q_hi[kk * 8 + t4] : 0u;
                 q_frag[kk][2] = g < group ? q_lo[kk * 8 + 4 + t4] : 0u;
                 q_frag[kk][3] = g + 8 < group ? q_hi[kk * 8 + 4 + t4] : 0u;
+            }
+            if constexpr (FROM_QKV) {
+                // RMS norm over the head and rotation of the pairs (c, c + 32): a thread holds
+                // columns 16 kk + 8 h + 2 t4 + e of rows g and g + 8, so a row's 64 values lie in the
+                // four threads of a quad and a pair lies in one thread (kk and kk + 2)
+                float ss[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q_frag[kk][r]));
+                        ss[r & 1] += v.x * v.x + v.y * v.y;
+                    }
+                float inv[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 1);
+                    ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 2);
+                    inv[r] = rsqrtf(ss[r] / (float)HEAD + a.eps);
+                }
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = kk * 16 + h * 8 + t4 * 2;  // and c + 1; partners c + 32, c + 33
+                        float cs[2], sn[2], w_lo[2], w_hi[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            cs[e] = __shfl_sync(0xffffffffu, cs_lane, c + e);
+                            sn[e] = __shfl_sync(0xffffffffu, sn_lane, c + e);
+                            w_lo[e] = wq_lo[kk * 4 + h * 2 + e];
+                            w_hi[e] = wq_hi[kk * 4 + h * 2 + e];
+                        }
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {  // rows g and g + 8
+                            const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q_frag[kk][h * 2 + r]));
+                            const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q_frag[kk + 2][h * 2 + r]));
+                            const float x0 = lo2.x * inv[r] * w_lo[0], y0 = hi2.x * inv[r] * w_hi[0];
+                            const float x1 = lo2.y * inv[r] * w_lo[1], y1 = hi2.y * inv[r] * w_hi[1];
+                            q_frag[kk][h * 2 + r] = pack2(x0 * cs[0] - y0 * sn[0], x1 * cs[1] - y1 * sn[1]);
+                            q_frag[kk + 2][h * 2 + r] = pack2(x0 * sn[0] + y0 * cs[0], x1 * sn[1] + y1 * cs[1]);
+                        }
+                    }
             }
         }
 #pragma unroll
@@ -184,6 +270,67 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             const uint32_t kt = smem_u32(ring + stage * STAGE_BYTES) + warp * 16 * ROW;
             const uint32_t vt = kt + TILE_BYTES;
             const int key0 = (tile0 + i) * TILE + warp * 16;
+            if constexpr (FROM_QKV) {
+                if (a.store && pos >= key0 && pos < key0 + 16) {
+                    // This token's own key and value are not in the cache yet: this warp owns their
+                    // row of the tile, makes them from the qkv row - eight lanes a head, the
+                    // arithmetic of the norm + rotate + store kernel, so that the cache holds the
+                    // same bits whichever kernel wrote a row - and writes them into the tile and
+                    // into the cache.  Lanes 0..7: the key; lanes 8..15: the value.
+                    const int l8 = lane & 7, what = lane >> 3;
+                    const int units = a.heads + 2 * a.kv_heads;
+                    const int unit = a.heads + (what == 0 ? 0 : a.kv_heads) + g_head;
+                    uint2 lo_raw = make_uint2(0u, 0u), hi_raw = lo_raw;
+                    if (what < 2) {
+                        const __nv_bfloat16* src = a.qkv + ((size_t)t * units + unit) * HEAD + 4 * l8;
+                        lo_raw = *reinterpret_cast<const uint2*>(src);
+                        hi_raw = *reinterpret_cast<const uint2*>(src + 32);
+                    }
+                    float x[4], y[4];
+                    unpack4(lo_raw, x);
+                    unpack4(hi_raw, y);
+                    float square = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) square += x[e] * x[e] + y[e] * y[e];
+                    square += __shfl_xor_sync(0xffffffffu, square, 1);
+                    square += __shfl_xor_sync(0xffffffffu, square, 2);
+                    square += __shfl_xor_sync(0xffffffffu, square, 4);
+                    float cs[4], sn[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {  // all lanes take part
+                        cs[e] = __shfl_sync(0xffffffffu, cs_lane, 4 * l8 + e);
+                        sn[e] = __shfl_sync(0xffffffffu, sn_lane, 4 * l8 + e);
+                    }
+                    if (what == 0) {
+                        const float inv = rsqrtf(square / (float)HEAD + a.eps);
+                        float out_lo[4], out_hi[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int p = 4 * l8 + e;
+                            const float xv = x[e] * inv * a.k_w[p], yv = y[e] * inv * a.k_w[p + 32];
+                            out_lo[e] = xv * cs[e] - yv * sn[e];
+                            out_hi[e] = xv * sn[e] + yv * cs[e];
+                        }
+                        lo_raw = pack4(out_lo);
+                        hi_raw = pack4(out_hi);
+                    }
+                    if (what < 2) {
+                        const int page = a.block_table[(size_t)seq * a.width + pos / a.page_size];
+                        const size_t cache_row = (size_t)page * a.page_size + pos % a.page_size;
+                        __nv_bfloat16* dst = (what == 0 ? a.k_cache : a.v_cache) + (cache_row * a.kv_heads + g_head) * HEAD + 4 * l8;
+                        *reinterpret_cast<uint2*>(dst) = lo_raw;
+                        *reinterpret_cast<uint2*>(dst + 32) = hi_raw;
+                        // the row in the tile: 16-byte piece (l8 >> 1) of the row's low half, piece 4 + .. of its high half
+                        const uint32_t r = (uint32_t)(pos - (tile0 + i) * TILE);
+                        const uint32_t row_addr = smem_u32(ring + stage * STAGE_BYTES) + what * TILE_BYTES + r * ROW;
+                        const uint32_t piece = l8 >> 1, inside = (l8 & 1) * 8;
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(row_addr + (((piece) ^ (r & 7)) << 4) + inside), "r"(lo_raw.x), "r"(lo_raw.y) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(row_addr + (((piece + 4) ^ (r & 7)) << 4) + inside), "r"(hi_raw.x), "r"(hi_raw.y) : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before a later copy refills the stage
+                    __syncwarp();
+                }
+            }
             if (key0 <= pos && key0 + 16 > lo) {  // warp-uniform: some of this warp's keys are seen
                 float s_acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 #pragma unroll
@@ -345,50 +492,20 @@ SHISO_API int shiso_decode_attention_fused_supported(int heads, int kv_heads, in
            page_size <= TILE && page_size % 8 == 0 && TILE % page_size == 0 && tc::encode_fn() != nullptr;
 }
 
-// As shiso_decode_attention, with `counters` (tokens * kv_heads ints that are zero between
-// launches; the kernel leaves them zero) and the number of pages of the caches.
-SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                           int table_width, const int* positions, const int* seq_of_token, float* scratch,
-                                           int* counters, void* out, int tokens, int heads, int kv_heads, int head_dim,
-                                           int page_size, long long num_pages, float scale, int window, int splits,
-                                           cudaStream_t stream) {
-    if (tokens <= 0) return SHISO_OK;
-    if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
-    if (!shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size)) return SHISO_ERR_UNSUPPORTED;
-    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SHISO_ERR_ALIGN;
-    if (tokens > 65535 || kv_heads > 65535) return SHISO_ERR_UNSUPPORTED;  // grid limits
-    const long long cache_rows = num_pages * page_size;
-    if (cache_rows + page_size > 0x7fffffffLL) return SHISO_ERR_UNSUPPORTED;
-    CUtensorMap mk, mv;
-    if (!tc::tensor_map_paged(k_cache, cache_rows, kv_heads, page_size, &mk) ||
-        !tc::tensor_map_paged(v_cache, cache_rows, kv_heads, page_size, &mv))
-        return SHISO_ERR_UNSUPPORTED;
-    DecodeTmaArgs a;
-    a.q = (const __nv_bfloat16*)q;
-    a.block_table = block_table;
-    a.positions = positions;
-    a.seq_of_token = seq_of_token;
-    a.partial = scratch;
-    a.counters = counters;
-    a.out = (__nv_bfloat16*)out;
-    a.status = shiso_tc_status_word();
-    a.width = table_width;
-    a.heads = heads;
-    a.kv_heads = kv_heads;
-    a.page_size = page_size;
-    a.splits = splits;
-    a.window = window;
-    a.cache_rows = (int)cache_rows;
-    a.scale_log2 = scale * 1.4426950408889634f;
+namespace {
+
+template <bool FROM_QKV>
+int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTmaArgs& a, int tokens, cudaStream_t stream) {
+    auto kernel = decode_tma_kernel<FROM_QKV>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(splits, kv_heads, tokens);
+    cfg.gridDim = dim3(a.splits, a.kv_heads, tokens);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
@@ -397,5 +514,90 @@ SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, c
     attr[0].val.programmaticStreamSerializationAllowed = shiso_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, decode_tma_kernel, mk, mv, a);
+    return (int)cudaLaunchKernelEx(&cfg, kernel, mk, mv, a);
+}
+
+// What both entry points check and fill in.
+int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* block_table, int table_width,
+                       const int* positions, const int* seq_of_token, float* scratch, int* counters, void* out, int tokens,
+                       int heads, int kv_heads, int head_dim, int page_size, long long num_pages, float scale, int window,
+                       int splits, DecodeTmaArgs* a, CUtensorMap* mk, CUtensorMap* mv) {
+    if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
+    if (!shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size)) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SHISO_ERR_ALIGN;
+    if (tokens > 65535 || kv_heads > 65535) return SHISO_ERR_UNSUPPORTED;  // grid limits
+    const long long cache_rows = num_pages * page_size;
+    if (cache_rows + page_size > 0x7fffffffLL) return SHISO_ERR_UNSUPPORTED;
+    if (!tc::tensor_map_paged(k_cache, cache_rows, kv_heads, page_size, mk) ||
+        !tc::tensor_map_paged(v_cache, cache_rows, kv_heads, page_size, mv))
+        return SHISO_ERR_UNSUPPORTED;
+    *a = DecodeTmaArgs{};
+    a->block_table = block_table;
+    a->positions = positions;
+    a->seq_of_token = seq_of_token;
+    a->partial = scratch;
+    a->counters = counters;
+    a->out = (__nv_bfloat16*)out;
+    a->status = shiso_tc_status_word();
+    a->width = table_width;
+    a->heads = heads;
+    a->kv_heads = kv_heads;
+    a->page_size = page_size;
+    a->splits = splits;
+    a->window = window;
+    a->cache_rows = (int)cache_rows;
+    a->scale_log2 = scale * 1.4426950408889634f;
+    return SHISO_OK;
+}
+
+}  // namespace
+
+// As shiso_decode_attention, with `counters` (tokens * kv_heads ints that are zero between
+// launches; the kernel leaves them zero) and the number of pages of the caches.
+SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                           int table_width, const int* positions, const int* seq_of_token, float* scratch,
+                                           int* counters, void* out, int tokens, int heads, int kv_heads, int head_dim,
+                                           int page_size, long long num_pages, float scale, int window, int splits,
+                                           cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if ((uintptr_t)q & 15) return SHISO_ERR_ALIGN;
+    DecodeTmaArgs a;
+    CUtensorMap mk, mv;
+    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token, scratch, counters,
+                                          out, tokens, heads, kv_heads, head_dim, page_size, num_pages, scale, window, splits, &a,
+                                          &mk, &mv);
+    if (status != SHISO_OK) return status;
+    a.q = (const __nv_bfloat16*)q;
+    return launch_decode_tma<false>(mk, mv, a, tokens, stream);
+}
+
+// The same from the rows of the qkv product, [T, (heads + 2 * kv_heads) * 64] bf16: the per-head RMS
+// norm (weights q_w, k_w [64], eps) and the rotation of all 64 values by position * inv_freq[32]
+// of the queries and of each token's new key happen in the kernel, and with `store` the new key
+// and value are written into the caches (with the bits the norm + rotate + store kernel writes).
+// One row per sequence.
+SHISO_API int shiso_decode_attention_from_qkv(const void* qkv, const float* q_w, const float* k_w, const float* inv_freq,
+                                              float eps, void* k_cache, void* v_cache, const int* block_table,
+                                              int table_width, const int* positions, const int* seq_of_token,
+                                              float* scratch, int* counters, void* out, int tokens, int heads, int kv_heads,
+                                              int head_dim, int page_size, long long num_pages, float scale, int window,
+                                              int splits, int store, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (!qkv || !q_w || !k_w || !inv_freq) return SHISO_ERR_SHAPE;
+    if ((uintptr_t)qkv & 15) return SHISO_ERR_ALIGN;
+    DecodeTmaArgs a;
+    CUtensorMap mk, mv;
+    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token, scratch, counters,
+                                          out, tokens, heads, kv_heads, head_dim, page_size, num_pages, scale, window, splits, &a,
+                                          &mk, &mv);
+    if (status != SHISO_OK) return status;
+    a.qkv = (const __nv_bfloat16*)qkv;
+    a.q_w = q_w;
+    a.k_w = k_w;
+    a.inv_freq = inv_freq;
+    a.k_cache = (__nv_bfloat16*)k_cache;
+    a.v_cache = (__nv_bfloat16*)v_cache;
+    a.eps = eps;
+    a.store = store;
+    return launch_decode_tma<true>(mk, mv, a, tokens, stream);
 }

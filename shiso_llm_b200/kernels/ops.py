@@ -517,6 +517,52 @@ def _decode_counters(device: torch.device, count: int) -> torch.Tensor:
     return held[-1]
 
 
+DECODE_FROM_QKV_MAX_TOKENS = 8  # rows up to which attention takes the qkv rows itself (batch 8 decodes 1 % faster with one launch fewer per layer; at 16 and 64 rows the longer start of every CTA costs 1.5 %)
+
+
+def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
+                              k_cache, v_cache, block_table, page_size, store, scale, window):
+    """``qk_norm_rope_store`` and ``paged_attention`` in one launch for steps of single tokens:
+    the attention kernel takes the rows of the qkv product, norms and rotates the queries and
+    each token's new key itself, and (with ``store``) writes the new key and value into the
+    caches, with the bits ``qk_norm_rope_store`` would write.  bfloat16, heads of 64 rotated
+    whole, both norms present, a handful of rows; None when the step or the sizes are others (the
+    caller then runs the two kernels)."""
+    lib = library()
+    if (
+        qkv.shape[0] > DECODE_FROM_QKV_MAX_TOKENS or qkv.dtype != torch.bfloat16 or not getattr(step, "all_decode", False) or q_w is None or k_w is None
+        or inv_freq is None or head_dim != 64 or rotary_dim != 64 or kv_heads <= 0
+        or not lib.shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size)
+    ):
+        return None
+    _check(qkv, "qkv", torch.bfloat16, 2)
+    tokens, width = qkv.shape
+    if width != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"qkv rows of {width} are not ({heads} + 2 x {kv_heads}) x {head_dim}")
+    for name, t in (("k cache", k_cache), ("v cache", v_cache)):
+        _check(t, name, torch.bfloat16, 4)
+        if t.shape[1:] != (page_size, kv_heads, head_dim):
+            raise KernelError(f"{name} of shape {tuple(t.shape)} does not fit pages of {page_size} x {kv_heads} x {head_dim}")
+    _check(block_table, "block table", torch.int32, 2)
+    _check(q_w, "q norm weight", torch.float32, 1)
+    _check(k_w, "k norm weight", torch.float32, 1)
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    if q_w.shape[0] != head_dim or k_w.shape[0] != head_dim or inv_freq.shape[0] != rotary_dim // 2:
+        raise KernelError("norm weights of the head size and one frequency per rotated pair are expected")
+    out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size, True)
+    scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
+    counters = _decode_counters(qkv.device, tokens * kv_heads)
+    status = lib.shiso_decode_attention_from_qkv(
+        _ptr(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), float(eps), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+        block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), _ptr(scratch), _ptr(counters), _ptr(out),
+        tokens, heads, kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), splits, int(bool(store)),
+        _stream(),
+    )
+    _done(status, "decode_attention_from_qkv")
+    return out
+
+
 def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table, page_size, scale, window, step,
                     general=False):
     """Attention of every row over its sequence's cache.  Steps of single tokens in bfloat16

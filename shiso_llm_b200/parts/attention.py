@@ -102,6 +102,16 @@ class GqaAttention(Mixer):
         store = cache.owner and not self.borrows_cache
         qkv = project(ops, x, self.qkv, self.env.dtype)
         inv_freq, rotary_dim = self.position.rotary()
+        from_qkv = getattr(ops, "decode_attention_from_qkv", None)
+        if from_qkv is not None and not self.borrows_cache and self.q_norm is not None and self.k_norm is not None:
+            # steps of single tokens: norm, rotation, cache store and attention in one launch
+            attn = from_qkv(
+                qkv, self.heads, self.kv_heads, self.head_dim, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
+                inv_freq, rotary_dim, step, cache.k, cache.v, step.block_tables[cache.group], cache.page_size, store,
+                self.scale, self.window or 0,
+            )
+            if attn is not None:
+                return DeferredLinear(ops, attn, self.out, self.env.dtype)
         q = ops.qk_norm_rope_store(
             qkv,
             self.heads,

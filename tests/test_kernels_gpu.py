@@ -269,6 +269,54 @@ def test_norm_rope_store_then_attention(dtype, case):
         close(got, want, dtype, f"attention window {window}", rel32=4e-6)
 
 
+@pytest.mark.parametrize("case", [(32, 8, 16), (12, 3, 8), (5, 1, 64), (7, 7, 32), (16, 1, 16)])
+@pytest.mark.parametrize("store", [True, False])
+def test_decode_attention_from_the_qkv_rows(case, store):
+    """Steps of single tokens, bfloat16, heads of 64: norm + rotation + cache store + attention
+    as one launch.  Against the two kernels it replaces: the caches must hold the same bits
+    afterwards (and nothing else may have changed), the outputs agree up to the rounding of
+    the queries; against the plain implementation too.  Sequences of one key, at a page's and
+    a tile's edge and thousands long, with and without a window, and with another layer's
+    cache (nothing is stored then)."""
+    heads, kv_heads, page = case
+    d = 64
+    starts = [0, page - 1, page, 63, 64, 700, 2100]  # seven rows: the engine sends up to eight this way
+    num_pages = sum(-(-(s + 1) // page) for s in starts) + 3
+    cpu, gpu, table = make_step([1] * len(starts), starts, page, num_pages, 170)
+    cpu.all_decode = gpu.all_decode = True
+    dtype = torch.bfloat16
+    T = len(starts)
+    qkv = rnd((T, (heads + 2 * kv_heads) * d), dtype, 171)
+    qw = 1.0 + 0.2 * rnd((d,), torch.float32, 172)
+    kw = 1.0 + 0.2 * rnd((d,), torch.float32, 173)
+    inv_freq = (10000.0 ** (-torch.arange(d // 2, dtype=torch.float64) * 2 / d)).float()
+    eps = 1e-5
+    k0 = rnd((num_pages, page, kv_heads, d), dtype, 174)
+    v0 = rnd((num_pages, page, kv_heads, d), dtype, 175)
+    scale = 1.0 / math.sqrt(d)
+    for window in (0, 50):
+        k_two, v_two, k_one, v_one = k0.clone().cuda(), v0.clone().cuda(), k0.clone().cuda(), v0.clone().cuda()
+        q = ops().qk_norm_rope_store(qkv.cuda(), heads, kv_heads, d, qw.cuda(), kw.cuda(), eps, inv_freq.cuda(), d, gpu,
+                                     k_two, v_two, table.cuda(), page, store)
+        two = ops().paged_attention(q, heads, kv_heads, d, k_two, v_two, table.cuda(), page, scale, window, gpu)
+        one = ops().decode_attention_from_qkv(qkv.cuda(), heads, kv_heads, d, qw.cuda(), kw.cuda(), eps, inv_freq.cuda(), d, gpu,
+                                              k_one, v_one, table.cuda(), page, store, scale, window)
+        ops().check_kernel_status()
+        assert one is not None
+        assert torch.equal(k_one, k_two) and torch.equal(v_one, v_two), "the caches differ from the two-kernel route's"
+        if not store:
+            assert torch.equal(k_one.cpu(), k0) and torch.equal(v_one.cpu(), v0)
+        close(one, two, dtype, f"from qkv against two kernels {case} window {window}")
+        kc, vc = k0.clone(), v0.clone()
+        want_q = ref.qk_norm_rope_store(qkv, heads, kv_heads, d, qw, kw, eps, inv_freq, d, cpu, kc, vc, table, page, store)
+        want = ref.paged_attention(want_q, heads, kv_heads, d, kc, vc, table, page, scale, window, cpu)
+        close(one, want, dtype, f"from qkv against the plain implementation {case} window {window}")
+    # other steps and sizes are declined
+    cpu2, gpu2, table2 = make_step([2], [5], page, num_pages, 176)
+    assert ops().decode_attention_from_qkv(qkv[:2].cuda(), heads, kv_heads, d, qw.cuda(), kw.cuda(), eps, inv_freq.cuda(), d, gpu2,
+                                           k0.cuda(), v0.cuda(), table2.cuda(), page, True, scale, 0) is None
+
+
 def test_attention_finds_a_far_key():
     """One key among hundreds is made to stand out; the output must be (almost) its value."""
     heads, kv_heads, d, page = 2, 1, 32, 16
