@@ -79,9 +79,20 @@ argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ best_v
     const float* row = logits + (size_t)row_index * vocab;
     const int begin = chunk * chunk_len, end = min(begin + chunk_len, vocab);
     Best mine{-INFINITY, 0x7fffffff};
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        const float v = row[i];
-        if (isfinite(v) && v > mine.v) mine = Best{v, i};
+    if (((vocab | chunk_len) & 3) == 0 && (((uintptr_t)logits) & 15) == 0) {
+        // four values per load; a thread still meets its values in ascending order of index
+        for (int i = begin + 4 * threadIdx.x; i < end; i += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            if (isfinite(v.x) && v.x > mine.v) mine = Best{v.x, i};
+            if (isfinite(v.y) && v.y > mine.v) mine = Best{v.y, i + 1};
+            if (isfinite(v.z) && v.z > mine.v) mine = Best{v.z, i + 2};
+            if (isfinite(v.w) && v.w > mine.v) mine = Best{v.w, i + 3};
+        }
+    } else {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+            const float v = row[i];
+            if (isfinite(v) && v > mine.v) mine = Best{v, i};
+        }
     }
     const Best r = block_best(mine, scratch);
     if (threadIdx.x == 0) {
@@ -273,7 +284,7 @@ SHISO_API int shiso_argmax_chunked(const float* logits, int* out, float* scratch
                                    cudaStream_t stream) {
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0 || chunks <= 0) return SHISO_ERR_SHAPE;
-    const int chunk_len = (vocab + chunks - 1) / chunks;
+    const int chunk_len = ((vocab + chunks - 1) / chunks + 3) / 4 * 4;  // a multiple of four: 16-byte loads where the row allows
     float* best_v = scratch;
     int* best_i = (int*)(scratch + (size_t)rows * chunks);
     launch_kernel(argmax_chunk_kernel, dim3(chunks, rows), 256, 0, stream, logits, best_v, best_i, vocab, chunk_len, chunks);
