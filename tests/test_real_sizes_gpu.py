@@ -100,3 +100,36 @@ def test_real_layer_sizes_long_portions_and_mixed_steps(sized, sized_long, dtype
     check_logits(replay.stack_rows(rows, "a", len(a)), ref_a, dtype, f"long request, {dtype}")
     check_logits(replay.stack_rows(rows, "b", len(b)), ref_b, dtype, f"second request, {dtype}")
     engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_sizes_a_dozen_decoding_requests(sized, dtype):
+    """Twelve requests of different lengths decoding together at the same layer sizes: steps of
+    twelve single tokens (products with tokens as the MMA's N operand and the residual add and
+    norm in their epilogues, the decode attention over twelve block tables, the serial short
+    conv), after their prompts went in as one mixed step; then nine of them go on (a step of
+    nine rows) while three have ended and given their pages back."""
+    from shiso_llm_b200.kernels import ops
+
+    document, plan, specs, stored, _, _ = sized
+    compute = torch.float32 if dtype == "float32" else torch.bfloat16
+    by = {s.name: s for s in specs}
+    tensors = {k: v.to("cuda", target_dtype(by[k], v.dtype, compute)) for k, v in stored.items()}
+    options = EngineOptions(dtype=dtype, ctx=256, page_size=16, kv_cache_tokens=12 * 80, max_num_seqs=12,
+                            max_num_batched_tokens=512)
+    engine = Engine.from_plan(plan, tensors, options, ops)
+    names = [f"r{i}" for i in range(12)]
+    prompts = {n: helpers.random_prompt(30 + 3 * i, document["vocab_size"], 40 + i) for i, n in enumerate(names)}
+    starts = {n: 17 + 2 * i for i, n in enumerate(names)}  # rows that go in with the first step
+    references = {n: plain_lfm2.plain_forward(document, stored, prompts[n]) for n in names}
+    steps = [([(n, prompts[n][: starts[n]], list(range(starts[n]))) for n in names], [])]
+    for k in range(8):
+        steps.append(([(n, [prompts[n][starts[n] + k]], [0]) for n in names], names[:3] if k == 7 else []))
+    for k in range(8, 13):
+        steps.append(([(n, [prompts[n][starts[n] + k]], [0]) for n in names[3:]], names[3:] if k == 12 else []))
+    rows = helpers.run_steps(engine, steps)
+    ops.check_kernel_status()
+    for i, n in enumerate(names):
+        seen = starts[n] + (8 if i < 3 else 13)
+        check_logits(replay.stack_rows(rows, n, seen), references[n][:seen], dtype, f"request {n} of twelve, {dtype}")
+    engine.cache.check()
