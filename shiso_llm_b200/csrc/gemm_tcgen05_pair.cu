@@ -20,6 +20,14 @@
 // the accumulator's columns 0..127 are gate and 128..255 up, and the epilogue writes
 // silu(gate) * up.
 //
+// Measured and dropped: dealing the work out as equal shares of all k blocks of all tiles laid
+// end to end, so that no wave of tiles is left part empty (96 tiles on 74 pairs), with the pair
+// that has a tile's first k block adding the partial accumulators the others leave in global
+// memory.  Right results, slower products: 2,048 x 6144 x 2048 took 50.0 us against 38.6,
+// 2,048 x 2048 x 2048 31.8 against 17.3 - every pair then ends with a tile it has to wait and
+// add for, the 19 MB of partial sums go through the L2 that already bounds the main loop, and
+// the pairs no longer walk the k blocks of neighbouring tiles in step.
+//
 // The loads carry no multicast qualifier.  Every wait is bounded by a clock limit; a CTA that
 // gives up sets the status word, and all CTAs still meet at the cluster barrier before TMEM is
 // freed.
