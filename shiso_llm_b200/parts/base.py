@@ -146,7 +146,8 @@ class Embedding(Part):
 
 class Head(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """``x[R, hidden]`` (compute dtype) -> float32 logits ``[R, vocab]``."""
+        """``x[R, hidden]`` (compute dtype) -> float32 logits ``[R, vocab]``.  A head that sets
+        ``takes_deferred_norm = True`` may be handed a ``DeferredNorm`` and starts with ``project``."""
         raise NotImplementedError
 
 

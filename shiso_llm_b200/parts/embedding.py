@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.spec import TensorSpec
-from .base import EMBEDDINGS, HEADS, Embedding, Head
+from .base import EMBEDDINGS, HEADS, Embedding, Head, project
 
 
 @EMBEDDINGS.register("token_embedding")
@@ -40,6 +40,8 @@ class TokenEmbedding(Embedding):
 
 @HEADS.register("linear_head")
 class LinearHead(Head):
+    takes_deferred_norm = True
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         p = spec.params
@@ -60,4 +62,5 @@ class LinearHead(Head):
         self.weight = tensors[self.tied_to if self.tied_to is not None else self.tensor_name]
 
     def forward(self, x):
-        return self.env.ops.linear(x, self.weight, torch.float32)
+        """Float32 logits of the rows ``x``, a tensor or a ``DeferredNorm``."""
+        return project(self.env.ops, x, self.weight, torch.float32)

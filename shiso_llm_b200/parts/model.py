@@ -82,7 +82,8 @@ class Model:
             return None
         if getattr(step, "wants_every_row", False):
             # every row in order (a decode step): the norm that closes the last block is the final norm
-            return self.head.forward(stream.normed(self.final_norm))
+            # (handed over unevaluated to a head that says it takes that: its product may apply the row scale itself)
+            return self.head.forward(stream.normed(self.final_norm, deferred=getattr(self.head, "takes_deferred_norm", False)))
         rows = step.want_rows
         delta = stream.take_pending()
         if delta is not None:
