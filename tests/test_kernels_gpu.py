@@ -744,3 +744,89 @@ def test_product_into_the_stream_declines_what_it_cannot_take():
     x = torch.zeros(65, 64, device="cuda", dtype=torch.bfloat16)
     assert ops().linear_into_stream(x, w, torch.zeros(65, 32, device="cuda"), nw, 1e-5) is None  # too many rows
     assert ops().linear_into_stream(x[:4].float(), w.float(), torch.zeros(4, 32, device="cuda"), nw, 1e-5) is None
+
+
+def _random_shapes(seed, count):
+    """Row counts on both sides of every dispatch boundary of the products, with feature and k
+    counts that are multiples of 8 but of nothing larger."""
+    g = torch.Generator().manual_seed(seed)
+    edges = [1, 7, 8, 9, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 511, 512, 513, 700]
+    shapes = []
+    for i in range(count):
+        T = edges[int(torch.randint(len(edges), (1,), generator=g))]
+        N = 8 * int(torch.randint(1, 160, (1,), generator=g))
+        K = 8 * int(torch.randint(1, 200, (1,), generator=g))
+        shapes.append((T, N, K))
+    return shapes
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_products_at_random_sizes_around_every_boundary(seed):
+    """Forty random (rows, features, k) per seed, rows chosen around the boundaries between the
+    product kernels: plain products (bfloat16 and float32 results, a bias) and gate/up pairs
+    against the plain reference."""
+    for T, N, K in _random_shapes(seed, 40):
+        x, w = rnd((T, K), torch.bfloat16, 1000 + T), rnd((N, K), torch.bfloat16, 2000 + N, 0.05)
+        bias = rnd((N,), torch.float32, 3000 + K)
+        got = ops().linear(x.cuda(), w.cuda(), torch.float32, bias.cuda())
+        close(got, ref.linear(x, w, torch.float32, bias), torch.float32, f"linear {(T, N, K)}", rel32=1e-5)
+        close(ops().linear(x.cuda(), w.cuda(), torch.bfloat16), ref.linear(x, w, torch.bfloat16), torch.bfloat16, f"linear bf16 {(T, N, K)}")
+        if N % 16 == 0:
+            close(ops().linear_swiglu(x.cuda(), w.cuda(), torch.bfloat16), ref.linear_swiglu(x, w, torch.bfloat16), torch.bfloat16,
+                  f"swiglu {(T, N, K)}")
+    ops().check_kernel_status()
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_decode_attention_at_random_sizes(seed):
+    """Random head counts, groups, head sizes, page sizes, lengths and windows through the
+    decode kernels (the TMA kernel for heads of 64, the cp.async kernel otherwise)."""
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda xs: xs[int(torch.randint(len(xs), (1,), generator=g))]
+    for i in range(12):
+        d = pick([16, 32, 48, 64, 64, 64, 96, 128])
+        page = pick([8, 16, 32, 64]) if d == 64 else pick([4, 8, 16])
+        kv_heads = pick([1, 2, 3, 5, 8])
+        heads = kv_heads * pick([1, 2, 3, 4, 7, 16])
+        starts = [int(torch.randint(0, 3000, (1,), generator=g)) for _ in range(pick([1, 3, 9]))]
+        window = pick([0, 0, 17, 300, 1025])
+        num_pages = sum(-(-(s + 1) // page) for s in starts) + 2
+        cpu, gpu, table = make_step([1] * len(starts), starts, page, num_pages, 500 + i)
+        cpu.all_decode = gpu.all_decode = True
+        k = rnd((num_pages, page, kv_heads, d), torch.bfloat16, 501 + i)
+        v = rnd((num_pages, page, kv_heads, d), torch.bfloat16, 502 + i)
+        q = rnd((len(starts), heads * d), torch.bfloat16, 503 + i)
+        scale = 1.0 / math.sqrt(d)
+        want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, scale, window, cpu)
+        got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
+        close(got, want, torch.bfloat16, f"decode attention {(heads, kv_heads, d, page, starts, window)}")
+    ops().check_kernel_status()
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_prompt_attention_at_random_sizes(seed):
+    """Random portions (long and short, starting anywhere in their sequences), head counts,
+    head sizes, pages and windows through the prompt attention kernels: the tensor-memory kernel
+    where a step has heads of 64 and a portion of 128 rows or more, the tiled kernel otherwise."""
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda xs: xs[int(torch.randint(len(xs), (1,), generator=g))]
+    for i in range(8):
+        d = pick([32, 64, 64, 64, 80, 128])
+        page = pick([8, 16, 32, 64]) if d == 64 else pick([4, 8, 16])
+        kv_heads = pick([1, 2, 4])
+        heads = kv_heads * pick([1, 2, 4])
+        q_lens = [pick([1, 2, 5, 40, 129, 200, 300]) for _ in range(pick([1, 2, 4]))]
+        starts = [int(torch.randint(0, 600, (1,), generator=g)) for _ in q_lens]
+        window = pick([0, 0, 9, 150, 700])
+        num_pages = sum(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 2
+        cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 600 + i)
+        cpu.h_q_start = gpu.h_q_start = cpu.q_start.tolist()
+        cpu.max_q_len = gpu.max_q_len = max(q_lens)
+        k = rnd((num_pages, page, kv_heads, d), torch.bfloat16, 601 + i)
+        v = rnd((num_pages, page, kv_heads, d), torch.bfloat16, 602 + i)
+        q = rnd((sum(q_lens), heads * d), torch.bfloat16, 603 + i)
+        scale = 1.0 / math.sqrt(d)
+        want = ref.paged_attention(q, heads, kv_heads, d, k, v, table, page, scale, window, cpu)
+        got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
+        close(got, want, torch.bfloat16, f"prompt attention {(heads, kv_heads, d, page, q_lens, starts, window)}")
+    ops().check_kernel_status()
