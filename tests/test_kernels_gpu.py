@@ -830,3 +830,37 @@ def test_prompt_attention_at_random_sizes(seed):
         got = ops().paged_attention(q.cuda(), heads, kv_heads, d, k.cuda(), v.cuda(), table.cuda(), page, scale, window, gpu)
         close(got, want, torch.bfloat16, f"prompt attention {(heads, kv_heads, d, page, q_lens, starts, window)}")
     ops().check_kernel_status()
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_stream_pair_at_random_sizes(seed, monkeypatch):
+    """The product into the residual stream and the scaled product behind it at random row
+    counts (1..192: both kernels that run the pair, one to three token tiles, every number of
+    K parts), widths and depths, with and without a gate/up pair."""
+    from shiso_llm_b200.kernels import ops as ops_module
+    monkeypatch.setattr(ops_module, "FUSED_NORM_MAX_TOKENS", 192)
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda xs: xs[int(torch.randint(len(xs), (1,), generator=g))]
+    for i in range(16):
+        T = pick([1, 3, 8, 9, 15, 16, 17, 32, 33, 64, 65, 100, 128, 129, 192])
+        H = 8 * int(torch.randint(1, 300, (1,), generator=g))
+        K1 = 8 * int(torch.randint(1, 300, (1,), generator=g))
+        N2 = 16 * int(torch.randint(1, 100, (1,), generator=g))
+        glu = bool(int(torch.randint(2, (1,), generator=g)))
+        x1 = rnd((T, K1), torch.bfloat16, 700 + i)
+        w1 = rnd((H, K1), torch.bfloat16, 701 + i, 0.05)
+        residual = rnd((T, H), torch.float32, 702 + i, 2.0)
+        norm_w = 1.0 + 0.2 * rnd((H,), torch.float32, 703 + i)
+        w2 = rnd((2 * N2 if glu else N2, H), torch.bfloat16, 704 + i, 0.05)
+        got = ops().linear_into_stream(x1.cuda(), w1.cuda(), residual.cuda(), norm_w.cuda(), 1e-5)
+        assert got is not None
+        summed, rows = got
+        want_sum = residual + ref.linear(x1, w1, torch.float32)
+        close(summed, want_sum, torch.float32, f"stream {(T, H, K1)}", rel32=1e-5)
+        assert torch.allclose(rows.partials.cpu()[:, :T].sum(0) / H, (want_sum.double() ** 2).mean(-1).float(), rtol=1e-5)
+        y = ops().linear_scaled(rows, w2.cuda(), torch.bfloat16, glu)
+        x = ref.rmsnorm(want_sum, norm_w, 1e-5, torch.bfloat16)
+        want = ref.linear_swiglu(x, w2, torch.bfloat16) if glu else ref.linear(x, w2, torch.bfloat16)
+        scale = (ref.linear_swiglu(x, w2, torch.float32) if glu else ref.linear(x, w2, torch.float32)).abs().max().item()
+        close(y, want, torch.bfloat16, f"scaled product {(T, H, K1, N2, glu)}", scale=2 * scale)
+    ops().check_kernel_status()
