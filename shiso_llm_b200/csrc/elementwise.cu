@@ -160,47 +160,72 @@ __global__ void rmsnorm_vec_kernel(float* residual, const AT* delta, const int* 
 }
 
 // Rows of up to 4,096 values kept in registers: 128 threads with Q groups of four values each,
-// all of a thread's loads in flight at once, no copy of the row in shared memory, and sixteen
-// CTAs to an SM, so that the 2,048 rows of a long prompt step are one wave (the kernel above
-// takes two waves of eight CTAs per SM for them; a 2,048-token step of a 2048-wide, 16-layer
-// model went from 3.91 to 3.87 ms).
+// all of a thread's loads in flight at once, no copy of the row in shared memory.  One wave of
+// CTAs walks the rows, the next row's loads in flight while this one is summed and written
+// (2,048 rows of 2,048 in a captured chain: 9.7 us = 5.2 TB/s of its 50 MB; one row per CTA 10.1 us;
+// the shared-memory kernel above 11.5 us).
 template <typename AT, int Q>
 __global__ void __launch_bounds__(128)
-rmsnorm_reg_kernel(float* residual, const AT* delta, const int* rows, const float* w, AT* out, int hidden, float eps) {
+rmsnorm_reg_kernel(float* residual, const AT* delta, const int* rows, const float* w, AT* out, int out_rows, int hidden,
+                   float eps) {
     pdl_begin();
     __shared__ float scratch[33];
-    const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
-    float* r = residual + (size_t)src_row * hidden;
-    const AT* d = delta ? delta + (size_t)src_row * hidden : nullptr;
-    AT* o = out + (size_t)blockIdx.x * hidden;
     const int quads = hidden / 4;
-    float4 v[Q], dv[Q];
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    // A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ..: the next row's loads are in flight
+    // while this row is summed and written, so that reads and writes overlap over the whole launch.
+    auto load_row = [&](int index, float4 (&v)[Q], float4 (&dv)[Q]) {
+        const int src_row = rows ? rows[index] : index;
+        const float* r = residual + (size_t)src_row * hidden;
+        const AT* d = delta ? delta + (size_t)src_row * hidden : nullptr;
 #pragma unroll
-    for (int q = 0; q < Q; ++q) {
-        const int i = threadIdx.x + q * 128;
-        v[q] = i < quads ? *reinterpret_cast<const float4*>(r + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        dv[q] = (d && i < quads) ? Pack4<AT>::load(d + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    float ss = 0.0f;
-#pragma unroll
-    for (int q = 0; q < Q; ++q) {
-        const int i = threadIdx.x + q * 128;
-        if (d) {
-            v[q].x += dv[q].x;
-            v[q].y += dv[q].y;
-            v[q].z += dv[q].z;
-            v[q].w += dv[q].w;
-            if (!rows && i < quads) *reinterpret_cast<float4*>(r + 4 * i) = v[q];
+        for (int q = 0; q < Q; ++q) {
+            const int i = threadIdx.x + q * 128;
+            v[q] = i < quads ? *reinterpret_cast<const float4*>(r + 4 * i) : zero;
+            dv[q] = (d && i < quads) ? Pack4<AT>::load(d + 4 * i) : zero;
         }
-        ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
-    }
-    const float inv = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    };
+    float4 v[Q], dv[Q], next_v[Q], next_dv[Q], wv[Q];
+    int index = blockIdx.x;
+    if (index >= out_rows) return;
+    load_row(index, v, dv);
 #pragma unroll
     for (int q = 0; q < Q; ++q) {
         const int i = threadIdx.x + q * 128;
-        if (i < quads) {
-            const float4 wv = *reinterpret_cast<const float4*>(w + 4 * i);
-            Pack4<AT>::store(o + 4 * i, make_float4(v[q].x * inv * wv.x, v[q].y * inv * wv.y, v[q].z * inv * wv.z, v[q].w * inv * wv.w));
+        wv[q] = i < quads ? *reinterpret_cast<const float4*>(w + 4 * i) : zero;
+    }
+    for (; index < out_rows; index += gridDim.x) {
+        const bool more = index + (int)gridDim.x < out_rows;
+        if (more) load_row(index + gridDim.x, next_v, next_dv);
+        float* r = residual + (size_t)(rows ? rows[index] : index) * hidden;
+        AT* o = out + (size_t)index * hidden;
+        float ss = 0.0f;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+            const int i = threadIdx.x + q * 128;
+            if (delta) {
+                v[q].x += dv[q].x;
+                v[q].y += dv[q].y;
+                v[q].z += dv[q].z;
+                v[q].w += dv[q].w;
+                if (!rows && i < quads) *reinterpret_cast<float4*>(r + 4 * i) = v[q];
+            }
+            ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
+        }
+        const float inv = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+            const int i = threadIdx.x + q * 128;
+            if (i < quads)
+                Pack4<AT>::store(o + 4 * i, make_float4(v[q].x * inv * wv[q].x, v[q].y * inv * wv[q].y, v[q].z * inv * wv[q].z,
+                                                        v[q].w * inv * wv[q].w));
+        }
+        if (more) {
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+                v[q] = next_v[q];
+                dv[q] = next_dv[q];
+            }
         }
     }
 }
@@ -208,10 +233,18 @@ rmsnorm_reg_kernel(float* residual, const AT* delta, const int* rows, const floa
 template <typename AT>
 static void launch_rmsnorm_reg(int groups, float* residual, const AT* delta, const int* rows, const float* w, AT* out,
                                int out_rows, int hidden, float eps, cudaStream_t stream) {
-    if (groups <= 1) launch_kernel(rmsnorm_reg_kernel<AT, 1>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
-    else if (groups <= 2) launch_kernel(rmsnorm_reg_kernel<AT, 2>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
-    else if (groups <= 4) launch_kernel(rmsnorm_reg_kernel<AT, 4>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
-    else launch_kernel(rmsnorm_reg_kernel<AT, 8>, out_rows, 128, 0, stream, residual, delta, rows, w, out, hidden, eps);
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count < 1) sm_count = 1;
+    }
+    const int per_sm = groups <= 1 ? 16 : (groups <= 2 ? 8 : (groups <= 4 ? 5 : 2));  // CTAs that fit an SM with the variant's registers (38 / 56 / 96 / 182)
+    const int grid = out_rows < sm_count * per_sm ? out_rows : sm_count * per_sm;
+    if (groups <= 1) launch_kernel(rmsnorm_reg_kernel<AT, 1>, grid, 128, 0, stream, residual, delta, rows, w, out, out_rows, hidden, eps);
+    else if (groups <= 2) launch_kernel(rmsnorm_reg_kernel<AT, 2>, grid, 128, 0, stream, residual, delta, rows, w, out, out_rows, hidden, eps);
+    else if (groups <= 4) launch_kernel(rmsnorm_reg_kernel<AT, 4>, grid, 128, 0, stream, residual, delta, rows, w, out, out_rows, hidden, eps);
+    else launch_kernel(rmsnorm_reg_kernel<AT, 8>, grid, 128, 0, stream, residual, delta, rows, w, out, out_rows, hidden, eps);
 }
 
 SHISO_API int shiso_rmsnorm(float* residual, const void* delta, const int* rows, const float* w, void* out,
