@@ -39,6 +39,7 @@ class LLM:
         ctx: int = 4096,
         page_size: int = 16,
         kv_cache_tokens: Optional[int] = None,
+        gpu_memory_utilization: Optional[float] = None,
         max_num_seqs: int = 4,
         max_num_batched_tokens: int = 2048,
         prefill_chunk: Optional[int] = None,
@@ -47,6 +48,8 @@ class LLM:
         device: str = "cuda:0",
         ops=None,
         lookahead: bool = True,
+        allow_small_pool: bool = False,
+        dump_layers: int = 0,
     ):
         """``model`` is a model folder (config.json + *.safetensors), or an ``Engine`` that is
         already built (then the engine's own options stand for dtype and cache sizes).
@@ -63,8 +66,9 @@ class LLM:
         else:
             options = EngineOptions(
                 dtype=dtype, ctx=ctx, page_size=page_size, kv_cache_tokens=kv_cache_tokens,
+                gpu_memory_utilization=gpu_memory_utilization,
                 max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, device=device,
-                cuda_graphs=cuda_graphs,
+                cuda_graphs=cuda_graphs, allow_small_pool=allow_small_pool, dump_layers=dump_layers,
             )
             self.engine = Engine.from_folder(model, options, ops)
         self.scheduler = Scheduler(
@@ -81,8 +85,16 @@ class LLM:
         self._in_flight = None  # (plan, host buffer, count, event) of the step whose tokens are on their way
         self._turn = 0
         pin = self.engine.device.type == "cuda"
-        rows = self.engine.fed_tokens.shape[0]
+        rows = self.engine.fed_tokens.shape[0]  # one entry per sequence and one for the status word
         self._host_picks = [torch.zeros(rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        # Kernels whose waits are bounded report a wait that ran out through a status word on the
+        # device.  The picking kernel of every step puts it behind the picks, so it reaches the
+        # host with the tokens; plans launched since the word was last seen clean wait here.
+        self._carries_status = bool(getattr(self.engine.env.ops, "CARRIES_STATUS", False))
+        self._unverified: list = []
+        # A diagnostic: called as ``logits_tap(plan, logits)`` with every step's logits (one row per
+        # sampling entry of the plan, in order) before a token is picked from them.
+        self.logits_tap = None
 
     # ------------------------------------------------------------------ low level
 
@@ -102,7 +114,13 @@ class LLM:
         return self.scheduler.has_work() or self._in_flight is not None
 
     def step(self) -> list:
-        """One scheduler decision and one engine step; returns the outputs that finished."""
+        """One scheduler decision and one engine step; returns the outputs that finished.
+
+        A step that cannot be launched (an exception from the engine) ends its own requests with
+        ``finish_reason = "error"`` and leaves the others as they were, as the reference does
+        with a failed pass (crates/shiso-runtime/src/scheduler/mod.rs:1918-1927).  So does a
+        step of which a kernel gave up on a bounded wait: the host learns of that when the
+        step's tokens arrive."""
         plan: StepPlan = self.scheduler.plan()
         launched = None
         if plan.entries:
@@ -116,20 +134,11 @@ class LLM:
                 if e.samples:
                     params.append(e.request.params)
                     positions.append(e.start + e.count)
-            logits = self.engine.step(entries)
-            launched = (plan, None, 0, None)
-            if logits is not None:
-                count = logits.shape[0]
-                picks = self.engine.fed_tokens[:count]
-                self.sampler.sample_into(logits, params, positions, picks)
-                host = self._host_picks[self._turn]
-                self._turn ^= 1
-                host[:count].copy_(picks, non_blocking=True)
-                event = None
-                if picks.is_cuda:
-                    event = torch.cuda.Event()
-                    event.record()
-                launched = (plan, host, count, event)
+            try:
+                launched = self._launch(plan, entries, params, positions)
+            except Exception as error:  # the step's requests fail; the engine took nothing for them
+                self.scheduler.fail_step(plan, f"the step could not run: {type(error).__name__}: {error}")
+                plan = StepPlan(preempted=plan.preempted, failed=plan.failed)
         self.scheduler.launched(plan)
         if self.lookahead:
             self._collect(self._in_flight)
@@ -137,6 +146,30 @@ class LLM:
         else:
             self._collect(launched)
         return [self._output(r) for r in self.scheduler.take_finished()]
+
+    def _launch(self, plan, entries, params, positions):
+        logits = self.engine.step(entries)
+        if self._carries_status:
+            self._unverified.append(plan)
+        if logits is None:
+            return (plan, None, 0, None)
+        count = logits.shape[0]
+        if self.logits_tap is not None:
+            self.logits_tap(plan, logits)
+        picks = self.engine.fed_tokens[:count]
+        carried = count + 1 if self._carries_status else count
+        if self._carries_status:
+            self.sampler.sample_into(logits, params, positions, picks, self.engine.fed_tokens[count:carried])
+        else:
+            self.sampler.sample_into(logits, params, positions, picks)
+        host = self._host_picks[self._turn]
+        self._turn ^= 1
+        host[:carried].copy_(self.engine.fed_tokens[:carried], non_blocking=True)
+        event = None
+        if picks.is_cuda:
+            event = torch.cuda.Event()
+            event.record()
+        return (plan, host, count, event)
 
     def drain(self) -> list:
         """Waits for the step that is still on its way (lookahead), so that every token the
@@ -146,13 +179,25 @@ class LLM:
         return [self._output(r) for r in self.scheduler.take_finished()]
 
     def _collect(self, launched) -> None:
-        """Waits for a launched step's tokens and hands them to the scheduler."""
+        """Waits for a launched step's tokens and hands them to the scheduler.  If the status
+        word that came with them says a kernel gave up, every step launched since the word was
+        last seen clean is failed instead: its requests end with an error."""
         if launched is None:
             return
         plan, host, count, event = launched
         if event is not None:
             event.synchronize()
-        self.scheduler.arrived(plan, host[:count].tolist() if count else [])
+        sampled = host[:count].tolist() if count else []
+        if count and self._carries_status:
+            at = next((i for i, p in enumerate(self._unverified) if p is plan), None)
+            covered = [plan] if at is None else self._unverified[: at + 1]
+            if at is not None:
+                del self._unverified[: at + 1]
+            if int(host[count]) != 0:
+                why = getattr(self.engine.env.ops, "GAVE_UP", "a kernel gave up on a bounded wait")
+                for suspect in covered:
+                    self.scheduler.fail_step(suspect, why)
+        self.scheduler.arrived(plan, sampled)
 
     @staticmethod
     def _output(req) -> Output:

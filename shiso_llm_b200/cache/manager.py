@@ -126,6 +126,19 @@ class CacheManager:
 
         self._held: dict = {}
 
+    @staticmethod
+    def costs(needs: list, page_size: int, dtype: torch.dtype) -> tuple:
+        """``(bytes of one page across every paged entry, bytes of one state slot)``: what the
+        pool's sizing needs to know about a model (the reference prices pages run by run the
+        same way, crates/shiso-engine/src/kv.rs:26-31,84-109,176-198)."""
+        page_bytes = state_bytes = 0
+        for need in needs:
+            if isinstance(need, PagedKV):
+                page_bytes += 2 * page_size * need.num_kv_heads * need.head_dim * dtype.itemsize
+            elif isinstance(need, FixedState):
+                state_bytes += need.numel * 4
+        return page_bytes, state_bytes
+
     # ------------------------------------------------------------------ views for the model
 
     def view(self, entry: int, owner: bool = True):
@@ -206,8 +219,11 @@ class CacheManager:
             held.tables[group.index].release_passed(group.pool, held.length)
 
     def cancel(self, request) -> None:
-        """The step that ``append`` prepared did not run; claimed pages stay with the request."""
-        self._held[request].reserved = 0
+        """The step that ``append`` prepared did not run: the pages it claimed go back."""
+        held = self._held[request]
+        held.reserved = 0
+        for group in self.groups:
+            held.tables[group.index].shrink(group.pool, held.length)
 
     def release(self, request) -> None:
         held = self._held.pop(request, None)

@@ -108,6 +108,12 @@ class BlockTable:
                 self._array = bigger
             self._array[have : len(self.pages)] = self.pages[have:]
 
+    def shrink(self, pool: PagePool, length: int) -> None:
+        """Gives back the pages beyond those ``length`` positions need (a claim that was not used)."""
+        keep = max(self.pages_for(length), self.first_live)
+        while len(self.pages) > keep:
+            pool.give_back(self.pages.pop())
+
     def release_passed(self, pool: PagePool, length: int) -> int:
         """Gives back pages that no later position can read: with a window ``w`` the
         query at position ``length`` (the next one) reads positions ``> length - w``."""

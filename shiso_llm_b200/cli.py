@@ -67,7 +67,8 @@ def cmd_info(args) -> int:
 
     arch, config = load_config(args.model)
     plan = arch.build_plan(config)
-    print(json.dumps({"architecture": arch.name, "config": config.to_dict(),
+    derived = {k: getattr(config, k) for k in ("intermediate_size", "head_dim") if hasattr(config, k)}
+    print(json.dumps({"architecture": arch.name, "config": config.to_dict(), "derived": derived,
                       "layers": [layer.mixer.kind for layer in plan.layers]}, indent=2))
     return 0
 
@@ -87,25 +88,88 @@ def parse_prompts(args, vocab: int) -> list:
     return prompts
 
 
+class FrontierRows:
+    """Writes the logits row at the end of every prompt - the row the request's first token is
+    picked from - as ``DIR/<request>.f32.npy`` (float32 ``[vocab]``) plus ``DIR/index.json``, after
+    the row dump of the reference's parity runner (crates/shiso-bench/src/bin/parity.rs:11-16).
+    Like that one it refuses to replace anything already there."""
+
+    def __init__(self, folder: str):
+        self.folder = folder
+        self.index = []
+        os.makedirs(folder, exist_ok=True)
+        if os.listdir(folder):
+            raise SystemExit(f"--dump-logits {folder}: the folder is not empty; a dump replaces nothing")
+
+    def __call__(self, plan, logits) -> None:
+        import numpy as np
+
+        row = 0
+        for entry in plan.entries:
+            if not entry.samples:
+                continue
+            request = entry.request
+            if entry.start + entry.count == len(request.prompt) and not request.preemptions:
+                name = f"{request.id}.f32.npy"
+                np.save(os.path.join(self.folder, name), logits[row].detach().float().cpu().numpy())
+                self.index.append({"request": request.id, "prompt_tokens": len(request.prompt),
+                                   "position": len(request.prompt) - 1, "file": name})
+            row += 1
+
+    def close(self) -> None:
+        with open(os.path.join(self.folder, "index.json"), "w", encoding="utf-8") as f:
+            json.dump({"dtype": "float32", "rows": self.index}, f, indent=2)
+            f.write("\n")
+
+
 def cmd_generate(args) -> int:
     from .api import LLM
     from .sampling import SamplingParams
 
-    llm = LLM(
-        args.model, dtype=args.dtype, ctx=args.ctx, page_size=args.page_size,
-        kv_cache_tokens=args.kv_cache_tokens, max_num_seqs=args.max_num_seqs,
-        max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk=args.prefill_chunk,
-        on_exhaustion=args.on_exhaustion, cuda_graphs=not args.no_cuda_graphs, device=args.device,
-        lookahead=not args.no_lookahead,
+    if (args.model is None) == (args.random_config is None):
+        raise SystemExit("give either -m/--model DIR or --random-config NAME")
+    common = dict(
+        dtype=args.dtype, ctx=args.ctx, page_size=args.page_size, kv_cache_tokens=args.kv_cache_tokens,
+        gpu_memory_utilization=args.gpu_memory_utilization, max_num_seqs=args.max_num_seqs,
+        max_num_batched_tokens=args.max_num_batched_tokens, cuda_graphs=not args.no_cuda_graphs, device=args.device,
+        dump_layers=args.dump_layers,
     )
+    if args.random_config is not None:
+        # weights drawn on the device from the seed (the distribution of `init-random`, not its
+        # numbers: that command draws on the host so that a folder is the same everywhere)
+        import torch
+
+        from .config import plan_from_document
+        from .engine import Engine, EngineOptions
+        from .engine.core import parse_dtype
+        from .parts import BuildEnv, Model
+        from .weights import random_device_tensors
+
+        path = preset_path(args.random_config)
+        if not os.path.isfile(path):
+            raise SystemExit(f"unknown preset {args.random_config!r}; available: {', '.join(preset_names())}")
+        with open(path, "r", encoding="utf-8") as f:
+            _, _, plan = plan_from_document(json.load(f))
+        specs = Model(plan, BuildEnv(dtype=torch.float32, device=torch.device("cpu"), ops=None)).tensor_specs()
+        tensors = random_device_tensors(specs, args.weights_seed, parse_dtype(args.dtype), torch.device(args.device))
+        engine = Engine.from_plan(plan, tensors, EngineOptions(**common))
+        llm = LLM(engine, prefill_chunk=args.prefill_chunk, on_exhaustion=args.on_exhaustion, lookahead=not args.no_lookahead)
+    else:
+        llm = LLM(args.model, prefill_chunk=args.prefill_chunk, on_exhaustion=args.on_exhaustion,
+                  lookahead=not args.no_lookahead, **common)
     prompts = parse_prompts(args, llm.engine.vocab_size)
     params = SamplingParams(
         temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p, seed=args.seed,
         max_new_tokens=args.max_tokens, stop_token_ids=tuple(args.stop_token_ids or ()), ignore_eos=args.ignore_eos,
+        bad_token_ids=tuple(args.bad_token_ids or ()),
     )
+    rows = FrontierRows(args.dump_logits) if args.dump_logits else None
+    llm.logits_tap = rows
     started = time.time()
     outputs = llm.generate(prompts, params)
     elapsed = time.time() - started
+    if rows is not None:
+        rows.close()
     for out in outputs:
         print(json.dumps({"request": out.request_id, "prompt_tokens": len(out.prompt_token_ids),
                           "token_ids": out.token_ids, "finish_reason": out.finish_reason, "error": out.error}))
@@ -120,7 +184,9 @@ def build_parser() -> argparse.ArgumentParser:
     sub = parser.add_subparsers(dest="command", required=True)
 
     g = sub.add_parser("generate", help="generate token ids for token-id prompts")
-    g.add_argument("-m", "--model", required=True, help="model folder (config.json + *.safetensors)")
+    g.add_argument("-m", "--model", help="model folder (config.json + *.safetensors)")
+    g.add_argument("--random-config", metavar="NAME", help=f"instead of a folder: random weights of a preset ({', '.join(preset_names())})")
+    g.add_argument("--weights-seed", type=int, default=0, help="seed of --random-config's weights")
     g.add_argument("--prompt-ids", action="append", help="comma- or space-separated token ids; repeatable")
     g.add_argument("--prompt-len", action="append", type=int, help="a uniform-random prompt of this length; repeatable")
     g.add_argument("--prompt-seed", type=int, default=0)
@@ -131,11 +197,14 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--min-p", type=float, default=0.0)
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--stop-token-ids", type=int, nargs="*")
+    g.add_argument("--bad-token-ids", type=int, nargs="*", help="token ids that are never emitted")
     g.add_argument("--ignore-eos", action="store_true")
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     g.add_argument("-c", "--ctx", type=int, default=4096)
     g.add_argument("--page-size", type=int, default=16)
-    g.add_argument("--kv-cache-tokens", type=int, default=None)
+    g.add_argument("--kv-cache-tokens", type=int, default=None, help="tokens the cache pool holds (default: max-num-seqs x ctx)")
+    g.add_argument("--gpu-memory-utilization", type=float, default=None,
+                   help="instead: the share of device memory this process may fill; the pool gets what is left of it")
     g.add_argument("--max-num-seqs", type=int, default=4)
     g.add_argument("--max-num-batched-tokens", type=int, default=2048)
     g.add_argument("--prefill-chunk", type=int, default=None)
@@ -144,6 +213,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--no-lookahead", action="store_true",
                    help="wait for each step's tokens on the host before planning the next step")
     g.add_argument("--device", default="cuda:0")
+    g.add_argument("--dump-logits", metavar="DIR", help="write the logits row at the end of every prompt to DIR")
+    g.add_argument("--dump-layers", type=int, choices=[0, 1, 2], default=0,
+                   help="print statistics of the residual stream after every layer (2: after every mixer and feed-forward) to stderr")
     g.set_defaults(func=cmd_generate)
 
     r = sub.add_parser("init-random", help="write a model folder with random weights")

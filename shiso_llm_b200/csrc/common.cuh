@@ -81,6 +81,11 @@ __device__ __forceinline__ void pdl_begin() {
 
 bool shiso_pdl_enabled();  // defined in elementwise.cu
 
+// The word in device memory that a kernel sets when one of its bounded waits ran out
+// (defined in gemm_tcgen05.cu).  The token-picking kernels hand it to the host with their
+// picks: they read it and set it back to zero.
+int* shiso_tc_status_word();
+
 template <typename... KArgs, typename... Args>
 static inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args&&... args) {

@@ -14,6 +14,14 @@
 //   min-p  keeps tokens with exp((l - max) / T) >= min_p.
 // Masses are summed as 2^-40 fixed-point integers, so the sums and therefore the
 // thresholds do not depend on the order in which threads add.
+//
+// Suppression: ids a request may never emit are set to -inf in its row before any pick
+// (crates/shiso-engine/src/sampling.rs:156-174; kernels/cuda/sample/sample.cu:18-26).
+//
+// Status: a picking kernel may be given a place `status_out` (by convention the entry after
+// the last pick); it moves the library's status word there and clears the word, so the host
+// learns with the tokens, and without another copy or wait, whether a kernel of the step gave
+// up on a bounded wait.
 #include "common.cuh"
 
 namespace {
@@ -54,8 +62,24 @@ __device__ Best block_best(Best mine, Best* scratch /* 32 */) {
     return r;
 }
 
-__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+__device__ __forceinline__ void hand_over_status(int* status_word, int* status_out) {
+    if (status_out != nullptr && status_word != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+        *status_out = atomicExch(status_word, 0);
+}
+
+__global__ void suppress_kernel(float* __restrict__ logits, const int* __restrict__ rows, const int* __restrict__ ids,
+                                int count, int num_rows, int vocab) {
     pdl_begin();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const int r = rows[i], id = ids[i];
+    if (r >= 0 && r < num_rows && id >= 0 && id < vocab) logits[(size_t)r * vocab + id] = -INFINITY;
+}
+
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab,
+                                                         int* status_word, int* status_out) {
+    pdl_begin();
+    hand_over_status(status_word, status_out);
     __shared__ Best scratch[32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
     Best mine{-INFINITY, 0x7fffffff};
@@ -102,8 +126,9 @@ argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ best_v
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i,
-                                    int* __restrict__ out, int chunks) {
+                                    int* __restrict__ out, int chunks, int* status_word, int* status_out) {
     pdl_begin();
+    hand_over_status(status_word, status_out);
     const int row_index = blockIdx.x;
     Best mine{-INFINITY, 0x7fffffff};
     for (int c = threadIdx.x; c < chunks; c += 32) {
@@ -198,8 +223,10 @@ __device__ unsigned radix_threshold(const float* __restrict__ row, int vocab, fl
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p,
-              const long long* __restrict__ keys, const int* __restrict__ positions, int* __restrict__ out, int vocab) {
+              const long long* __restrict__ keys, const int* __restrict__ positions, int* __restrict__ out, int vocab,
+              int* status_word, int* status_out) {
     pdl_begin();
+    hand_over_status(status_word, status_out);
     __shared__ Best scratch[32];
     __shared__ unsigned long long hist[256];
     __shared__ unsigned shared_u[2];
@@ -263,31 +290,44 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 }  // namespace
 
-SHISO_API int shiso_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+// `status_out` (may be null) receives the status word, which is cleared; see the file's head.
+SHISO_API int shiso_argmax(const float* logits, int* out, int rows, int vocab, int* status_out, cudaStream_t stream) {
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0) return SHISO_ERR_SHAPE;
-    launch_kernel(argmax_kernel, rows, THREADS, 0, stream, logits, out, vocab);
+    launch_kernel(argmax_kernel, rows, THREADS, 0, stream, logits, out, vocab, status_out ? shiso_tc_status_word() : nullptr,
+                  status_out);
+    return launch_status();
+}
+
+// Sets logits[rows[i], ids[i]] to -inf for i < count.
+SHISO_API int shiso_suppress(float* logits, const int* rows, const int* ids, int count, int num_rows, int vocab,
+                             cudaStream_t stream) {
+    if (count <= 0) return SHISO_OK;
+    if (vocab <= 0 || num_rows <= 0) return SHISO_ERR_SHAPE;
+    launch_kernel(suppress_kernel, ceil_div_u(count, 256), 256, 0, stream, logits, rows, ids, count, num_rows, vocab);
     return launch_status();
 }
 
 SHISO_API int shiso_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
                            const float* min_p, const long long* keys, const int* positions, int* out, int rows,
-                           int vocab, cudaStream_t stream) {
+                           int vocab, int* status_out, cudaStream_t stream) {
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0) return SHISO_ERR_SHAPE;
-    launch_kernel(sample_kernel, rows, THREADS, 0, stream, logits, temperature, top_k, top_p, min_p, keys, positions, out, vocab);
+    launch_kernel(sample_kernel, rows, THREADS, 0, stream, logits, temperature, top_k, top_p, min_p, keys, positions, out, vocab,
+                  status_out ? shiso_tc_status_word() : nullptr, status_out);
     return launch_status();
 }
 
 // Two-stage greedy pick; `scratch` holds rows * chunks floats followed by rows * chunks ints.
 SHISO_API int shiso_argmax_chunked(const float* logits, int* out, float* scratch, int rows, int vocab, int chunks,
-                                   cudaStream_t stream) {
+                                   int* status_out, cudaStream_t stream) {
     if (rows <= 0) return SHISO_OK;
     if (vocab <= 0 || chunks <= 0) return SHISO_ERR_SHAPE;
     const int chunk_len = ((vocab + chunks - 1) / chunks + 3) / 4 * 4;  // a multiple of four: 16-byte loads where the row allows
     float* best_v = scratch;
     int* best_i = (int*)(scratch + (size_t)rows * chunks);
     launch_kernel(argmax_chunk_kernel, dim3(chunks, rows), 256, 0, stream, logits, best_v, best_i, vocab, chunk_len, chunks);
-    launch_kernel(argmax_final_kernel, rows, 32, 0, stream, best_v, best_i, out, chunks);
+    launch_kernel(argmax_final_kernel, rows, 32, 0, stream, best_v, best_i, out, chunks,
+                  status_out ? shiso_tc_status_word() : nullptr, status_out);
     return launch_status();
 }

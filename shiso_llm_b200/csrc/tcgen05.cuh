@@ -26,8 +26,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
-// Waits for the phase with the given parity; false when the clock limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Waits for the phase with the given parity, at most `limit` clock cycles; false when they ran out.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, unsigned long long limit) {
     const uint32_t addr = smem_u32(bar);
     const unsigned long long start = clock64();
     while (true) {
@@ -40,8 +40,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - start > limit) return false;
     }
+}
+
+// Waits for the phase with the given parity; false when the clock limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    return mbar_wait_limit(bar, parity, WAIT_LIMIT_CYCLES);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {

@@ -321,6 +321,26 @@ class Scheduler:
 
     # ------------------------------------------------------------------ after the step
 
+    def fail_step(self, plan: StepPlan, why: str) -> list:
+        """The step did not run, or what it computed is not valid: its requests end with reason
+        ``error`` and give their cache back; every other request goes on.  This is what the
+        reference does with a pass that fails (crates/shiso-runtime/src/scheduler/mod.rs:1918-1927).
+        Tokens that were sampled but never reached the host are dropped.  Returns the requests
+        that ended."""
+        failed = []
+        for entry in plan.entries:
+            req = entry.request
+            if req.state == FINISHED:
+                continue
+            while req.output and req.output[-1] == PENDING:
+                req.output.pop()
+            req.pending_row = None
+            req.error = why
+            self._retire(req, "error")
+            self.stats["failed"] += 1
+            failed.append(req)
+        return failed
+
     def launched(self, plan: StepPlan) -> None:
         """The step is on its way: its tokens count as computed, and a placeholder stands where
         each sampled token will go."""

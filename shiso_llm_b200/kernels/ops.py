@@ -52,7 +52,39 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 
 
 _RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
-_DEVICE_INDEX = None
+_DEVICE_INDEX = None  # the one device this process's kernel library works on, once bound
+
+
+def resolve_binding(wanted_index, bound_index, current_index) -> int:
+    """Which device an engine asked for ends up on, or the refusal.  ``wanted_index`` is the
+    index the caller named (None for a bare "cuda"), ``bound_index`` the device the library is
+    bound to already (None: not yet), ``current_index`` the process's current device."""
+    index = current_index if wanted_index is None else wanted_index
+    if bound_index is not None and index != bound_index:
+        raise KernelError(
+            f"this process's kernel library works on cuda:{bound_index} (attributes of its kernels, its status word and "
+            f"its counters live there); an engine on cuda:{index} needs a process of its own"
+        )
+    return index
+
+
+def bind_device(device) -> int:
+    """Binds the kernel library to ``device`` (a torch.device of type cuda) and makes it the
+    current device; returns its index.  The library keeps per-process state for one device -
+    which kernels were given their shared-memory attribute, the status word of the bounded
+    waits, the decode attention's counters - and every launch goes to the current device's
+    stream, so all engines of a process share one device; another one is refused here, before
+    a pointer of one device could reach a kernel on another."""
+    global _DEVICE_INDEX
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise KernelError(f"the CUDA kernels cannot run on {device}")
+    index = resolve_binding(device.index, _DEVICE_INDEX, torch.cuda.current_device())
+    if index >= torch.cuda.device_count():
+        raise KernelError(f"cuda:{index} does not exist: this process sees {torch.cuda.device_count()} device(s)")
+    torch.cuda.set_device(index)
+    _DEVICE_INDEX = index
+    return index
 
 
 def _stream() -> int:
@@ -411,12 +443,24 @@ def linear_simple(x, w, out_dtype, bias=None):
     return out
 
 
+CARRIES_STATUS = True  # argmax and sample take ``status_out``
+GAVE_UP = "a kernel gave up waiting on a barrier; what it wrote is not valid"
+
+
 def check_kernel_status() -> None:
-    """Raises when a bounded wait inside a tensor-core kernel ran out since the last call.
-    Synchronises the device; not for use while a stream is being captured."""
+    """Raises when a bounded wait inside a kernel ran out since the status word was last read
+    (here, or by a token-picking kernel that was given a place for it).  Synchronises the
+    device; not for use while a stream is being captured."""
     status = library().shiso_gemm_tcgen05_status()
     if status != 0:
-        raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (status {status}); its output is not valid")
+        raise KernelError(f"{GAVE_UP} (status {status})")
+
+
+def selftest_bounded_wait(limit_cycles: int = 4000) -> None:
+    """Launches one CTA that waits ``limit_cycles`` clock cycles on a barrier nobody arrives at
+    and then gives up, as any kernel here does when a wait runs out: the status word is set and
+    the kernel returns.  For tests of what the host does then."""
+    _done(library().shiso_selftest_bounded_wait(int(limit_cycles), _stream()), "selftest_bounded_wait")
 
 
 # --------------------------------------------------------------------------- short convolution
@@ -658,27 +702,52 @@ def _picks(out, rows, device):
     return out
 
 
-def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def _status_place(status_out) -> int:
+    if status_out is None:
+        return 0
+    _check(status_out, "status_out", torch.int32, 1)
+    if status_out.shape[0] != 1:
+        raise KernelError("status_out is one int32")
+    return status_out.data_ptr()
+
+
+def suppress(logits: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """Sets ``logits[rows[i], ids[i]]`` to -inf, in place, before a pick
+    (crates/shiso-engine/src/sampling.rs:156-174; kernels/cuda/sample/sample.cu:18-26)."""
+    _check(logits, "logits", torch.float32, 2)
+    _check(rows, "rows", torch.int32, 1)
+    _check(ids, "ids", torch.int32, 1)
+    if rows.shape != ids.shape:
+        raise KernelError(f"{rows.shape[0]} rows for {ids.shape[0]} ids")
+    _done(library().shiso_suppress(_ptr(logits), _ptr(rows), _ptr(ids), rows.shape[0], logits.shape[0], logits.shape[1],
+                                   _stream()), "suppress")
+    return logits
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, status_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The index of each row's largest value (the smallest index among equals), int32, written
-    to ``out`` when one is given."""
+    to ``out`` when one is given.  ``status_out`` (one int32) receives the status word of the
+    bounded waits, which is cleared: see ``check_kernel_status``."""
     _check(logits, "logits", torch.float32, 2)
     rows, vocab = logits.shape
     out = _picks(out, rows, logits.device)
+    status = _status_place(status_out)
     if vocab >= 8192:
         # chunks of at least 1,024 values; no more blocks (rows x chunks)
         # than a few waves: 64 rows x 64 chunks of four values a thread took 13.6 us for 17 MB
         chunks = max(1, min(128, -(-vocab // 1024), -(-4 * _sm_count() // rows)))
         scratch = torch.empty((2 * rows * chunks,), dtype=torch.float32, device=logits.device)
-        status = library().shiso_argmax_chunked(_ptr(logits), _ptr(out), _ptr(scratch), rows, vocab, chunks, _stream())
-        _done(status, "argmax", 2)
+        code = library().shiso_argmax_chunked(_ptr(logits), _ptr(out), _ptr(scratch), rows, vocab, chunks, status, _stream())
+        _done(code, "argmax", 2)
         return out
-    _done(library().shiso_argmax(_ptr(logits), _ptr(out), rows, vocab, _stream()), "argmax")
+    _done(library().shiso_argmax(_ptr(logits), _ptr(out), rows, vocab, status, _stream()), "argmax")
     return out
 
 
-def sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None) -> torch.Tensor:
+def sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None, status_out=None) -> torch.Tensor:
     """Keyed sampling, one row per request: float32 ``temperature``/``top_p``/``min_p``,
-    int32 ``top_k`` (0 = off) and ``positions``, int64 ``keys``, all of length rows."""
+    int32 ``top_k`` (0 = off) and ``positions``, int64 ``keys``, all of length rows.
+    ``status_out`` as in ``argmax``."""
     _check(logits, "logits", torch.float32, 2)
     rows = logits.shape[0]
     for name, t, dt in (
@@ -692,7 +761,7 @@ def sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None) 
     out = _picks(out, rows, logits.device)
     status = library().shiso_sample(
         _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(keys), _ptr(positions),
-        _ptr(out), rows, logits.shape[1], _stream(),
+        _ptr(out), rows, logits.shape[1], _status_place(status_out), _stream(),
     )
     _done(status, "sample")
     return out

@@ -232,9 +232,10 @@ class Stream:
     added: the next norm adds it while it normalises (one fused kernel), which is how
     the reference closes every block (crates/shiso-engine/src/layers.rs:2476-2498)."""
 
-    def __init__(self, residual: torch.Tensor):
+    def __init__(self, residual: torch.Tensor, observer: Optional[Callable] = None):
         self.residual = residual
         self.pending: Optional[torch.Tensor] = None
+        self.observer = observer  # a diagnostic: called with the stream after every ``add``
 
     def normed(self, norm: Norm, deferred: bool = False):
         """The normed rows; with ``deferred`` a ``DeferredNorm`` that computes them when (and how)
@@ -262,6 +263,8 @@ class Stream:
         if self.pending is not None:
             raise RuntimeError("a block output is already waiting to be added to the residual")
         self.pending = delta
+        if self.observer is not None:
+            self.observer(self)
 
 
 class Block(Part):

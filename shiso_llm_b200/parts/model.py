@@ -13,8 +13,34 @@ from typing import Optional
 import torch
 
 from ..weights.spec import TensorSpec
-from .base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, Stream
+from .base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, DeferredLinear, Stream
 from .plan import ModelPlan
+
+
+def stream_value(stream: Stream) -> torch.Tensor:
+    """The residual stream as float32 rows, with the block output that is still waiting to be
+    added, without touching the stream: a product that has not run is run on the side."""
+    x = stream.residual
+    waiting = stream.pending
+    if waiting is None:
+        return x.clone()
+    if isinstance(waiting, DeferredLinear):
+        waiting = waiting.materialize()
+    return x + waiting.to(x.dtype)
+
+
+def residual_stats(label: str, x: torch.Tensor) -> str:
+    """One line about a block of float32 rows: element count, root mean square and largest
+    magnitude of the finite values, zeros, non-finite values and the first four values - the
+    line of the reference's layer dump (crates/shiso-engine/src/trace.rs:49-138)."""
+    flat = x.detach().to(torch.float64).flatten().cpu()
+    finite = torch.isfinite(flat)
+    good = flat[finite]
+    rms = float(good.pow(2).mean().sqrt()) if good.numel() else 0.0
+    absmax = float(good.abs().max()) if good.numel() else 0.0
+    first = [float(v) for v in flat[:4]]
+    return (f"{label}: n={flat.numel()} rms={rms:.6e} absmax={absmax:.6e} zeros={int((good == 0).sum())} "
+            f"non_finite={int((~finite).sum())} first={first}")
 
 
 class Model:
@@ -66,18 +92,28 @@ class Model:
 
     # ------------------------------------------------------------------ one step
 
-    def forward(self, step, cache) -> Optional[torch.Tensor]:
+    def forward(self, step, cache, layer_hook=None, add_hook=None) -> Optional[torch.Tensor]:
         """Runs the rows of ``step`` through every run entry; returns float32 logits
-        ``[len(step.want_rows), vocab]`` or None when no row is wanted."""
+        ``[len(step.want_rows), vocab]`` or None when no row is wanted.
+
+        ``layer_hook(position, stream)`` is called after the embedding (position -1) and after
+        every run entry; ``stream_value(stream)`` gives the residual rows at that point.
+        ``add_hook(stream)`` is called whenever a part leaves its output on the stream (after the
+        mixer and after the feed-forward of a block).  Both are diagnostics: they synchronise,
+        so a step with a hook is never captured."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet: load or bind them first")
-        stream = Stream(self.embedding.forward(step))
+        stream = Stream(self.embedding.forward(step), add_hook)
+        if layer_hook is not None:
+            layer_hook(-1, stream)
         for pos, entry in enumerate(self.plan.order):
             if entry.cache_of is None:
                 view = cache.view(pos)
             else:
                 view = cache.view(entry.cache_of, owner=False)
             self.blocks[entry.layer].forward(stream, step, view)
+            if layer_hook is not None:
+                layer_hook(pos, stream)
         if step.num_wanted == 0:
             return None
         if getattr(step, "wants_every_row", False):

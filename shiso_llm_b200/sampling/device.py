@@ -22,13 +22,22 @@ class DeviceSampler:
         sampled token will occupy in its sequence.  Returns host ints."""
         return self.sample_into(logits, params, positions, None).tolist()
 
-    def sample_into(self, logits, params: Sequence[SamplingParams], positions: Sequence[int], out) -> torch.Tensor:
+    def sample_into(self, logits, params: Sequence[SamplingParams], positions: Sequence[int], out,
+                    status_out=None) -> torch.Tensor:
         """The same, leaving the picks on the device: in ``out`` (int32 ``[R]``) when one is
-        given.  Nothing waits for the device."""
+        given.  Nothing waits for the device.  Rows whose request names ``bad_token_ids`` have
+        those logits set to -inf first, in place.  ``status_out`` (one int32 on the device) is
+        handed to the picking kernel, which leaves the status word of the kernels' bounded
+        waits there (``ops.check_kernel_status``)."""
         if logits.shape[0] != len(params):
             raise ValueError(f"{logits.shape[0]} rows of logits for {len(params)} requests")
+        extra = {} if status_out is None else {"status_out": status_out}
+        if any(p.bad_token_ids for p in params):
+            pairs = [(r, t) for r, p in enumerate(params) for t in p.bad_token_ids]
+            both = torch.tensor(pairs, dtype=torch.int32).t().contiguous().to(self.device, non_blocking=True)
+            self.ops.suppress(logits, both[0], both[1])
         if all(p.greedy for p in params):
-            return self.ops.argmax(logits, out)
+            return self.ops.argmax(logits, out, **extra)
         clamped = [p.clamped() for p in params]
         host = torch.tensor(
             [[c[0] if not p.greedy else 0.0, c[2], c[3]] for c, p in zip(clamped, params)], dtype=torch.float32
@@ -47,6 +56,7 @@ class DeviceSampler:
             keys.to(dev, non_blocking=True),
             ints[:, 1].contiguous(),
             out,
+            **extra,
         )
         return picks
 

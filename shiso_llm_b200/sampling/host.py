@@ -55,6 +55,16 @@ def argmax(logits) -> int:
     return int(np.argmax(np.where(finite, row, -np.inf)))
 
 
+def suppress(logits, ids) -> np.ndarray:
+    """A copy of the row with -inf at every id of ``ids``, so that no pick after it can choose
+    one; an id past the row is ignored (crates/shiso-engine/src/sampling.rs:156-174)."""
+    row = np.array(logits, dtype=np.float32, copy=True)
+    for i in ids:
+        if 0 <= i < row.shape[0]:
+            row[i] = -np.inf
+    return row
+
+
 def _fixed_mass(scaled: np.ndarray) -> np.ndarray:
     return (np.exp(scaled.astype(np.float32)).astype(np.float32) * np.float32(1099511627776.0)).astype(np.uint64)
 
@@ -93,6 +103,8 @@ def candidate_mask(logits, params: SamplingParams) -> np.ndarray:
 
 def keyed_sample(logits, params: SamplingParams, key: int, position: int) -> int:
     row = np.asarray(logits, dtype=np.float32)
+    if params.bad_token_ids:
+        row = suppress(row, params.bad_token_ids)
     if params.greedy or not np.isfinite(row).any():
         return argmax(row)
     keep = candidate_mask(row, params)
@@ -131,6 +143,8 @@ def stream_sample(logits, params: SamplingParams, rng: Xorshift64Star) -> int:
     (crates/shiso-engine/src/sampling.rs:521-591); without top-k and with top_p >= 1 the
     walk is in vocabulary order (sampling.rs:432-478)."""
     row = np.asarray(logits, dtype=np.float32)
+    if params.bad_token_ids:
+        row = suppress(row, params.bad_token_ids)
     finite = np.isfinite(row)
     if params.greedy or not finite.any():
         return argmax(row)

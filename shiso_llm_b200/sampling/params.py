@@ -4,7 +4,9 @@ Field names and meanings follow the reference's ``SamplingParams`` and request f
 (crates/shiso-core/src/model.rs:530-567; crates/shiso-ir/src/request.rs:33-85):
 ``temperature <= 0`` means greedy and draws nothing; ``top_k`` 0 / None is off;
 ``top_p`` outside (0, 1] is treated as 1; ``min_p`` below 0 as 0.  The neutral setting
-is (1.0, off, 1.0, 0.0).
+is (1.0, off, 1.0, 0.0).  ``bad_token_ids`` are ids the request may never emit: their
+logits are set to -inf before any pick, greedy or not
+(crates/shiso-engine/src/sampling.rs:156-174).
 """
 
 from __future__ import annotations
@@ -25,12 +27,16 @@ class SamplingParams:
     max_new_tokens: int = 16
     stop_token_ids: Sequence[int] = field(default_factory=tuple)
     ignore_eos: bool = False
+    bad_token_ids: Sequence[int] = field(default_factory=tuple)
 
     def __post_init__(self):
         if self.max_new_tokens < 0:
             raise ValueError(f"max_new_tokens = {self.max_new_tokens} must not be negative")
         if self.top_k is not None and self.top_k < 0:
             raise ValueError(f"top_k = {self.top_k} must not be negative")
+        self.bad_token_ids = tuple(int(t) for t in self.bad_token_ids)
+        if any(t < 0 for t in self.bad_token_ids):
+            raise ValueError(f"bad_token_ids = {self.bad_token_ids}: token ids are not negative")
 
     @property
     def greedy(self) -> bool:

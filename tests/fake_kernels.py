@@ -202,9 +202,26 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
     return out.reshape(T, heads * d).to(q.dtype)
 
 
-def argmax(logits, out=None):
-    """Lowest id among the maxima (crates/shiso-engine/src/sampling.rs:91-154)."""
-    picks = torch.argmax(logits, dim=-1).to(torch.int32)
+CARRIES_STATUS = True
+GAVE_UP = "a kernel gave up waiting on a barrier; what it wrote is not valid"
+STATUS_WORD = [0]  # a test sets it to imitate a kernel whose bounded wait ran out
+
+
+def hand_over_status(status_out):
+    if status_out is not None:
+        status_out[0] = STATUS_WORD[0]
+        STATUS_WORD[0] = 0
+
+
+def suppress(logits, rows, ids):
+    logits[rows.long(), ids.long()] = float("-inf")
+    return logits
+
+
+def argmax(logits, out=None, status_out=None):
+    """Lowest id among the finite maxima (crates/shiso-engine/src/sampling.rs:91-154)."""
+    hand_over_status(status_out)
+    picks = torch.argmax(torch.where(torch.isfinite(logits), logits, torch.full_like(logits, float("-inf"))), dim=-1).to(torch.int32)
     if out is None:
         return picks
     out.copy_(picks)

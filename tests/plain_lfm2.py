@@ -50,7 +50,7 @@ def plain_rope_half_split(v, positions, theta, rotary_dim=None):
     d = v.shape[-1]
     rot = d if rotary_dim is None else rotary_dim
     half = rot // 2
-    i = torch.arange(half, dtype=torch.float64)
+    i = torch.arange(half, dtype=torch.float64, device=v.device)
     inv_freq = theta ** (-2.0 * i / rot)
     angle = positions.to(torch.float64)[:, None] * inv_freq[None, :]
     cos = torch.cos(angle).to(v.dtype)[:, None, :]
@@ -78,8 +78,8 @@ def plain_short_conv(n, w_in, conv_w, conv_b, w_out, rnd=lambda t: t):
     p = rnd(n @ w_in.T)
     b, c, x = p[:, :H], p[:, H : 2 * H], p[:, 2 * H :]
     u = b * x
-    padded = torch.cat([torch.zeros(L - 1, H, dtype=u.dtype), u], dim=0)
-    acc = torch.zeros(T, H, dtype=u.dtype)
+    padded = torch.cat([torch.zeros(L - 1, H, dtype=u.dtype, device=u.device), u], dim=0)
+    acc = torch.zeros(T, H, dtype=u.dtype, device=u.device)
     for j in range(L):
         acc = acc + conv_w[:, j][None, :] * padded[j : j + T]
     if conv_b is not None:
@@ -99,14 +99,14 @@ def plain_attention(n, w_q, w_k, w_v, w_o, q_norm_w, k_norm_w, eps, theta, n_hea
     inclusive (kernels/cuda/dense/dense_attn.cuh:60,87-88,110); softmax; W_o."""
     T, _ = n.shape
     d = w_q.shape[0] // n_heads
-    positions = torch.arange(T)
+    positions = torch.arange(T, device=n.device)
     q = rnd(n @ w_q.T).reshape(T, n_heads, d)
     k = rnd(n @ w_k.T).reshape(T, n_kv_heads, d)
     v = rnd(n @ w_v.T).reshape(T, n_kv_heads, d)
     q = rnd(plain_rope_half_split(plain_rmsnorm(q, q_norm_w, eps), positions, theta))
     k = rnd(plain_rope_half_split(plain_rmsnorm(k, k_norm_w, eps), positions, theta))
     group = n_heads // n_kv_heads
-    out = torch.zeros(T, n_heads, d, dtype=n.dtype)
+    out = torch.zeros(T, n_heads, d, dtype=n.dtype, device=n.device)
     scale = 1.0 / math.sqrt(d)
     for h in range(n_heads):
         g = h // group
@@ -128,8 +128,14 @@ def plain_swiglu(n, w_gate, w_up, w_down, rnd=lambda t: t):
     return rnd(m @ w_down.T)
 
 
-def plain_forward(config, tensors, ids, dtype=torch.float64, round_to=None, return_hidden=False):
-    """Logits ``[T, V]`` of one whole sequence.
+def plain_forward(config, tensors, ids, dtype=torch.float64, round_to=None, return_hidden=False, device=None, rows=None,
+                  layer_hook=None):
+    """Logits ``[T, V]`` of one whole sequence (of the positions ``rows`` only when given).
+
+    ``device`` moves the arithmetic (the same float64 formulas) to another device, so that a
+    model of real size is a matter of seconds; tensors that already are in ``dtype`` on that
+    device are used as they are.  ``layer_hook(i, x)`` is called with the residual stream
+    after every layer.
 
     Order inside a layer: pre-norm, mixer, residual, feed-forward norm, SwiGLU,
     residual; then the final norm (the tensor named after the embedding) and the
@@ -139,10 +145,10 @@ def plain_forward(config, tensors, ids, dtype=torch.float64, round_to=None, retu
         rnd = lambda t: t
     else:
         rnd = lambda t: t.to(round_to).to(dtype)
-    w = {k: v.to(dtype) for k, v in tensors.items()}
+    w = {k: v.to(device=device, dtype=dtype) for k, v in tensors.items()}
     H = config["hidden_size"]
     eps = config["norm_eps"]
-    ids = torch.as_tensor(ids, dtype=torch.long)
+    ids = torch.as_tensor(ids, dtype=torch.long, device=device)
     x = plain_embedding(ids, w["model.embed_tokens.weight"])
     for i, kind in enumerate(config["layer_types"]):
         p = f"model.layers.{i}"
@@ -183,6 +189,10 @@ def plain_forward(config, tensors, ids, dtype=torch.float64, round_to=None, retu
             w[f"{p}.feed_forward.w2.weight"],
             rnd,
         )
+        if layer_hook is not None:
+            layer_hook(i, x)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long, device=x.device)]
     nf = rnd(plain_rmsnorm(x, w["model.embedding_norm.weight"], eps))
     tied = config.get("tie_embedding", config.get("tie_word_embeddings", True))
     head = w["model.embed_tokens.weight"] if tied else w["lm_head.weight"]

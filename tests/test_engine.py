@@ -20,7 +20,8 @@ from shiso_llm_b200.weights import random_tensors
 from tolerances import check_logits
 
 
-def _fake_sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None):
+def _fake_sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None, status_out=None):
+    fake_kernels.hand_over_status(status_out)
     picks = []
     for r in range(logits.shape[0]):
         p = SamplingParams(temperature=float(temperature[r]), top_k=int(top_k[r]), top_p=float(top_p[r]), min_p=float(min_p[r]))
@@ -125,13 +126,13 @@ def test_sampling_is_the_same_under_every_cut_and_after_preemption(tmp_path, bac
     cut = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=32,
               prefill_chunk=13, **backend_args(backend))
     assert [o.token_ids for o in cut.generate(prompts, params)] == [o.token_ids for o in base]
-    tight = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, kv_cache_tokens=208, max_num_seqs=4,
+    tight = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, kv_cache_tokens=208, allow_small_pool=True, max_num_seqs=4,
                 max_num_batched_tokens=32, prefill_chunk=13, **backend_args(backend))
     outs = tight.generate(prompts, params)
     assert [o.token_ids for o in outs] == [o.token_ids for o in base]
     assert tight.scheduler.stats["preempted"] > 0
     tight.engine.cache.check()
-    failing = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, kv_cache_tokens=208, max_num_seqs=4,
+    failing = LLM(str(tmp_path), dtype="float32", ctx=256, page_size=16, kv_cache_tokens=208, allow_small_pool=True, max_num_seqs=4,
                   max_num_batched_tokens=32, prefill_chunk=13, on_exhaustion="fail", **backend_args(backend))
     outs = failing.generate(prompts, params)
     assert any(o.finish_reason == "error" and "kv pool" in o.error for o in outs)

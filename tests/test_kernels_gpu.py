@@ -393,6 +393,71 @@ def test_sample_kernel_follows_the_host_rule():
     assert same >= 4 * 6 - 1
 
 
+def test_suppressed_ids_on_the_device_follow_the_host_rule():
+    """``bad_token_ids``: -inf before the pick, in the greedy kernels (one and two stages) and in
+    the keyed kernel; rows without such ids are not touched; the pick equals the host's."""
+    import numpy as np
+
+    from shiso_llm_b200.sampling import DeviceSampler, SamplingParams, candidate_mask, keyed_sample
+
+    sampler = DeviceSampler(ops(), "cuda")
+    for vocab in (3000, 20000):
+        logits = rnd((4, vocab), torch.float32, 60 + vocab, 2.0)
+        order = [torch.argsort(logits[r], descending=True).tolist() for r in range(4)]
+        cases = [
+            SamplingParams(temperature=0.0, bad_token_ids=order[0][:3]),
+            SamplingParams(temperature=0.0),
+            SamplingParams(temperature=0.0, bad_token_ids=[order[2][0], vocab + 5]),  # an id past the row is ignored
+            SamplingParams(temperature=0.0, bad_token_ids=order[3][1:4]),
+        ]
+        dev = logits.cuda()
+        assert sampler.sample(dev, cases, [0] * 4) == [order[0][3], order[1][0], order[2][1], order[3][0]]
+        assert torch.isneginf(dev.cpu()[0, order[0][:3]]).all() and torch.equal(dev.cpu()[1], logits[1])
+        mixed = [
+            SamplingParams(temperature=1.1, top_k=50, seed=4, bad_token_ids=order[0][:25]),
+            SamplingParams(temperature=0.0, bad_token_ids=order[1][:1]),
+            SamplingParams(temperature=0.9, top_p=0.7, seed=5),
+            SamplingParams(temperature=1.0, seed=6, bad_token_ids=order[3][:2]),
+        ]
+        for position in (0, 9, 300):
+            picks = sampler.sample(logits.cuda(), mixed, [position] * 4)
+            for r, (p, pick) in enumerate(zip(mixed, picks)):
+                assert pick not in p.bad_token_ids
+                row = logits[r].numpy()
+                if p.greedy:
+                    assert pick == keyed_sample(row, p, p.seed, position)
+                else:
+                    cut = row.copy()
+                    cut[[t for t in p.bad_token_ids if t < vocab]] = -np.inf
+                    assert candidate_mask(cut, p)[pick]
+            assert picks[1] == order[1][1]
+
+
+def test_the_status_word_travels_with_the_picks():
+    """A picking kernel that is given a place for it moves the status word there and clears it."""
+    logits = rnd((3, 20000), torch.float32, 70).cuda()
+    small = rnd((3, 500), torch.float32, 71).cuda()
+    out = torch.full((4,), -7, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    ops().check_kernel_status()
+    for rows in (logits, small):
+        ops().argmax(rows, out[:3], out[3:4])
+        assert out[3].item() == 0
+        ops().selftest_bounded_wait(3000)
+        ops().argmax(rows, out[:3], out[3:4])
+        assert out[3].item() == 1 and out[:3].tolist() == rows.argmax(-1).tolist()
+        ops().argmax(rows, out[:3], out[3:4])
+        assert out[3].item() == 0
+        ops().check_kernel_status()  # the kernel cleared it
+    from shiso_llm_b200.sampling import DeviceSampler, SamplingParams
+
+    ops().selftest_bounded_wait(3000)
+    DeviceSampler(ops(), "cuda").sample_into(small, [SamplingParams(temperature=0.9, seed=r) for r in range(3)], [5, 6, 7],
+                                             out[:3], out[3:4])
+    assert out[3].item() == 1
+    ops().check_kernel_status()
+
+
 @pytest.mark.parametrize("case", [(4, 2, 16, 4), (3, 1, 32, 16), (32, 8, 64, 16), (6, 6, 48, 8), (8, 1, 128, 16), (2, 1, 256, 4), (5, 5, 80, 16), (32, 2, 64, 16), (36, 2, 32, 8),
                                   (6, 2, 64, 8), (5, 1, 64, 32), (12, 4, 64, 64), (7, 7, 64, 16), (4, 2, 64, 4)])
 def test_decode_attention_split_keys(case):

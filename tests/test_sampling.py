@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from shiso_llm_b200.sampling import (
-    SamplingParams, Xorshift64Star, argmax, candidate_mask, keyed_sample, keyed_uniform, stream_sample,
+    SamplingParams, Xorshift64Star, argmax, candidate_mask, keyed_sample, keyed_uniform, stream_sample, suppress,
 )
 
 
@@ -100,3 +100,23 @@ def test_parameter_clamps():
     assert SamplingParams(min_p=-1.0).clamped()[3] == 0.0 and SamplingParams(top_k=5000).clamped()[1] == 1024
     with pytest.raises(ValueError):
         SamplingParams(top_k=-1)
+
+
+def test_suppressed_ids_are_never_picked():
+    """``bad_token_ids`` become -inf before any pick, greedy or not; an id past the row is
+    ignored and the caller's row is not changed (crates/shiso-engine/src/sampling.rs:156-174)."""
+    r = row(6)
+    best, second = np.argsort(-r)[:2]
+    assert keyed_sample(r, SamplingParams(temperature=0.0, bad_token_ids=[int(best)]), 0, 0) == second
+    assert r[best] > r[second]  # untouched
+    cut = suppress(r, [int(best), 10**6])
+    assert np.isneginf(cut[best]) and np.isfinite(cut).sum() == len(r) - 1
+    bad = [int(i) for i in np.argsort(-r)[:20]]
+    params = SamplingParams(temperature=1.2, top_k=30, bad_token_ids=bad, seed=3)
+    picks = {keyed_sample(r, params, 3, p) for p in range(200)}
+    assert picks and not picks & set(bad) and picks <= set(int(i) for i in np.argsort(-r)[20:50])
+    rng = Xorshift64Star(2)
+    assert not {stream_sample(r, params, rng) for _ in range(100)} & set(bad)
+    assert keyed_sample(r, SamplingParams(temperature=0.0, bad_token_ids=list(range(len(r)))), 0, 0) == 0  # nothing left
+    with pytest.raises(ValueError):
+        SamplingParams(bad_token_ids=[-1])
