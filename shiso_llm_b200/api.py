@@ -76,6 +76,7 @@ class LLM:
             SchedulerConfig(
                 max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                 prefill_chunk=prefill_chunk, ctx=ctx, on_exhaustion=on_exhaustion,
+                portion_multiple=self.engine.model.plan.portion_multiple,
             ),
             self.engine.model.plan.eos_token_ids,
         )

@@ -11,9 +11,10 @@ everything.  Within a group every entry has its own K and V buffer
 page id names the same rows in all of them, as the reference's pages do
 (crates/shiso-engine/src/kv.rs:18-31,97-109).
 
-Fixed state.  One float32 buffer ``[num_slots, floats_per_slot]``; every fixed-state
-entry owns a column range of it, so one request's state of every such layer lies in
-one row and is zeroed by one fill when the slot is assigned.
+Fixed state.  One buffer ``[num_slots, bytes_per_slot]``; every fixed-state entry owns a
+16-byte-aligned column range of it, seen in the entry's own element type (float32 unless
+it asks otherwise), so one request's state of every such layer lies in one row and is
+zeroed by one fill when the slot is assigned.
 
 Requests.  ``append`` claims what ``n`` more tokens need in every group, all or
 nothing, and raises ``OutOfPages`` otherwise (the reference fails the session there:
@@ -97,10 +98,10 @@ class CacheManager:
                     self.groups.append(group)
                     by_window[need.window] = group
                 group = by_window[need.window]
-                shape = (num_pages, page_size, need.num_kv_heads, need.head_dim)
+                kv_dtype = need.dtype if need.dtype is not None else dtype
                 self._views[pos] = PagedKVView(
-                    k=torch.zeros(shape, dtype=dtype, device=self.device),
-                    v=torch.zeros(shape, dtype=dtype, device=self.device),
+                    k=torch.zeros((num_pages, page_size, need.num_kv_heads, need.head_dim), dtype=kv_dtype, device=self.device),
+                    v=torch.zeros((num_pages, page_size, need.num_kv_heads, need.value_dim), dtype=kv_dtype, device=self.device),
                     page_size=page_size,
                     group=group.index,
                     kv_heads=need.num_kv_heads,
@@ -109,19 +110,19 @@ class CacheManager:
         self.num_pages = num_pages
         self.max_blocks = max_blocks_per_request or num_pages
 
-        # Fixed-size state: one row per slot, one column range per entry.
+        # Fixed-size state: one row of bytes per slot, one aligned column range per entry.
         offsets, total = {}, 0
         for pos, need in enumerate(needs):
             if isinstance(need, FixedState):
                 offsets[pos] = total
-                total += need.numel
-        self.floats_per_slot = total
+                total += -(-need.nbytes // 16) * 16
+        self.bytes_per_slot = total
         self.slots = SlotPool(num_slots)
         self.num_slots = num_slots
-        self.state = torch.zeros((num_slots, max(total, 1)), dtype=torch.float32, device=self.device)
+        self.state = torch.zeros((num_slots, max(total, 16)), dtype=torch.uint8, device=self.device)
         for pos, off in offsets.items():
             need = needs[pos]
-            view = self.state[:, off : off + need.numel].unflatten(1, need.shape)
+            view = self.state[:, off : off + need.nbytes].view(need.dtype).unflatten(1, need.shape)
             self._views[pos] = FixedStateView(state=view)
 
         self._held: dict = {}
@@ -134,9 +135,10 @@ class CacheManager:
         page_bytes = state_bytes = 0
         for need in needs:
             if isinstance(need, PagedKV):
-                page_bytes += 2 * page_size * need.num_kv_heads * need.head_dim * dtype.itemsize
+                itemsize = (need.dtype if need.dtype is not None else dtype).itemsize
+                page_bytes += page_size * need.num_kv_heads * (need.head_dim + need.value_dim) * itemsize
             elif isinstance(need, FixedState):
-                state_bytes += need.numel * 4
+                state_bytes += -(-need.nbytes // 16) * 16
         return page_bytes, state_bytes
 
     # ------------------------------------------------------------------ views for the model
@@ -201,7 +203,7 @@ class CacheManager:
             raise OutOfPages(-(-new_length // self.page_size), self.max_blocks, "blocks per request allowed")
         if fresh:
             slot = self.slots.take()  # raises OutOfPages before anything else is taken
-            if self.floats_per_slot:
+            if self.bytes_per_slot:
                 self.state[slot].zero_()
             held = _Held([BlockTable(self.page_size, g.window) for g in self.groups], slot)
             self._held[request] = held

@@ -9,7 +9,9 @@ One decision per step (``plan``), pure host bookkeeping over the cache manager's
    running requests still reading their prompt, oldest first, then waiting requests in
    arrival order while a sequence slot, a state slot and pages for all of the request's
    tokens so far are free.
-   A portion is at most ``prefill_chunk`` tokens and may end anywhere.  (The reference gives
+   A portion is at most ``prefill_chunk`` tokens and may end anywhere, unless the model's plan
+   names a ``portion_multiple``: then every portion but a request's last is a multiple of it
+   (the reference's prefill grid, crates/shiso-runtime/src/scheduler/config.rs:35-44).  (The reference gives
    one prompt portion per tick to the oldest prefilling sequence only, batching.rs:219-227,
    and never mixes it with the decode pass; here both share one step.)
 3. When a decode row cannot get a page: with ``on_exhaustion = "preempt"`` the youngest
@@ -55,8 +57,19 @@ class SchedulerConfig:
     prefill_chunk: Optional[int] = None  # longest prompt portion; None: the token budget
     ctx: int = 4096
     on_exhaustion: str = "preempt"  # or "fail"
+    portion_multiple: int = 1  # portions that are not a request's last are multiples of this
 
     def __post_init__(self):
+        if self.portion_multiple < 1:
+            raise ValueError("portion_multiple must be at least 1")
+        if self.portion_multiple > 1:
+            room = min(self.max_num_batched_tokens - (self.max_num_seqs - 1), self.prefill_chunk or self.max_num_batched_tokens)
+            if room < self.portion_multiple:
+                raise ValueError(
+                    f"portion_multiple = {self.portion_multiple}: beside {self.max_num_seqs - 1} decoding rows a step of "
+                    f"{self.max_num_batched_tokens} tokens (prefill_chunk {self.prefill_chunk}) leaves {room} tokens, so a "
+                    f"prompt could never advance"
+                )
         if self.on_exhaustion not in ("preempt", "fail"):
             raise ValueError(f"on_exhaustion = {self.on_exhaustion!r}: expected 'preempt' or 'fail'")
         if self.max_num_seqs <= 0 or self.max_num_batched_tokens <= 0:
@@ -235,7 +248,7 @@ class Scheduler:
             if (req.state != RUNNING or req.decoding or req.remaining <= 0 or budget <= 0
                     or any(e.request is req for e in plan.entries)):
                 continue
-            count = self._portion(req, min(req.remaining, budget, chunk), free)
+            count = self._on_grid(req, self._portion(req, min(req.remaining, budget, chunk), free))
             if count <= 0:
                 continue
             claim(self.cache.pages_needed(req.id, count))
@@ -251,7 +264,9 @@ class Scheduler:
             # portion: a request admitted on less would soon be preempted again.
             if not fits(req, req.remaining)[0]:
                 break
-            count = min(req.remaining, budget, chunk)
+            count = self._on_grid(req, min(req.remaining, budget, chunk))
+            if count <= 0:
+                break  # what is left of this step's budget is less than one grid cell
             self.waiting.popleft()
             req.state = RUNNING
             self.running.append(req)
@@ -271,6 +286,13 @@ class Scheduler:
             else:
                 self._fail(residents[-1], "kv pool: no request can make progress", plan)
         return plan
+
+    def _on_grid(self, req: Request, count: int) -> int:
+        """``count`` cut down to the plan's grid unless the portion reaches the request's last token."""
+        multiple = self.config.portion_multiple
+        if multiple > 1 and count < req.remaining:
+            count -= count % multiple
+        return count
 
     def _portion(self, req: Request, want: int, free) -> int:
         """The longest portion <= want whose pages are free now (0 when not even one token fits)."""

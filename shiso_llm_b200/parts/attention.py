@@ -27,8 +27,7 @@ from ..config.errors import UnsupportedShape
 from ..weights.spec import TensorSpec
 from .base import MIXERS, NORMS, POSITION_ENCODINGS, DeferredLinear, Mixer, PagedKV, project
 
-MAX_HEAD_DIM = 256
-HEAD_DIM_STEP = 16
+MAX_HEAD_DIM = 256  # what the general attention kernel keeps of a head in a warp's registers
 
 
 @MIXERS.register("gqa_attention")
@@ -44,11 +43,10 @@ class GqaAttention(Mixer):
         self.head_dim = int(p["head_dim"])
         if self.heads % self.kv_heads:
             raise UnsupportedShape("num_kv_heads", self.kv_heads, f"does not divide {self.heads} query heads")
-        if self.head_dim % HEAD_DIM_STEP or not 0 < self.head_dim <= MAX_HEAD_DIM:
-            raise UnsupportedShape(
-                "head_dim", self.head_dim,
-                f"the attention kernels take head sizes in steps of {HEAD_DIM_STEP} up to {MAX_HEAD_DIM}",
-            )
+        # Any head size up to 256 runs: the tensor-core kernels take sizes in steps of 16 (the
+        # kernel table sends other sizes, in either compute type, to the general kernel).
+        if not 0 < self.head_dim <= MAX_HEAD_DIM:
+            raise UnsupportedShape("head_dim", self.head_dim, f"the attention kernels take head sizes up to {MAX_HEAD_DIM}")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
         self.window = int(p["window"]) if p.get("window") else None
         self.borrows_cache = bool(p.get("borrows_cache", False))
@@ -95,7 +93,7 @@ class GqaAttention(Mixer):
     def cache_spec(self):
         if self.borrows_cache:
             return None
-        return PagedKV(self.kv_heads, self.head_dim, self.window)
+        return PagedKV(self.kv_heads, self.head_dim, self.window)  # values as wide as keys, in the compute type
 
     def forward(self, x, step, cache):
         ops = self.env.ops

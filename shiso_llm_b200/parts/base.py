@@ -46,18 +46,28 @@ class BuildEnv:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of every position, in pages.  ``window`` = how many of the most
-    recent positions are ever read again (None: all of them)."""
+    recent positions are ever read again (None: all of them).  Values may have another width
+    than keys (``v_head_dim``; None: the same), and the entry may ask for an element type of
+    its own (``dtype``; None: the engine's compute type)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
 class FixedState:
-    """Per-request state of fixed size (float32 elements), zero for a new request."""
+    """Per-request state of fixed size, zero for a new request; float32 unless the entry asks
+    for another element type."""
 
     shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
 
     @property
     def numel(self) -> int:
@@ -65,6 +75,10 @@ class FixedState:
         for d in self.shape:
             n *= d
         return n
+
+    @property
+    def nbytes(self) -> int:
+        return self.numel * self.dtype.itemsize
 
 
 # --------------------------------------------------------------------------- part classes

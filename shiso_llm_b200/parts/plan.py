@@ -75,8 +75,15 @@ class ModelPlan:
     head: PartSpec
     eos_token_ids: tuple[int, ...] = ()
     max_position: Optional[int] = None
+    # A portion of a prompt that is not the request's last must be a multiple of this many tokens,
+    # so that every portion starts on that grid: what a mixer needs whose recurrence is evaluated
+    # in chunks of fixed length (the reference cuts on such a grid for its chunked delta-net,
+    # crates/shiso-runtime/src/scheduler/config.rs:35-44).  1: a portion may end anywhere.
+    portion_multiple: int = 1
 
     def __post_init__(self):
+        if self.portion_multiple < 1:
+            raise ValueError(f"portion_multiple = {self.portion_multiple} must be at least 1")
         if not self.order:
             raise ValueError("a model plan needs at least one run entry")
         for pos, entry in enumerate(self.order):

@@ -58,17 +58,40 @@ def test_layout_groups_and_state_views():
     assert m.view(2) is None
     s0, s3 = m.view(0).state, m.view(3).state
     assert s0.shape == (3, 2, 8) and s3.shape == (3, 3, 8)
-    assert m.floats_per_slot == 16 + 24 and s0.stride(0) == 40 and s3.stride(0) == 40
+    assert m.bytes_per_slot == 4 * (16 + 24) and s0.stride(0) == 40 and s3.stride(0) == 40 and s0.dtype == torch.float32
     assert m.view(1, owner=False).owner is False and m.view(1).owner is True
     windowed = manager(needs=[PagedKV(2, 16), PagedKV(2, 16, window=6), PagedKV(2, 16, window=6)])
     assert len(windowed.groups) == 2 and windowed.view(1).group == windowed.view(2).group != windowed.view(0).group
 
 
+def test_entries_may_name_their_own_widths_and_element_types():
+    """Values narrower than keys, a cache in another element type than the compute type, and
+    fixed state that is not float32: each entry's view has what it asked for, ranges of one slot
+    do not overlap, and one fill zeroes a slot."""
+    needs = [FixedState((3, 5), torch.bfloat16), PagedKV(2, 24, v_head_dim=8, dtype=torch.float16),
+             FixedState((7,), torch.int32), PagedKV(1, 16), FixedState((2, 2))]
+    m = manager(needs=needs)
+    assert m.view(1).k.shape == (12, 4, 2, 24) and m.view(1).v.shape == (12, 4, 2, 8)
+    assert m.view(1).k.dtype == m.view(1).v.dtype == torch.float16 and m.view(3).k.dtype == torch.float32
+    a, b, c = m.view(0).state, m.view(2).state, m.view(4).state
+    assert (a.shape, a.dtype) == ((3, 3, 5), torch.bfloat16) and (b.shape, b.dtype) == ((3, 7), torch.int32)
+    assert (c.shape, c.dtype) == ((3, 2, 2), torch.float32)
+    assert m.bytes_per_slot == 32 + 32 + 16  # 30, 28 and 16 bytes, each range 16-byte aligned
+    a.fill_(1.0), b.fill_(2), c.fill_(3.0)
+    assert (a == 1.0).all() and (b == 2).all() and (c == 3.0).all()  # no range reaches into another
+    m.append("r", 1)
+    slot = m.slot_of("r")
+    assert (a[slot] == 0).all() and (b[slot] == 0).all() and (c[slot] == 0).all() and (a[1 - slot if slot < 2 else 0] == 1.0).all()
+    page_bytes, state_bytes = m.costs(needs, 4, torch.float32)
+    assert page_bytes == 4 * 2 * (24 + 8) * 2 + 4 * 1 * 32 * 4 and state_bytes == 80
+
+
 def test_append_commit_release_and_zeroed_slot():
     m = manager()
-    m.state.fill_(7.0)
+    m.state.view(torch.float32).fill_(7.0)
     assert m.append("a", 5) == 0
-    assert (m.state[m.slot_of("a")] == 0).all() and (m.state == 7.0).sum() == 2 * 40
+    floats = m.state.view(torch.float32)
+    assert (floats[m.slot_of("a")] == 0).all() and (floats == 7.0).sum() == 2 * 40
     m.commit("a")
     assert m.length("a") == 5 and m.block_table("a", 0) == [0, 1]
     assert m.append("a", 3) == 5  # still fits page 1
