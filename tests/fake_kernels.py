@@ -157,8 +157,9 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
         if not rotary_dim:
             return v
         half = rotary_dim // 2
-        # the angle is formed in float32, as the kernel does
-        angle = (step.positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]).to(F64)
+        # the angle in float64 from the float32 frequency table the kernel is given: a kernel that
+        # forms it in float32 is off by up to position * 2^-24 radians, which its test allows for
+        angle = step.positions.to(F64)[:, None] * inv_freq.to(F64)[None, :]
         cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
         out = v.clone()
         a, b = v[..., :half], v[..., half:rotary_dim]

@@ -103,8 +103,23 @@ def test_greedy_generation_through_the_entry_point(tmp_path, backend):
         want = [plain_lfm2.plain_greedy(doc, tensors, p, 16) for p in prompts]
         llm = LLM(str(folder), dtype="float32", ctx=128, page_size=16, max_num_seqs=4, max_num_batched_tokens=32,
                   prefill_chunk=13, **backend_args(backend))
+        seen = {}  # (request, position) -> the logits row a token was picked from
+
+        def tap(plan, logits, seen=seen):
+            rows = logits.float().cpu()
+            for row, entry in zip(rows, [e for e in plan.entries if e.samples]):
+                seen[(entry.request.id, entry.start + entry.count - 1)] = row
+
+        llm.logits_tap = tap
         outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=16))
         assert [o.token_ids for o in outs] == want and all(o.finish_reason == "length" for o in outs)
+        # equal ids say little where the tiny model repeats itself: every row a token was picked from
+        # is compared too
+        for out, prompt in zip(outs, prompts):
+            ref = plain_lfm2.plain_forward(doc, tensors, prompt + out.token_ids[:-1])
+            places = range(len(prompt) - 1, len(prompt) + 15)
+            got = torch.stack([seen[(out.request_id, p)] for p in places])
+            check_logits(got, ref[len(prompt) - 1 :], "float32", f"rows that generation picked from, tiny {name}")
         llm.engine.cache.check()
         assert llm.engine.cache.slots.free_slots == 4
 
@@ -244,3 +259,109 @@ def test_toy_parts_register_build_and_step_without_touching_the_framework(backen
         engine.cache.check()
     finally:
         toy_parts.unregister()
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_a_plan_with_a_portion_grid_typed_state_and_narrow_values(backend):
+    """A toy model whose plan names ``portion_multiple`` 4, whose first mixer keeps float64
+    state and refuses portions that start off the grid, and whose second mixer caches values
+    narrower than its keys in float32: built and generated with through the scheduler, which
+    must cut every prompt on the grid, without a change to the package."""
+    toy_parts.register()
+    try:
+        plan = toy_parts.grid_plan()
+        args = backend_args(backend)
+        from shiso_llm_b200.parts import BuildEnv, Model
+        from shiso_llm_b200.weights.loader import target_dtype
+
+        specs = Model(plan, BuildEnv(torch.float32, torch.device("cpu"), None)).tensor_specs()
+        stored = random_tensors(specs, 5, 0.08, "bfloat16", 0.1)
+        ops = args["ops"]
+        if ops is None:
+            from shiso_llm_b200.kernels import ops
+        by_name = {s.name: s for s in specs}
+        tensors = {k: v.to(args["device"], target_dtype(by_name[k], v.dtype, torch.float32)) for k, v in stored.items()}
+        options = EngineOptions(dtype="float32", ctx=64, page_size=4, max_num_seqs=3, max_num_batched_tokens=16, device=args["device"])
+        engine = Engine.from_plan(plan, tensors, options, ops)
+        needs = engine.model.cache_needs()
+        assert needs[0].dtype == torch.float64 and needs[1].value_dim == toy_parts.V_DIM and needs[1].dtype == torch.float32
+        ids = helpers.random_prompt(30, toy_parts.VOCAB, 12)
+        ref = toy_parts.grid_reference(stored, ids)
+        rows = helpers.run_steps(engine, helpers.portions("g", ids, [8, 4, 12, 4, 2]))  # every start on the grid
+        check_logits(replay.stack_rows(rows, "g", 30), ref, "float32", "grid model in portions")
+        with pytest.raises(AssertionError, match="off the grid"):
+            helpers.run_steps(engine, helpers.portions("bad", ids, [5, 3]))
+        engine.finish("bad")
+
+        def greedy(prompt, steps):
+            out, seq = [], list(prompt)
+            for _ in range(steps):
+                out.append(int(toy_parts.grid_reference(stored, seq)[-1].argmax()))
+                seq.append(out[-1])
+            return out
+
+        prompts = [helpers.random_prompt(n, toy_parts.VOCAB, 20 + n) for n in (3, 13, 22, 9)]
+        # 16 tokens a step, portions of at most 10: cut to 8 beside decode rows; lengths 13 and 22 end off the grid
+        llm = LLM(engine, prefill_chunk=10)
+        assert llm.scheduler.config.portion_multiple == 4
+        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=6))
+        assert [o.token_ids for o in outs] == [greedy(p, 6) for p in prompts]
+        assert llm.scheduler.stats["steps"] > 6
+        engine.cache.check()
+        with pytest.raises(ValueError, match="could never advance"):
+            LLM(engine, prefill_chunk=3)
+    finally:
+        toy_parts.unregister()
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_a_head_size_that_is_no_multiple_of_16(tmp_path, backend):
+    """hidden 96 with 4 heads gives heads of 24: legal for the architecture, and run by the
+    general kernels in both compute types."""
+    doc = dict(helpers.TINY_B, num_attention_heads=4, num_key_value_heads=2)
+    tensors = helpers.make_folder(tmp_path, doc, 4)
+    toks = helpers.random_prompt(50, doc["vocab_size"], 8)
+    ref = plain_lfm2.plain_forward(doc, tensors, toks)
+    for dtype in dtypes(backend):
+        engine = helpers.make_engine(tmp_path, dtype, page_size=8, kv_cache_tokens=128, ctx=128, max_num_batched_tokens=64,
+                                     **backend_args(backend))
+        assert engine.config.head_dim == 24
+        steps = helpers.whole("w", toks) + helpers.portions("p", toks, [7, 1, 20, 2]) + helpers.tail_one_by_one("t", toks, 12)
+        rows = helpers.run_steps(engine, steps)
+        for name in "wpt":
+            check_logits(replay.stack_rows(rows, name, 50), ref, dtype, f"head size 24, {dtype}, {name}")
+
+
+@pytest.mark.gpu
+def test_more_decode_batch_sizes_than_captured_graphs_are_kept(tmp_path):
+    """Thirty requests that end one after the other: decode steps of 30, 29, .. 1 rows, more
+    sizes than the 24 graphs that are kept, then 30 rows again (its graph was dropped meanwhile
+    and is captured anew).  Logits stay those of the plain implementation throughout."""
+    doc, seed = helpers.TINY["A"]
+    tensors = helpers.make_folder(tmp_path, doc, seed)
+    count = 30
+    for dtype in ("float32", "bfloat16"):
+        engine = helpers.make_engine(tmp_path, dtype, page_size=16, ctx=64, max_num_seqs=count, max_num_batched_tokens=256)
+        assert engine.graphs is not None and engine.graphs.max_graphs < count
+        names = [f"r{i}" for i in range(count)]
+        tokens = {n: helpers.random_prompt(6 + count + 3, doc["vocab_size"], 300 + i) for i, n in enumerate(names)}
+        steps = [([(n, tokens[n][:6], [5]) for n in names], [])]
+        at = 6
+        for live in range(count, 0, -1):  # after a step of `live` rows the last of them ends
+            steps.append(([(n, [tokens[n][at]], [0]) for n in names[:live]], [names[live - 1]]))
+            at += 1
+        rows = helpers.run_steps(engine, steps)
+        assert len(engine.graphs._graphs) == engine.graphs.max_graphs and count not in engine.graphs._graphs
+        again = [f"s{i}" for i in range(count)]
+        steps = [([(n, tokens[f"r{i}"][:6], [5]) for i, n in enumerate(again)], []),
+                 ([(n, [tokens[f"r{i}"][6]], [0]) for i, n in enumerate(again)], again)]
+        rows.update(helpers.run_steps(engine, steps))
+        assert count in engine.graphs._graphs
+        for i, n in enumerate(names):
+            decoded = count - i  # request i took part in the steps of 30 .. i + 1 rows
+            ref = plain_lfm2.plain_forward(doc, tensors, tokens[n][: 6 + decoded])
+            places = sorted(rows[n])
+            assert places == list(range(5, 6 + decoded))
+            check_logits(torch.stack([rows[n][p] for p in places]), ref[5:], dtype, f"request {n} through {decoded} batch sizes, {dtype}")
+            check_logits(torch.stack([rows[f"s{i}"][p] for p in (5, 6)]), ref[5:7], dtype, f"request s{i} after the graph came back")
+        engine.cache.check()

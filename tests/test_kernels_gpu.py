@@ -29,10 +29,13 @@ def rnd(shape, dtype, seed, scale=1.0):
     return (torch.randn(shape, generator=g) * scale).to(dtype)
 
 
-def close(got, want, dtype, what, rel32=2e-6, scale=None):
+def close(got, want, dtype, what, rel32=2e-6, scale=None, slack=0.0):
+    """``slack`` is added to the relative bound (times the scale): the share of an error source
+    that grows with something else than the values, such as a rotation angle's rounding."""
     got, want = got.double().cpu(), want.double().cpu()
     s = scale if scale is not None else max(want.abs().max().item(), 1e-6)
     err = (got - want).abs().max().item()
+    rel32 = rel32 + slack
     # bfloat16: both sides round their result to bfloat16, so where the unrounded values
     # straddle a rounding boundary they differ by one unit in the last place, which is between
     # 2^-8 and 2^-7 of the value; one such unit at the largest value is the bound.
@@ -256,8 +259,11 @@ def test_norm_rope_store_then_attention(dtype, case):
     got_q = ops().qk_norm_rope_store(
         qkv.cuda(), heads, kv_heads, d, qw.cuda(), kw.cuda(), eps, inv_freq.cuda(), rot, gpu, kg, vg, table.cuda(), page, True
     )
-    close(got_q, want_q, dtype, "q after norm and rotation", rel32=4e-6)
-    close(kg, kc, dtype, "k cache", rel32=4e-6)
+    # the kernel multiplies position and frequency in float32: the angle is off by up to
+    # position * 2^-24 radians (the plain reference forms it in float64), and so is the rotated value
+    angle_slack = max(s + n for s, n in zip(starts, q_lens)) * 2.0 ** -24
+    close(got_q, want_q, dtype, "q after norm and rotation", rel32=4e-6, slack=angle_slack)
+    close(kg, kc, dtype, "k cache", rel32=4e-6, slack=angle_slack)
     assert torch.equal(vg.cpu(), vc), "values are stored raw"
     written = (kc != k0).flatten(1).any(1)
     assert torch.equal(kg.cpu()[~written], k0[~written]), "rows of other positions must not change"

@@ -117,7 +117,7 @@ def test_short_conv_part(dtype, taps, bias):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,head_dim", [(6, 2, 48), (5, 1, 16), (2, 2, 80)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(6, 2, 48), (5, 1, 16), (2, 2, 80), (4, 2, 24)])
 def test_attention_part(dtype, heads, kv_heads, head_dim):
     hidden = 96
 

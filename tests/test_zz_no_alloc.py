@@ -6,8 +6,10 @@ memory to a pool of their own, or they sit on a path where the device-wide synch
 cudaMalloc is not acceptable.  For them the partial results live in a fixed array inside the
 library.  The test runs the entry point twice in a row (the second call with other sizes, so
 it meets the first call's leftovers in the shared array) and compares each result with the
-ordinary entry point, which takes its scratch from the caller; and it checks that a call
-too large for the array is refused with a clear message and launches nothing.
+ordinary entry point, which takes its scratch from the caller, and with the plain attention
+of ``fake_kernels`` (the reference the ordinary entry point is itself tested against, so
+that the two entry points cannot be wrong together); and it checks that a call too large
+for the array is refused with a clear message and launches nothing.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run
 every other test.  It passes alone in a fresh process and after the other tests.
@@ -82,6 +84,15 @@ def agree(got, want):
     assert (got.float() - want.float()).abs().max().item() <= 2 ** -7 * scale
 
 
+def plain(p, window):
+    """The same attention by ``fake_kernels.paged_attention`` (float64 on the CPU)."""
+    import fake_kernels
+
+    step = SimpleNamespace(seq_of_token=p.seq.cpu(), positions=p.positions.cpu())
+    return fake_kernels.paged_attention(p.q.cpu(), p.heads, p.kv_heads, p.d, p.k.cpu(), p.v.cpu(), p.table.cpu(), p.page,
+                                        1.0 / math.sqrt(p.d), window, step)
+
+
 def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch():
     lib = load()
     first = problem(1, [700, 1, 16, 2100, 33], heads=8, kv_heads=2, d=64, page=16)
@@ -92,6 +103,7 @@ def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch():
         status, want = run(lib, p, splits, window, static=False)
         assert status == 0
         agree(got, want)
+        agree(got.cpu(), plain(p, window))
 
 
 def test_a_call_beyond_the_array_is_refused_and_launches_nothing():

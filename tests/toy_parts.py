@@ -6,6 +6,10 @@ framework's files.  They are not models of anything; each comes with a plain ref
 ``s_t = sigmoid(a) * s_{t-1} + x_t``, output ``W s_t``.
 ``routed_ff`` feed-forward: a router picks one of E small linear experts per token.
 ``rope_linear`` position encoding: a partial rotation with a linear frequency ladder.
+``narrow_value_attention`` mixer: one head whose values are narrower than its keys, cached in
+an element type of its own (what a latent-KV mixer asks of the cache manager).
+``decay_sum`` with ``grid``: the state is float64 and the mixer insists that every portion
+starts on a grid, as a recurrence evaluated in chunks of fixed length would.
 """
 
 from __future__ import annotations
@@ -14,7 +18,7 @@ import torch
 
 from shiso_llm_b200.parts import (
     FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, FeedForward, FixedState, LayerSpec, Mixer, ModelPlan,
-    PartSpec, PositionEncoding, RunEntry,
+    PagedKV, PartSpec, PositionEncoding, RunEntry,
 )
 from shiso_llm_b200.weights import VECTOR, TensorSpec
 
@@ -36,18 +40,65 @@ class DecaySum(Mixer):
         self.out = tensors[f"{self.prefix}.out.weight"]
 
     def cache_spec(self):
-        return FixedState((self.hidden,))
+        grid = self.spec.params.get("grid")
+        return FixedState((self.hidden,), torch.float64) if grid else FixedState((self.hidden,))
 
     def forward(self, x, step, cache):
-        a = torch.sigmoid(self.decay.float() * 50.0)
+        grid = self.spec.params.get("grid")
+        if grid:
+            assert cache.state.dtype == torch.float64
+            lens = [b - a for a, b in zip(step.h_q_start[:-1], step.h_q_start[1:])]
+            # single tokens take the recurrent form anywhere; a portion must start on the grid
+            assert all(p % grid == 0 for p, n in zip(step.h_start_pos, lens) if n > 1), \
+                f"a portion starts off the grid of {grid}: {step.h_start_pos}"
+        a = torch.sigmoid(self.decay.float() * 50.0).to(cache.state.dtype)
         rows = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         for i in range(step.num_seqs):
             s = cache.state[step.h_state_slots[i]].clone()
             for t in range(step.h_q_start[i], step.h_q_start[i + 1]):
-                s = a * s + x[t].float()
+                s = a * s + x[t].to(s.dtype)
                 rows[t] = s
             cache.state[step.h_state_slots[i]] = s
         return self.env.ops.linear(rows.to(x.dtype), self.out, self.env.dtype)
+
+
+class NarrowValueAttention(Mixer):
+    """One attention head with keys of ``k_dim`` and values of ``v_dim`` columns, cached in
+    float32 whatever the compute type: plain tensor code over the step's block table."""
+
+    graph_safe = False
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.k_dim, self.v_dim, self.prefix = p["hidden_size"], p["k_dim"], p["v_dim"], p["prefix"]
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.q.weight", (self.k_dim, self.hidden)), TensorSpec(f"{self.prefix}.k.weight", (self.k_dim, self.hidden)),
+                TensorSpec(f"{self.prefix}.v.weight", (self.v_dim, self.hidden)), TensorSpec(f"{self.prefix}.o.weight", (self.hidden, self.v_dim))]
+
+    def bind(self, tensors):
+        self.w = {n: tensors[f"{self.prefix}.{n}.weight"] for n in "qkvo"}
+
+    def cache_spec(self):
+        return PagedKV(1, self.k_dim, v_head_dim=self.v_dim, dtype=torch.float32)
+
+    def forward(self, x, step, cache):
+        ops, page = self.env.ops, cache.page_size
+        assert cache.k.shape[-1] == self.k_dim and cache.v.shape[-1] == self.v_dim and cache.k.dtype == torch.float32
+        q, k, v = (ops.linear(x, self.w[n], torch.float32) for n in "qkv")
+        table = step.block_tables[cache.group].long()
+        pos, seq = step.positions.long(), step.seq_of_token.long()
+        rows = table[seq, pos // page] * page + pos % page
+        keys, values = cache.k.view(-1, self.k_dim), cache.v.view(-1, self.v_dim)
+        keys[rows], values[rows] = k, v
+        out = torch.empty((x.shape[0], self.v_dim), dtype=torch.float32, device=x.device)
+        for t in range(x.shape[0]):
+            span = torch.arange(int(pos[t]) + 1, device=x.device)
+            seen = table[seq[t], span // page] * page + span % page
+            weights = torch.softmax(keys[seen].double() @ q[t].double() * 0.5, 0)
+            out[t] = (weights @ values[seen].double()).float()
+        return ops.linear(out.to(x.dtype), self.w["o"], self.env.dtype)
 
 
 class RoutedFF(FeedForward):
@@ -90,12 +141,14 @@ class RopeLinear(PositionEncoding):
 
 def register():
     MIXERS.register("decay_sum", DecaySum)
+    MIXERS.register("narrow_value_attention", NarrowValueAttention)
     FEED_FORWARDS.register("routed_ff", RoutedFF)
     POSITION_ENCODINGS.register("rope_linear", RopeLinear)
 
 
 def unregister():
     MIXERS.unregister("decay_sum")
+    MIXERS.unregister("narrow_value_attention")
     FEED_FORWARDS.unregister("routed_ff")
     POSITION_ENCODINGS.unregister("rope_linear")
 
@@ -198,4 +251,59 @@ def toy_reference(w, ids):
             h = x + attention(rms(x, "l1.n1.weight"), "l1.attn", False)
             x = h + routed(rms(h, "l1.n2.weight"))
     x = x + attention(rms(x, "l2.n1.weight"), "l2.attn", True)
+    return rms(x, "final.weight") @ w["emb.weight"].T
+
+
+GRID, K_DIM, V_DIM = 4, 12, 5
+
+
+def grid_plan() -> ModelPlan:
+    """Layer 0: decay_sum that insists on portions starting on a grid of 4 and keeps float64
+    state + SwiGLU.  Layer 1: an attention head with values narrower than keys in a float32
+    cache, no feed-forward.  The plan names the grid; the scheduler cuts prompts on it."""
+
+    def norm(name, size=HIDDEN):
+        return PartSpec("rmsnorm", {"tensor": name, "size": size, "eps": EPS})
+
+    layers = (
+        LayerSpec("l0", PartSpec("pre_norm"), PartSpec("decay_sum", {"hidden_size": HIDDEN, "prefix": "l0.mix", "grid": GRID}),
+                  norm("l0.n1.weight"),
+                  PartSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": 40, "gate": "l0.g.weight", "up": "l0.u.weight", "down": "l0.d.weight"}),
+                  norm("l0.n2.weight")),
+        LayerSpec("l1", PartSpec("pre_norm"),
+                  PartSpec("narrow_value_attention", {"hidden_size": HIDDEN, "k_dim": K_DIM, "v_dim": V_DIM, "prefix": "l1.attn"}),
+                  norm("l1.n1.weight"), None, None),
+    )
+    return ModelPlan(
+        architecture="ToyGridForCausalLM", hidden_size=HIDDEN, vocab_size=VOCAB,
+        embedding=PartSpec("token_embedding", {"tensor": "emb.weight", "vocab_size": VOCAB, "hidden_size": HIDDEN}),
+        layers=layers, order=(RunEntry(0), RunEntry(1)), final_norm=norm("final.weight"),
+        head=PartSpec("linear_head", {"vocab_size": VOCAB, "hidden_size": HIDDEN, "tied_to": "emb.weight", "tensor": None}),
+        portion_multiple=GRID,
+    )
+
+
+def grid_reference(w, ids):
+    """The grid model over one whole sequence in float64, no cache."""
+    w = {k: v.double() for k, v in w.items()}
+    T = len(ids)
+
+    def rms(x, name):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + EPS) * w[name]
+
+    x = w["emb.weight"][torch.as_tensor(ids)]
+    n = rms(x, "l0.n1.weight")
+    a = torch.sigmoid(w["l0.mix.decay"].float() * 50.0).double()
+    s, rows = torch.zeros(HIDDEN, dtype=torch.float64), []
+    for t in range(T):
+        s = a * s + n[t]
+        rows.append(s)
+    h = x + torch.stack(rows) @ w["l0.mix.out.weight"].T
+    n = rms(h, "l0.n2.weight")
+    g, u = n @ w["l0.g.weight"].T, n @ w["l0.u.weight"].T
+    x = h + (g / (1 + torch.exp(-g)) * u) @ w["l0.d.weight"].T
+    n = rms(x, "l1.n1.weight")
+    q, k, v = (n @ w[f"l1.attn.{m}.weight"].T for m in "qkv")
+    scores = (q @ k.T * 0.5).masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+    x = x + (torch.softmax(scores, -1) @ v) @ w["l1.attn.o.weight"].T
     return rms(x, "final.weight") @ w["emb.weight"].T
