@@ -11,9 +11,15 @@ token ids in, sampled ids out every step).  ``prefill`` is one 2,048-token promp
 requests' cache) to the measured HBM bandwidth; ``points`` holds batch 1 and 64.
 
 Protocol after the reference's bench crate (crates/shiso-bench/src/measure.rs:10-33,62-77;
-decode.rs:12-22): warm-up discarded, greedy sampling with end-of-sequence ignored so every
-run takes every step.  The model's weights (1.8 GB) are read every step and exceed the
-126 MB L2, so consecutive steps do not reuse cached inputs.
+decode.rs:12-22): one warm-up repetition is discarded, then seven repetitions are timed, each
+on fresh requests at the same context (prompts read again, W warm-up steps, then exactly K
+timed steps); the MEDIAN repetition is reported with the spread (slowest / fastest - 1), and a
+spread above 2 % is flagged, not hidden.  Sampling is greedy with end-of-sequence ignored so
+every run takes every step; the read-back of the tokens lies inside the end-to-end window.
+The model's weights (1.8 GB) are read every step and exceed the 126 MB L2, so consecutive
+steps do not reuse cached inputs.  ``points`` also carries the two serving workloads of the
+survey's table (350M shape: 64 concurrent requests; 2.6B shape: a long prompt in portions
+beside 32 decoding streams), unless ``--points`` leaves them out.
 """
 
 from __future__ import annotations
@@ -154,9 +160,23 @@ def prefill_flops(costs, config, tokens):
     return gemm + attention
 
 
-def run_workload(args, config, plan, full_layers) -> int:
+def load_preset(name, layers=None):
+    from shiso_llm_b200.cli import preset_path
+    from shiso_llm_b200.config import plan_from_document
+
+    with open(preset_path(name)) as f:
+        document = json.load(f)
+    full_layers = document["num_hidden_layers"]
+    if layers is not None and layers < full_layers:
+        document["layer_types"] = document["layer_types"][:layers]
+        document["num_hidden_layers"] = layers
+    _, config, plan = plan_from_document(document)
+    return config, plan, full_layers
+
+
+def run_workload(workload, preset, config, plan, full_layers) -> dict:
     """The two serving workloads beside the headline: whole requests through the scheduler and the
-    Python entry point, host token ids in and out, wall-clock time."""
+    Python entry point, host token ids in and out, wall-clock time.  Returns the record."""
     import torch
 
     from shiso_llm_b200 import LLM, SamplingParams
@@ -188,11 +208,11 @@ def run_workload(args, config, plan, full_layers) -> int:
 
     base = {
         "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "unit": "tok/s", "higher_is_better": True,
-        "config": {"model": f"{args.preset} (random weights)", "layers_run": config.num_hidden_layers,
+        "config": {"model": f"{preset} (random weights)", "layers_run": config.num_hidden_layers,
                    "layers_full": full_layers, "hidden_size": config.hidden_size,
                    "intermediate_size": config.intermediate_size, "page_size": 16},
     }
-    if args.workload == "serve":
+    if workload == "serve":
         count, new_tokens, chunk = 64, 128, 512
         lengths = torch.randint(16, 2049, (count,), generator=gen).tolist()
         options = EngineOptions(dtype="bfloat16", ctx=4096, page_size=16, kv_cache_tokens=count * (2048 + new_tokens + 64),
@@ -205,12 +225,12 @@ def run_workload(args, config, plan, full_layers) -> int:
             steps, seconds = drive(llm)
             llm.scheduler.take_finished()
         produced = count * new_tokens
-        print(json.dumps({**base, "metric": "generated tok/s, 64 concurrent requests, prompts 16..2048, 512-token portions, "
-                          "128 new tokens each (continuous batching through LLM.step)",
-                          "value": produced / seconds, "seconds": seconds, "steps": steps,
-                          "prompt_tokens": sum(lengths), "prompt_tok_s": sum(lengths) / seconds,
-                          "generated_tokens": produced, "preempted": llm.scheduler.stats["preempted"]}))
-        return 0
+        return {**base, "metric": "generated tok/s, 64 concurrent requests, prompts 16..2048, 512-token portions, "
+                "128 new tokens each (continuous batching through LLM.step)",
+                "value": produced / seconds, "seconds": seconds, "steps": steps,
+                "prompt_tokens": sum(lengths), "prompt_tok_s": sum(lengths) / seconds,
+                "generated_tokens": produced, "preempted": llm.scheduler.stats["preempted"],
+                "graph_steps": getattr(llm.engine, "graph_steps", None)}
     # mixed: 32 streams decode while one long prompt is read in portions; then 64 streams decode
     streams, long_prompt, chunk, new_tokens = 32, 8192, 1024, 256
     options = EngineOptions(dtype="bfloat16", ctx=8192 + 512, page_size=16,
@@ -240,10 +260,9 @@ def run_workload(args, config, plan, full_layers) -> int:
             llm.abort(rid)
         llm.drain()
         llm.scheduler.take_finished()
-    print(json.dumps({**base, "metric": "prompt tok/s of one 8,192-token prompt read in 1,024-token portions beside 32 "
-                      "decoding streams; then decode tok/s at batch 64 (through LLM.step)",
-                      "value": results["mixed"]["prompt_tok_s"], **results}))
-    return 0
+    return {**base, "metric": "prompt tok/s of one 8,192-token prompt read in 1,024-token portions beside 32 "
+            "decoding streams; then decode tok/s at batch 64 (through LLM.step)",
+            "value": results["mixed"]["prompt_tok_s"], **results}
 
 
 def main() -> int:
@@ -255,7 +274,9 @@ def main() -> int:
     parser.add_argument("--preset", default="lfm2-1.2b")
     parser.add_argument("--layers", type=int, default=None, help="run only the first N layers (recorded in config)")
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--points", default="1,64", help="other decode batch sizes to report")
+    parser.add_argument("--points", default="1,64,serve_350m,mixed_2p6b",
+                        help="what else to report: decode batch sizes, and the serving workloads serve_350m / mixed_2p6b; 'none' for nothing")
+    parser.add_argument("--reps", type=int, default=7, help="timed repetitions of the K-step block (after one that is discarded)")
     parser.add_argument("--no-cuda-graphs", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--workload", choices=["decode", "serve", "mixed"], default="decode",
@@ -284,30 +305,26 @@ def main() -> int:
     import torch
 
     from shiso_llm_b200 import LLM, SamplingParams
-    from shiso_llm_b200.cli import preset_path
-    from shiso_llm_b200.config import plan_from_document
     from shiso_llm_b200.engine import Engine, EngineOptions, StepEntry
     from shiso_llm_b200.engine.batch import MetaLayout
     from shiso_llm_b200.kernels import ops
     from shiso_llm_b200.parts import BuildEnv, Model
     from shiso_llm_b200.weights import random_device_tensors
 
-    with open(preset_path(args.preset)) as f:
-        document = json.load(f)
-    full_layers = document["num_hidden_layers"]
-    if args.layers is not None and args.layers < full_layers:
-        document["layer_types"] = document["layer_types"][: args.layers]
-        document["num_hidden_layers"] = args.layers
-    _, config, plan = plan_from_document(document)
-
+    config, plan, full_layers = load_preset(args.preset, args.layers)
     device = torch.device("cuda:0")
     if args.workload != "decode":
-        return run_workload(args, config, plan, full_layers)
-    batches = [args.batch] + [int(b) for b in args.points.split(",") if b.strip() and b.strip().lower() != "none"]
+        print(json.dumps(run_workload(args.workload, args.preset, config, plan, full_layers)))
+        return 0
+    names = [b.strip().lower() for b in args.points.split(",") if b.strip() and b.strip().lower() != "none"]
+    batches = [args.batch] + [int(b) for b in names if b.isdigit()]
     max_batch = max(batches)
-    budget = PROMPT_LEN + NEW_TOKENS + 64
+    reps = max(3, args.reps)
+    # a repetition's requests: prompt, warm-up steps, the end-to-end block and the device-timed block
+    budget = PROMPT_LEN + 2 * (args.steps + args.warmup) + 64
+    ctx = max(4096, -(-budget // 16) * 16)
     options = EngineOptions(
-        dtype="bfloat16", ctx=4096, page_size=16, kv_cache_tokens=max_batch * budget,
+        dtype="bfloat16", ctx=ctx, page_size=16, kv_cache_tokens=max(max_batch * budget, ctx),
         max_num_seqs=max_batch, max_num_batched_tokens=PROMPT_LEN, cuda_graphs=not args.no_cuda_graphs,
     )
     ops.require()
@@ -322,11 +339,11 @@ def main() -> int:
     def prompts(n):
         return [torch.randint(0, config.vocab_size, (PROMPT_LEN,), generator=gen).tolist() for _ in range(n)]
 
-    def measure_decode(batch: int, steps: int, warmup: int) -> dict:
-        """Batch ``batch`` decode over 2,048-token prompts: end to end through LLM.step, then
-        device-timed through Engine.step on the same requests."""
+    def one_repetition(batch: int, steps: int, warmup: int, profile: bool) -> dict:
+        """Fresh requests: prompts of 2,048 tokens, ``warmup`` decode steps, then ``steps`` steps end
+        to end through LLM.step and ``steps`` steps device-timed through Engine.step."""
         llm = LLM(engine)
-        params = SamplingParams(temperature=0.0, max_new_tokens=NEW_TOKENS, ignore_eos=True)
+        params = SamplingParams(temperature=0.0, max_new_tokens=steps + warmup + 8, ignore_eos=True)
         for p in prompts(batch):
             llm.add_request(p, params)
         # prompts are admitted one per step; run until every request is decoding
@@ -334,9 +351,8 @@ def main() -> int:
             llm.step()
         for _ in range(warmup):
             llm.step()
+        llm.drain()
         torch.cuda.synchronize()
-        clocks = ClockSampler()
-        clocks.start()
         t0 = time.perf_counter()
         for _ in range(steps):
             llm.step()
@@ -347,43 +363,60 @@ def main() -> int:
 
         # device-timed: the same requests, next tokens fed without waiting for the host
         requests = list(llm.scheduler.running)
-        tokens = [r.tokens[-1] for r in requests]
-        entries = [StepEntry(r.id, [t], [0]) for r, t in zip(requests, tokens)]
+        entries = [StepEntry(r.id, [r.tokens[-1]], [0]) for r in requests]
         for _ in range(3):
             ops.argmax(engine.step(entries))
         torch.cuda.synchronize()
         launches_before = ops.launch_count
         replays_before = engine.graphs.replays if engine.graphs else 0
+        first_context = sum(engine.cache.length(r.id) for r in requests) / batch
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if args.profiler_range == "decode" and batch == args.batch:
+        if profile:
             torch.cuda.cudart().cudaProfilerStart()
         start.record()
         for _ in range(steps):
             ops.argmax(engine.step(entries))
         end.record()
         torch.cuda.synchronize()
-        if args.profiler_range == "decode" and batch == args.batch:
+        if profile:
             torch.cuda.cudart().cudaProfilerStop()
+        ops.check_kernel_status()
         device_ms = start.elapsed_time(end)
-        clock_info = clocks.stop()
         launches = ops.launch_count - launches_before
         if engine.graphs:
             launches += (engine.graphs.replays - replays_before) * engine.graphs.launches(batch)
-        context = sum(engine.cache.length(r.id) for r in requests) / batch
+        context = first_context + (steps - 1) / 2.0  # the mean over the timed steps
         for r in requests:
             llm.abort(r.id)
+        llm.drain()
+        return {"device_ms": device_ms / steps, "e2e_ms": e2e_s / steps * 1e3, "launches": launches, "context": context}
+
+    def measure_decode(batch: int, steps: int, warmup: int, sampler=None) -> dict:
+        """The median of ``reps`` repetitions after one that is discarded."""
+        one_repetition(batch, steps, warmup, False)
+        if sampler is not None:
+            sampler.start()
+        runs = [one_repetition(batch, steps, warmup, args.profiler_range == "decode" and batch == args.batch and i == 0)
+                for i in range(reps)]
+        clock_info = sampler.stop() if sampler is not None else None
+        device = sorted(r["device_ms"] for r in runs)
+        e2e = sorted(r["e2e_ms"] for r in runs)
+        ms, e2e_ms = statistics.median(device), statistics.median(e2e)
+        context = runs[0]["context"]
         step_bytes = costs["weight_bytes"] + batch * (context * costs["kv_bytes_per_token"] + costs["state_bytes_per_request"])
-        ms = device_ms / steps
+        spread = device[-1] / device[0] - 1.0
         return {
-            "batch": batch, "tok_s": batch * steps / (device_ms / 1e3), "ms_per_step": ms,
-            "e2e_tok_s": batch * steps / e2e_s, "e2e_ms_per_step": e2e_s / steps * 1e3,
-            "launches": launches, "context": context, "clocks": clock_info,
-            "bytes": step_bytes, "gbs": step_bytes / (ms / 1e3) / 1e9,
+            "batch": batch, "tok_s": batch / (ms / 1e3), "ms_per_step": ms, "spread": spread,
+            "spread_over_2_percent": spread > 0.02, "repetitions": reps,
+            "e2e_tok_s": batch / (e2e_ms / 1e3), "e2e_ms_per_step": e2e_ms, "e2e_spread": e2e[-1] / e2e[0] - 1.0,
+            "launches": runs[0]["launches"], "context": context, "clocks": clock_info,
+            "bytes_per_step": step_bytes, "gbs": step_bytes / (ms / 1e3) / 1e9,
+            "frac": step_bytes / (ms / 1e3) / 1e9 / peak["hbm_gbs"],
             "h2d": 4 * MetaLayout(batch, batch, batch, len(engine.cache.groups), engine.cache.max_blocks).total,
-            "d2h": 4 * batch,
+            "d2h": 4 * (batch + 1),
         }
 
-    def measure_prefill(reps: int = 5, warmup: int = 3) -> dict:
+    def measure_prefill(reps: int = 11, warmup: int = 3) -> dict:
         times = []
         for i in range(warmup + reps):
             tokens = prompts(1)[0]
@@ -402,23 +435,48 @@ def main() -> int:
             engine.finish(request)
             if i >= warmup:
                 times.append(start.elapsed_time(end))
+        ops.check_kernel_status()
         ms = statistics.median(times)
         flops = prefill_flops(costs, config, PROMPT_LEN)
         return {
             "value": PROMPT_LEN / (ms / 1e3), "tokens": PROMPT_LEN, "ms": ms,
             "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12),
-            "tflops": flops / (ms / 1e3) / 1e12, "spread": max(times) / min(times) - 1.0,
+            "tflops": flops / (ms / 1e3) / 1e12, "spread": max(times) / min(times) - 1.0, "repetitions": reps,
         }
 
-    main_point = measure_decode(args.batch, args.steps, args.warmup)
-    points = {}
+    main_point = measure_decode(args.batch, args.steps, args.warmup, ClockSampler())
+    points, details = {}, {}
+
+    def detail(m):
+        return {k: m[k] for k in ("tok_s", "ms_per_step", "spread", "bytes_per_step", "gbs", "frac", "e2e_tok_s", "context")}
+
+    details[f"decode_b{args.batch}"] = detail(main_point)
     for b in batches[1:]:
         try:
-            points[f"decode_b{b}"] = measure_decode(b, args.steps, args.warmup)["tok_s"]
+            m = measure_decode(b, args.steps, args.warmup)
+            points[f"decode_b{b}"] = m["tok_s"]
+            points[f"decode_b{b}_frac"] = m["frac"]
+            details[f"decode_b{b}"] = detail(m)
         except Exception as e:  # a point that cannot run is reported, not hidden
             points[f"decode_b{b}"] = None
             points[f"decode_b{b}_error"] = f"{type(e).__name__}: {e}"[:200]
     prefill = None if args.skip_prefill else measure_prefill()
+
+    # the serving workloads of the other two shapes, each with a model of its own
+    del engine, tensors
+    torch.cuda.empty_cache()
+    for name, workload, preset in (("serve_350m", "serve", "lfm2-350m"), ("mixed_2p6b", "mixed", "lfm2-2.6b")):
+        if name not in names:
+            continue
+        try:
+            other_config, other_plan, other_layers = load_preset(preset)
+            record = run_workload(workload, preset, other_config, other_plan, other_layers)
+            points[name] = record["value"]
+            details[name] = {k: v for k, v in record.items() if k not in ("config", "impl", "n_gpus", "dtype", "data", "higher_is_better")}
+        except Exception as e:
+            points[name] = None
+            points[f"{name}_error"] = f"{type(e).__name__}: {e}"[:200]
+        torch.cuda.empty_cache()
 
     line = {
         "metric": "decode tok/s at batch 8 (LFM2-1.2B-shaped, bf16, 2048-token prompts)",
@@ -428,6 +486,8 @@ def main() -> int:
         "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": main_point["ms_per_step"],
+        "spread": main_point["spread"],
+        "repetitions": reps,
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
@@ -459,15 +519,17 @@ def main() -> int:
         "clocks": main_point["clocks"],
         "e2e": {
             "value": main_point["e2e_tok_s"], "unit": "tok/s", "ms_per_step": main_point["e2e_ms_per_step"],
+            "spread": main_point["e2e_spread"],
             "h2d_bytes_per_step": main_point["h2d"], "d2h_bytes_per_step": main_point["d2h"],
         },
         "gpu_launches": main_point["launches"],
         "prefill": prefill,
         "roofline": {
             "bound": "hbm", "achieved": main_point["gbs"], "peak": peak["hbm_gbs"], "unit": "GB/s",
-            "frac": main_point["gbs"] / peak["hbm_gbs"], "bytes_per_step": main_point["bytes"],
+            "frac": main_point["frac"], "bytes_per_step": main_point["bytes_per_step"],
         },
         "points": points,
+        "point_details": details,
     }
     print(json.dumps(line))
     return 0
