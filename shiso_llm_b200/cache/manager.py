@@ -79,13 +79,21 @@ class CacheManager:
         dtype: torch.dtype,
         device,
         max_blocks_per_request: Optional[int] = None,
+        scratch_tokens: int = 0,
     ):
+        """``scratch_tokens`` > 0 adds, behind the pool, pages for that many positions and one
+        state slot that no request ever holds (``scratch_pages``, ``scratch_slot``): the rows
+        with which a step is padded to a captured shape write there."""
         if page_size <= 0:
             raise ValueError(f"page size must be positive, got {page_size}")
         self.page_size = page_size
         self.dtype = dtype
         self.device = torch.device(device)
         self.needs = list(needs)
+        scratch_pages = -(-scratch_tokens // page_size) if scratch_tokens > 0 else 0
+        self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))
+        self.scratch_slot = num_slots if scratch_tokens > 0 else None
+        buffer_pages = num_pages + scratch_pages
         self.groups: list[_Group] = []
         self._views: list = [None] * len(needs)
         by_window: dict = {}
@@ -100,8 +108,8 @@ class CacheManager:
                 group = by_window[need.window]
                 kv_dtype = need.dtype if need.dtype is not None else dtype
                 self._views[pos] = PagedKVView(
-                    k=torch.zeros((num_pages, page_size, need.num_kv_heads, need.head_dim), dtype=kv_dtype, device=self.device),
-                    v=torch.zeros((num_pages, page_size, need.num_kv_heads, need.value_dim), dtype=kv_dtype, device=self.device),
+                    k=torch.zeros((buffer_pages, page_size, need.num_kv_heads, need.head_dim), dtype=kv_dtype, device=self.device),
+                    v=torch.zeros((buffer_pages, page_size, need.num_kv_heads, need.value_dim), dtype=kv_dtype, device=self.device),
                     page_size=page_size,
                     group=group.index,
                     kv_heads=need.num_kv_heads,
@@ -119,7 +127,7 @@ class CacheManager:
         self.bytes_per_slot = total
         self.slots = SlotPool(num_slots)
         self.num_slots = num_slots
-        self.state = torch.zeros((num_slots, max(total, 16)), dtype=torch.uint8, device=self.device)
+        self.state = torch.zeros((num_slots + (1 if scratch_tokens > 0 else 0), max(total, 16)), dtype=torch.uint8, device=self.device)
         for pos, off in offsets.items():
             need = needs[pos]
             view = self.state[:, off : off + need.nbytes].view(need.dtype).unflatten(1, need.shape)

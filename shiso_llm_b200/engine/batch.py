@@ -109,8 +109,16 @@ class StepBuilder:
     def _iota(self, n: int) -> np.ndarray:
         return self._arange[:n]
 
-    def build(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepMeta:
-        """``starts[i]`` = positions the cache held for entry ``i`` before this step."""
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], pad=None) -> StepMeta:
+        """``starts[i]`` = positions the cache held for entry ``i`` before this step.
+
+        ``pad = (tokens, sequences, wanted)`` fills the step up to a captured shape: behind the
+        entries come made-up sequences (token 0 from position 0) that read and write only the
+        cache manager's scratch pages and scratch slot, all but the last of one row; wanted rows
+        are filled up with row 0.  The entries' rows, sequences and wanted rows keep their
+        places, so the first ``sum(len(e.want))`` rows of the logits are theirs."""
+        if pad is not None:
+            return self._build_padded(entries, starts, pad)
         num_seqs = len(entries)
         lens = [len(e.tokens) for e in entries]
         num_tokens = sum(lens)
@@ -215,5 +223,104 @@ class StepBuilder:
             h_q_start=q_start.tolist(),
             h_start_pos=list(starts),
             h_state_slots=slots,
+            requests=requests,
+        )
+
+    def _build_padded(self, entries, starts, pad) -> StepMeta:
+        pad_tokens, pad_seqs, pad_wanted = pad
+        cache = self.cache
+        if self.fixed_width is None or cache.scratch_slot is None:
+            raise RuntimeError("a padded step needs a builder with a fixed table width and a cache with scratch pages")
+        real_seqs = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        real_tokens = sum(lens)
+        real_wanted = sum(len(e.want) for e in entries)
+        made_up = pad_seqs - real_seqs
+        spare = pad_tokens - real_tokens
+        if made_up < 1 or spare < made_up or pad_wanted < real_wanted or pad_tokens > self.max_tokens or pad_seqs > self.max_seqs:
+            raise ValueError(f"a step of {real_tokens} tokens in {real_seqs} sequences does not fit the shape {pad}")
+        last = spare - (made_up - 1)  # rows of the last made-up sequence
+        if last > len(cache.scratch_pages) * cache.page_size:
+            raise ValueError(f"{last} padding rows in one sequence exceed the cache's scratch pages")
+        lens = lens + [1] * (made_up - 1) + [last]
+        starts = list(starts) + [0] * made_up
+        width = self.fixed_width
+        lay = MetaLayout(pad_tokens, pad_seqs, pad_wanted, self.num_groups, width)
+
+        turn = self._turn
+        self._turn ^= 1
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        stage = self._staging[turn]
+        host = stage.numpy()
+        requests = [e.request for e in entries]
+        slots = [cache.slot_of(r) for r in requests] + [cache.scratch_slot] * made_up
+        host[lay.start_pos : lay.start_pos + pad_seqs] = starts
+        host[lay.state_slots : lay.state_slots + pad_seqs] = slots
+        q_start = np.zeros(pad_seqs + 1, dtype=np.int32)
+        np.cumsum(lens, out=q_start[1:])
+        host[lay.q_start : lay.q_start + pad_seqs + 1] = q_start
+        host[lay.token_ids + real_tokens : lay.token_ids + pad_tokens] = 0
+        host[lay.feed_index : lay.feed_index + pad_tokens] = -1
+        want_at = lay.want_rows
+        for i in range(pad_seqs):
+            a, b = int(q_start[i]), int(q_start[i + 1])
+            host[lay.positions + a : lay.positions + b] = np.arange(starts[i], starts[i] + lens[i], dtype=np.int32)
+            host[lay.seq_of_token + a : lay.seq_of_token + b] = i
+            if i >= real_seqs:
+                continue
+            e = entries[i]
+            host[lay.token_ids + a : lay.token_ids + b] = e.tokens
+            if e.feed is not None:
+                if lens[i] != 1:
+                    raise ValueError(f"request {e.request!r}: only a single token can be fed from the device")
+                host[lay.feed_index + a] = e.feed
+            for w in e.want:
+                if not 0 <= w < lens[i]:
+                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {lens[i]} tokens")
+                host[want_at] = a + w
+                want_at += 1
+        host[want_at : lay.want_rows + pad_wanted] = 0
+        scratch = np.resize(np.asarray(cache.scratch_pages, dtype=np.int32), width)
+        for g in range(self.num_groups):
+            at = lay.tables + g * lay.table_elems
+            tables = host[at : at + pad_seqs * width].reshape(pad_seqs, width)
+            cache.fill_block_tables(requests, g, tables[:real_seqs])
+            tables[real_seqs:] = scratch
+
+        dev = self.device_block
+        dev[: lay.total].copy_(stage[: lay.total], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[turn] = ev
+
+        def part(at, n):
+            return dev[at : at + n]
+
+        return StepMeta(
+            num_tokens=pad_tokens,
+            num_seqs=pad_seqs,
+            num_wanted=pad_wanted,
+            token_ids=part(lay.token_ids, pad_tokens),
+            positions=part(lay.positions, pad_tokens),
+            seq_of_token=part(lay.seq_of_token, pad_tokens),
+            q_start=part(lay.q_start, pad_seqs + 1),
+            start_pos=part(lay.start_pos, pad_seqs),
+            state_slots=part(lay.state_slots, pad_seqs),
+            want_rows=part(lay.want_rows, pad_wanted),
+            block_tables=[
+                part(lay.tables + g * lay.table_elems, pad_seqs * width).view(pad_seqs, width)
+                for g in range(self.num_groups)
+            ],
+            max_q_len=max(lens),
+            max_context=max(s + n for s, n in zip(starts, lens)),
+            all_decode=False,
+            wants_every_row=False,
+            feed_index=part(lay.feed_index, pad_tokens) if self.fed_tokens is not None else None,
+            fed_tokens=self.fed_tokens,
+            h_q_start=[],  # a captured step sizes its launches by capacity, not by this step's lengths
+            h_start_pos=[],
+            h_state_slots=[],
             requests=requests,
         )

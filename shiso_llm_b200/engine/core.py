@@ -30,6 +30,7 @@ from ..parts.base import BuildEnv
 from ..parts.model import Model
 from ..weights.loader import load_weights
 from .batch import StepBuilder, StepEntry
+from .graphs import NOT_RUN
 
 _DTYPES = {
     "bfloat16": torch.bfloat16,
@@ -71,7 +72,8 @@ class EngineOptions:
     max_num_seqs: int = 4
     max_num_batched_tokens: int = 2048
     device: str = "cuda:0"
-    cuda_graphs: bool = True  # replay captured graphs for steps of single decoded tokens
+    cuda_graphs: bool = True  # replay captured graphs: decode steps by batch size, mixed steps by padded shape
+    graph_mixed_steps: bool = True  # with cuda_graphs: also capture steps that hold prompt portions
     allow_small_pool: bool = False
     dump_layers: int = 0  # 1: a line of residual statistics per run entry; 2: per mixer and feed-forward too
 
@@ -158,6 +160,7 @@ class Engine:
         self.builder.fed_tokens = self.fed_tokens
         self.steps_run = 0
         self.graphs = None
+        self.step_graphs = None
         level = options.dump_layers or int(os.environ.get("SHISO_LAYER_DUMP", "0") or 0)
         self.layer_hook = self.add_hook = None  # diagnostics; a step with a hook is never captured
         if level:
@@ -170,6 +173,16 @@ class Engine:
             )
             decode_builder.fed_tokens = self.fed_tokens
             self.graphs = DecodeGraphs(model, cache, decode_builder)
+            if options.graph_mixed_steps and cache.scratch_slot is not None:
+                from .graphs import StepGraphs, sequence_bucket, token_bucket
+
+                most_seqs = sequence_bucket(options.max_num_seqs + 1)
+                padded_builder = StepBuilder(
+                    cache, self.device, token_bucket(options.max_num_batched_tokens + most_seqs), most_seqs,
+                    fixed_table_width=cache.max_blocks,
+                )
+                padded_builder.fed_tokens = self.fed_tokens
+                self.step_graphs = StepGraphs(model, cache, padded_builder)
 
     def enable_layer_dump(self, level: int = 1, out=None) -> None:
         """Prints a line of statistics of the residual stream (count, rms, largest magnitude,
@@ -198,7 +211,7 @@ class Engine:
         """Runs a two-token request through a prompt step and a decode step and drops it, so
         that every kernel has been loaded before the first graph capture."""
         probe = ("__warm_up__",)
-        graphs, self.graphs = self.graphs, None
+        graphs, self.graphs = self.graphs, None  # (without decode graphs no step is captured)
         try:
             self.step([StepEntry(probe, [0], [])])
             self.step([StepEntry(probe, [0], [0])])
@@ -264,6 +277,8 @@ class Engine:
             dtype,
             device,
             max_blocks_per_request=min(blocks_per_request, num_pages),
+            # rows that pad a step to a captured shape live on pages and a slot of their own
+            scratch_tokens=64 if options.cuda_graphs and options.graph_mixed_steps else 0,
         )
         engine = cls(model, cache, options)
         if engine.graphs is not None:
@@ -321,12 +336,14 @@ class Engine:
             for e in entries:
                 starts.append(self.cache.append(e.request, len(e.tokens)))
                 claimed.append(e.request)
-            if (
-                self.graphs is not None and not hooked
-                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-            ):
-                logits = self.graphs.run(entries, starts)
-            else:
+            ran = False
+            if self.graphs is not None and not hooked:
+                if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+                    logits, ran = self.graphs.run(entries, starts), True
+                elif self.step_graphs is not None:
+                    logits = self.step_graphs.run(entries, starts)
+                    ran = logits is not NOT_RUN
+            if not ran:
                 meta = self.builder.build(entries, starts)
                 if hooked:
                     logits = self.model.forward(meta, self.cache, self.layer_hook, self.add_hook)

@@ -365,3 +365,75 @@ def test_more_decode_batch_sizes_than_captured_graphs_are_kept(tmp_path):
             check_logits(torch.stack([rows[n][p] for p in places]), ref[5:], dtype, f"request {n} through {decoded} batch sizes, {dtype}")
             check_logits(torch.stack([rows[f"s{i}"][p] for p in (5, 6)]), ref[5:7], dtype, f"request s{i} after the graph came back")
         engine.cache.check()
+
+
+def test_a_padded_step_leaves_the_entries_rows_as_they_are(tmp_path):
+    """The padding of a captured shape - made-up sequences on scratch pages and a scratch slot,
+    wanted rows filled up - changes nothing for the step's own rows, sequences and state: the
+    same trace through padded steps and through plain steps gives the same logits, with the
+    plain stand-in kernels on the CPU."""
+    from shiso_llm_b200.engine.batch import StepBuilder
+    from shiso_llm_b200.engine.graphs import sequence_bucket, token_bucket
+
+    doc, seed = helpers.TINY["B"]
+    tensors = helpers.make_folder(tmp_path, doc, seed)
+    requests = {f"r{i}": helpers.random_prompt(n, doc["vocab_size"], 40 + i) for i, n in enumerate((37, 21, 9, 50))}
+    reference = {rid: plain_lfm2.plain_forward(doc, tensors, toks) for rid, toks in requests.items()}
+    engine = helpers.make_engine(tmp_path, "float32", ops=fake_kernels, page_size=4, kv_cache_tokens=256, ctx=64,
+                                 max_num_seqs=4, max_num_batched_tokens=64)
+    assert engine.cache.scratch_slot == 4 and len(engine.cache.scratch_pages) == 16
+    builder = StepBuilder(engine.cache, "cpu", 128, 8, fixed_table_width=engine.cache.max_blocks)
+    rows, consumed = {}, {}
+    for entries, end in replay.mixed_trace(requests, 7, 256):
+        batch = [StepEntry(r, t, w[-1:]) for r, t, w in entries]  # at most one wanted row per sequence
+        seqs = sequence_bucket(len(batch) + 1)
+        shape = (token_bucket(sum(len(e.tokens) for e in batch) + seqs - len(batch)), seqs, seqs)
+        starts = [engine.cache.append(e.request, len(e.tokens)) for e in batch]
+        meta = builder.build(batch, starts, pad=shape)
+        assert (meta.num_tokens, meta.num_seqs, meta.num_wanted) == shape and not meta.h_q_start
+        logits = engine.model.forward(meta, engine.cache)
+        at = 0
+        for e in batch:
+            engine.cache.commit(e.request)
+            base = consumed.get(e.request, 0)
+            for w in e.want:
+                rows.setdefault(e.request, {})[base + w] = logits[at].clone()
+                at += 1
+            consumed[e.request] = base + len(e.tokens)
+        for r in end:
+            engine.finish(r)
+        engine.cache.check()
+    for rid, toks in requests.items():
+        places = sorted(rows[rid])
+        assert len(places) > 5
+        check_logits(torch.stack([rows[rid][p] for p in places]), reference[rid][places], "float32", f"padded steps, {rid}")
+    assert engine.cache.free_pages() == [64] and engine.cache.slots.free_slots == 4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_steps_replayed_from_captured_graphs(tmp_path, dtype):
+    """The same mixed trace twice under other names: every shape of the first pass that comes
+    again is captured and replayed (portions beside decoded tokens, padded to the shape), pages
+    and slots are reused between the passes, and every logits row is the plain implementation's."""
+    doc, seed = helpers.TINY["B"]
+    tensors = helpers.make_folder(tmp_path, doc, seed)
+    lengths = [70, 40, 7, 33, 90, 64]
+    requests = {f"r{i}": helpers.random_prompt(n, doc["vocab_size"], 60 + i) for i, n in enumerate(lengths)}
+    reference = {rid: plain_lfm2.plain_forward(doc, tensors, toks) for rid, toks in requests.items()}
+    engine = helpers.make_engine(tmp_path, dtype, page_size=16, kv_cache_tokens=320, ctx=128, max_num_seqs=4,
+                                 max_num_batched_tokens=64)
+    assert engine.step_graphs is not None
+    for round_ in range(3):
+        trace = replay.mixed_trace({f"{round_}-{k}": v for k, v in requests.items()}, 5, 320, portion_sizes=(2, 3, 16, 31, 13))
+        trace = [([(r, t, w[-1:]) for r, t, w in entries], end) for entries, end in trace]
+        rows = helpers.run_steps(engine, trace)
+        for rid, toks in requests.items():
+            places = sorted(rows[f"{round_}-{rid}"])
+            got = torch.stack([rows[f"{round_}-{rid}"][p] for p in places])
+            check_logits(got, reference[rid][places], dtype, f"round {round_} {dtype} {rid}")
+    from shiso_llm_b200.kernels import ops
+
+    ops.check_kernel_status()
+    assert engine.step_graphs.captures >= 3 and engine.step_graphs.replays > 20
+    engine.cache.check()
