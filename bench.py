@@ -174,6 +174,13 @@ def load_preset(name, layers=None):
     return config, plan, full_layers
 
 
+def graph_replays(engine) -> dict:
+    return {"decode": engine.graphs.replays if engine.graphs else 0,
+            "mixed": engine.step_graphs.replays if engine.step_graphs else 0,
+            "mixed_shapes_captured": engine.step_graphs.captures if engine.step_graphs else 0,
+            "steps": engine.steps_run}
+
+
 def run_workload(workload, preset, config, plan, full_layers) -> dict:
     """The two serving workloads beside the headline: whole requests through the scheduler and the
     Python entry point, host token ids in and out, wall-clock time.  Returns the record."""
@@ -219,7 +226,7 @@ def run_workload(workload, preset, config, plan, full_layers) -> dict:
                                 max_num_seqs=count, max_num_batched_tokens=chunk + count)
         llm = LLM(Engine.from_plan(plan, tensors, options), prefill_chunk=chunk)
         params = SamplingParams(temperature=0.0, max_new_tokens=new_tokens, ignore_eos=True)
-        for rep in range(2):  # the first pass warms up (graph captures, tensor maps); the second is timed
+        for rep in range(3):  # two passes warm up (a step's shape is captured when it comes again); the third is timed
             for n in lengths:
                 llm.add_request(prompt(n), params)
             steps, seconds = drive(llm)
@@ -230,7 +237,7 @@ def run_workload(workload, preset, config, plan, full_layers) -> dict:
                 "value": produced / seconds, "seconds": seconds, "steps": steps,
                 "prompt_tokens": sum(lengths), "prompt_tok_s": sum(lengths) / seconds,
                 "generated_tokens": produced, "preempted": llm.scheduler.stats["preempted"],
-                "graph_steps": getattr(llm.engine, "graph_steps", None)}
+                "graph_replays": graph_replays(llm.engine)}
     # mixed: 32 streams decode while one long prompt is read in portions; then 64 streams decode
     streams, long_prompt, chunk, new_tokens = 32, 8192, 1024, 256
     options = EngineOptions(dtype="bfloat16", ctx=8192 + 512, page_size=16,
@@ -239,7 +246,7 @@ def run_workload(workload, preset, config, plan, full_layers) -> dict:
     llm = LLM(Engine.from_plan(plan, tensors, options), prefill_chunk=chunk)
     params = SamplingParams(temperature=0.0, max_new_tokens=4096, ignore_eos=True)
     results = {}
-    for rep in range(2):
+    for rep in range(3):
         ids = [llm.add_request(prompt(1024), params).id for _ in range(streams)]
         drive(llm, until=lambda: all(r.decoding for r in llm.scheduler.running) and not llm.scheduler.waiting)
         long_request = llm.add_request(prompt(long_prompt), SamplingParams(temperature=0.0, max_new_tokens=1, ignore_eos=True))
@@ -262,7 +269,7 @@ def run_workload(workload, preset, config, plan, full_layers) -> dict:
         llm.scheduler.take_finished()
     return {**base, "metric": "prompt tok/s of one 8,192-token prompt read in 1,024-token portions beside 32 "
             "decoding streams; then decode tok/s at batch 64 (through LLM.step)",
-            "value": results["mixed"]["prompt_tok_s"], **results}
+            "value": results["mixed"]["prompt_tok_s"], **results, "graph_replays": graph_replays(llm.engine)}
 
 
 def main() -> int:

@@ -229,6 +229,9 @@ class StepBuilder:
     def _build_padded(self, entries, starts, pad) -> StepMeta:
         pad_tokens, pad_seqs, pad_wanted = pad
         cache = self.cache
+        # a step of single tokens that all want their row stays one when every made-up sequence
+        # brings one row too: the kernels for such steps serve it
+        decode = pad_tokens == pad_seqs == pad_wanted and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         if self.fixed_width is None or cache.scratch_slot is None:
             raise RuntimeError("a padded step needs a builder with a fixed table width and a cache with scratch pages")
         real_seqs = len(entries)
@@ -280,7 +283,10 @@ class StepBuilder:
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {lens[i]} tokens")
                 host[want_at] = a + w
                 want_at += 1
-        host[want_at : lay.want_rows + pad_wanted] = 0
+        if decode:
+            host[lay.want_rows : lay.want_rows + pad_wanted] = self._iota(pad_wanted) if pad_wanted <= len(self._arange) else np.arange(pad_wanted)
+        else:
+            host[want_at : lay.want_rows + pad_wanted] = 0
         scratch = np.resize(np.asarray(cache.scratch_pages, dtype=np.int32), width)
         for g in range(self.num_groups):
             at = lay.tables + g * lay.table_elems
@@ -315,8 +321,8 @@ class StepBuilder:
             ],
             max_q_len=max(lens),
             max_context=max(s + n for s, n in zip(starts, lens)),
-            all_decode=False,
-            wants_every_row=False,
+            all_decode=decode,
+            wants_every_row=decode,
             feed_index=part(lay.feed_index, pad_tokens) if self.fed_tokens is not None else None,
             fed_tokens=self.fed_tokens,
             h_q_start=[],  # a captured step sizes its launches by capacity, not by this step's lengths

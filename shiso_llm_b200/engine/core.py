@@ -166,11 +166,10 @@ class Engine:
         if level:
             self.enable_layer_dump(level)
         if options.cuda_graphs and self.device.type == "cuda" and model.graph_safe:
-            from .graphs import DecodeGraphs
+            from .graphs import DecodeGraphs, decode_bucket
 
-            decode_builder = StepBuilder(
-                cache, self.device, options.max_num_seqs, options.max_num_seqs, fixed_table_width=cache.max_blocks
-            )
+            most = decode_bucket(options.max_num_seqs) if cache.scratch_slot is not None else options.max_num_seqs
+            decode_builder = StepBuilder(cache, self.device, most, most, fixed_table_width=cache.max_blocks)
             decode_builder.fed_tokens = self.fed_tokens
             self.graphs = DecodeGraphs(model, cache, decode_builder)
             if options.graph_mixed_steps and cache.scratch_slot is not None:

@@ -20,21 +20,39 @@ from collections import OrderedDict
 import torch
 
 
+def decode_bucket(seqs: int) -> int:
+    """The captured batch size a decode step of ``seqs`` rows runs as: itself up to 8 rows (the
+    products for a handful of rows are kernels of their own), then the next multiple of 8, from
+    64 on of 16.  A workload that drains walks through a dozen graphs instead of one per size."""
+    if seqs <= 8:
+        return seqs
+    if seqs <= 64:
+        return -(-seqs // 8) * 8
+    return -(-seqs // 16) * 16
+
+
 class DecodeGraphs:
     def __init__(self, model, cache, builder, max_graphs: int = 24):
         self.model = model
         self.cache = cache
         self.builder = builder  # a StepBuilder with a fixed table width
         self.max_graphs = max_graphs
-        self._graphs: OrderedDict = OrderedDict()  # num_seqs -> (graph, logits)
+        self._graphs: OrderedDict = OrderedDict()  # captured batch size -> (graph, logits)
         self.replays = 0
         self.launches_per_graph: dict = {}
 
     def run(self, entries, starts):
         """Uploads the step's metadata and replays (capturing first if needed) the graph for
-        this many sequences.  Every entry wants its one row.  Returns logits [S, vocab]."""
-        meta = self.builder.build(entries, starts)
-        key = meta.num_seqs
+        this many sequences, or for the next captured size with made-up rows on the cache's
+        scratch page behind the step's own.  Every entry wants its one row.  Returns logits
+        [S, vocab]."""
+        seqs = len(entries)
+        key = decode_bucket(seqs)
+        if key == seqs or key > self.builder.max_seqs or self.cache.scratch_slot is None:
+            key = seqs
+            meta = self.builder.build(entries, starts)
+        else:
+            meta = self.builder.build(entries, starts, pad=(key, key, key))
         held = self._graphs.get(key)
         if held is None:
             held = self._capture(meta)
@@ -46,7 +64,7 @@ class DecodeGraphs:
         graph, logits = held
         graph.replay()
         self.replays += 1
-        return logits
+        return logits if key == seqs else logits[:seqs]
 
     def _capture(self, meta):
         ops = self.model.env.ops
@@ -59,7 +77,7 @@ class DecodeGraphs:
         return graph, logits
 
     def launches(self, num_seqs: int) -> int:
-        return self.launches_per_graph.get(num_seqs, 0)
+        return self.launches_per_graph.get(decode_bucket(num_seqs), self.launches_per_graph.get(num_seqs, 0))
 
 
 NOT_RUN = object()  # StepGraphs.run: the caller runs the step kernel by kernel
