@@ -44,11 +44,116 @@
 //
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the kernel
 // carries on (its result is then wrong, and the host raises when it reads the word).
-#include "gemm_stream.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
-using namespace stream;
+using tc::mbar_arrive;
+using tc::mbar_expect_tx;
+using tc::mbar_init;
+using tc::mbar_wait;
+using tc::smem_u32;
+
+constexpr int KC = 1024;                       // columns per stage
+constexpr int ROWS = 16;                       // weight rows per tile
+constexpr int ROW_BYTES = KC * 2 + 16;         // padded row of a stage
+constexpr int STAGE_BYTES = ROWS * ROW_BYTES;  // 33,024
+constexpr int STAGES = 3;                      // two CTAs (this kernel's and its successor's) must fit an SM
+constexpr int CONSUMERS = 4;                   // warps; each takes 256 columns of a chunk
+constexpr int KB = KC / CONSUMERS / 64;        // 64-wide k blocks per warp and chunk
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int PARTIAL_STRIDE = 16;             // tokens per row of the partials table
+constexpr int EARLY_PARTIALS = 8;
+
+enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_CONV = 2 };
+constexpr int CONV_CHANNELS = 5;  // channels of a CONV tile: their B, C and x rows are 15 of its 16 rows
+constexpr int CONV_MAX_TAPS = 4;
+
+struct StreamArgs {
+    const __nv_bfloat16* x;  // [T, K]
+    const __nv_bfloat16* w;  // [N, K]
+    const float* bias;       // [N] or null (plain products only)
+    void* y;                 // plain [T, N]; GLU [T, inter]
+    int T, N, K, inter, out_f32, mode;
+    int tiles;               // 16-row tiles (GLU: 8 gate + 8 up rows)
+    int* status;
+    // STREAM epilogue
+    const float* res_in;
+    float* res_out;
+    const float* next_norm_w;
+    __nv_bfloat16* x_out;
+    float* partials_out;     // [tiles, PARTIAL_STRIDE]
+    // SCALED epilogue
+    const float* partials_in;
+    int partial_count, norm_k;
+    float eps;
+    // CONV epilogue: w is a short convolution's input projection [3 * hidden, K] (rows B, C, x) and
+    // every sequence brings one row; y[t, ch] = C * (sum_j conv_w[ch][j] * window_j + conv_bias[ch])
+    // where the window is the sequence's last taps - 1 gated inputs B * x followed by this row's,
+    // and the state moves on by one row.  B, C and x are rounded to bfloat16 first, as a product
+    // that stores them would.
+    const float* conv_w;        // [hidden, conv_taps]
+    const float* conv_bias;     // [hidden] or null
+    float* conv_state;          // [slots][conv_taps - 1][hidden], conv_slot_stride floats between slots
+    long long conv_slot_stride;
+    const int* conv_seq_of_token;  // [T]
+    const int* conv_slots;         // [sequences]
+    int conv_taps, hidden;
+};
+
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Activations were written by a predecessor grid: coherent loads, after the dependency wait.
+__device__ __forceinline__ uint4 load_activation16(const __nv_bfloat16* p, bool valid) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) {
+        asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    }
+    return v;
+}
+
+__device__ __forceinline__ float load_stream1(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void consumer_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+}
+
+// Row of W behind row r (0..15) of a tile, or -1.
+template <bool CONV>
+__device__ __forceinline__ int tile_row(const StreamArgs& a, int tile, int r) {
+    if constexpr (CONV) {
+        const int ch = tile * CONV_CHANNELS + r % CONV_CHANNELS;
+        return (r < 3 * CONV_CHANNELS && ch < a.hidden) ? (r / CONV_CHANNELS) * a.hidden + ch : -1;
+    }
+    if (a.mode == MODE_GLU) {
+        const int f = tile * 8 + (r & 7);
+        return f < a.inter ? (r < 8 ? f : a.inter + f) : -1;
+    }
+    const int row = tile * ROWS + r;
+    return row < a.N ? row : -1;
+}
 
 // HELD: the chunks of K whose activations a lane keeps in registers for the whole kernel (K <= HELD *
 // KC); they are the same for every tile, and a reload per chunk would put an L2 round trip into
@@ -407,7 +512,9 @@ int launch_as(const StreamArgs& a, int sm_count, cudaStream_t stream) {
     return launch_status();
 }
 
-int launch_now(const StreamArgs& a, int sm_count, cudaStream_t stream) {
+int launch_stream(StreamArgs& a, int sm_count, cudaStream_t stream) {
+    a.tiles = a.mode == MODE_GLU ? (a.inter + 7) / 8 : a.mode == MODE_CONV ? (a.hidden + CONV_CHANNELS - 1) / CONV_CHANNELS : (a.N + ROWS - 1) / ROWS;
+    a.status = shiso_tc_status_word();
     const int chunks = (a.K + KC - 1) / KC;
     // NT = 1: one 8-token tile per weight fragment.  With two (9..16 rows) the held activations
     // took the registers of a second CTA per SM, and a decode step at batch 16 ran at 17.9k
@@ -423,18 +530,7 @@ int launch_now(const StreamArgs& a, int sm_count, cudaStream_t stream) {
     return launch_as<1, 0, false>(a, sm_count, stream);
 }
 
-// Completes the arguments; then the product joins the chain that is being collected, if one is
-// open (gemm_stream_chain.cu), or is launched as a kernel of its own.
-int launch_stream(StreamArgs& a, int sm_count, cudaStream_t stream) {
-    a.tiles = a.mode == MODE_GLU ? (a.inter + 7) / 8 : a.mode == MODE_CONV ? (a.hidden + CONV_CHANNELS - 1) / CONV_CHANNELS : (a.N + ROWS - 1) / ROWS;
-    a.status = shiso_tc_status_word();
-    if (shiso_chain_collect(a, stream)) return SHISO_OK;
-    return launch_now(a, sm_count, stream);
-}
-
 }  // namespace
-
-int shiso_stream_launch_one(const stream::StreamArgs& a, int sm_count, cudaStream_t stream) { return launch_now(a, sm_count, stream); }
 
 // x [T, K] bf16 (T <= 8), w [N, K] bf16, K a multiple of 8, pointers 16-byte aligned.
 // inter == 0: y[T, N] = x w^T (+ bias).  inter > 0: N == 2 * inter, y[T, inter] = silu(x gate^T) * (x up^T).

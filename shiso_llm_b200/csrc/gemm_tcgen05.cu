@@ -462,18 +462,13 @@ SHISO_API int shiso_gemm_tcgen05_supported(int K, const void* x, const void* w) 
     return encode_fn() != nullptr ? 1 : 0;
 }
 
-extern "C" int shiso_chain_reset();  // gemm_stream_chain.cu
-
 // Reads and clears the status word: non-zero when a bounded wait inside a kernel ran out.
 SHISO_API int shiso_gemm_tcgen05_status() {
     int* word = shiso_tc_status_word();
     if (!word) return -1;
     int host = 0;
     if (cudaMemcpy(&host, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (host) {
-        cudaMemset(word, 0, sizeof(int));
-        shiso_chain_reset();  // a kernel that gave up between two products of a chain left their counters standing
-    }
+    if (host) cudaMemset(word, 0, sizeof(int));
     return host;
 }
 

@@ -53,13 +53,6 @@ _SIGNATURES = {
     "shiso_sample": [P, P, P, P, P, P, P, P, I, I, P, P],
     "shiso_suppress": [P, P, P, I, I, I, P],
     "shiso_selftest_bounded_wait": [LL, P],
-    "shiso_chain_begin": [I],
-    "shiso_chain_flush": [P],
-    "shiso_chain_end": [P],
-    "shiso_chain_abort": [],
-    "shiso_chain_pending": [],
-    "shiso_chain_launches": [],
-    "shiso_chain_reset": [],
 }
 
 

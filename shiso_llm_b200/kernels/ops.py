@@ -120,63 +120,6 @@ def _done(status: int, what: str, launches: int = 1) -> None:
     launch_count += launches
 
 
-# --------------------------------------------------------------------------- chained products
-#
-# A step of up to 8 bfloat16 rows runs its weight-streaming products as chains: between
-# ``begin_step`` and ``end_step`` those products are collected by the library instead of launched,
-# and everything else in this table first launches what was collected, as ONE persistent kernel
-# (csrc/gemm_stream_chain.cu).  The tensors a collected product returns are filled only by that
-# launch, so nothing but functions of this table may touch them meanwhile: the model opens a chain
-# only when all of its parts say that they launch through the table alone.
-
-CHAIN_MAX_TOKENS = 8  # rows up to which the products are the weight-streaming kernel's
-CHAIN_PRODUCTS = True  # False: every product is a kernel of its own
-_CHAIN_OPEN = False
-_CHAIN_LAUNCHES = 0  # the library's count of kernels launched for collected products, as last seen
-
-
-def _count_chain_launches() -> None:
-    global launch_count, _CHAIN_LAUNCHES
-    now = library().shiso_chain_launches()
-    launch_count += now - _CHAIN_LAUNCHES
-    _CHAIN_LAUNCHES = now
-
-
-def begin_step(step, table_only: bool = False) -> None:
-    """Called by the model before a step's first launch."""
-    global _CHAIN_OPEN
-    if _CHAIN_OPEN:
-        abort_step()
-    if CHAIN_PRODUCTS and table_only and step.num_tokens <= CHAIN_MAX_TOKENS:
-        _done(library().shiso_chain_begin(_sm_count()), "chain_begin", 0)
-        _CHAIN_OPEN = True
-
-
-def end_step() -> None:
-    """Called by the model after a step's last launch: what is still collected is launched."""
-    global _CHAIN_OPEN
-    if _CHAIN_OPEN:
-        _CHAIN_OPEN = False
-        _done(library().shiso_chain_end(_stream()), "chained products", 0)
-        _count_chain_launches()
-
-
-def abort_step() -> None:
-    """The step failed on the host: what was collected is dropped."""
-    global _CHAIN_OPEN
-    _CHAIN_OPEN = False
-    library().shiso_chain_abort()
-
-
-def _flush() -> None:
-    """Launches the collected products: the next launch reads what they write."""
-    if _CHAIN_OPEN:
-        lib = library()
-        if lib.shiso_chain_pending():
-            _done(lib.shiso_chain_flush(_stream()), "chained products", 0)
-            _count_chain_launches()
-
-
 # --------------------------------------------------------------------------- rows
 
 
@@ -184,7 +127,6 @@ def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=No
     """Rows of ``table`` for ``ids``.  Where ``feed_index[t] >= 0`` the id is read on the device
     from ``fed_tokens[feed_index[t]]`` instead (a token picked a step earlier that the host has
     not seen)."""
-    _flush()
     _check(ids, "ids", torch.int32, 1)
     _check(table, "embedding table", None, 2)
     tokens, (vocab, hidden) = ids.shape[0], table.shape
@@ -204,7 +146,6 @@ def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=No
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-    _flush()
     _check(x, "x", torch.float32, 2)
     _check(rows, "rows", torch.int32, 1)
     out = torch.empty((rows.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
@@ -219,7 +160,6 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
 def add_rmsnorm(residual, delta, w, eps, out_dtype, rows=None):
     """``residual`` float32 [T, H]; ``delta`` [T, H] in the output type or None; returns
     norm(residual + delta).  Without ``rows`` the sum is stored back into ``residual``."""
-    _flush()
     _check(residual, "residual", torch.float32, 2)
     _check(w, "norm weight", torch.float32, 1)
     tokens, hidden = residual.shape
@@ -242,7 +182,6 @@ def add_rmsnorm(residual, delta, w, eps, out_dtype, rows=None):
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    _flush()
     _check(gate_up, "gate_up", None, 2)
     tokens, two_inter = gate_up.shape
     if two_inter % 2:
@@ -291,9 +230,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         status = lib.shiso_gemm_stream(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
         )
-        _done(status, "linear (streaming)", 0 if _CHAIN_OPEN else 1)
+        _done(status, "linear (streaming)")
         return out
-    _flush()
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05_pair(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
@@ -333,9 +271,8 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
             _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
             _sm_count(), _stream(),
         )
-        _done(status, "linear_swiglu (streaming)", 0 if _CHAIN_OPEN else 1)
+        _done(status, "linear_swiglu (streaming)")
         return out
-    _flush()
     lib = library()
     if (
         x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16
@@ -409,13 +346,12 @@ def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
             tokens, n, k, _sm_count(), _stream(),
         )
     else:
-        _flush()
         partials = torch.empty((lib.shiso_gemm_tcgen05_into_partial_rows(n), tokens), dtype=torch.float32, device=x.device)
         status = lib.shiso_gemm_tcgen05_into(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
             tokens, n, k, _sm_count(), _stream(),
         )
-    _done(status, "linear_into_stream", 0 if streaming and _CHAIN_OPEN else 1)
+    _done(status, "linear_into_stream")
     return summed, ScaledRows(rows, partials, eps)
 
 
@@ -438,12 +374,11 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
             tokens, n, k, inter, _sm_count(), _stream(),
         )
     else:
-        _flush()
         status = lib.shiso_gemm_tcgen05_scaled(
             _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.partials.shape[1], rows.eps, _ptr(w), _ptr(out),
             _code(out), tokens, n, k, inter, _sm_count(), _stream(),
         )
-    _done(status, "linear_scaled", 0 if _CHAIN_OPEN else 1)
+    _done(status, "linear_scaled")
     return out
 
 
@@ -490,7 +425,7 @@ def linear_short_conv(x, in_proj, taps, bias, state, step):
             _ptr(step.seq_of_token), _ptr(step.state_slots), _ptr(y), _code(y), tokens, hidden, k, n_taps,
             _sm_count(), _stream(),
         )
-        _done(status, "linear_short_conv", 0 if _CHAIN_OPEN else 1)
+        _done(status, "linear_short_conv")
         return y
     proj = linear_scaled(rows, in_proj, xt.dtype) if rows is not None else linear(xt, in_proj, xt.dtype)
     return short_conv(proj, taps, bias, state, step)
@@ -498,7 +433,6 @@ def linear_short_conv(x, in_proj, taps, bias, state, step):
 
 def linear_simple(x, w, out_dtype, bias=None):
     """The CUDA-core product for any element types (used by tests to compare kernels)."""
-    _flush()
     _check(x, "x", None, 2)
     _check(w, "w", None, 2)
     out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
@@ -517,7 +451,6 @@ def check_kernel_status() -> None:
     """Raises when a bounded wait inside a kernel ran out since the status word was last read
     (here, or by a token-picking kernel that was given a place for it).  Synchronises the
     device; not for use while a stream is being captured."""
-    _flush()
     status = library().shiso_gemm_tcgen05_status()
     if status != 0:
         raise KernelError(f"{GAVE_UP} (status {status})")
@@ -527,7 +460,6 @@ def selftest_bounded_wait(limit_cycles: int = 4000) -> None:
     """Launches one CTA that waits ``limit_cycles`` clock cycles on a barrier nobody arrives at
     and then gives up, as any kernel here does when a wait runs out: the status word is set and
     the kernel returns.  For tests of what the host does then."""
-    _flush()
     _done(library().shiso_selftest_bounded_wait(int(limit_cycles), _stream()), "selftest_bounded_wait")
 
 
@@ -537,7 +469,6 @@ def selftest_bounded_wait(limit_cycles: int = 4000) -> None:
 def short_conv(proj, taps, bias, state, step):
     """``proj[T, 3H]`` -> ``y[T, H]``; ``state`` is the float32 view ``[slots, taps-1, H]`` of
     the slot buffer (rows of one slot contiguous) and is updated for the step's sequences."""
-    _flush()
     _check(proj, "proj", None, 2)
     _check(taps, "conv taps", torch.float32, 2)
     tokens, h3 = proj.shape
@@ -565,7 +496,6 @@ def short_conv(proj, taps, bias, state, step):
 
 def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
                        k_cache, v_cache, block_table, page_size, store):
-    _flush()
     _check(qkv, "qkv", None, 2)
     tokens, width = qkv.shape
     if width != (heads + 2 * kv_heads) * head_dim:
@@ -642,7 +572,6 @@ def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv
     caches, with the bits ``qk_norm_rope_store`` would write.  bfloat16, heads of 64 rotated
     whole, both norms present, a handful of rows; None when the step or the sizes are others (the
     caller then runs the two kernels)."""
-    _flush()
     lib = library()
     if (
         qkv.shape[0] > DECODE_FROM_QKV_MAX_TOKENS or qkv.dtype != torch.bfloat16 or not getattr(step, "all_decode", False) or q_w is None or k_w is None
@@ -684,7 +613,6 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
     take the split-key decode kernel (keys and values read once per KV head); other bfloat16
     steps take the tiled tensor-core kernel; float32 and head sizes above 128 take the general
     kernel.  ``general=True`` forces the general kernel (tests compare the routes)."""
-    _flush()
     _check(q, "q", None, 2)
     tokens = q.shape[0]
     if q.shape[1] != heads * head_dim:
@@ -786,7 +714,6 @@ def _status_place(status_out) -> int:
 def suppress(logits: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """Sets ``logits[rows[i], ids[i]]`` to -inf, in place, before a pick
     (crates/shiso-engine/src/sampling.rs:156-174; kernels/cuda/sample/sample.cu:18-26)."""
-    _flush()
     _check(logits, "logits", torch.float32, 2)
     _check(rows, "rows", torch.int32, 1)
     _check(ids, "ids", torch.int32, 1)
@@ -801,7 +728,6 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, status_out:
     """The index of each row's largest value (the smallest index among equals), int32, written
     to ``out`` when one is given.  ``status_out`` (one int32) receives the status word of the
     bounded waits, which is cleared: see ``check_kernel_status``."""
-    _flush()
     _check(logits, "logits", torch.float32, 2)
     rows, vocab = logits.shape
     out = _picks(out, rows, logits.device)
@@ -822,7 +748,6 @@ def sample(logits, temperature, top_k, top_p, min_p, keys, positions, out=None, 
     """Keyed sampling, one row per request: float32 ``temperature``/``top_p``/``min_p``,
     int32 ``top_k`` (0 = off) and ``positions``, int64 ``keys``, all of length rows.
     ``status_out`` as in ``argmax``."""
-    _flush()
     _check(logits, "logits", torch.float32, 2)
     rows = logits.shape[0]
     for name, t, dt in (

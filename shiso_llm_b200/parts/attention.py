@@ -32,8 +32,6 @@ MAX_HEAD_DIM = 256  # what the general attention kernel keeps of a head in a war
 
 @MIXERS.register("gqa_attention")
 class GqaAttention(Mixer):
-    table_only = True
-
     takes_deferred_norm = True
 
     def __init__(self, spec, env):

@@ -93,10 +93,6 @@ class Part:
     step's sequences sets it to False and its model runs decode steps without graphs."""
 
     graph_safe = True
-    # The part reads and writes device memory through the kernel table alone (no tensor
-    # arithmetic of its own between two calls of the table).  The table may then hold launches
-    # back and run several of them as one kernel; a part that says False never sees that.
-    table_only = False
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec

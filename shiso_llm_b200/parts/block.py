@@ -13,8 +13,6 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
-    table_only = True
-
     def __init__(self, spec, env, layer):
         super().__init__(spec, env)
         self.name = layer.name

@@ -15,8 +15,6 @@ from .base import EMBEDDINGS, HEADS, Embedding, Head, project
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    table_only = True
-
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.tensor_name = spec.params["tensor"]
@@ -42,8 +40,6 @@ class TokenEmbedding(Embedding):
 
 @HEADS.register("linear_head")
 class LinearHead(Head):
-    table_only = True
-
     takes_deferred_norm = True
 
     def __init__(self, spec, env):

@@ -17,8 +17,6 @@ from .base import FEED_FORWARDS, DeferredLinear, FeedForward, project
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    table_only = True
-
     takes_deferred_norm = True
 
     def __init__(self, spec, env):

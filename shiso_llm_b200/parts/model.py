@@ -52,7 +52,6 @@ class Model:
         self.final_norm = NORMS.build(plan.final_norm, env)
         self.head = HEADS.build(plan.head, env)
         self.bound = False
-        self._table_only = self.table_only
 
     # ------------------------------------------------------------------ weights
 
@@ -70,23 +69,14 @@ class Model:
             part.bind(tensors)
         self.bound = True
 
-    def _all_parts(self):
+    @property
+    def graph_safe(self) -> bool:
         def walk(part):
             yield part
             for sub in part.sub_parts():
                 yield from walk(sub)
 
-        return [p for top in self.parts() for p in walk(top)]
-
-    @property
-    def graph_safe(self) -> bool:
-        return all(p.graph_safe for p in self._all_parts())
-
-    @property
-    def table_only(self) -> bool:
-        """Every part launches through the kernel table alone, so the table may hold launches
-        back and fuse them (``Part.table_only``)."""
-        return all(p.table_only for p in self._all_parts())
+        return all(p.graph_safe for top in self.parts() for p in walk(top))
 
     # ------------------------------------------------------------------ cache needs
 
@@ -113,20 +103,6 @@ class Model:
         so a step with a hook is never captured."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet: load or bind them first")
-        ops = self.env.ops
-        begin = getattr(ops, "begin_step", None)
-        if begin is None or layer_hook is not None or add_hook is not None:
-            return self._forward(step, cache, layer_hook, add_hook)
-        begin(step, self._table_only)
-        try:
-            logits = self._forward(step, cache, None, None)
-        except BaseException:
-            ops.abort_step()
-            raise
-        ops.end_step()
-        return logits
-
-    def _forward(self, step, cache, layer_hook, add_hook):
         stream = Stream(self.embedding.forward(step), add_hook)
         if layer_hook is not None:
             layer_hook(-1, stream)

@@ -14,8 +14,6 @@ from .base import NORMS, Norm
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    table_only = True
-
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.tensor_name = spec.params["tensor"]

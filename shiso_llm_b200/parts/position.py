@@ -18,8 +18,6 @@ from .base import POSITION_ENCODINGS, PositionEncoding
 
 @POSITION_ENCODINGS.register("rope_half_split")
 class RopeHalfSplit(PositionEncoding):
-    table_only = True
-
     def __init__(self, spec, env, head_dim: int):
         super().__init__(spec, env)
         self.theta = float(spec.params["theta"])
@@ -35,8 +33,6 @@ class RopeHalfSplit(PositionEncoding):
 
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
-    table_only = True
-
     """Leaves queries and keys as they are."""
 
     def __init__(self, spec, env, head_dim: int):

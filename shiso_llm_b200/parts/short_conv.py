@@ -23,8 +23,6 @@ MAX_TAPS = 8
 
 @MIXERS.register("short_conv")
 class ShortConv(Mixer):
-    table_only = True
-
     takes_deferred_norm = True
 
     def __init__(self, spec, env):

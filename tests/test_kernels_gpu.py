@@ -935,96 +935,3 @@ def test_stream_pair_at_random_sizes(seed, monkeypatch):
         scale = (ref.linear_swiglu(x, w2, torch.float32) if glu else ref.linear(x, w2, torch.float32)).abs().max().item()
         close(y, want, torch.bfloat16, f"scaled product {(T, H, K1, N2, glu)}", scale=2 * scale)
     ops().check_kernel_status()
-
-
-@pytest.mark.parametrize("case", [(8, 2048, 5632, 3, 3000), (1, 640, 2200, 2, 1000), (5, 1032, 1000, 4, 77), (3, 96, 40, 3, 40), (8, 264, 2056, 3, 520)])
-def test_chained_products_equal_the_products_one_by_one(case):
-    """The products of two decode layers and a head - output projection into the stream, the next
-    one's input projection with the short convolution in its epilogue (row scale pending),
-    SwiGLU pair, down projection, a plain product with float32 output - collected and run as
-    ONE persistent kernel with barriers between them.  Every output, the residual stream and the
-    convolution's state must equal, bit for bit, what the same products give as kernels of their
-    own: widths that fill no tile, K of one, two and several chunks, a chain longer than one
-    launch takes, products with fewer tiles than there are SMs."""
-    T, H, inter, taps, vocab = case
-    table = ops()
-    cpu, gpu, _ = make_step([1] * T, [2 + i for i in range(T)], 4, 64, 500, num_slots=9)
-    gpu.all_decode, gpu.max_q_len = True, 1
-    eps = 1e-5
-
-    def weights(seed):
-        g = lambda shape, k, scale=0.05: rnd(shape, torch.bfloat16, seed + k, scale).cuda()
-        return {
-            "out": g((H, H), 1), "in": g((3 * H, H), 2), "conv_out": g((H, H), 3), "gate_up": g((2 * inter, H), 4),
-            "down": g((H, inter), 5), "taps": rnd((H, taps), torch.float32, seed + 6).cuda(),
-            "bias": rnd((H,), torch.float32, seed + 7).cuda(),
-            "norms": [(1.0 + 0.2 * rnd((H,), torch.float32, seed + 8 + i)).cuda() for i in range(3)],
-        }
-
-    layers = [weights(510), weights(530), weights(550)]  # three layers: 13 products and the head's: more than one launch takes
-    head = rnd((vocab, H), torch.bfloat16, 570, 0.05).cuda()
-    x0 = rnd((T, H), torch.bfloat16, 571).cuda()
-    residual0 = rnd((T, H), torch.float32, 572, 2.0).cuda()
-    state0 = rnd((9, taps - 1, H), torch.float32, 573).cuda()
-
-    def run(chained):
-        states = [state0.clone() for _ in layers]
-        outs = []
-        if chained:
-            table.begin_step(SimpleNamespace(num_tokens=T), True)
-        residual, x = residual0, x0
-        for w, state in zip(layers, states):
-            residual, rows = table.linear_into_stream(x, w["out"], residual, w["norms"][0], eps)
-            y = table.linear_short_conv(rows, w["in"], w["taps"], w["bias"], state, gpu)
-            residual, rows = table.linear_into_stream(y, w["conv_out"], residual, w["norms"][1], eps, w["bias"])
-            mid = table.linear_scaled(rows, w["gate_up"], torch.bfloat16, True)
-            residual, rows = table.linear_into_stream(mid, w["down"], residual, w["norms"][2], eps)
-            x = table.linear(mid, w["down"], torch.bfloat16)
-            outs += [y, mid, residual, rows.x, rows.partials, x]
-        logits = table.linear_scaled(rows, head, torch.float32)
-        if chained:
-            assert table.library().shiso_chain_pending() > 0
-            table.end_step()
-        torch.cuda.synchronize()
-        table.check_kernel_status()
-        return outs + [logits] + states
-
-    alone = run(False)
-    launches_before = table.launch_count
-    chained = run(True)
-    assert table.launch_count - launches_before == 2, "19 products are two launches of at most 16"
-    for i, (a, b) in enumerate(zip(alone, chained)):
-        assert torch.equal(a, b), f"output {i} differs by {(a.float() - b.float()).abs().max().item()}"
-    # and a second time over the same buffers' addresses (the barriers' counters were left at zero)
-    again = run(True)
-    for i, (a, b) in enumerate(zip(alone, again)):
-        assert torch.equal(a, b), f"second run: output {i} differs"
-    assert torch.isfinite(alone[-len(layers) - 1]).all()
-
-
-def test_a_launch_that_is_no_product_first_runs_the_collected_products():
-    """Anything else in the kernel table launches the collected products before itself: a norm
-    over a collected product's output sees that output."""
-    table = ops()
-    x = rnd((4, 512), torch.bfloat16, 580).cuda()
-    w = rnd((512, 512), torch.bfloat16, 581, 0.05).cuda()
-    residual = rnd((4, 512), torch.float32, 582).cuda()
-    nw = torch.ones(512).cuda()
-    want = table.add_rmsnorm(residual.clone(), table.linear(table.linear(x, w, torch.bfloat16), w, torch.bfloat16), nw, 1e-5, torch.bfloat16)
-    table.begin_step(SimpleNamespace(num_tokens=4), True)
-    y = table.linear(table.linear(x, w, torch.bfloat16), w, torch.bfloat16)
-    assert table.library().shiso_chain_pending() == 2
-    got = table.add_rmsnorm(residual.clone(), y, nw, 1e-5, torch.bfloat16)
-    assert table.library().shiso_chain_pending() == 0
-    table.end_step()
-    assert torch.equal(got, want)
-    # a step that fails on the host drops what was collected
-    table.begin_step(SimpleNamespace(num_tokens=4), True)
-    table.linear(x, w, torch.bfloat16)
-    table.abort_step()
-    assert table.library().shiso_chain_pending() == 0
-    # more rows than the streaming products take: nothing is collected
-    table.begin_step(SimpleNamespace(num_tokens=9), True)
-    table.linear(x, w, torch.bfloat16)
-    assert table.library().shiso_chain_pending() == 0
-    table.end_step()
