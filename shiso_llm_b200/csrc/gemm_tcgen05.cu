@@ -164,20 +164,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     };
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: TMA loads, one stage per 64-wide k block
-        for (int i = 0; i < kb_count; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
+        // ---- producer: TMA loads, one stage per 64-wide k block.  Weights depend on no
+        // predecessor, the activations do: the weights of every stage of the ring are asked for
+        // before the dependency wait, so that they travel under the predecessor's tail.
+        auto load_weights = [&](int i) {
+            uint8_t* a = smem + (i % STAGES) * STAGE_BYTES;
+            mbar_expect_tx(&full[i % STAGES], STAGE_BYTES);
+            const int k = (kb_begin + i) * BK;
+            tma_load_2d(a, &map_w, k, feature0, &full[i % STAGES]);
+            if (GLU) tma_load_2d(a + A_BYTES, &map_w, k, p.inter + feature0, &full[i % STAGES]);
+        };
+        auto load_tokens = [&](int i) {
+            tma_load_2d(smem + (i % STAGES) * STAGE_BYTES + A_TILES * A_BYTES, &map_x, (kb_begin + i) * BK, token0, &full[i % STAGES]);
+        };
+        const int ahead = kb_count < STAGES ? kb_count : STAGES;
+        for (int i = 0; i < ahead; ++i) load_weights(i);
+        pdl_wait();
+        for (int i = 0; i < ahead; ++i) load_tokens(i);
+        for (int i = ahead; i < kb_count; ++i) {
+            if (!mbar_wait(&empty[i % STAGES], ((i / STAGES) - 1) & 1)) {
                 *failed = 1;
                 break;
             }
-            uint8_t* a = smem + s * STAGE_BYTES;
-            mbar_expect_tx(&full[s], STAGE_BYTES);
-            const int k = (kb_begin + i) * BK;
-            tma_load_2d(a, &map_w, k, feature0, &full[s]);
-            if (GLU) tma_load_2d(a + A_BYTES, &map_w, k, p.inter + feature0, &full[s]);
-            if (i == 0) pdl_wait();  // weights depend on no predecessor; the activations do
-            tma_load_2d(a + A_TILES * A_BYTES, &map_x, k, token0, &full[s]);
+            load_weights(i);
+            load_tokens(i);
         }
         ask_early();
     } else if (warp == 1 && lane == 0) {

@@ -125,7 +125,7 @@ def test_linear(shape, xw):
 
 
 @pytest.mark.parametrize("shape", [(512, 256, 64), (700, 1000, 264), (1030, 2048, 2048), (2048, 6144, 512), (515, 520, 5632),
-                                   (193, 2048, 2048), (300, 776, 520)])
+                                   (193, 2048, 2048), (300, 776, 520), (600, 2048, 8192), (257, 16384, 2048)])
 def test_linear_on_sm_pairs(shape):
     """From 193 bfloat16 rows a plain product runs on pairs of SMs (one 256-row tile per pair, each CTA
     loading half of both operands): row counts that leave the second CTA of the last pair with
@@ -611,7 +611,8 @@ def test_prefill_attention_never_reads_outside_its_range():
 @pytest.mark.parametrize("shape", [(1, 96, 64), (8, 2048, 2048), (5, 1000, 96), (8, 300, 200), (16, 2048, 5632), (13, 48, 264), (3, 16, 8),
                                    (8, 4800, 1032), (2, 24, 3080), (24, 2048, 2048), (32, 1000, 264), (17, 40, 5632),
                                    (64, 6144, 2048), (33, 2048, 5632), (50, 776, 264), (64, 48, 8), (40, 11264, 2048),
-                                   (65, 2048, 2048), (100, 776, 264), (128, 6144, 2048), (129, 2048, 5632), (192, 11264, 2048), (177, 40, 72)])
+                                   (65, 2048, 2048), (100, 776, 264), (128, 6144, 2048), (129, 2048, 5632), (192, 11264, 2048), (177, 40, 72),
+                                   (8, 2048, 8192), (8, 16384, 2048), (64, 2048, 8192), (48, 16384, 2048)])  # a feed-forward of 8,192 (block_ff_dim 12,288)
 def test_skinny_linear_and_fused_swiglu(shape):
     """A handful of bfloat16 rows take the weight-streaming kernel, up to 192 the tensor-memory
     kernel with tokens as the MMA's N operand (tiles of at most 64 tokens, K split over a
@@ -711,7 +712,8 @@ def test_input_projection_with_the_convolution_in_its_epilogue(case, scaled):
     assert torch.equal(ya, yb) and torch.equal(s_a, s_b)
 
 
-@pytest.mark.parametrize("shape", [(40, 600, 264), (130, 256, 512), (300, 1000, 96), (513, 2 * 5632, 2048), (777, 2 * 1000, 96), (2048, 2 * 264, 520)])
+@pytest.mark.parametrize("shape", [(40, 600, 264), (130, 256, 512), (300, 1000, 96), (513, 2 * 5632, 2048), (777, 2 * 1000, 96), (2048, 2 * 264, 520),
+                                   (520, 2 * 8192, 2048)])
 def test_tensor_core_product_with_fused_swiglu(shape):
     """More than a handful of bfloat16 rows: gate and up accumulate side by side in tensor
     memory and the epilogue applies the activation (token tiles of 64, 128 and 256; feature
