@@ -99,14 +99,19 @@ class LLM:
 
     # ------------------------------------------------------------------ low level
 
-    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None):
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None, extras=None):
+        """``extras``: values of the model's further per-row inputs (``ModelPlan.row_inputs``) for
+        the prompt, name -> one int per token; tokens the request produces get their position."""
         if request_id is None:
             request_id = self._next_id
             self._next_id += 1
         vocab = self.engine.vocab_size
         if any(t < 0 or t >= vocab for t in prompt):
             raise ValueError(f"a prompt token lies outside the vocabulary of {vocab}")
-        return self.scheduler.add(request_id, prompt, params or SamplingParams())
+        unknown = set(extras or ()) - set(self.engine.model.plan.row_inputs)
+        if unknown:
+            raise ValueError(f"the model reads no per-row input named {sorted(unknown)}")
+        return self.scheduler.add(request_id, prompt, params or SamplingParams(), extras)
 
     def abort(self, request_id) -> bool:
         return self.scheduler.abort(request_id)
@@ -131,7 +136,8 @@ class LLM:
                     tokens = [0]  # a placeholder: the device reads the token a sampler left it
                 else:
                     tokens = e.request.token_slice(e.start, e.count)
-                entries.append(StepEntry(e.request.id, tokens, [e.count - 1] if e.samples else [], e.feed))
+                entries.append(StepEntry(e.request.id, tokens, [e.count - 1] if e.samples else [], e.feed,
+                                         e.request.extras_slice(e.start, e.count)))
                 if e.samples:
                     params.append(e.request.params)
                     positions.append(e.start + e.count)

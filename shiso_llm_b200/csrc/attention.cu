@@ -4,7 +4,8 @@
 // and key head is RMS-normalised over head_dim with a [head_dim] weight, then rotated in
 // half-split pairs (i, i + rotary_dim/2) by the angle pos * inv_freq[i]
 // (dense_common.cuh:166-180; the frequency ladder arrives as a table computed once on
-// the host); the key is cached normalised and rotated, the value raw, at row
+// the host) - or, when the caller says `interleaved`, in adjacent pairs (2i, 2i + 1), which
+// is how some checkpoints are exported; the key is cached normalised and rotated, the value raw, at row
 // table[pos / page] * page + pos % page (dense_common.cuh:120-126).
 //
 // Attention follows kernels/cuda/dense/dense_attn.cuh:44-180: per (row, head) an online
@@ -44,7 +45,7 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
                           const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                           int table_width, AT* __restrict__ k_cache, AT* __restrict__ v_cache,
                           AT* __restrict__ q_out, int tokens, int heads, int kv_heads, int head_dim,
-                          int rotary_dim, int page_size, float eps, int store, int per_warp) {
+                          int rotary_dim, int page_size, float eps, int store, int per_warp, int interleaved) {
     pdl_begin();
     constexpr int PAIRS = HD_MAX / 64;  // rotation pairs a lane can hold
     constexpr int TAIL = HD_MAX / 32;   // unrotated elements a lane can hold
@@ -59,14 +60,17 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
     if (u_first >= u_last) return;
     const int half = rotary_dim / 2;
     const AT* token_row = qkv + (size_t)t * units * head_dim;
+    // the two elements of rotation pair p: (p, p + half), or neighbours (2p, 2p + 1)
+    auto first_of = [&](int p) { return interleaved ? 2 * p : p; };
+    auto second_of = [&](int p) { return interleaved ? 2 * p + 1 : p + half; };
 
     auto load_unit = [&](int u, UnitRegs<HD_MAX>& r) {
         const AT* src = token_row + (size_t)u * head_dim;
 #pragma unroll
         for (int j = 0; j < PAIRS; ++j) {
             const int p = lane + 32 * j;
-            r.a[j] = p < half ? to_f32(src[p]) : 0.0f;
-            r.b[j] = p < half ? to_f32(src[p + half]) : 0.0f;
+            r.a[j] = p < half ? to_f32(src[first_of(p)]) : 0.0f;
+            r.b[j] = p < half ? to_f32(src[second_of(p)]) : 0.0f;
         }
 #pragma unroll
         for (int j = 0; j < TAIL; ++j) {
@@ -115,9 +119,9 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
             for (int j = 0; j < PAIRS; ++j) {
                 const int p = lane + 32 * j;
                 if (p < half) {
-                    const float x = cur.a[j] * inv * w[p], y = cur.b[j] * inv * w[p + half];
-                    dst[p] = from_f32<AT>(x * cs[j] - y * sn[j]);
-                    dst[p + half] = from_f32<AT>(x * sn[j] + y * cs[j]);
+                    const float x = cur.a[j] * inv * w[first_of(p)], y = cur.b[j] * inv * w[second_of(p)];
+                    dst[first_of(p)] = from_f32<AT>(x * cs[j] - y * sn[j]);
+                    dst[second_of(p)] = from_f32<AT>(x * sn[j] + y * cs[j]);
                 }
             }
 #pragma unroll
@@ -130,8 +134,8 @@ qk_norm_rope_store_kernel(const AT* __restrict__ qkv, const float* __restrict__ 
             for (int j = 0; j < PAIRS; ++j) {
                 const int p = lane + 32 * j;
                 if (p < half) {
-                    dst[p] = from_f32<AT>(cur.a[j]);
-                    dst[p + half] = from_f32<AT>(cur.b[j]);
+                    dst[first_of(p)] = from_f32<AT>(cur.a[j]);
+                    dst[second_of(p)] = from_f32<AT>(cur.b[j]);
                 }
             }
 #pragma unroll
@@ -333,13 +337,14 @@ SHISO_API int shiso_qk_norm_rope_store(const void* qkv, int act_dtype, const flo
                                        const float* inv_freq, const int* positions, const int* seq_of_token,
                                        const int* block_table, int table_width, void* k_cache, void* v_cache,
                                        void* q_out, int tokens, int heads, int kv_heads, int head_dim,
-                                       int rotary_dim, int page_size, float eps, int store, cudaStream_t stream) {
+                                       int rotary_dim, int page_size, float eps, int store, int interleaved,
+                                       cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (head_dim <= 0 || head_dim > MAX_HEAD_DIM || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
         return SHISO_ERR_SHAPE;
     if (rotary_dim > 0 && !inv_freq) return SHISO_ERR_SHAPE;
     const int units = heads + 2 * kv_heads;
-    if (act_dtype == SHISO_BF16 && head_dim == 64 && rotary_dim == 64 &&
+    if (act_dtype == SHISO_BF16 && head_dim == 64 && rotary_dim == 64 && !interleaved &&
         (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q_out) & 7) == 0) {
         // groups of four heads: one per warp when there are few, up to eight in a row when there are many
         const int groups = ((store ? units : heads) + 3) / 4;
@@ -361,7 +366,7 @@ SHISO_API int shiso_qk_norm_rope_store(const void* qkv, int act_dtype, const flo
         using T = std::remove_pointer_t<decltype(typed)>;
         launch_kernel(kernel, blocks, WARPS * 32, 0, stream, (const T*)qkv, q_w, k_w, inv_freq, positions, seq_of_token,
                       block_table, table_width, (T*)k_cache, (T*)v_cache, (T*)q_out, tokens, heads, kv_heads, head_dim,
-                      rotary_dim, page_size, eps, store, per_warp);
+                      rotary_dim, page_size, eps, store, per_warp, interleaved ? 1 : 0);
     };
     if (act_dtype == SHISO_F32) {
         float* tag = nullptr;

@@ -35,6 +35,9 @@ class StepEntry:
     # engine's ``fed_tokens`` buffer (where a sampler left it a step earlier); ``tokens`` then
     # holds a placeholder.
     feed: Optional[int] = None
+    # Values of the model's further per-row inputs (``ModelPlan.row_inputs``): name -> one int per
+    # token of this entry.  A name that is left out gets the rows' positions.
+    extras: Optional[dict] = None
 
 
 @dataclass
@@ -58,6 +61,7 @@ class StepMeta:
     wants_every_row: bool = False  # want_rows is 0, 1, .. T-1: logits of all rows, in order
     feed_index: Optional[torch.Tensor] = None  # [T] index into fed_tokens, or -1: the id in token_ids stands
     fed_tokens: Optional[torch.Tensor] = None  # the engine's buffer of tokens picked on the device
+    extras: dict = field(default_factory=dict)  # name -> [T] int32, the model's further per-row inputs
     h_q_start: list = field(default_factory=list)
     h_start_pos: list = field(default_factory=list)
     h_state_slots: list = field(default_factory=list)
@@ -71,7 +75,7 @@ def _align(n: int, a: int = 4) -> int:
 class MetaLayout:
     """Offsets (in int32 elements) of every array inside the staging block."""
 
-    def __init__(self, num_tokens: int, num_seqs: int, num_wanted_cap: int, num_groups: int, width: int):
+    def __init__(self, num_tokens: int, num_seqs: int, num_wanted_cap: int, num_groups: int, width: int, num_extras: int = 0):
         t, s = _align(num_tokens), _align(num_seqs)
         self.token_ids = 0
         self.positions = t
@@ -83,21 +87,25 @@ class MetaLayout:
         self.want_rows = self.state_slots + s
         self.tables = self.want_rows + _align(num_wanted_cap)
         self.table_elems = _align(num_seqs * width)
-        self.total = self.tables + num_groups * self.table_elems
+        self.extras = self.tables + num_groups * self.table_elems  # num_extras arrays of t entries
+        self.extra_elems = t
+        self.total = self.extras + num_extras * t
 
 
 class StepBuilder:
     """Builds ``StepMeta`` from entries and the cache manager's holdings."""
 
-    def __init__(self, cache, device, max_tokens: int, max_seqs: int, fixed_table_width: Optional[int] = None):
+    def __init__(self, cache, device, max_tokens: int, max_seqs: int, fixed_table_width: Optional[int] = None,
+                 row_inputs: Sequence[str] = ()):
         self.cache = cache
+        self.row_inputs = tuple(row_inputs)
         self.device = torch.device(device)
         self.max_tokens = max_tokens
         self.max_seqs = max_seqs
         self.num_groups = len(cache.groups)
         self.fixed_width = fixed_table_width
         width = fixed_table_width or cache.max_blocks
-        cap = MetaLayout(max_tokens, max_seqs, max_tokens, self.num_groups, width).total
+        cap = MetaLayout(max_tokens, max_seqs, max_tokens, self.num_groups, width, len(self.row_inputs)).total
         pin = self.device.type == "cuda"
         self._staging = [torch.zeros(cap, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self._events = [None, None]
@@ -108,6 +116,23 @@ class StepBuilder:
 
     def _iota(self, n: int) -> np.ndarray:
         return self._arange[:n]
+
+    def _fill_extras(self, host, lay, entries, q_start, num_tokens: int) -> None:
+        """The model's further per-row inputs: the rows' positions unless an entry brings values."""
+        for j, name in enumerate(self.row_inputs):
+            at = lay.extras + j * lay.extra_elems
+            host[at : at + num_tokens] = host[lay.positions : lay.positions + num_tokens]
+            for i, e in enumerate(entries):
+                values = e.extras.get(name) if e.extras else None
+                if values is None:
+                    continue
+                a, b = int(q_start[i]), int(q_start[i + 1])
+                if len(values) != b - a:
+                    raise ValueError(f"request {e.request!r}: {len(values)} values of {name!r} for {b - a} tokens")
+                host[at + a : at + b] = values
+
+    def _extras(self, part, lay, num_tokens: int) -> dict:
+        return {name: part(lay.extras + j * lay.extra_elems, num_tokens) for j, name in enumerate(self.row_inputs)}
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], pad=None) -> StepMeta:
         """``starts[i]`` = positions the cache held for entry ``i`` before this step.
@@ -132,7 +157,7 @@ class StepBuilder:
             )
         requests = [e.request for e in entries]
         width = self.fixed_width or self.cache.max_blocks_held(requests)
-        lay = MetaLayout(num_tokens, num_seqs, num_wanted, self.num_groups, width)
+        lay = MetaLayout(num_tokens, num_seqs, num_wanted, self.num_groups, width, len(self.row_inputs))
 
         turn = self._turn
         self._turn ^= 1
@@ -189,6 +214,8 @@ class StepBuilder:
             at = lay.tables + g * lay.table_elems
             self.cache.fill_block_tables(requests, g, host[at : at + num_seqs * width].reshape(num_seqs, width))
 
+        if self.row_inputs:
+            self._fill_extras(host, lay, entries, q_start, num_tokens)
         dev = self.device_block
         dev[: lay.total].copy_(stage[: lay.total], non_blocking=True)
         if self.device.type == "cuda":
@@ -220,6 +247,7 @@ class StepBuilder:
             wants_every_row=single and every_row,
             feed_index=part(lay.feed_index, num_tokens) if self.fed_tokens is not None else None,
             fed_tokens=self.fed_tokens,
+            extras=self._extras(part, lay, num_tokens),
             h_q_start=q_start.tolist(),
             h_start_pos=list(starts),
             h_state_slots=slots,
@@ -248,7 +276,7 @@ class StepBuilder:
         lens = lens + [1] * (made_up - 1) + [last]
         starts = list(starts) + [0] * made_up
         width = self.fixed_width
-        lay = MetaLayout(pad_tokens, pad_seqs, pad_wanted, self.num_groups, width)
+        lay = MetaLayout(pad_tokens, pad_seqs, pad_wanted, self.num_groups, width, len(self.row_inputs))
 
         turn = self._turn
         self._turn ^= 1
@@ -294,6 +322,8 @@ class StepBuilder:
             cache.fill_block_tables(requests, g, tables[:real_seqs])
             tables[real_seqs:] = scratch
 
+        if self.row_inputs:
+            self._fill_extras(host, lay, entries, q_start, pad_tokens)
         dev = self.device_block
         dev[: lay.total].copy_(stage[: lay.total], non_blocking=True)
         if self.device.type == "cuda":
@@ -325,6 +355,7 @@ class StepBuilder:
             wants_every_row=decode,
             feed_index=part(lay.feed_index, pad_tokens) if self.fed_tokens is not None else None,
             fed_tokens=self.fed_tokens,
+            extras=self._extras(part, lay, pad_tokens),
             h_q_start=[],  # a captured step sizes its launches by capacity, not by this step's lengths
             h_start_pos=[],
             h_state_slots=[],

@@ -150,8 +150,9 @@ class Engine:
         self.env = model.env
         self.device = model.env.device
         self.vocab_size = model.plan.vocab_size
+        row_inputs = model.plan.row_inputs
         self.builder = StepBuilder(
-            cache, self.device, options.max_num_batched_tokens, options.max_num_seqs
+            cache, self.device, options.max_num_batched_tokens, options.max_num_seqs, row_inputs=row_inputs
         )
         # Tokens picked on the device from the last step's logits, one per sampling row; an entry
         # with ``feed = j`` takes its token from index j without the host having seen it.
@@ -169,7 +170,7 @@ class Engine:
             from .graphs import DecodeGraphs, decode_bucket
 
             most = decode_bucket(options.max_num_seqs) if cache.scratch_slot is not None else options.max_num_seqs
-            decode_builder = StepBuilder(cache, self.device, most, most, fixed_table_width=cache.max_blocks)
+            decode_builder = StepBuilder(cache, self.device, most, most, fixed_table_width=cache.max_blocks, row_inputs=row_inputs)
             decode_builder.fed_tokens = self.fed_tokens
             self.graphs = DecodeGraphs(model, cache, decode_builder)
             if options.graph_mixed_steps and cache.scratch_slot is not None:
@@ -178,7 +179,7 @@ class Engine:
                 most_seqs = sequence_bucket(options.max_num_seqs + 1)
                 padded_builder = StepBuilder(
                     cache, self.device, token_bucket(options.max_num_batched_tokens + most_seqs), most_seqs,
-                    fixed_table_width=cache.max_blocks,
+                    fixed_table_width=cache.max_blocks, row_inputs=row_inputs,
                 )
                 padded_builder.fed_tokens = self.fed_tokens
                 self.step_graphs = StepGraphs(model, cache, padded_builder)
@@ -318,6 +319,11 @@ class Engine:
             for w in e.want:
                 if not 0 <= w < count:
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {count} tokens")
+            for name, values in (e.extras or {}).items():
+                if name not in self.model.plan.row_inputs:
+                    raise ValueError(f"request {e.request!r}: the model reads no per-row input named {name!r}")
+                if len(values) != count:
+                    raise ValueError(f"request {e.request!r}: {len(values)} values of {name!r} for {count} tokens")
         if not entries:
             raise ValueError("a step needs at least one token")
         if total > self.builder.max_tokens or len(entries) > self.builder.max_seqs:

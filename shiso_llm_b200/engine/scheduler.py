@@ -93,6 +93,15 @@ class Request:
     preemptions: int = 0
     arrival: int = 0
     pending_row: Optional[int] = None  # which of the last step's sampling rows holds its pending token
+    extras: Optional[dict] = None  # further per-row inputs of the prompt: name -> one int per prompt token
+
+    def extras_slice(self, start: int, count: int) -> Optional[dict]:
+        """The further per-row inputs of ``tokens[start : start + count]``: the prompt's own values,
+        and the position for every token the request produced itself."""
+        if not self.extras:
+            return None
+        n = len(self.prompt)
+        return {name: [values[p] if p < n else p for p in range(start, start + count)] for name, values in self.extras.items()}
 
     @property
     def tokens(self) -> list:
@@ -151,13 +160,18 @@ class Scheduler:
 
     # ------------------------------------------------------------------ requests
 
-    def add(self, request_id, prompt: Sequence[int], params: SamplingParams) -> Request:
+    def add(self, request_id, prompt: Sequence[int], params: SamplingParams, extras: Optional[dict] = None) -> Request:
         prompt = [int(t) for t in prompt]
         stop = frozenset(int(t) for t in params.stop_token_ids)
         if not params.ignore_eos:
             stop = stop | self.eos
         req = Request(request_id, prompt, params, stop, arrival=self._arrivals)
         self._arrivals += 1
+        if extras:
+            req.extras = {name: [int(v) for v in values] for name, values in extras.items()}
+            for name, values in req.extras.items():
+                if len(values) != len(prompt):
+                    return self._refuse(req, f"{len(values)} values of {name!r} for a prompt of {len(prompt)} tokens")
         if not prompt:
             return self._refuse(req, "empty prompt")
         if len(prompt) >= self.config.ctx:

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "shiso_gemm_stream_scaled": [P, P, I, F, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_stream_conv": [P, P, I, F, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, P],
     "shiso_short_conv": [P, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, I, P],
-    "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
+    "shiso_qk_norm_rope_store": [P, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "shiso_decode_attention": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
     "shiso_decode_attention_fused_supported": [I, I, I, I],

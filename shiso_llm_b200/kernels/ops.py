@@ -495,7 +495,9 @@ def short_conv(proj, taps, bias, state, step):
 
 
 def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
-                       k_cache, v_cache, block_table, page_size, store):
+                       k_cache, v_cache, block_table, page_size, store, interleaved=False):
+    """Per-head norm, rotation and cache store.  The rotation pairs are ``(i, i + rotary_dim/2)``,
+    or neighbours ``(2i, 2i + 1)`` with ``interleaved``."""
     _check(qkv, "qkv", None, 2)
     tokens, width = qkv.shape
     if width != (heads + 2 * kv_heads) * head_dim:
@@ -521,7 +523,8 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
         _ptr(qkv), _code(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq) if rotary_dim else 0,
         _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), block_table.shape[1],
         _ptr(k_cache) if do_store else 0, _ptr(v_cache) if do_store else 0, _ptr(q),
-        tokens, heads, kv_heads, head_dim, int(rotary_dim), page_size, float(eps), int(do_store), _stream(),
+        tokens, heads, kv_heads, head_dim, int(rotary_dim), page_size, float(eps), int(do_store), int(bool(interleaved)),
+        _stream(),
     )
     _done(status, "qk_norm_rope_store")
     return q
@@ -565,7 +568,7 @@ DECODE_FROM_QKV_MAX_TOKENS = 8  # rows up to which attention takes the qkv rows 
 
 
 def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
-                              k_cache, v_cache, block_table, page_size, store, scale, window):
+                              k_cache, v_cache, block_table, page_size, store, scale, window, interleaved=False):
     """``qk_norm_rope_store`` and ``paged_attention`` in one launch for steps of single tokens:
     the attention kernel takes the rows of the qkv product, norms and rotates the queries and
     each token's new key itself, and (with ``store``) writes the new key and value into the
@@ -575,6 +578,7 @@ def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv
     lib = library()
     if (
         qkv.shape[0] > DECODE_FROM_QKV_MAX_TOKENS or qkv.dtype != torch.bfloat16 or not getattr(step, "all_decode", False) or q_w is None or k_w is None
+        or interleaved
         or inv_freq is None or head_dim != 64 or rotary_dim != 64 or kv_heads <= 0
         or not lib.shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size)
     ):

@@ -100,8 +100,10 @@ class GqaAttention(Mixer):
         store = cache.owner and not self.borrows_cache
         qkv = project(ops, x, self.qkv, self.env.dtype)
         inv_freq, rotary_dim = self.position.rotary()
+        interleaved = bool(getattr(self.position, "interleaved", False))
+        pairing = {"interleaved": True} if interleaved else {}  # handed on only when it is not the usual one
         from_qkv = getattr(ops, "decode_attention_from_qkv", None)
-        if from_qkv is not None and not self.borrows_cache and self.q_norm is not None and self.k_norm is not None:
+        if from_qkv is not None and not interleaved and not self.borrows_cache and self.q_norm is not None and self.k_norm is not None:
             # steps of single tokens: norm, rotation, cache store and attention in one launch
             attn = from_qkv(
                 qkv, self.heads, self.kv_heads, self.head_dim, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
@@ -126,6 +128,7 @@ class GqaAttention(Mixer):
             step.block_tables[cache.group],
             cache.page_size,
             store,
+            **pairing,
         )
         attn = ops.paged_attention(
             q,

@@ -122,9 +122,13 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    # Which two elements of a head form rotation pair i: False - (i, i + rotary_dim/2), the
+    # half-split pairing; True - the neighbours (2i, 2i + 1).
+    interleaved = False
+
     def rotary(self):
-        """``(inv_freq, rotary_dim)``: the encoding rotates the pairs ``(i, i + rotary_dim/2)``
-        of every query and key head by the angle ``position * inv_freq[i]`` (float32
+        """``(inv_freq, rotary_dim)``: the encoding rotates pair i of every query and key head
+        (see ``interleaved``) by the angle ``position * inv_freq[i]`` (float32
         ``[rotary_dim / 2]`` on the device); ``(None, 0)`` leaves heads as they are.
         The fused norm + rotate + store kernel applies it."""
         raise NotImplementedError

@@ -80,6 +80,12 @@ class ModelPlan:
     # in chunks of fixed length (the reference cuts on such a grid for its chunked delta-net,
     # crates/shiso-runtime/src/scheduler/config.rs:35-44).  1: a portion may end anywhere.
     portion_multiple: int = 1
+    # Names of further int32 arrays, one value per row, that parts of this model read from the
+    # step (``step.extras[name]``) beside token ids and positions: more position streams, segment
+    # ids and the like (the reference keeps such arrays in its batch metadata,
+    # crates/shiso-engine/src/attn.rs:244-284).  A caller gives them per entry
+    # (``StepEntry.extras``); a row for which none is given gets its position.
+    row_inputs: tuple[str, ...] = ()
 
     def __post_init__(self):
         if self.portion_multiple < 1:

@@ -141,7 +141,7 @@ def _cache_rows(block_table, seq_of_token, positions, page_size):
 
 
 def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
-                       k_cache, v_cache, block_table, page_size, store):
+                       k_cache, v_cache, block_table, page_size, store, interleaved=False):
     T = qkv.shape[0]
     d = head_dim
     x = qkv.to(F64)
@@ -162,6 +162,11 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
         angle = step.positions.to(F64)[:, None] * inv_freq.to(F64)[None, :]
         cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
         out = v.clone()
+        if interleaved:  # pairs of neighbours (2i, 2i + 1)
+            a, b = v[..., 0:rotary_dim:2], v[..., 1:rotary_dim:2]
+            out[..., 0:rotary_dim:2] = a * cos - b * sin
+            out[..., 1:rotary_dim:2] = a * sin + b * cos
+            return out
         a, b = v[..., :half], v[..., half:rotary_dim]
         out[..., :half] = a * cos - b * sin
         out[..., half:rotary_dim] = a * sin + b * cos

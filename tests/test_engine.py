@@ -439,3 +439,76 @@ def test_mixed_steps_replayed_from_captured_graphs(tmp_path, dtype):
     ops.check_kernel_status()
     assert engine.step_graphs.captures >= 3 and engine.step_graphs.replays > 20
     engine.cache.check()
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_a_model_that_reads_a_further_per_row_input(backend):
+    """A plan may name further int arrays with one value per row (``row_inputs``): entries bring
+    them (``StepEntry.extras``), requests bring them for their prompt (``add_request(..,
+    extras=..)``), rows without a value get their position, and a toy mixer reads them from the
+    step - cut into portions and mixed with other requests like everything else."""
+    toy_parts.register()
+    try:
+        plan = toy_parts.segment_plan()
+        args = backend_args(backend)
+        from shiso_llm_b200.parts import BuildEnv, Model
+        from shiso_llm_b200.weights.loader import target_dtype
+
+        specs = Model(plan, BuildEnv(torch.float32, torch.device("cpu"), None)).tensor_specs()
+        stored = random_tensors(specs, 8, 0.3, "bfloat16", 0.1)
+        ops = args["ops"]
+        if ops is None:
+            from shiso_llm_b200.kernels import ops
+        by_name = {s.name: s for s in specs}
+        tensors = {k: v.to(args["device"], target_dtype(by_name[k], v.dtype, torch.float32)) for k, v in stored.items()}
+        options = EngineOptions(dtype="float32", ctx=64, page_size=4, max_num_seqs=3, max_num_batched_tokens=32, device=args["device"])
+        engine = Engine.from_plan(plan, tensors, options, ops)
+        ids_a, ids_b = helpers.random_prompt(20, toy_parts.VOCAB, 1), helpers.random_prompt(9, toy_parts.VOCAB, 2)
+        seg_a = [(7 * i) % 11 for i in range(20)]
+        ref_a = toy_parts.segment_reference(stored, ids_a, seg_a)
+        ref_b = toy_parts.segment_reference(stored, ids_b, list(range(9)))  # no values given: the positions
+        steps = [
+            [StepEntry("a", ids_a[:6], list(range(6)), extras={"segment": seg_a[:6]}), StepEntry("b", ids_b[:4], list(range(4)))],
+            [StepEntry("b", ids_b[4:], list(range(5))), StepEntry("a", ids_a[6:19], list(range(13)), extras={"segment": seg_a[6:19]})],
+            [StepEntry("a", ids_a[19:], [0], extras={"segment": seg_a[19:]})],
+        ]
+        got_a, got_b = [], []
+        for entries in steps:
+            logits = engine.step(entries).cpu()
+            at = 0
+            for e in entries:
+                (got_a if e.request == "a" else got_b).append(logits[at : at + len(e.want)])
+                at += len(e.want)
+        check_logits(torch.cat(got_a), ref_a, "float32", "per-row input given by the entries")
+        check_logits(torch.cat(got_b), ref_b, "float32", "per-row input left to the positions")
+        with pytest.raises(ValueError, match="no per-row input named"):
+            engine.step([StepEntry("c", [1, 2], [], extras={"colour": [0, 0]})])
+        with pytest.raises(ValueError, match="values of 'segment' for 2 tokens"):
+            engine.step([StepEntry("c", [1, 2], [], extras={"segment": [0]})])
+        assert not engine.cache.has("c")
+        engine.finish("a"), engine.finish("b")
+
+        # through the entry point: the prompt's values come with the request, produced tokens get their position
+        def greedy(prompt, segments, steps):
+            seq, seg, out = list(prompt), list(segments), []
+            for _ in range(steps):
+                out.append(int(toy_parts.segment_reference(stored, seq, seg)[-1].argmax()))
+                seg.append(len(seq))
+                seq.append(out[-1])
+            return out
+
+        llm = LLM(engine, prefill_chunk=7)
+        llm.add_request(ids_a, SamplingParams(temperature=0.0, max_new_tokens=5), extras={"segment": seg_a})
+        llm.add_request(ids_b, SamplingParams(temperature=0.0, max_new_tokens=5))
+        done = []
+        while llm.has_unfinished():
+            done += llm.step()
+        done += llm.drain()
+        by_id = {o.request_id: o.token_ids for o in done}
+        assert by_id[0] == greedy(ids_a, seg_a, 5) and by_id[1] == greedy(ids_b, list(range(9)), 5)
+        with pytest.raises(ValueError, match="no per-row input"):
+            llm.add_request(ids_b, extras={"colour": [0] * 9})
+        refused = llm.add_request(ids_b, extras={"segment": [1, 2]})
+        assert refused.finish_reason == "error" and "values of 'segment'" in refused.error
+    finally:
+        toy_parts.unregister()

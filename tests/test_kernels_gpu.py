@@ -275,6 +275,34 @@ def test_norm_rope_store_then_attention(dtype, case):
         close(got, want, dtype, f"attention window {window}", rel32=4e-6)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(4, 2, 16, 4, 16), (6, 3, 48, 8, 32), (8, 2, 64, 16, 64), (5, 5, 80, 16, 40), (2, 1, 24, 4, 24)])
+def test_rotation_over_pairs_of_neighbours(dtype, case):
+    """A position encoding may pair neighbours (2i, 2i + 1) instead of (i, i + rotary_dim / 2):
+    the same kernel with the other pairing, also for bfloat16 heads of 64 (which otherwise take
+    the kernel that knows the half-split pairing only) and for a head size that is no multiple
+    of 16; and the two pairings differ."""
+    heads, kv_heads, d, page, rot = case
+    q_lens, starts = [3, 1, 9], [0, 20, 5]
+    cpu, gpu, table = make_step(q_lens, starts, page, 32, 190)
+    qkv = rnd((cpu.num_tokens, (heads + 2 * kv_heads) * d), dtype, 191)
+    qw, kw = 1.0 + 0.2 * rnd((d,), torch.float32, 192), 1.0 + 0.2 * rnd((d,), torch.float32, 193)
+    inv_freq = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float()
+    k0, v0 = rnd((32, page, kv_heads, d), dtype, 194), rnd((32, page, kv_heads, d), dtype, 195)
+    results = {}
+    for interleaved in (True, False):
+        kc, vc, kg, vg = k0.clone(), v0.clone(), k0.clone().cuda(), v0.clone().cuda()
+        want = ref.qk_norm_rope_store(qkv, heads, kv_heads, d, qw, kw, 1e-5, inv_freq, rot, cpu, kc, vc, table, page, True, interleaved)
+        got = ops().qk_norm_rope_store(qkv.cuda(), heads, kv_heads, d, qw.cuda(), kw.cuda(), 1e-5, inv_freq.cuda(), rot, gpu, kg, vg,
+                                       table.cuda(), page, True, interleaved=interleaved)
+        slack = 30 * 2.0 ** -24
+        close(got, want, dtype, f"q, interleaved={interleaved}", rel32=4e-6, slack=slack)
+        close(kg, kc, dtype, f"k cache, interleaved={interleaved}", rel32=4e-6, slack=slack)
+        assert torch.equal(vg.cpu(), vc)
+        results[interleaved] = got.float().cpu()
+    assert (results[True] - results[False]).abs().max() > 0.05
+
+
 @pytest.mark.parametrize("case", [(32, 8, 16), (12, 3, 8), (5, 1, 64), (7, 7, 32), (16, 1, 16)])
 @pytest.mark.parametrize("store", [True, False])
 def test_decode_attention_from_the_qkv_rows(case, store):

@@ -5,7 +5,8 @@ framework's files.  They are not models of anything; each comes with a plain ref
 ``decay_sum`` mixer: per-request state of its own (a running, decayed sum per channel),
 ``s_t = sigmoid(a) * s_{t-1} + x_t``, output ``W s_t``.
 ``routed_ff`` feed-forward: a router picks one of E small linear experts per token.
-``rope_linear`` position encoding: a partial rotation with a linear frequency ladder.
+``rope_linear`` position encoding: a partial rotation with a linear frequency ladder, over
+pairs of neighbouring elements (2i, 2i + 1) instead of the half-split pairs LFM2 uses.
 ``narrow_value_attention`` mixer: one head whose values are narrower than its keys, cached in
 an element type of its own (what a latent-KV mixer asks of the cache manager).
 ``decay_sum`` with ``grid``: the state is float64 and the mixer insists that every portion
@@ -101,6 +102,27 @@ class NarrowValueAttention(Mixer):
         return ops.linear(out.to(x.dtype), self.w["o"], self.env.dtype)
 
 
+class SegmentBias(Mixer):
+    """A mixer that reads a further per-row input of the step: ``W x + table[segment]`` with the
+    row's ``segment`` taken from ``step.extras["segment"]`` (modulo the table's rows)."""
+
+    graph_safe = False
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.rows, self.prefix = spec.params["hidden_size"], spec.params["rows"], spec.params["prefix"]
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.w.weight", (self.hidden, self.hidden)), TensorSpec(f"{self.prefix}.table.weight", (self.rows, self.hidden))]
+
+    def bind(self, tensors):
+        self.w, self.table = tensors[f"{self.prefix}.w.weight"], tensors[f"{self.prefix}.table.weight"]
+
+    def forward(self, x, step, cache):
+        segment = step.extras["segment"].long() % self.rows
+        return (self.env.ops.linear(x, self.w, torch.float32) + self.table[segment].float()).to(x.dtype)
+
+
 class RoutedFF(FeedForward):
     graph_safe = False
 
@@ -131,6 +153,7 @@ class RoutedFF(FeedForward):
 class RopeLinear(PositionEncoding):
     def __init__(self, spec, env, head_dim):
         super().__init__(spec, env)
+        self.interleaved = bool(spec.params.get("interleaved", False))
         self.rotary_dim = spec.params["rotary_dim"]
         n = self.rotary_dim // 2
         self.inv_freq = (spec.params["top"] * (1.0 - torch.arange(n, dtype=torch.float64) / n)).float().to(env.device)
@@ -142,6 +165,7 @@ class RopeLinear(PositionEncoding):
 def register():
     MIXERS.register("decay_sum", DecaySum)
     MIXERS.register("narrow_value_attention", NarrowValueAttention)
+    MIXERS.register("segment_bias", SegmentBias)
     FEED_FORWARDS.register("routed_ff", RoutedFF)
     POSITION_ENCODINGS.register("rope_linear", RopeLinear)
 
@@ -149,6 +173,7 @@ def register():
 def unregister():
     MIXERS.unregister("decay_sum")
     MIXERS.unregister("narrow_value_attention")
+    MIXERS.unregister("segment_bias")
     FEED_FORWARDS.unregister("routed_ff")
     POSITION_ENCODINGS.unregister("rope_linear")
 
@@ -171,7 +196,7 @@ def toy_plan() -> ModelPlan:
             "q_proj": f"{prefix}.q.weight", "k_proj": f"{prefix}.k.weight", "v_proj": f"{prefix}.v.weight",
             "out_proj": f"{prefix}.o.weight",
             "q_norm": norm(f"{prefix}.qn.weight", HEAD_DIM), "k_norm": None if borrows else norm(f"{prefix}.kn.weight", HEAD_DIM),
-            "position": PartSpec("rope_linear", {"rotary_dim": ROT, "top": 0.7}),
+            "position": PartSpec("rope_linear", {"rotary_dim": ROT, "top": 0.7, "interleaved": True}),
         })
 
     layers = (
@@ -207,8 +232,8 @@ def toy_reference(w, ids):
         angle = (pos.float()[:, None] * inv[None, :]).double()
         c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
         out = v.clone()
-        a, b = v[..., :n], v[..., n:ROT]
-        out[..., :n], out[..., n:ROT] = a * c - b * s, a * s + b * c
+        a, b = v[..., 0:ROT:2], v[..., 1:ROT:2]  # neighbours form a pair
+        out[..., 0:ROT:2], out[..., 1:ROT:2] = a * c - b * s, a * s + b * c
         return out
 
     def decay_sum(n):
@@ -306,4 +331,35 @@ def grid_reference(w, ids):
     q, k, v = (n @ w[f"l1.attn.{m}.weight"].T for m in "qkv")
     scores = (q @ k.T * 0.5).masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
     x = x + (torch.softmax(scores, -1) @ v) @ w["l1.attn.o.weight"].T
+    return rms(x, "final.weight") @ w["emb.weight"].T
+
+
+SEGMENTS = 5
+
+
+def segment_plan() -> ModelPlan:
+    """One layer whose mixer reads a further per-row input, ``segment``, that the plan names."""
+
+    def norm(name):
+        return PartSpec("rmsnorm", {"tensor": name, "size": HIDDEN, "eps": EPS})
+
+    layers = (LayerSpec("l0", PartSpec("pre_norm"), PartSpec("segment_bias", {"hidden_size": HIDDEN, "rows": SEGMENTS, "prefix": "l0.mix"}),
+                        norm("l0.n1.weight"), None, None),)
+    return ModelPlan(
+        architecture="ToySegmentForCausalLM", hidden_size=HIDDEN, vocab_size=VOCAB,
+        embedding=PartSpec("token_embedding", {"tensor": "emb.weight", "vocab_size": VOCAB, "hidden_size": HIDDEN}),
+        layers=layers, order=(RunEntry(0),), final_norm=norm("final.weight"),
+        head=PartSpec("linear_head", {"vocab_size": VOCAB, "hidden_size": HIDDEN, "tied_to": "emb.weight", "tensor": None}),
+        row_inputs=("segment",),
+    )
+
+
+def segment_reference(w, ids, segments):
+    w = {k: v.double() for k, v in w.items()}
+
+    def rms(x, name):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + EPS) * w[name]
+
+    x = w["emb.weight"][torch.as_tensor(ids)]
+    x = x + rms(x, "l0.n1.weight") @ w["l0.mix.w.weight"].T + w["l0.mix.table.weight"][torch.as_tensor(segments) % SEGMENTS]
     return rms(x, "final.weight") @ w["emb.weight"].T
