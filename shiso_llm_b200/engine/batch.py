@@ -268,12 +268,13 @@ class StepBuilder:
         real_wanted = sum(len(e.want) for e in entries)
         made_up = pad_seqs - real_seqs
         spare = pad_tokens - real_tokens
-        if made_up < 1 or spare < made_up or pad_wanted < real_wanted or pad_tokens > self.max_tokens or pad_seqs > self.max_seqs:
+        fits = (made_up == 0 and spare == 0) or (made_up >= 1 and spare >= made_up)
+        if not fits or pad_wanted < real_wanted or pad_tokens > self.max_tokens or pad_seqs > self.max_seqs:
             raise ValueError(f"a step of {real_tokens} tokens in {real_seqs} sequences does not fit the shape {pad}")
-        last = spare - (made_up - 1)  # rows of the last made-up sequence
+        last = spare - (made_up - 1) if made_up else 0  # rows of the last made-up sequence
         if last > len(cache.scratch_pages) * cache.page_size:
             raise ValueError(f"{last} padding rows in one sequence exceed the cache's scratch pages")
-        lens = lens + [1] * (made_up - 1) + [last]
+        lens = lens + ([1] * (made_up - 1) + [last] if made_up else [])
         starts = list(starts) + [0] * made_up
         width = self.fixed_width
         lay = MetaLayout(pad_tokens, pad_seqs, pad_wanted, self.num_groups, width, len(self.row_inputs))

@@ -176,7 +176,7 @@ class Engine:
             if options.graph_mixed_steps and cache.scratch_slot is not None:
                 from .graphs import StepGraphs, sequence_bucket, token_bucket
 
-                most_seqs = sequence_bucket(options.max_num_seqs + 1)
+                most_seqs = 2 * sequence_bucket(options.max_num_seqs)
                 padded_builder = StepBuilder(
                     cache, self.device, token_bucket(options.max_num_batched_tokens + most_seqs), most_seqs,
                     fixed_table_width=cache.max_blocks, row_inputs=row_inputs,

@@ -94,11 +94,25 @@ def token_bucket(tokens: int) -> int:
 
 
 def sequence_bucket(seqs: int) -> int:
-    """The captured sequence count: the next power of two, at least 2."""
-    n = 2
+    """The captured sequence count: the next power of two."""
+    n = 1
     while n < seqs:
         n *= 2
     return n
+
+
+def padded_shape(tokens: int, seqs: int) -> tuple:
+    """``(rows, sequences)`` a step of ``tokens`` rows in ``seqs`` sequences runs as.  Rows that
+    are added need a made-up sequence to belong to, and every made-up sequence a row; a step
+    that lies on the grid already (2,048 rows of one prompt) is taken as it is, so that padding
+    never costs a product another tile of tokens where it can be helped."""
+    many = sequence_bucket(seqs)
+    while True:
+        made_up = many - seqs
+        rows = token_bucket(tokens + made_up)
+        if made_up > 0 or rows == tokens:
+            return rows, many
+        many *= 2
 
 
 class StepGraphs:
@@ -134,9 +148,9 @@ class StepGraphs:
         """``(rows, sequences, wanted, long)`` the step is padded to, or None when it does not fit."""
         tokens = sum(len(e.tokens) for e in entries)
         wanted = sum(len(e.want) for e in entries)
-        seqs = sequence_bucket(len(entries) + 1)
-        rows = token_bucket(tokens + seqs - len(entries))
-        spare_last = rows - tokens - (seqs - len(entries) - 1)
+        rows, seqs = padded_shape(tokens, len(entries))
+        made_up = seqs - len(entries)
+        spare_last = rows - tokens - (made_up - 1) if made_up else 0
         if (rows > self.builder.max_tokens or seqs > self.builder.max_seqs or wanted > seqs
                 or spare_last > len(self.cache.scratch_pages) * self.cache.page_size):
             return None

@@ -375,7 +375,11 @@ def test_a_padded_step_leaves_the_entries_rows_as_they_are(tmp_path):
     same trace through padded steps and through plain steps gives the same logits, with the
     plain stand-in kernels on the CPU."""
     from shiso_llm_b200.engine.batch import StepBuilder
-    from shiso_llm_b200.engine.graphs import sequence_bucket, token_bucket
+    from shiso_llm_b200.engine.graphs import padded_shape
+
+    assert padded_shape(2048, 1) == (2048, 1) and padded_shape(512, 4) == (512, 4)  # on the grid already: taken as they are
+    assert padded_shape(2049, 1) == (2112, 2) and padded_shape(512, 3) == (576, 4) and padded_shape(70, 4) == (128, 8)
+    assert padded_shape(549, 38) == (576, 64) and padded_shape(5, 2) == (16, 4) and padded_shape(16, 2) == (16, 2)
 
     doc, seed = helpers.TINY["B"]
     tensors = helpers.make_folder(tmp_path, doc, seed)
@@ -388,8 +392,8 @@ def test_a_padded_step_leaves_the_entries_rows_as_they_are(tmp_path):
     rows, consumed = {}, {}
     for entries, end in replay.mixed_trace(requests, 7, 256):
         batch = [StepEntry(r, t, w[-1:]) for r, t, w in entries]  # at most one wanted row per sequence
-        seqs = sequence_bucket(len(batch) + 1)
-        shape = (token_bucket(sum(len(e.tokens) for e in batch) + seqs - len(batch)), seqs, seqs)
+        padded_rows, seqs = padded_shape(sum(len(e.tokens) for e in batch), len(batch))
+        shape = (padded_rows, seqs, seqs)
         starts = [engine.cache.append(e.request, len(e.tokens)) for e in batch]
         meta = builder.build(batch, starts, pad=shape)
         assert (meta.num_tokens, meta.num_seqs, meta.num_wanted) == shape and not meta.h_q_start

@@ -134,15 +134,19 @@ def test_linear_on_sm_pairs(shape):
     T, N, K = shape
     x, w = rnd((T, K), torch.bfloat16, 140), rnd((N, K), torch.bfloat16, 141, 0.05)
     bias = rnd((N,), torch.float32, 142)
+    # The tensor core rounds its float32 accumulator once per 16-wide k block, so the error of a
+    # float32 result grows with K: 1e-5 of the largest value was fixed for K up to 5,632 and is
+    # scaled from there for longer sums.
+    rel32 = 1e-5 * max(1.0, K / 5632)
     for out_dtype in (torch.bfloat16, torch.float32):
         got = ops().linear(x.cuda(), w.cuda(), out_dtype)
         ops().check_kernel_status()
-        close(got, ref.linear(x, w, out_dtype), out_dtype, f"pair linear {shape} -> {out_dtype}", rel32=1e-5)
+        close(got, ref.linear(x, w, out_dtype), out_dtype, f"pair linear {shape} -> {out_dtype}", rel32=rel32)
     got = ops().linear(x.cuda(), w.cuda(), torch.float32, bias.cuda())
-    close(got, ref.linear(x, w, torch.float32, bias), torch.float32, f"pair linear {shape} with bias", rel32=1e-5)
+    close(got, ref.linear(x, w, torch.float32, bias), torch.float32, f"pair linear {shape} with bias", rel32=rel32)
     # the rows of a long step are those of a short one (other kernel, same sums up to rounding)
     short = ops().linear(x[:100].contiguous().cuda(), w.cuda(), torch.float32, bias.cuda())
-    close(got[:100], short, torch.float32, "pair against single-SM kernel", rel32=1e-5)
+    close(got[:100], short, torch.float32, "pair against single-SM kernel", rel32=rel32)
 
 
 def test_linear_rows_do_not_depend_on_the_batch():
