@@ -513,10 +513,10 @@ int sm_count_of_device() {
 }
 
 // A plain product (p.inter == 0), with whatever epilogue mode p carries.
-int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStream_t stream) {
+int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStream_t stream, int tile_override = 0) {
     const int T = p.T, N = p.N, K = p.K;
     const int total_kb = (K + BK - 1) / BK;
-    const int bn = token_tile(T);
+    const int bn = tile_override > 0 ? tile_override : token_tile(T);
     CUtensorMap mw, mx;
     if (!tensor_map(w, N, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
 
@@ -525,9 +525,15 @@ int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStre
     // per SM; each CTA keeps >= 2 k blocks).  Any cluster size up to 8 will do: 48 feature tiles
     // take 3 CTAs each (144 CTAs), not 4 (192: a second wave for a quarter of the work).
     const int tiles = (int)ceil_div_u(N, BM) * (int)ceil_div_u(T, bn);
-    int splits = sm_count / (tiles > 0 ? tiles : 1);
+    // (portions of several token tiles: two CTAs are resident per SM and a long K is worth splitting
+    // further - 2048 x 5632 at 576 rows: 31.2 us whole, 22.2 us in two parts, 288 CTAs - but clusters of
+    // more than two on a grid near the 296 places wait for a second wave: 2,304 of K in 4 parts took
+    // 12.5 us as 256 CTAs and 22.1 us as 288)
+    const int room = tile_override > 0 ? 2 * sm_count : sm_count;
+    int splits = room / (tiles > 0 ? tiles : 1);
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
-    while (splits > 1 && total_kb / splits < 2) --splits;
+    while (tile_override > 0 && splits > 2 && tiles * splits > 7 * sm_count / 4) --splits;
+    while (splits > 1 && total_kb / splits < (tile_override > 0 ? 8 : 2)) --splits;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
 #define SHISO_PICK(BN_)                                                        \
     switch (splits) {                                                          \
@@ -586,6 +592,22 @@ SHISO_API int shiso_gemm_tcgen05(const void* x, const void* w, const float* bias
     p.bias = bias;
     p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     return run_plain(p, x, w, sm_count, stream);
+}
+
+// The same product with token tiles of 64 whatever T is.  For portions of a few hundred rows and a
+// matrix of few rows the kernels for long portions have a handful of 256 x 256 tiles for 148 SMs
+// (2,048 x 5632 at 512 rows: 16 tiles, 29.8 us measured on the 1,024-wide shape); here the same
+// product is ceil(N / 128) x ceil(T / 64) CTAs, with K split over a cluster while they are few.
+// The caller decides (kernels/ops.py).
+SHISO_API int shiso_gemm_tcgen05_tokens64(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T,
+                                          int N, int K, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return SHISO_OK;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    GemmParams p = blank_params(T, N, K);
+    p.y = y;
+    p.bias = bias;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    return run_plain(p, x, w, sm_count, stream, 64);
 }
 
 // silu(x gate^T) * (x up^T) for w = [gate; up] of shape [2 * inter, K]; y [T, inter].

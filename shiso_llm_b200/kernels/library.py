@@ -25,6 +25,7 @@ _SIGNATURES = {
     "shiso_swiglu": [P, P, I, I, I, P],
     "shiso_gemm_simple": [P, I, P, I, P, P, I, I, I, I, P],
     "shiso_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, P],
+    "shiso_gemm_tcgen05_tokens64": [P, P, P, P, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_swiglu": [P, P, P, I, I, I, I, P],
     "shiso_gemm_tcgen05_prompt": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_prefill_attention_tc_supported": [I, I],

@@ -196,6 +196,14 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 _SM_COUNT = None
 PROMPT_MIN_TOKENS = 193  # from here the persistent tensor-memory kernels (tokens as the MMA's M operand): plain products on pairs of SMs; below, 64-token tiles with K split over a cluster are faster
+# Portions of a few hundred rows times a matrix of few rows: the kernel for long portions would have a
+# handful of 256 x 256 tiles for 74 pairs of SMs and walk a long K alone.  Up to FEW_PAIR_TILES such
+# tiles, and while tiles of 128 features x 64 tokens stay within the CTAs that are resident at once, the
+# product runs as those tiles on single SMs with K split over a cluster (576 rows: 2048 x 5632 31.2 ->
+# 22.2 us, 2048 x 2048 14.9 -> 12.3 us, 3072 x 2048 17.2 -> 14.6 us; 1024 x 4608 at 512 rows 26.2 -> 12.5 us;
+# 6144 x 2048 at 512 rows would lose, 18.0 -> 28.2 us, and is left where it was).
+FEW_PAIR_TILES = 36
+FEW_TILES_MAX_TOKENS = 1024
 PAIR_MIN_TOKENS_GLU = 512  # gate/up pairs below this stay on single SMs: the pairs' 256-token tiles would leave a second, nearly empty wave
 
 
@@ -231,6 +239,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
         )
         _done(status, "linear (streaming)")
+        return out
+    if (
+        both_bf16 and PROMPT_MIN_TOKENS <= tokens <= FEW_TILES_MAX_TOKENS
+        and -(-tokens // 256) * -(-n // 256) <= FEW_PAIR_TILES and -(-tokens // 64) * -(-n // 128) <= 2 * _sm_count()
+        and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w))
+    ):
+        status = lib.shiso_gemm_tcgen05_tokens64(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _sm_count(), _stream()
+        )
+        _done(status, "linear (tcgen05, token tiles of 64)")
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05_pair(

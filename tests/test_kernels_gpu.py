@@ -126,11 +126,14 @@ def test_linear(shape, xw):
 
 @pytest.mark.parametrize("shape", [(512, 256, 64), (700, 1000, 264), (1030, 2048, 2048), (2048, 6144, 512), (515, 520, 5632),
                                    (193, 2048, 2048), (300, 776, 520), (600, 2048, 8192), (257, 16384, 2048)])
-def test_linear_on_sm_pairs(shape):
+def test_linear_on_sm_pairs(shape, monkeypatch):
     """From 193 bfloat16 rows a plain product runs on pairs of SMs (one 256-row tile per pair, each CTA
     loading half of both operands): row counts that leave the second CTA of the last pair with
     few or no rows, feature counts that leave its weight half partly or wholly outside the
     matrix, one and many k steps, more tiles than pairs; bfloat16 and float32 results, a bias."""
+    from shiso_llm_b200.kernels import ops as ops_module
+
+    monkeypatch.setattr(ops_module, "FEW_PAIR_TILES", 0)  # this kernel, also where the table would choose token tiles of 64
     T, N, K = shape
     x, w = rnd((T, K), torch.bfloat16, 140), rnd((N, K), torch.bfloat16, 141, 0.05)
     bias = rnd((N,), torch.float32, 142)
@@ -147,6 +150,33 @@ def test_linear_on_sm_pairs(shape):
     # the rows of a long step are those of a short one (other kernel, same sums up to rounding)
     short = ops().linear(x[:100].contiguous().cuda(), w.cuda(), torch.float32, bias.cuda())
     close(got[:100], short, torch.float32, "pair against single-SM kernel", rel32=rel32)
+
+
+@pytest.mark.parametrize("shape", [(576, 2048, 5632), (512, 1024, 4608), (300, 776, 520), (1000, 1000, 264), (193, 40, 72), (768, 3072, 1024),
+                                   (1024, 2048, 2048), (260, 6144, 2048), (640, 136, 8192)])
+def test_linear_of_a_few_hundred_rows_on_token_tiles_of_64(shape, monkeypatch):
+    """A portion of a few hundred rows times a matrix of few rows: the product runs as tiles of 128
+    features x 64 tokens on single SMs, K split over clusters of 1 to 8 CTAs, instead of a handful
+    of 256 x 256 tiles on pairs of SMs.  Row and feature counts that fill no tile, K of one block
+    and of many, both result types, a bias; and the same rows through the kernel for long portions."""
+    from shiso_llm_b200.kernels import ops as ops_module
+
+    T, N, K = shape
+    assert -(-T // 256) * -(-N // 256) <= ops_module.FEW_PAIR_TILES and T <= ops_module.FEW_TILES_MAX_TOKENS
+    x, w = rnd((T, K), torch.bfloat16, 143), rnd((N, K), torch.bfloat16, 144, 0.05)
+    bias = rnd((N,), torch.float32, 145)
+    rel32 = 1e-5 * max(1.0, K / 5632)
+    before = ops_module.launch_count
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = ops().linear(x.cuda(), w.cuda(), out_dtype)
+        ops().check_kernel_status()
+        close(got, ref.linear(x, w, out_dtype), out_dtype, f"token tiles of 64 {shape} -> {out_dtype}", rel32=rel32)
+    got = ops().linear(x.cuda(), w.cuda(), torch.float32, bias.cuda())
+    close(got, ref.linear(x, w, torch.float32, bias), torch.float32, f"token tiles of 64 {shape} with bias", rel32=rel32)
+    assert ops_module.launch_count - before == 3
+    monkeypatch.setattr(ops_module, "FEW_PAIR_TILES", 0)
+    pairs = ops().linear(x.cuda(), w.cuda(), torch.float32, bias.cuda())
+    close(got, pairs, torch.float32, "token tiles of 64 against SM pairs", rel32=rel32)
 
 
 def test_linear_rows_do_not_depend_on_the_batch():
