@@ -521,18 +521,18 @@ int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStre
     if (!tensor_map(w, N, K, BM, &mw) || !tensor_map(x, T, K, bn, &mx)) return SHISO_ERR_UNSUPPORTED;
 
     if (bn == 256) return launch<256, 4, 1>(mw, mx, p, stream);
-    // Few tokens: split K over a cluster so that the grid is one wave that covers the SMs (one CTA
-    // per SM; each CTA keeps >= 2 k blocks).  Any cluster size up to 8 will do: 48 feature tiles
-    // take 3 CTAs each (144 CTAs), not 4 (192: a second wave for a quarter of the work).
+    // Few tokens: split K over a cluster so that the grid covers the SMs, up to the two CTAs that are
+    // resident on each (every CTA keeps >= 2 k blocks; 48 feature tiles take 5 CTAs each, 240 CTAs:
+    // decode at batch 16 / 32 / 64 gained 2.2 / 3.8 / 1.8 % over one CTA per SM).
     const int tiles = (int)ceil_div_u(N, BM) * (int)ceil_div_u(T, bn);
     // (portions of several token tiles: two CTAs are resident per SM and a long K is worth splitting
     // further - 2048 x 5632 at 576 rows: 31.2 us whole, 22.2 us in two parts, 288 CTAs - but clusters of
     // more than two on a grid near the 296 places wait for a second wave: 2,304 of K in 4 parts took
     // 12.5 us as 256 CTAs and 22.1 us as 288)
-    const int room = tile_override > 0 ? 2 * sm_count : sm_count;
+    const int room = 2 * sm_count;
     int splits = room / (tiles > 0 ? tiles : 1);
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
-    while (tile_override > 0 && splits > 2 && tiles * splits > 7 * sm_count / 4) --splits;
+    while (splits > 2 && tiles * splits > 7 * sm_count / 4) --splits;
     while (splits > 1 && total_kb / splits < (tile_override > 0 ? 8 : 2)) --splits;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
 #define SHISO_PICK(BN_)                                                        \
