@@ -132,7 +132,7 @@ class StepGraphs:
     (crates/shiso-engine/src/layers.rs:861-1027) and captures decode passes only
     (crates/shiso-engine/src/stack.rs:1199-1239)."""
 
-    def __init__(self, model, cache, builder, max_graphs: int = 64):
+    def __init__(self, model, cache, builder, max_graphs: int = 32):
         self.model = model
         self.cache = cache
         self.builder = builder  # fixed table width, sized for the largest padded shape
