@@ -40,7 +40,17 @@
 // row: 30.0 against 26.7 us for the four products of a layer in a captured chain.)
 // (Asking, from inside this kernel, for the matrix the step reads next to be brought into L2 was
 // measured too - cp.async.bulk.prefetch.L2 over a slice per CTA - and made the whole step slower:
-// the stream already keeps memory busy, and the extra requests only delay its own rows.)
+// the stream already keeps memory busy, and the extra requests only delay its own rows.  Asked
+// for only by the producer warp after its own last copy, and only for the first 4 to 48 MB of the
+// matrix that comes next, it is no better: 29.3 us for the four products of a layer without,
+// 29.3 / 29.4 / 30.1 / 30.9 / 36.6 us with 4 / 8 / 16 / 24 / 48 MB.)
+// (Where a product's time goes, from %globaltimer stamps in a captured chain at 8 rows: a
+// successor's producer starts about 1 us before its predecessor's last CTA ends; its consumers
+// leave the dependency wait 0.5 to 0.8 us after that end; the activations they then ask for
+// arrive 1.0 to 1.3 us later, behind the 14 MB of weights the rings keep in flight; from the
+// first product to the last the stream runs at 4.9 to 5.4 TB/s; the epilogue of the last tile
+// takes 0.5 us.  Launching the successor at the predecessor's first cycle instead of after its
+// last copy moves none of these: 29.9 us a layer either way.)
 // (Built, measured and left out: all products between two attention kernels as ONE persistent
 // kernel - the producer warps walk the whole list of products without a stop, the consumers of
 // all CTAs meet at a counter in global memory between two products, six stages of 33 KB or
