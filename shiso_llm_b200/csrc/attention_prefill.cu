@@ -86,9 +86,9 @@ flash_prefill_kernel(PrefillArgs a) {
 
     // ---- which (sequence, tile) is this CTA?
     if (threadIdx.x == 0) {
-        // the last tiles of a portion have the most keys: they take the first CTAs, so that the
-        // grid's tail is made of short ones
-        int left = gridDim.x - 1 - blockIdx.x, found = -1, row0 = 0;
+        // the last tiles of a portion have the most keys: they take the first CTAs of every head
+        // chunk (the grid's fast index), so that the grid's tail is made of short ones
+        int left = gridDim.y - 1 - blockIdx.y, found = -1, row0 = 0;
         for (int s = 0; s < a.num_seqs; ++s) {
             const int tiles = (a.q_start[s + 1] - a.q_start[s] + BM - 1) / BM;
             if (left < tiles) {
@@ -111,8 +111,8 @@ flash_prefill_kernel(PrefillArgs a) {
     const int last_pos = first_pos + rows - 1;
     const int group = a.heads / a.kv_heads;
     const int chunks = (group + HG - 1) / HG;          // head chunks per KV head
-    const int kv_head = blockIdx.y / chunks;
-    const int head0 = kv_head * group + (blockIdx.y % chunks) * HG;
+    const int kv_head = blockIdx.x / chunks;
+    const int head0 = kv_head * group + (blockIdx.x % chunks) * HG;
     const int heads_here = min(HG, kv_head * group + group - head0);
     const int* table = a.block_table + (size_t)seq * a.width;
     const int key_lo = a.window > 0 ? max(0, first_pos + 1 - a.window) : 0;  // the smallest key any row sees
@@ -314,7 +314,7 @@ int launch_heads(const PrefillArgs& a, int tiles, cudaStream_t stream) {
         }
     }
     const int group = a.heads / a.kv_heads;
-    dim3 grid(tiles, a.kv_heads * ((group + HG - 1) / HG));
+    dim3 grid(a.kv_heads * ((group + HG - 1) / HG), tiles);
     launch_kernel(kernel, grid, HG * 128, SMEM, stream, a);
     return launch_status();
 }
@@ -341,7 +341,7 @@ SHISO_API int shiso_prefill_attention(const void* q, const void* k_cache, const 
                                       float scale, int window, cudaStream_t stream) {
     if (num_seqs <= 0 || max_tiles <= 0) return SHISO_OK;
     if (kv_heads <= 0 || heads % kv_heads) return SHISO_ERR_SHAPE;
-    if (head_dim % 16 || head_dim < 16 || head_dim > 128) return SHISO_ERR_UNSUPPORTED;
+    if (head_dim % 16 || head_dim < 16 || head_dim > 128 || max_tiles > 65535) return SHISO_ERR_UNSUPPORTED;
     PrefillArgs a;
     a.q = (const __nv_bfloat16*)q;
     a.k_cache = (const __nv_bfloat16*)k_cache;

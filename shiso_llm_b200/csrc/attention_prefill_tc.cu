@@ -105,8 +105,11 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_init(o_full, 1);
         shared_ints[0] = 0;
         // which (sequence, tile) is this CTA?  The last tiles of a portion have the most keys:
-        // they take the first CTAs, so that the grid's tail is made of short ones.
-        int left = gridDim.x - 1 - blockIdx.x, found = -1, row0 = 0;
+        // they take the first CTAs - of every head, the head being the grid's fast index - so
+        // that the grid's tail is made of short ones.  (With the tile as the fast index each
+        // head's long tiles came after the short ones of the head before, the last heads began
+        // their longest tiles in the second wave, and a 2,048-row portion took 85 us, not 52.)
+        int left = gridDim.y - 1 - blockIdx.y, found = -1, row0 = 0;
         for (int s = 0; s < a.num_seqs; ++s) {
             const int tiles = (a.q_start[s + 1] - a.q_start[s] + BQ - 1) / BQ;
             if (left < tiles) {
@@ -138,7 +141,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int rows = min(BQ, a.q_start[seq + 1] - first_token);
     const int first_pos = a.start_pos[seq] + row0;
     const int last_pos = first_pos + rows - 1;
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kv_head = head / (a.heads / a.kv_heads);
     const int key_lo = a.window > 0 ? max(0, first_pos + 1 - a.window) : 0;  // the smallest key any row sees
     const int tile_first = key_lo / BKEY, tile_last = last_pos / BKEY;
@@ -381,7 +384,7 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
                                          cudaStream_t stream) {
     if (num_seqs <= 0 || max_tiles <= 0 || tokens <= 0) return SHISO_OK;
     if (kv_heads <= 0 || heads % kv_heads) return SHISO_ERR_SHAPE;
-    if (!shiso_prefill_attention_tc_supported(HEAD, page_size)) return SHISO_ERR_UNSUPPORTED;
+    if (!shiso_prefill_attention_tc_supported(HEAD, page_size) || max_tiles > 65535) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SHISO_ERR_ALIGN;
     const long long cache_rows = num_pages * page_size;
     if (cache_rows + page_size > 0x7fffffffLL) return SHISO_ERR_UNSUPPORTED;
@@ -412,7 +415,7 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(max_tiles, heads);
+    cfg.gridDim = dim3(heads, max_tiles);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
