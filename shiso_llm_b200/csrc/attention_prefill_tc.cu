@@ -67,6 +67,42 @@ __device__ __forceinline__ void tmem_ld_pin32(uint32_t* r) {
     tmem_ld_pin(r + 16);
 }
 
+// The softmax is bound by the instructions it issues, so it is written with the widest ones the
+// SM has: a maximum of three, and multiply-add / add on pairs of floats held in a 64-bit register.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 // (the bound of 256 threads caps the registers at 128: registers are handed out for groups of four
 // warps, so a CTA of six warps takes as many as one of eight, and two CTAs must fit an SM)
 __global__ void __launch_bounds__(256, 2)
@@ -235,27 +271,28 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             float alpha = 1.0f, tile_sum = 0.0f, new_max = row_max;
             auto softmax_tile = [&](auto open_tag) {
                 constexpr bool OPEN = decltype(open_tag)::value;
-                uint32_t raw[32], ahead[32];
-                // pass 1: the row's maximum over the tile (the next 32 columns travel while these are read)
+                // Two register blocks of 32 columns take turns: one travels from tensor memory
+                // while the other is worked on.
+                uint32_t blk_a[32], blk_b[32];
+                auto seen = [&](int key) { return key <= my_pos && (a.window <= 0 || key > my_pos - a.window); };
+                // pass 1: the row's maximum over the tile
                 float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one of 128 links
-                tmem_ld32_issue(lane_base, ahead);
-#pragma unroll 1
-                for (int c = 0; c < BKEY; c += 32) {
-                    tmem_ld_wait();
-                    tmem_ld_pin32(ahead);
+                auto max_block = [&](const uint32_t* raw, int c) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) raw[i] = ahead[i];
-                    tmem_ld32_issue(lane_base + (c + 32 < BKEY ? c + 32 : 0), ahead);  // the last one is pass 2's first
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        bool seen = true;
+                    for (int i = 0; i < 32; i += 2) {
+                        float v0 = __uint_as_float(raw[i]), v1 = __uint_as_float(raw[i + 1]);
                         if (!OPEN) {
-                            const int key = key0 + c + i;
-                            seen = key <= my_pos && (a.window <= 0 || key > my_pos - a.window);
+                            if (!seen(key0 + c + i)) v0 = -INFINITY;
+                            if (!seen(key0 + c + i + 1)) v1 = -INFINITY;
                         }
-                        if (seen) part_max[i & 3] = fmaxf(part_max[i & 3], __uint_as_float(raw[i]));
+                        part_max[(i >> 1) & 3] = max3(part_max[(i >> 1) & 3], v0, v1);
                     }
-                }
+                };
+                tmem_ld32_issue(lane_base, blk_a);
+                tmem_ld_wait(); tmem_ld_pin32(blk_a); tmem_ld32_issue(lane_base + 32, blk_b); max_block(blk_a, 0);
+                tmem_ld_wait(); tmem_ld_pin32(blk_b); tmem_ld32_issue(lane_base + 64, blk_a); max_block(blk_b, 32);
+                tmem_ld_wait(); tmem_ld_pin32(blk_a); tmem_ld32_issue(lane_base + 96, blk_b); max_block(blk_a, 64);
+                tmem_ld_wait(); tmem_ld_pin32(blk_b); tmem_ld32_issue(lane_base, blk_a); max_block(blk_b, 96);  // pass 2's first block is on its way
                 // the scale is positive: the maximum commutes with it
                 const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * a.scale_log2;
                 new_max = fmaxf(row_max, tile_max);
@@ -266,41 +303,38 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     if (!mbar_wait(o_full, (it - 1) & 1)) failed = true;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
-                        // some row of this warp has a new maximum: O *= exp2(old - new), in tensor memory
+                        // some row of this warp has a new maximum: O *= exp2(old - new), in tensor
+                        // memory (block a is on its way: its wait comes first, block b is free)
+                        tmem_ld_wait();
 #pragma unroll 1
                         for (int c = 0; c < HEAD; c += 32) {
-                            tmem_ld32_issue(lane_base + BKEY + c, raw);
+                            tmem_ld32_issue(lane_base + BKEY + c, blk_b);
                             tmem_ld_wait();
-                            tmem_ld_pin32(raw);
+                            tmem_ld_pin32(blk_b);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
-                            tmem_st32(lane_base + BKEY + c, raw);
+                            for (int i = 0; i < 32; ++i) blk_b[i] = __float_as_uint(__uint_as_float(blk_b[i]) * alpha);
+                            tmem_st32(lane_base + BKEY + c, blk_b);
                         }
                         tmem_st_wait();
                     }
                 }
                 // pass 2: exponentials, their sum, and P into shared memory
-                float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 1
-                for (int c = 0; c < BKEY; c += 32) {
-                    tmem_ld_wait();
-                    tmem_ld_pin32(ahead);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) raw[i] = ahead[i];
-                    if (c + 32 < BKEY) tmem_ld32_issue(lane_base + c + 32, ahead);
+                const uint64_t scale2 = pack2(a.scale_log2, a.scale_log2), minus_base2 = pack2(-base, -base);
+                uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+                auto exp_block = [&](const uint32_t* raw, int c) {
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float p0 = ex2(__uint_as_float(raw[i]) * a.scale_log2 - base);
-                        float p1 = ex2(__uint_as_float(raw[i + 1]) * a.scale_log2 - base);
+                        float p0, p1;
+                        unpack2(fma2(pack2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), scale2, minus_base2), p0, p1);
+                        p0 = ex2(p0);
+                        p1 = ex2(p1);
                         if (!OPEN) {
-                            const int key = key0 + c + i;
-                            if (!(key <= my_pos && (a.window <= 0 || key > my_pos - a.window))) p0 = 0.0f;
-                            if (!(key + 1 <= my_pos && (a.window <= 0 || key + 1 > my_pos - a.window))) p1 = 0.0f;
+                            if (!seen(key0 + c + i)) p0 = 0.0f;
+                            if (!seen(key0 + c + i + 1)) p1 = 0.0f;
                         }
-                        part_sum[(i >> 1) & 3] += p0 + p1;
-                        __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+                        sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
+                        packed[i >> 1] = bf16x2(p0, p1);
                     }
                     // 32 keys = four 16-byte chunks of this row, in the block of 64 keys they belong to
 #pragma unroll
@@ -309,8 +343,15 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                         uint8_t* dst = p_s + (chunk >> 3) * (BQ * ROW) + r * ROW + (((chunk & 7) ^ (r & 7)) << 4);
                         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                     }
-                }
-                tile_sum = (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
+                };
+                tmem_ld_wait(); tmem_ld_pin32(blk_a); tmem_ld32_issue(lane_base + 32, blk_b); exp_block(blk_a, 0);
+                tmem_ld_wait(); tmem_ld_pin32(blk_b); tmem_ld32_issue(lane_base + 64, blk_a); exp_block(blk_b, 32);
+                tmem_ld_wait(); tmem_ld_pin32(blk_a); tmem_ld32_issue(lane_base + 96, blk_b); exp_block(blk_a, 64);
+                tmem_ld_wait(); tmem_ld_pin32(blk_b); exp_block(blk_b, 96);
+                float s0, s1, s2, s3;
+                unpack2(sum2[0], s0, s1);
+                unpack2(sum2[1], s2, s3);
+                tile_sum = (s0 + s1) + (s2 + s3);
             };
             if (open) softmax_tile(std::true_type{});
             else softmax_tile(std::false_type{});
