@@ -241,6 +241,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int it = 0; it < num_tiles; ++it) {
                 const int s = it & 1;
                 if (!mbar_wait(p_full, it & 1)) failed = true;   // P is written, S and O_tile are read
+                // the next tile's scores first: its softmax can begin while P V is still running
+                if (it + 1 < num_tiles) scores(it + 1);
                 if (!mbar_wait(&v_full[0], it & 1)) failed = true;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = smem_u32(v_s);
@@ -250,7 +252,6 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                               idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(o_full);
                 umma_commit(&v_empty[0]);
-                if (it + 1 < num_tiles) scores(it + 1);
             }
         }
     } else {
