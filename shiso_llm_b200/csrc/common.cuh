@@ -4,7 +4,8 @@
 // Sums, norm statistics, softmax, rotation angles and the residual stream are
 // always float.  No file is built with --use_fast_math: expf, sinf, cosf and
 // rsqrtf below are the accurate library entries, as the reference keeps them for
-// its attention and rotation kernels (kernels/cuda/dense/KERNEL.toml:20-36).
+// its attention and rotation kernels (kernels/cuda/dense/KERNEL.toml:20-36).  The exceptions
+// say so where they stand: exponentials of the tensor-memory prompt attention, and silu_times.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -60,6 +61,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     float total = (lane < nwarps) ? scratch[lane] : 0.0f;
     total = warp_sum(total);
     return total;
+}
+
+// silu(g) * u in the epilogue of a bfloat16 gate/up product, with the exponential and the
+// reciprocal from the special-function unit (relative error about 2^-22, far below the bfloat16
+// the result is rounded to).  The library's expf and an IEEE division took 8.7 us for the last
+// 128 x 128 tile of a CTA of the prompt kernels: one warp to a scheduler, and nothing to hide
+// their latency behind.  (The float32 path keeps expf and the division.)
+__device__ __forceinline__ float silu_times(float g, float u) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r * u;
 }
 
 // ---- programmatic dependent launch ---------------------------------------------------------

@@ -493,7 +493,7 @@ gemm_stream_kernel(StreamArgs a) {
                 }
                 if (a.mode == MODE_GLU) {
                     if (rows[0] >= 0) {
-                        const float v = lo / (1.0f + expf(-lo)) * hi;
+                        const float v = silu_times(lo, hi);
                         const size_t at = (size_t)token * a.inter + rows[0];
                         if (a.out_f32) ((float*)a.y)[at] = v;
                         else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);

@@ -294,7 +294,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             gate[j] *= sc;
                             up[j] *= sc;
                         }
-                        const float v = gate[j] / (1.0f + expf(-gate[j])) * up[j];
+                        const float v = silu_times(gate[j], up[j]);
                         const size_t at = (size_t)token * p.inter + feature;
                         if (p.out_f32) store_out<float>((float*)p.y, at, v);
                         else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v);
@@ -386,7 +386,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (scaled) sum[t] *= scale_s[j % MAX_FUSED_BN];
             }
             float v = sum[0] + b;
-            if (GLU) v = sum[0] / (1.0f + expf(-sum[0])) * sum[A_TILES - 1];
+            if (GLU) v = silu_times(sum[0], sum[A_TILES - 1]);
             if (into) {
                 join_stream(token0 + j, v, before);
             } else if (live) {

@@ -127,25 +127,43 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     }
 }
 
+// 32 bytes in one store: a whole sector per thread.  (With two 16-byte stores per sector the last
+// 128 x 256 tile of a CTA - every CTA writes its last tile at the same time - took 3.6 to 5.0 us
+// from the last MMA to the last store, 1.5 us with the stores taken out and 3.1 us with these.
+// Turning a warp's rows through shared memory so that every store instruction writes whole
+// 128-byte lines was no faster, 3.3 to 3.6 us: what is left is the 9 MB that all CTAs write at once.)
+__device__ __forceinline__ void store32(void* dst, const uint32_t* r) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(dst), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ void store16(const PairParams& p, int token, int feature, const float* v) {
     // 16 consecutive features of one token; rows of y are 16-byte aligned (N % 8 == 0 is checked on the host)
     if (feature + 16 <= p.N) {
         if (p.out_f32) {
-            float4* dst = reinterpret_cast<float4*>((float*)p.y + (size_t)token * p.N + feature);
+            float* dst = (float*)p.y + (size_t)token * p.N + feature;
+            if (((uintptr_t)dst & 31) == 0) {
+                store32(dst, reinterpret_cast<const uint32_t*>(v));
+                store32(dst + 8, reinterpret_cast<const uint32_t*>(v + 8));
+            } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else {
-            uint4 lo, hi;
-            __nv_bfloat162* l = reinterpret_cast<__nv_bfloat162*>(&lo);
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&hi);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                l[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                h[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
+                for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
             }
-            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.y + (size_t)token * p.N + feature);
-            dst[0] = lo;
-            dst[1] = hi;
+        } else {
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                packed[i] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.y + (size_t)token * p.N + feature;
+            if (((uintptr_t)dst & 31) == 0) {
+                store32(dst, packed);
+            } else {
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
         }
     } else {
 #pragma unroll
@@ -303,7 +321,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     const int feature = n0 + c + 16 * q;
                     if (GLU) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * __uint_as_float(r[q + 2][i]);
+                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]));
                     } else if (p.bias) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)

@@ -213,7 +213,7 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     const int feature = n0 + c + 16 * q;
                     if (GLU) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * __uint_as_float(r[q + 2][i]);
+                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]));
                     } else if (p.bias) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
