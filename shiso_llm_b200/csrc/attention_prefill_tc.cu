@@ -40,10 +40,9 @@ constexpr int HEAD = 64;  // head size
 constexpr int ROW = 128;  // bytes per row of a tile (64 bf16)
 constexpr int Q_BYTES = BQ * ROW;
 constexpr int KV_BYTES = BKEY * ROW;
-constexpr int P_BYTES = 2 * BQ * ROW;  // two blocks of 64 keys
 constexpr int THREADS = 192;           // warps 0-3 softmax, 4 producer, 5 MMA
-constexpr int SMEM_BYTES = Q_BYTES + 3 * KV_BYTES + P_BYTES + 1024 + 256;  // 97.25 KB: two CTAs per SM
-constexpr int TMEM_COLS = 256;         // 128 for S, 64 for O_tile
+constexpr int SMEM_BYTES = Q_BYTES + 3 * KV_BYTES + 1024 + 256;  // two CTAs per SM
+constexpr int TMEM_COLS = 256;         // 128 for S, 64 for O, 64 for P (two bfloat16 a column)
 
 struct TcArgs {
     const int* block_table;  // [S, width]
@@ -54,7 +53,10 @@ struct TcArgs {
     int width, num_seqs, heads, kv_heads, page_size, window;
     int cache_rows;          // pages * page size: a row coordinate from here on reads zeros
     float scale_log2;        // scale * log2(e)
+    long long* stamps;
 };
+long long* g_stamps = nullptr;
+#define CK(i) do { if (a.stamps && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && it == 8) a.stamps[i] = clock64(); } while (0)
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -113,8 +115,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Q_BYTES;        // [2][KV_BYTES]
     uint8_t* v_s = k_s + 2 * KV_BYTES;   // one stage: the value tile is wanted only after the softmax
-    uint8_t* p_s = v_s + KV_BYTES;       // [2 blocks][BQ][ROW]
-    uint64_t* bars = (uint64_t*)(p_s + P_BYTES);
+    uint64_t* bars = (uint64_t*)(v_s + KV_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;   // [2]
     uint64_t* k_empty = bars + 3;  // [2]
@@ -223,8 +224,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(BQ, BKEY);
             const uint32_t idesc_o = umma_idesc(BQ, HEAD) | (1u << 16);  // B (the value tile) is MN-major
-            const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + BKEY;
-            const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+            const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + BKEY, p_tmem = tmem_base + BKEY + HEAD;
+            const uint32_t q_addr = smem_u32(q_s);
             auto scores = [&](int it) {
                 const int s = it & 1;
                 if (!mbar_wait(&k_full[s], (it >> 1) & 1)) failed = true;
@@ -248,8 +249,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const uint32_t v_addr = smem_u32(v_s);
 #pragma unroll
                 for (int ks = 0; ks < BKEY / UMMA_K; ++ks)
-                    umma_bf16(o_tmem, umma_desc(p_addr + (ks >> 2) * (BQ * ROW) + (ks & 3) * 32), umma_desc(v_addr + ks * 16 * ROW),
-                              idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
+                    umma_bf16_a_tmem(o_tmem, p_tmem + ks * (UMMA_K / 2), umma_desc(v_addr + ks * 16 * ROW), idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(o_full);
                 umma_commit(&v_empty[0]);
             }
@@ -265,8 +265,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const int key0 = (tile_first + it) * BKEY;
             // every key of the tile is seen by every row of the CTA: no mask, nothing to zero
             const bool open = key0 + BKEY - 1 <= first_pos && (a.window <= 0 || key0 > first_pos + BQ - 1 - a.window);
+            CK(0);
             if (!mbar_wait(s_full, it & 1)) failed = true;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            CK(1);
             // The two passes over the row's scores, compiled twice: for a tile every row sees whole
             // (OPEN, most of them) without a single comparison, and with the mask.
             float alpha = 1.0f, tile_sum = 0.0f, new_max = row_max;
@@ -299,6 +301,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 new_max = fmaxf(row_max, tile_max);
                 const float base = new_max == -INFINITY ? 0.0f : new_max;  // a row that has seen nothing yet
                 alpha = ex2(row_max - base);                               // exp2(-inf) = 0 on the first tile
+                CK(2);
                 if (it > 0) {
                     // the product of the tile before is complete: O may be rescaled, P overwritten
                     if (!mbar_wait(o_full, (it - 1) & 1)) failed = true;
@@ -319,6 +322,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                         tmem_st_wait();
                     }
                 }
+                CK(3);
                 // pass 2: exponentials, their sum, and P into shared memory
                 const uint64_t scale2 = pack2(a.scale_log2, a.scale_log2), minus_base2 = pack2(-base, -base);
                 uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
@@ -337,18 +341,14 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                         sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
                         packed[i >> 1] = bf16x2(p0, p1);
                     }
-                    // 32 keys = four 16-byte chunks of this row, in the block of 64 keys they belong to
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int chunk = (c >> 3) + q;  // 0..15 over the tile
-                        uint8_t* dst = p_s + (chunk >> 3) * (BQ * ROW) + r * ROW + (((chunk & 7) ^ (r & 7)) << 4);
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                    }
+                    // 32 keys = 16 columns of this lane's row of P
+                    tmem_st16(lane_base + BKEY + HEAD + (c >> 1), packed);
                 };
                 tmem_ld_wait(); tmem_ld_pin32(blk_a); tmem_ld32_issue(lane_base + 32, blk_b); exp_block(blk_a, 0);
                 tmem_ld_wait(); tmem_ld_pin32(blk_b); tmem_ld32_issue(lane_base + 64, blk_a); exp_block(blk_b, 32);
                 tmem_ld_wait(); tmem_ld_pin32(blk_a); tmem_ld32_issue(lane_base + 96, blk_b); exp_block(blk_a, 64);
                 tmem_ld_wait(); tmem_ld_pin32(blk_b); exp_block(blk_b, 96);
+                CK(4);
                 float s0, s1, s2, s3;
                 unpack2(sum2[0], s0, s1);
                 unpack2(sum2[1], s2, s3);
@@ -368,10 +368,12 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     for (int i = 0; i < ROW / 16; ++i) row[i] = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and V) written by threads, read by the MMA
+            tmem_st_wait();  // P is in tensor memory
+            if (!open) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // value rows zeroed by threads, read by the MMA
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
+            CK(5);
 
         }
         pdl_trigger();
@@ -411,6 +413,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
 }  // namespace
 
+SHISO_API int shiso_flash_set_stamps(long long* ptr) { g_stamps = ptr; return 0; }
+
 // Whether the tensor-memory kernel takes this case (the caller falls back to the mma.sync kernel).
 SHISO_API int shiso_prefill_attention_tc_supported(int head_dim, int page_size) {
     return head_dim == HEAD && page_size >= 8 && page_size <= BKEY && page_size % 8 == 0 && BKEY % page_size == 0 &&
@@ -448,6 +452,7 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
     a.window = window;
     a.cache_rows = (int)cache_rows;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.stamps = g_stamps;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
