@@ -288,11 +288,13 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     if (!(key <= my_pos && (a.window <= 0 || key > my_pos - a.window))) sv[i] = __float_as_uint(-INFINITY);
                 }
             }
-            float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one of 64 links
+            float part_max[8];  // eight chains of four links, not one of 64
 #pragma unroll
-            for (int i = 0; i < BKEY; i += 2) part_max[(i >> 1) & 3] = max3(part_max[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+            for (int j = 0; j < 8; ++j) part_max[j] = fmaxf(__uint_as_float(sv[2 * j]), __uint_as_float(sv[2 * j + 1]));
+#pragma unroll
+            for (int i = 16; i < BKEY; i += 2) part_max[(i >> 1) & 7] = max3(part_max[(i >> 1) & 7], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
             // the scale is positive: the maximum commutes with it
-            const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * a.scale_log2;
+            const float tile_max = fmaxf(max3(part_max[0], part_max[1], part_max[2]), max3(max3(part_max[3], part_max[4], part_max[5]), part_max[6], part_max[7])) * a.scale_log2;
             // raised only by a tile that exceeds it clearly (the comparison is false for a row that
             // has seen nothing in this tile either: minus infinity on both sides)
             const float new_max = tile_max - row_max > RAISE_STEP ? tile_max : row_max;

@@ -29,8 +29,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Waits for the phase with the given parity, at most `limit` clock cycles; false when they ran out.
 __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, unsigned long long limit) {
     const uint32_t addr = smem_u32(bar);
-    const unsigned long long start = clock64();
-    while (true) {
+    auto probe = [&]() {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -39,7 +38,12 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, 
             : "=r"(done)
             : "r"(addr), "r"(parity)
             : "memory");
-        if (done) return true;
+        return done != 0;
+    };
+    if (probe()) return true;  // the common case reads no clock
+    const unsigned long long start = clock64();
+    while (true) {
+        if (probe()) return true;
         if (clock64() - start > limit) return false;
     }
 }
