@@ -6,12 +6,16 @@
 // first version gave a CTA 16 weight rows and let it ask for all of them at once; a matrix of
 // more than two such CTAs per SM then runs in waves, and every wave pays the memory latency
 // again.)  One CTA per SM walks its share of the 16-row tiles.  A producer warp - lane r copies
-// weight row r - keeps a ring of three shared-memory stages full with bulk copies
-// (cp.async.bulk, 1,024 columns of a row each, completion counted on an mbarrier), up to 96 KB
+// weight row r - keeps a ring of four shared-memory stages full with bulk copies
+// (cp.async.bulk, 1,024 columns of a row each, completion counted on an mbarrier), up to 129 KB
 // ahead of the consumers and independent of them; it starts before the predecessor in the
-// dependent-launch chain has finished, and because a CTA takes less than half of an SM's shared
-// memory and registers, the successor's CTA moves in beside it and starts its own stream under
-// this one's tail.  Four consumer warps split a chunk's columns (256 each), read their 16-byte
+// dependent-launch chain has finished, as soon as that kernel's CTA has left the SM.  (Three
+// stages let the successor's CTA move in beside this one and start its own stream under this
+// one's tail; the deeper ring is worth more: 26.4 against 28.4 us for the four products of a
+// layer, and five or six stages are no better than four, 27.0 and 26.9 us.  Memory answers a
+// request in about 2 us when it is this busy, so 6.5 TB/s want some 13 MB on their way, and
+// three stages on 148 SMs are 14.6 MB only while every stage is being filled.)
+// Four consumer warps split a chunk's columns (256 each), read their 16-byte
 // pieces of the two weight rows a lane owns from shared memory (rows are padded by 16 bytes,
 // which spreads them over the banks) and feed mma.sync m16n8k16: weights are the M operand, tokens
 // the N operand; a lane's 8 consecutive k values feed two MMAs as (k0..k3 | k4..k7) and the
@@ -80,7 +84,7 @@ constexpr int KC = 1024;                       // columns per stage
 constexpr int ROWS = 16;                       // weight rows per tile
 constexpr int ROW_BYTES = KC * 2 + 16;         // padded row of a stage
 constexpr int STAGE_BYTES = ROWS * ROW_BYTES;  // 33,024
-constexpr int STAGES = 3;                      // two CTAs (this kernel's and its successor's) must fit an SM
+constexpr int STAGES = 4;                      // measured: 3 (two CTAs fit an SM), 5 and 6 are slower
 constexpr int CONSUMERS = 4;                   // warps; each takes 256 columns of a chunk
 constexpr int KB = KC / CONSUMERS / 64;        // 64-wide k blocks per warp and chunk
 constexpr int THREADS = (CONSUMERS + 1) * 32;
