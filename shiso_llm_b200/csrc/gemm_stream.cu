@@ -14,7 +14,8 @@
 // one's tail; the deeper ring is worth more: 26.4 against 28.4 us for the four products of a
 // layer, and five or six stages are no better than four, 27.0 and 26.9 us.  Memory answers a
 // request in about 2 us when it is this busy, so 6.5 TB/s want some 13 MB on their way, and
-// three stages on 148 SMs are 14.6 MB only while every stage is being filled.)
+// three stages on 148 SMs are 14.6 MB only while every stage is being filled.  Three stages
+// of 2,048 columns - whole rows of a 2048-wide matrix in one copy - took 29.0 us.)
 // Four consumer warps split a chunk's columns (256 each), read their 16-byte
 // pieces of the two weight rows a lane owns from shared memory (rows are padded by 16 bytes,
 // which spreads them over the banks) and feed mma.sync m16n8k16: weights are the M operand, tokens

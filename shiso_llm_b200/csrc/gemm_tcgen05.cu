@@ -422,8 +422,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // ---------------------------------------------------------------------------- host side
 
-template <int BN, int STAGES, int SPLITS, bool GLU = false>
+constexpr int SPLIT_STAGES = 6, WHOLE_STAGES = 8;  // wanted; see fit_stages
+
+// Stages of a CTA: for plain products as many (up to `wanted`) as leave room for a second CTA on
+// the SM, for gate/up pairs, whose CTA has an SM to itself anyway, as many as fit.
+constexpr int fit_stages(int wanted, int bn, int splits, bool glu) {
+    const int stage = (glu ? 2 : 1) * BM * BK * 2 + bn * BK * 2;
+    const int inbox = splits > 1 ? (glu ? 2 : 1) * splits * ((bn + splits - 1) / splits) * BM * 4 : 0;
+    const int room = glu ? 227 * 1024 : 113 * 1024;
+    int stages = wanted;
+    while (stages > 3 && stages * stage + inbox + 2560 > room) --stages;
+    return stages;
+}
+
+template <int BN, int WANTED_STAGES, int SPLITS, bool GLU = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
+    constexpr int STAGES = fit_stages(WANTED_STAGES, BN, SPLITS, GLU);
     constexpr int STAGE_BYTES = (GLU ? 2 : 1) * BM * BK * 2 + BN * BK * 2;
     constexpr int PARTIAL_BYTES = SPLITS > 1 ? (GLU ? 2 : 1) * SPLITS * ((BN + SPLITS - 1) / SPLITS) * BM * 4 : 0;
     constexpr int TILE_BYTES = STAGES * STAGE_BYTES + PARTIAL_BYTES;
@@ -537,14 +551,14 @@ int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStre
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
 #define SHISO_PICK(BN_)                                                        \
     switch (splits) {                                                          \
-        case 1: return launch<BN_, 4, 1>(mw, mx, p, stream);                   \
-        case 2: return launch<BN_, 3, 2>(mw, mx, p, stream);                   \
-        case 3: return launch<BN_, 3, 3>(mw, mx, p, stream);                   \
-        case 4: return launch<BN_, 3, 4>(mw, mx, p, stream);                   \
-        case 5: return launch<BN_, 3, 5>(mw, mx, p, stream);                   \
-        case 6: return launch<BN_, 3, 6>(mw, mx, p, stream);                   \
-        case 7: return launch<BN_, 3, 7>(mw, mx, p, stream);                   \
-        default: return launch<BN_, 3, 8>(mw, mx, p, stream);                  \
+        case 1: return launch<BN_, WHOLE_STAGES, 1>(mw, mx, p, stream);                   \
+        case 2: return launch<BN_, SPLIT_STAGES, 2>(mw, mx, p, stream);                   \
+        case 3: return launch<BN_, SPLIT_STAGES, 3>(mw, mx, p, stream);                   \
+        case 4: return launch<BN_, SPLIT_STAGES, 4>(mw, mx, p, stream);                   \
+        case 5: return launch<BN_, SPLIT_STAGES, 5>(mw, mx, p, stream);                   \
+        case 6: return launch<BN_, SPLIT_STAGES, 6>(mw, mx, p, stream);                   \
+        case 7: return launch<BN_, SPLIT_STAGES, 7>(mw, mx, p, stream);                   \
+        default: return launch<BN_, SPLIT_STAGES, 8>(mw, mx, p, stream);                  \
     }
     if (bn == 16) { SHISO_PICK(16) }
     if (bn == 32) { SHISO_PICK(32) }
@@ -569,10 +583,10 @@ int run_glu(GemmParams p, const void* x, const void* w, cudaStream_t stream) {
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
 #define SHISO_PICK_GLU(BN_)                                                          \
     switch (splits) {                                                                \
-        case 1: return launch<BN_, 4, 1, true>(mw, mx, p, stream);                   \
-        case 2: return launch<BN_, 3, 2, true>(mw, mx, p, stream);                   \
-        case 3: return launch<BN_, 3, 3, true>(mw, mx, p, stream);                   \
-        default: return launch<BN_, 3, 4, true>(mw, mx, p, stream);                  \
+        case 1: return launch<BN_, WHOLE_STAGES, 1, true>(mw, mx, p, stream);                   \
+        case 2: return launch<BN_, SPLIT_STAGES, 2, true>(mw, mx, p, stream);                   \
+        case 3: return launch<BN_, SPLIT_STAGES, 3, true>(mw, mx, p, stream);                   \
+        default: return launch<BN_, SPLIT_STAGES, 4, true>(mw, mx, p, stream);                  \
     }
     if (bn == 16) { SHISO_PICK_GLU(16) }
     if (bn == 32) { SHISO_PICK_GLU(32) }
