@@ -148,22 +148,47 @@ short_conv_run_kernel(const __nv_bfloat16* proj, const float* __restrict__ w, co
     }
     float win[TAPS - 1][8];
     int cur_seq = -1;
-    constexpr int AHEAD = 4;  // rows whose loads are in flight together
+    // The rows just before the run usually belong to the same sequence: they and their sequence
+    // numbers are asked for together with the first rows, and when the numbers agree the window is
+    // made of them; otherwise it is refilled below, two dependent lookups later.
+    uint4 before_b[TAPS - 1], before_x[TAPS - 1];
+    int before_seq[TAPS - 1];
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {
+        const int t = t0 - (TAPS - 1) + j;
+        before_seq[j] = t >= 0 ? seq_of_token[t] : -1;
+        const __nv_bfloat16* row = proj + (size_t)(t >= 0 ? t : 0) * 3 * hidden + ch;
+        before_b[j] = *reinterpret_cast<const uint4*>(row);
+        before_x[j] = *reinterpret_cast<const uint4*>(row + 2 * hidden);
+    }
+    constexpr int AHEAD = 8;  // rows whose loads are in flight together
     for (int tb = t0; tb < t1; tb += AHEAD) {
         uint4 braw[AHEAD], craw[AHEAD], xraw[AHEAD];
+        int seq_of[AHEAD];
 #pragma unroll
         for (int i = 0; i < AHEAD; ++i) {
             const int t = min(tb + i, t1 - 1);
+            seq_of[i] = seq_of_token[t];
             const __nv_bfloat16* row = proj + (size_t)t * 3 * hidden + ch;
             braw[i] = *reinterpret_cast<const uint4*>(row);
             craw[i] = *reinterpret_cast<const uint4*>(row + hidden);
             xraw[i] = *reinterpret_cast<const uint4*>(row + 2 * hidden);
         }
+        if (tb == t0) {
+            bool same = true;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) same = same && before_seq[j] == seq_of[0];
+            if (same) {
+                cur_seq = seq_of[0];
+#pragma unroll
+                for (int j = 0; j < TAPS - 1; ++j) gated8(before_b[j], before_x[j], win[j]);
+            }
+        }
 #pragma unroll
         for (int i = 0; i < AHEAD; ++i) {
             const int t = tb + i;
             if (t >= t1) break;
-            const int s = seq_of_token[t];
+            const int s = seq_of[i];
             if (s != cur_seq) {
                 cur_seq = s;
                 const int first = q_start[s];
