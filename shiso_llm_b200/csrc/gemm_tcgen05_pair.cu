@@ -33,6 +33,12 @@
 // 17.3 us for 2,048 x 2048 x 2048, 38.7 against 38.6 for 6144 features: the epilogue's time is
 // not in how its stores are shaped.)
 //
+// (Measured and dropped: the residual add and the first half of the next RMS norm in this
+// epilogue, as the kernels for a few rows have them.  A product of 2,048 x 2,048 features is one
+// tile a pair, so its whole epilogue stands at the kernel's end; reading and writing the float
+// stream there took the tail from 3.1 to 14.8 us - more than the 10 us of the norm kernel it
+// would replace - and even as whole lines the 42 MB would all move in that tail.)
+//
 // The loads carry no multicast qualifier.  Every wait is bounded by a clock limit; a CTA that
 // gives up sets the status word, and all CTAs still meet at the cluster barrier before TMEM is
 // freed.
