@@ -39,6 +39,12 @@
 // stream there took the tail from 3.1 to 14.8 us - more than the 10 us of the norm kernel it
 // would replace - and even as whole lines the 42 MB would all move in that tail.)
 //
+// (Measured and dropped: pair tiles narrower than 256 weight rows where that saves a wave -
+// 72 tiles of 240 for 2,048 features instead of 64 of 256 on 74 pairs, 128 tiles of 192 for
+// 3,072 features instead of 96 of 256.  The prompt step took 3.26 ms either way; with 240 rows for
+// every product 3.29 ms, with 192 rows 3.87 ms: a narrower tile brings less arithmetic per byte
+// it loads, and that costs what the fuller waves save.)
+//
 // The loads carry no multicast qualifier.  Every wait is bounded by a clock limit; a CTA that
 // gives up sets the status word, and all CTAs still meet at the cluster barrier before TMEM is
 // freed.
