@@ -273,6 +273,7 @@ def run_workload(workload, preset, config, plan, full_layers) -> dict:
 
 
 def main() -> int:
+    global PROMPT_LEN
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=64)
@@ -281,6 +282,8 @@ def main() -> int:
     parser.add_argument("--preset", default="lfm2-1.2b")
     parser.add_argument("--layers", type=int, default=None, help="run only the first N layers (recorded in config)")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                        help="tokens of every prompt, and of the prompt step that is timed (the contract's line: 2,048)")
     parser.add_argument("--points", default="1,64,serve_350m,mixed_2p6b",
                         help="what else to report: decode batch sizes, and the serving workloads serve_350m / mixed_2p6b; 'none' for nothing")
     parser.add_argument("--reps", type=int, default=7, help="timed repetitions of the K-step block (after one that is discarded)")
@@ -295,6 +298,7 @@ def main() -> int:
                         help="bracket the device-timed decode steps (or the prefill steps) with cudaProfilerStart/Stop, "
                              "for `ncu --profile-from-start off`")
     args = parser.parse_args()
+    PROMPT_LEN = args.prompt_len
 
     if args.impl == "reference":
         print(json.dumps({
@@ -487,7 +491,7 @@ def main() -> int:
         torch.cuda.empty_cache()
 
     line = {
-        "metric": "decode tok/s at batch 8 (LFM2-1.2B-shaped, bf16, 2048-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} ({args.preset.upper()}-shaped, bf16, {PROMPT_LEN}-token prompts)",
         "value": main_point["tok_s"],
         "unit": "tok/s",
         "n_gpus": 1,
@@ -505,7 +509,7 @@ def main() -> int:
         "config": {
             "model": f"{args.preset} (random weights)",
             "global_batch": args.batch,
-            "seq_len": 4096,
+            "seq_len": ctx,
             "parallelism": "single-gpu",
             "layers_run": config.num_hidden_layers,
             "layers_full": full_layers,
