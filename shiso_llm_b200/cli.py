@@ -165,11 +165,16 @@ def cmd_generate(args) -> int:
     )
     rows = FrontierRows(args.dump_logits) if args.dump_logits else None
     llm.logits_tap = rows
+    profiler = llm.engine.enable_launch_profile(args.profile_dir) if args.profile_dir else None
     started = time.time()
     outputs = llm.generate(prompts, params)
     elapsed = time.time() - started
     if rows is not None:
         rows.close()
+    if profiler is not None:
+        llm.engine.disable_launch_profile()
+        profiler.write()
+        print(profiler.text(), file=sys.stderr)
     for out in outputs:
         print(json.dumps({"request": out.request_id, "prompt_tokens": len(out.prompt_token_ids),
                           "token_ids": out.token_ids, "finish_reason": out.finish_reason, "error": out.error}))
@@ -216,6 +221,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--dump-logits", metavar="DIR", help="write the logits row at the end of every prompt to DIR")
     g.add_argument("--dump-layers", type=int, choices=[0, 1, 2], default=0,
                    help="print statistics of the residual stream after every layer (2: after every mixer and feed-forward) to stderr")
+    g.add_argument("--profile-dir", metavar="DIR",
+                   help="time every kernel launch of every step (steps then run kernel by kernel) and write launches.json / launches.txt to DIR")
     g.set_defaults(func=cmd_generate)
 
     r = sub.add_parser("init-random", help="write a model folder with random weights")

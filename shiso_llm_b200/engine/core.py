@@ -164,6 +164,9 @@ class Engine:
         self.step_graphs = None
         level = options.dump_layers or int(os.environ.get("SHISO_LAYER_DUMP", "0") or 0)
         self.layer_hook = self.add_hook = None  # diagnostics; a step with a hook is never captured
+        self.profiler = None  # kernels.profile.StepProfiler while launches are being timed
+        # SHISO_NVTX=1: every step is an NVTX range named by its shape (for `ncu --nvtx --nvtx-include`)
+        self.nvtx = self.device.type == "cuda" and os.environ.get("SHISO_NVTX", "0") not in ("", "0")
         if level:
             self.enable_layer_dump(level)
         if options.cuda_graphs and self.device.type == "cuda" and model.graph_safe:
@@ -206,6 +209,22 @@ class Engine:
 
         self.layer_hook = after_entry
         self.add_hook = after_add if level >= 2 else None
+
+    def enable_launch_profile(self, folder=None):
+        """Times every launch of every step from now on (kernels/profile.py) and returns the
+        ``StepProfiler`` that collects the rows; steps run kernel by kernel meanwhile.
+        ``disable_launch_profile`` ends it.  The reference's ``--profile-dir``
+        (crates/shiso-runtime/src/options.rs:139-146, crates/shiso-core/src/profile.rs:1-80)."""
+        from ..kernels.profile import StepProfiler
+
+        if not hasattr(self.env.ops, "profile_start"):
+            raise ValueError("this kernel table has no launch profiler")
+        self.profiler = StepProfiler(folder)
+        return self.profiler
+
+    def disable_launch_profile(self):
+        profiler, self.profiler = self.profiler, None
+        return profiler
 
     def warm_up(self) -> None:
         """Runs a two-token request through a prompt step and a decode step and drops it, so
@@ -342,7 +361,11 @@ class Engine:
                 starts.append(self.cache.append(e.request, len(e.tokens)))
                 claimed.append(e.request)
             ran = False
-            if self.graphs is not None and not hooked:
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(f"step {self.steps_run}: {total} tokens, {len(entries)} sequences")
+            if self.profiler is not None:
+                self.env.ops.profile_start()
+            if self.graphs is not None and not hooked and self.profiler is None:
                 if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
                     logits, ran = self.graphs.run(entries, starts), True
                 elif self.step_graphs is not None:
@@ -354,7 +377,17 @@ class Engine:
                     logits = self.model.forward(meta, self.cache, self.layer_hook, self.add_hook)
                 else:
                     logits = self.model.forward(meta, self.cache)
+            if self.profiler is not None:
+                samples, wall_us, span_us = self.env.ops.profile_stop()
+                decode = all(len(e.tokens) == 1 for e in entries)
+                self.profiler.add("decode" if decode else "prompt", samples, wall_us, span_us)
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
         except BaseException:
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
+            if self.profiler is not None and getattr(self.env.ops, "_region", None) is not None:
+                self.env.ops.profile_stop()
             # Nothing of the step counts: claims are undone, and a request this step saw for the
             # first time holds nothing afterwards.  (Pages a known request grew into stay with it:
             # they hold no position yet and its next step uses them.)

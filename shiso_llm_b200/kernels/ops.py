@@ -110,7 +110,54 @@ def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
         raise KernelError(f"{name}: expected {ndim} dimensions, got shape {tuple(t.shape)}")
 
 
-def _done(status: int, what: str, launches: int = 1) -> None:
+_region = None  # the open profile region, if any (kernels/profile.py)
+_plain_library = library
+
+
+class _TimedLibrary:
+    """The kernel library while a region is open: an event is recorded before every call."""
+
+    def __init__(self, lib):
+        self._lib = lib
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if not name.startswith("shiso_"):
+            return fn
+
+        def call(*args):
+            if _region is not None:
+                _region.before()
+            return fn(*args)
+
+        return call
+
+
+def profile_start() -> None:
+    """Opens a region: until ``profile_stop`` every launch stands between two events."""
+    global _region, library
+    from .profile import Region
+
+    if _region is not None:
+        raise KernelError("a profile region is already open")
+    require()
+    timed = _TimedLibrary(_plain_library())
+    library = lambda: timed  # noqa: E731
+    _region = Region(torch)
+
+
+def profile_stop():
+    """Closes the region: ((kernel, shape, launches, microseconds) in launch order, host
+    microseconds, microseconds from the first launch's start to the last one's end)."""
+    global _region, library
+    if _region is None:
+        raise KernelError("no profile region is open")
+    region, _region = _region, None
+    library = _plain_library
+    return region.close()
+
+
+def _done(status: int, what: str, launches: int = 1, shape=()) -> None:
     global launch_count
     if status != 0:
         why = _ERRORS.get(status)
@@ -118,6 +165,8 @@ def _done(status: int, what: str, launches: int = 1) -> None:
             why = f"CUDA error {status} at launch"
         raise KernelError(f"{what}: {why} (status {status})")
     launch_count += launches
+    if _region is not None:
+        _region.mark(what, "x".join(str(int(d)) for d in shape), launches)
 
 
 # --------------------------------------------------------------------------- rows
@@ -141,7 +190,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=No
     status = library().shiso_embed(
         _ptr(ids), _ptr(feed_index), _ptr(fed_tokens), _ptr(table), _code(table), _ptr(out), tokens, hidden, vocab, _stream()
     )
-    _done(status, "embed")
+    _done(status, "embed", shape=(tokens, hidden))
     return out
 
 
@@ -177,7 +226,7 @@ def add_rmsnorm(residual, delta, w, eps, out_dtype, rows=None):
     status = library().shiso_rmsnorm(
         _ptr(residual), _ptr(delta), _ptr(rows), _ptr(w), _ptr(out), _code(out), out_rows, hidden, float(eps), _stream()
     )
-    _done(status, "rmsnorm")
+    _done(status, "rmsnorm" if delta is None else "add + rmsnorm", shape=(out_rows, hidden))
     return out
 
 
@@ -238,7 +287,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         status = lib.shiso_gemm_stream(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
         )
-        _done(status, "linear (streaming)")
+        _done(status, "linear (streaming)", shape=(tokens, n, k))
         return out
     if (
         both_bf16 and PROMPT_MIN_TOKENS <= tokens <= FEW_TILES_MAX_TOKENS
@@ -248,24 +297,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         status = lib.shiso_gemm_tcgen05_tokens64(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _sm_count(), _stream()
         )
-        _done(status, "linear (tcgen05, token tiles of 64)")
+        _done(status, "linear (tcgen05, token tiles of 64)", shape=(tokens, n, k))
         return out
     if both_bf16 and tokens >= PROMPT_MIN_TOKENS and n % 8 == 0 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05_pair(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, 0, _sm_count(), _stream()
         )
-        _done(status, "linear (tcgen05, persistent)")
+        _done(status, "linear (tcgen05, persistent)", shape=(tokens, n, k))
         return out
     if both_bf16 and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _sm_count(), _stream()
         )
-        _done(status, "linear (tcgen05)")
+        _done(status, "linear (tcgen05)", shape=(tokens, n, k))
         return out
     status = lib.shiso_gemm_simple(
         _ptr(x), _code(x), _ptr(w), _code(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _stream()
     )
-    _done(status, "linear")
+    _done(status, "linear", shape=(tokens, n, k))
     return out
 
 
@@ -289,7 +338,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
             _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter, k, two_inter // 2,
             _sm_count(), _stream(),
         )
-        _done(status, "linear_swiglu (streaming)")
+        _done(status, "linear_swiglu (streaming)", shape=(tokens, two_inter, k))
         return out
     lib = library()
     if (
@@ -303,12 +352,12 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
                 _ptr(x), _ptr(gate_up), 0, _ptr(out), _code(out), tokens, two_inter // 2, k, two_inter // 2,
                 _sm_count(), _stream(),
             )
-            _done(status, "linear_swiglu (tcgen05, persistent)")
+            _done(status, "linear_swiglu (tcgen05, persistent)", shape=(tokens, two_inter, k))
             return out
         status = lib.shiso_gemm_tcgen05_swiglu(
             _ptr(x), _ptr(gate_up), _ptr(out), _code(out), tokens, two_inter // 2, k, _stream()
         )
-        _done(status, "linear_swiglu (tcgen05)")
+        _done(status, "linear_swiglu (tcgen05)", shape=(tokens, two_inter, k))
         return out
     return swiglu(linear(x, gate_up, out_dtype))
 
@@ -369,7 +418,7 @@ def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
             _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(summed), _ptr(next_norm_w), _ptr(rows), _ptr(partials),
             tokens, n, k, _sm_count(), _stream(),
         )
-    _done(status, "linear_into_stream")
+    _done(status, "linear_into_stream" + (" (streaming)" if streaming else " (tcgen05)"), shape=(tokens, n, k))
     return summed, ScaledRows(rows, partials, eps)
 
 
@@ -396,7 +445,7 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
             _ptr(x), _ptr(rows.partials), rows.partials.shape[0], rows.partials.shape[1], rows.eps, _ptr(w), _ptr(out),
             _code(out), tokens, n, k, inter, _sm_count(), _stream(),
         )
-    _done(status, "linear_scaled")
+    _done(status, "linear_scaled", shape=(tokens, n, k))
     return out
 
 
@@ -443,7 +492,7 @@ def linear_short_conv(x, in_proj, taps, bias, state, step):
             _ptr(step.seq_of_token), _ptr(step.state_slots), _ptr(y), _code(y), tokens, hidden, k, n_taps,
             _sm_count(), _stream(),
         )
-        _done(status, "linear_short_conv")
+        _done(status, "linear_short_conv (streaming)", shape=(tokens, 3 * hidden, k))
         return y
     proj = linear_scaled(rows, in_proj, xt.dtype) if rows is not None else linear(xt, in_proj, xt.dtype)
     return short_conv(proj, taps, bias, state, step)
@@ -505,7 +554,7 @@ def short_conv(proj, taps, bias, state, step):
         _ptr(step.seq_of_token), _ptr(step.q_start), _ptr(step.state_slots), _ptr(y),
         tokens, step.num_seqs, hidden, n_taps, 1, int(getattr(step, "max_q_len", 0)), _stream(),
     )
-    _done(status, "short_conv", 2)
+    _done(status, "short_conv", 2, shape=(tokens, hidden))
     return y
 
 
@@ -544,7 +593,7 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, 
         tokens, heads, kv_heads, head_dim, int(rotary_dim), page_size, float(eps), int(do_store), int(bool(interleaved)),
         _stream(),
     )
-    _done(status, "qk_norm_rope_store")
+    _done(status, "qk_norm_rope_store", shape=(tokens, heads + 2 * kv_heads, head_dim))
     return q
 
 
@@ -625,7 +674,7 @@ def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv
         tokens, heads, kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), splits, int(bool(store)),
         _stream(),
     )
-    _done(status, "decode_attention_from_qkv")
+    _done(status, "decode_attention_from_qkv", shape=(tokens, heads, head_dim))
     return out
 
 
@@ -663,14 +712,14 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
                 _ptr(step.seq_of_token), _ptr(scratch), _ptr(counters), _ptr(out), tokens, heads, kv_heads, head_dim,
                 page_size, k_cache.shape[0], float(scale), int(window), splits, _stream(),
             )
-            _done(status, "decode_attention (fused)")
+            _done(status, "decode_attention (fused)", shape=(tokens, heads, head_dim))
             return out
         status = lib.shiso_decode_attention(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
             _ptr(step.seq_of_token), _ptr(scratch), _ptr(out), tokens, heads, kv_heads, head_dim, page_size,
             float(scale), int(window), splits, _stream(),
         )
-        _done(status, "decode_attention", 2)
+        _done(status, "decode_attention", 2, shape=(tokens, heads, head_dim))
         return out
     elif (
         q.dtype == torch.bfloat16 and tokens >= TC_ATTENTION_MIN_TOKENS
@@ -688,7 +737,7 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
             _ptr(step.start_pos), _ptr(out), tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
             k_cache.shape[0], float(scale), int(window), _stream(),
         )
-        _done(status, "prefill_attention (tcgen05)")
+        _done(status, "prefill_attention (tcgen05)", shape=(tokens, heads, head_dim))
         return out
     elif q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= PREFILL_MAX_HEAD_DIM:
         starts = getattr(step, "h_q_start", None)
@@ -701,14 +750,14 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
             _ptr(step.start_pos), _ptr(out), step.num_seqs, tiles, heads, kv_heads, head_dim, page_size,
             float(scale), int(window), _stream(),
         )
-        _done(status, "prefill_attention")
+        _done(status, "prefill_attention", shape=(tokens, heads, head_dim))
         return out
     status = lib.shiso_paged_attention(
         _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(step.positions), _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, head_dim,
         page_size, float(scale), int(window), _stream(),
     )
-    _done(status, "paged_attention")
+    _done(status, "paged_attention", shape=(tokens, heads, head_dim))
     return out
 
 
