@@ -67,6 +67,9 @@ struct GemmParams {
     const float* norm_w;
     __nv_bfloat16* x_out;
     float* into_partials;
+    // rows of `y`, the stream, the bias and the norm weight may be read and written four features
+    // at a time (their width is a multiple of 4 and their pointers are 16-byte aligned)
+    int vec4;
 };
 
 constexpr int MAX_FUSED_BN = 64;  // token tiles of the SCALED / INTO modes (their scales lie in shared memory)
@@ -157,12 +160,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     auto stream_value = [&](int token) {
         return (feature < p.N && token < p.T) ? p.res_in[(size_t)token * p.N + feature] : 0.0f;
     };
+    // (Rows of a width that is no multiple of 4, or pointers off a 16-byte boundary, take the same
+    // path with one element per load and store: p.vec4.)
+    // With K split over a cluster the sums are finished by other threads than own the accumulator
+    // rows: a warp takes tokens warp, warp + 4, .. of its CTA's share, a lane four consecutive
+    // features of the tile (16-byte loads of the partial sums, one warp-wide sum of squares a token).
+    constexpr int EARLY4 = 2;
+    const int feature4 = feature0 + 4 * lane;
+    float4 norm_weight4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 early4[EARLY4];
+    // four consecutive floats from `limit`-wide rows; past the row's end zeros
+    auto load4 = [&](const float* base, size_t row_offset, int first, int limit) {
+        float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (p.vec4) {
+            if (first < limit) r = *reinterpret_cast<const float4*>(base + row_offset + first);
+        } else {
+            if (first < limit) r.x = base[row_offset + first];
+            if (first + 1 < limit) r.y = base[row_offset + first + 1];
+            if (first + 2 < limit) r.z = base[row_offset + first + 2];
+            if (first + 3 < limit) r.w = base[row_offset + first + 3];
+        }
+        return r;
+    };
+    auto stream_value4 = [&](int token) {
+        return token < p.T ? load4(p.res_in, (size_t)token * p.N, feature4, p.N) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    };
     auto ask_early = [&]() {
         if (!into) return;
         pdl_wait();  // the stream is the predecessor's
-        norm_weight = feature < p.N ? p.norm_w[feature] : 0.0f;
+        if constexpr (SPLITS > 1) {
+            norm_weight4 = load4(p.norm_w, 0, feature4, p.N);
 #pragma unroll
-        for (int u = 0; u < EARLY; ++u) early[u] = stream_value(token0 + first_own + u * own_stride);
+            for (int u = 0; u < EARLY4; ++u) early4[u] = stream_value4(token0 + (warp + 4 * u) * SPLITS + first_own);
+        } else {
+            norm_weight = feature < p.N ? p.norm_w[feature] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < EARLY; ++u) early[u] = stream_value(token0 + first_own + u * own_stride);
+        }
     };
 
     if (warp == 0 && lane == 0) {
@@ -372,61 +406,105 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         cluster.sync();
         const int out_rows = GLU ? p.inter : p.N;
-        const bool live = feature < out_rows;
-        const float b = (!GLU && p.bias && live) ? p.bias[feature] : 0.0f;
-        // Tokens first .. first + COUNT - 1 of this CTA's share: every partial sum of the batch is
-        // asked for before the first one is used.  False past the tile or the step (the same in
-        // every thread).  (Clock stamps put this phase at 210 to 410 cycles a token at 64 rows -
-        // 2.2 us of a product's 10 - with or without its stores; batching the loads gained 1.5 %
-        // of a decode step at batch 64.)
-        auto finish = [&](int first, auto count_tag, const float* before) {
-            constexpr int COUNT = decltype(count_tag)::value;
-            float part[COUNT][A_TILES][SPLITS];
+        // Token `i` of this CTA's share (i = warp, warp + 4, ..), four features a lane; `pair` of
+        // them at a time, all their partial sums asked for before the first is used.  False past
+        // the share, the tile or the step (the same in every lane of the warp).
+        const bool live4 = feature4 < out_rows;
+        float4 bias4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (!GLU && p.bias) bias4 = load4(p.bias, 0, feature4, out_rows);
+        const float4* inbox4 = reinterpret_cast<const float4*>(inbox);
+        // four values at `at` = row start + feature4 of `limit`-wide rows
+        auto store4_f32 = [&](float* base, size_t at, float4 v, int limit) {
+            if (p.vec4) {
+                *reinterpret_cast<float4*>(base + at) = v;
+            } else {
+                base[at] = v.x;
+                if (feature4 + 1 < limit) base[at + 1] = v.y;
+                if (feature4 + 2 < limit) base[at + 2] = v.z;
+                if (feature4 + 3 < limit) base[at + 3] = v.w;
+            }
+        };
+        auto store4_bf16 = [&](__nv_bfloat16* base, size_t at, float4 v, int limit) {
+            if (p.vec4) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                *reinterpret_cast<uint2*>(base + at) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+                base[at] = __float2bfloat16_rn(v.x);
+                if (feature4 + 1 < limit) base[at + 1] = __float2bfloat16_rn(v.y);
+                if (feature4 + 2 < limit) base[at + 2] = __float2bfloat16_rn(v.z);
+                if (feature4 + 3 < limit) base[at + 3] = __float2bfloat16_rn(v.w);
+            }
+        };
+        auto finish_pair = [&](int u0, const float4* before) {
+            float4 part[2][A_TILES][SPLITS];
 #pragma unroll
-            for (int u = 0; u < COUNT; ++u)
+            for (int u = 0; u < 2; ++u) {
+                const int i = warp + 4 * (u0 + u);
 #pragma unroll
                 for (int t = 0; t < A_TILES; ++t)
 #pragma unroll
                     for (int r = 0; r < SPLITS; ++r)
-                        part[u][t][r] = first + u < OWN ? inbox[(((size_t)t * SPLITS + r) * OWN + first + u) * BM + warp * 32 + lane] : 0.0f;
+                        part[u][t][r] = i < OWN ? inbox4[((((size_t)t * SPLITS + r) * OWN + i) * BM) / 4 + lane] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
 #pragma unroll
-            for (int u = 0; u < COUNT; ++u) {
-                const int j = (first + u) * SPLITS + (int)rank;
-                if (first + u >= OWN || j >= BN || token0 + j >= p.T) return false;
-                float sum[A_TILES];
+            for (int u = 0; u < 2; ++u) {
+                const int i = warp + 4 * (u0 + u);
+                const int j = i * SPLITS + (int)rank;
+                if (i >= OWN || j >= BN || token0 + j >= p.T) return false;
+                const int token = token0 + j;
+                float4 sum[A_TILES];
 #pragma unroll
                 for (int t = 0; t < A_TILES; ++t) {
-                    sum[t] = 0.0f;
+                    sum[t] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                    for (int r = 0; r < SPLITS; ++r) sum[t] += part[u][t][r];  // rank order
-                    if (scaled) sum[t] *= scale_s[j % MAX_FUSED_BN];
+                    for (int r = 0; r < SPLITS; ++r) {  // rank order
+                        sum[t].x += part[u][t][r].x;
+                        sum[t].y += part[u][t][r].y;
+                        sum[t].z += part[u][t][r].z;
+                        sum[t].w += part[u][t][r].w;
+                    }
+                    if (scaled) {
+                        const float sc = scale_s[j % MAX_FUSED_BN];
+                        sum[t].x *= sc; sum[t].y *= sc; sum[t].z *= sc; sum[t].w *= sc;
+                    }
                 }
-                float v = sum[0] + b;
-                if (GLU) v = silu_times(sum[0], sum[A_TILES - 1]);
+                float4 v;
+                if (GLU) {
+                    v = make_float4(silu_times(sum[0].x, sum[A_TILES - 1].x), silu_times(sum[0].y, sum[A_TILES - 1].y),
+                                    silu_times(sum[0].z, sum[A_TILES - 1].z), silu_times(sum[0].w, sum[A_TILES - 1].w));
+                } else {
+                    v = make_float4(sum[0].x + bias4.x, sum[0].y + bias4.y, sum[0].z + bias4.z, sum[0].w + bias4.w);
+                }
                 if (into) {
-                    join_stream(token0 + j, v, before[u]);
-                } else if (live) {
-                    const size_t at = (size_t)(token0 + j) * out_rows + feature;
-                    if (p.out_f32) store_out<float>((float*)p.y, at, v);
-                    else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v);
+                    float4 r4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (live4) {
+                        const size_t at = (size_t)token * p.N + feature4;
+                        r4 = make_float4(before[u].x + v.x, before[u].y + v.y, before[u].z + v.z, before[u].w + v.w);
+                        // (features past the row's end: v and the stream's value are zero there)
+                        store4_f32(p.res_out, at, r4, p.N);
+                        store4_bf16(p.x_out, at, make_float4(r4.x * norm_weight4.x, r4.y * norm_weight4.y, r4.z * norm_weight4.z, r4.w * norm_weight4.w), p.N);
+                    }
+                    // the token's sum of squares over the tile's 128 features: one warp has them all
+                    const float square = warp_sum((r4.x * r4.x + r4.y * r4.y) + (r4.z * r4.z + r4.w * r4.w));
+                    if (lane == 0) p.into_partials[(size_t)blockIdx.x * p.T + token] = square;
+                } else if (live4) {
+                    const size_t at = (size_t)token * out_rows + feature4;
+                    if (p.out_f32) store4_f32((float*)p.y, at, v, out_rows);
+                    else store4_bf16((__nv_bfloat16*)p.y, at, v, out_rows);
                 }
             }
             return true;
         };
-        constexpr int BATCH = 4;
-        constexpr int FIRST = OWN < EARLY ? OWN : EARLY;  // tokens whose stream values are here already
-        bool more = true;
+        constexpr int PER_WARP = (OWN + 3) / 4;  // tokens a warp may have to finish
+        bool more = finish_pair(0, early4);      // (EARLY4 == 2: the first pair's stream values are here)
+        for (int u0 = 2; u0 < PER_WARP && more; u0 += 2) {
+            float4 before[2];
 #pragma unroll
-        for (int i = 0; i < FIRST; i += BATCH) more = more && finish(i, std::integral_constant<int, BATCH>{}, early + i);
-        if (OWN > EARLY && more) {
-            for (int i = EARLY; i < OWN && more; i += BATCH) {
-                float before[BATCH];  // further stream values are asked for a batch at a time
-#pragma unroll
-                for (int u = 0; u < BATCH; ++u) before[u] = into ? stream_value(token0 + (i + u) * SPLITS + (int)rank) : 0.0f;
-                more = finish(i, std::integral_constant<int, BATCH>{}, before);
-            }
+            for (int u = 0; u < 2; ++u)
+                before[u] = into ? stream_value4(token0 + (warp + 4 * (u0 + u)) * SPLITS + (int)rank) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            more = finish_pair(u0, before);
         }
-        if (into) leave_squares(SPLITS, (int)rank);
+
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -479,6 +557,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, cudaStrea
     attr[1].val.programmaticStreamSerializationAllowed = shiso_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
+    {
+        const int out_rows = GLU ? p.inter : p.N;
+        const uintptr_t pointers = (uintptr_t)p.y | (uintptr_t)p.bias | (uintptr_t)p.res_in | (uintptr_t)p.res_out |
+                                   (uintptr_t)p.norm_w | (uintptr_t)p.x_out;
+        p.vec4 = (out_rows % 4 == 0 && (pointers & 15) == 0) ? 1 : 0;
+    }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, p);
     return (int)e;
 }
