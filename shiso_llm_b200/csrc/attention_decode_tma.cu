@@ -6,7 +6,7 @@
 // per query head: kernels/cuda/dense/dense_attn.cuh:44-180).  What differs is how the bytes
 // move.  A producer warp brings every page of a 64-key tile with one 3-D TMA box (page rows x
 // one head x 64 values, 128-byte swizzle), each lane looking its own page up in the block
-// table, into a ring of four tiles with full/empty mbarriers: a CTA with four tiles or fewer
+// table, into a ring of six tiles with full/empty mbarriers: a CTA with six tiles or fewer
 // has all of its keys and values in flight at once, and a long part streams without a
 // CTA-wide barrier per tile.  Four consumer warps take 16 keys of a tile each (Q K^T and P V
 // as m16n8k16 MMAs, float softmax statistics) and are merged at the end.
@@ -22,6 +22,13 @@
 // scheduling of many short CTAs hides better: batch 64 x 2,190 keys in 4 parts took 81 us
 // against 68 us here, in 8 parts 147 against 87.
 //
+// Where a call's time goes, from %globaltimer stamps of every CTA (batch 8 x 2,158 keys, 4 parts
+// of 9 tiles, a call every 16.4 us in a captured chain): the CTAs are resident and their first
+// tiles loaded before the predecessor ends; the queries are ready 1.0 us after the dependency
+// wait; the tiles take 4.6 to 9.5 us with a ring of four (6.4 us at most with six: batch 8
+// 17.0 -> 14.5 us, 8,192 keys 39.8 -> 31.9 us, a decode step at batch 64 58.0k -> 61.9k tokens/s);
+// the four warps' merge and the part's store 1.3 us; counter, fence and the last CTA's merge 3.8 us.
+//
 // Every wait is bounded by a clock limit and reports through the status word.
 #include "tcgen05.cuh"
 
@@ -34,7 +41,7 @@ constexpr int TILE = 64;           // keys per tile
 constexpr int ROW = HEAD * 2;      // bytes per key or value row
 constexpr int TILE_BYTES = TILE * ROW;
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // keys, then values
-constexpr int STAGES = 4;
+constexpr int STAGES = 6;           // two CTAs fit an SM; with four (three CTAs an SM) a part of nine tiles went round the ring twice
 constexpr int CONSUMERS = 4;
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int KSTEPS = HEAD / 16;
@@ -106,9 +113,9 @@ __device__ __forceinline__ uint2 pack4(const float* v) {
 }
 
 // FROM_QKV: a variant of its own (what it holds would cost the plain kernel registers).
-// (five warps take the registers of eight: the bound of 256 threads x 3 CTAs caps them at 85 a thread)
+// (five warps take the registers of eight: the bound of 256 threads x 2 CTAs caps them at 128 a thread)
 template <bool FROM_QKV>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 2)
 decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeTmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // [STAGES][keys | values]
