@@ -11,10 +11,11 @@
 // CTA-wide barrier per tile.  Four consumer warps take 16 keys of a tile each (Q K^T and P V
 // as m16n8k16 MMAs, float softmax statistics) and are merged at the end.
 //
-// The parts of one (sequence, KV head) count themselves off on a counter; the CTA that
-// arrives last adds the parts up in index order and writes the output, so there is no second
-// launch, and the result does not depend on which CTA came last.  The counter is back at
-// zero when the kernel ends.
+// The parts of one (sequence, KV head) are a thread-block cluster (at most 8): every part sends
+// its heads' results to the CTA that merges that head, through the cluster's shared memory; the
+// cluster meets once and each CTA adds up what it was sent in part order and writes its heads'
+// output, so there is no second launch and no traffic through global memory, and the result does
+// not depend on which CTA finished last.
 //
 // Measured and dropped: one wave of persistent CTAs that walk (part, KV head, sequence) items
 // with the ring running on across items.  The hand-over at the end of an item (fence, counter,
@@ -47,7 +48,9 @@ constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int KSTEPS = HEAD / 16;
 constexpr int DTILES = HEAD / 8;
 constexpr int MERGE_ROW = HEAD + 2;  // floats: output, running maximum (log2 units), sum
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 128;
+constexpr int MAX_PARTS = 8;        // the parts of a (sequence, KV head) are a thread-block cluster (portable size)
+constexpr int INBOX_ROWS = 32;      // rows a CTA may be sent: parts x the heads it merges, below 16 + 8
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + INBOX_ROWS * MERGE_ROW * 4 + 1024 + 128;
 static_assert(CONSUMERS * 16 * MERGE_ROW * 4 <= STAGES * STAGE_BYTES, "the merge area lies over the ring");
 
 struct DecodeTmaArgs {
@@ -55,8 +58,8 @@ struct DecodeTmaArgs {
     const int* block_table;   // [S, width]
     const int* positions;     // [T]
     const int* seq_of_token;  // [T]
-    float* partial;           // [T, heads, splits, 66]
-    int* counters;            // [T, kv_heads], zero between launches
+    float* partial;           // unused since the parts merge through the cluster's shared memory
+    int* counters;            // unused likewise
     __nv_bfloat16* out;       // [T, heads * 64]
     int* status;
     int width, heads, kv_heads, page_size, splits, window;
@@ -97,6 +100,22 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// All threads of all CTAs of the cluster meet.
+__device__ __forceinline__ void cluster_meet() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The shared::cluster address of `local` (an address in this CTA's shared memory) in CTA `rank`.
+__device__ __forceinline__ uint32_t in_cta(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void store_remote(uint32_t address, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
 
 __device__ __forceinline__ void unpack4(uint2 raw, float* v) {
@@ -119,9 +138,10 @@ __global__ void __launch_bounds__(256, 2)
 decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeTmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // [STAGES][keys | values]
-    uint64_t* full = (uint64_t*)(ring + STAGES * STAGE_BYTES);
+    uint64_t* full = (uint64_t*)(ring + STAGES * STAGE_BYTES);  // barriers and flags: 256 bytes
     uint64_t* empty = full + STAGES;
-    int* shared_ints = (int*)(empty + STAGES);  // [0] failed, [1] this CTA merges the parts
+    int* shared_ints = (int*)(empty + STAGES);  // [0] failed
+    float* inbox = (float*)(ring + STAGES * STAGE_BYTES + 256);  // [INBOX_ROWS][MERGE_ROW]: what the parts send this CTA
     float* merge = (float*)ring;                // after the loop: [CONSUMERS][16][MERGE_ROW]
 
     const int split = blockIdx.x, g_head = blockIdx.y, t = blockIdx.z;
@@ -140,7 +160,10 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const int parts = (n_tiles + per_part - 1) / per_part;  // parts that have keys
     const int tile0 = first_tile + split * per_part;
     const int my_tiles = min(per_part, last_tile + 1 - tile0);
-    if (my_tiles <= 0) return;  // uniform: a part past the sequence's end
+    if (my_tiles <= 0) {  // uniform: a part past the sequence's end has nothing to send
+        if (parts > 1) cluster_meet();
+        return;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -148,7 +171,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             mbar_init(&empty[s], CONSUMERS);
         }
         shared_ints[0] = 0;
-        shared_ints[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -409,7 +431,10 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
     pdl_trigger();
     if (failed) shared_ints[0] = 1;
-    if (warp == CONSUMERS) return;
+    if (warp == CONSUMERS) {
+        if (parts > 1) cluster_meet();
+        return;
+    }
 
     // ---- the four warps' results side by side (over the ring: every tile has been consumed)
     consumer_sync();
@@ -431,6 +456,13 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
     consumer_sync();
     const bool alone = parts == 1;  // nothing to merge with: the output is written here
+    // Head h of the group is merged by part h % parts, which keeps the rows the parts send it at
+    // inbox[(h / parts) * parts + part]: every part's result leaves for its head's CTA through
+    // the cluster's shared memory, the cluster meets once, and each CTA adds up the rows of its
+    // heads in part order.  (The parts used to leave their rows in global memory and count
+    // themselves off on a counter there, the last one adding them up: fence, counter and its
+    // reads took 3.8 us after the last part was written.)
+    const uint32_t inbox_local = smem_u32(inbox);
     for (int i = tid; i < group * HEAD; i += CONSUMERS * 32) {
         const int h = i / HEAD, col = i % HEAD;
         float m = -INFINITY;
@@ -442,51 +474,36 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             sum += f * src[HEAD + 1];
             o += f * src[col];
         }
-        const size_t head = (size_t)t * a.heads + g_head * group + h;
         if (alone) {
+            const size_t head = (size_t)t * a.heads + g_head * group + h;
             a.out[head * HEAD + col] = __float2bfloat16_rn(sum > 0.0f ? o / sum : 0.0f);
         } else {
-            float* dst = a.partial + (head * a.splits + split) * MERGE_ROW;
-            dst[col] = o;
+            const uint32_t row = in_cta(inbox_local, (uint32_t)(h % parts)) + (uint32_t)(((h / parts) * parts + split) * MERGE_ROW) * 4u;
+            store_remote(row + col * 4u, o);
             if (col == 0) {
-                dst[HEAD] = m;
-                dst[HEAD + 1] = sum;
+                store_remote(row + HEAD * 4u, m);
+                store_remote(row + (HEAD + 1) * 4u, sum);
             }
         }
     }
     if (!alone) {
-        // count this part off; the last one of the (sequence, KV head) adds the parts up
-        __threadfence();
-        consumer_sync();
-        if (tid == 0) {
-            int* counter = a.counters + (size_t)t * a.kv_heads + g_head;
-            const int before = atomicAdd(counter, 1);
-            if (before == parts - 1) {
-                *counter = 0;  // no other part touches it any more in this launch
-                shared_ints[1] = 1;
+        cluster_meet();
+        for (int i = tid; i < group * HEAD; i += CONSUMERS * 32) {
+            const int h = i / HEAD, col = i % HEAD;
+            if (h % parts != split) continue;
+            const float* base = inbox + (size_t)(h / parts) * parts * MERGE_ROW;
+            float m = -INFINITY;
+            for (int s = 0; s < parts; ++s) m = fmaxf(m, base[s * MERGE_ROW + HEAD]);
+            float sum = 0.0f, acc = 0.0f;
+            for (int s = 0; s < parts; ++s) {  // part order
+                const float sm = base[s * MERGE_ROW + HEAD];
+                const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
+                sum += f * base[s * MERGE_ROW + HEAD + 1];
+                acc += f * base[s * MERGE_ROW + col];
             }
+            const size_t head = (size_t)t * a.heads + g_head * group + h;
+            a.out[head * HEAD + col] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
         }
-        consumer_sync();
-        if (shared_ints[1] != 0) {
-            __threadfence();
-            for (int i = tid; i < group * HEAD; i += CONSUMERS * 32) {
-                const int h = i / HEAD, col = i % HEAD;
-                const size_t head = (size_t)t * a.heads + g_head * group + h;
-                const float* base = a.partial + head * a.splits * MERGE_ROW;
-                float m = -INFINITY;
-                for (int s = 0; s < parts; ++s) m = fmaxf(m, __ldcg(base + s * MERGE_ROW + HEAD));
-                float sum = 0.0f, acc = 0.0f;
-                for (int s = 0; s < parts; ++s) {
-                    const float sm = __ldcg(base + s * MERGE_ROW + HEAD);
-                    const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
-                    sum += f * __ldcg(base + s * MERGE_ROW + HEAD + 1);
-                    acc += f * __ldcg(base + s * MERGE_ROW + col);
-                }
-                a.out[head * HEAD + col] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
-            }
-        }
-    } else {
-        consumer_sync();
     }
     if (tid == 0 && shared_ints[0] != 0 && a.status) atomicExch(a.status, 1);
 }
@@ -516,11 +533,15 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const Decode
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = shiso_pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;  // the parts of a (sequence, KV head)
+    attr[1].val.clusterDim.x = a.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     return (int)cudaLaunchKernelEx(&cfg, kernel, mk, mv, a);
 }
 
@@ -530,6 +551,7 @@ int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* bloc
                        int heads, int kv_heads, int head_dim, int page_size, long long num_pages, float scale, int window,
                        int splits, DecodeTmaArgs* a, CUtensorMap* mk, CUtensorMap* mv) {
     if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
+    if (splits > MAX_PARTS) return SHISO_ERR_UNSUPPORTED;
     if (!shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size)) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SHISO_ERR_ALIGN;
     if (tokens > 65535 || kv_heads > 65535) return SHISO_ERR_UNSUPPORTED;  // grid limits
@@ -559,8 +581,8 @@ int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* bloc
 
 }  // namespace
 
-// As shiso_decode_attention, with `counters` (tokens * kv_heads ints that are zero between
-// launches; the kernel leaves them zero) and the number of pages of the caches.
+// As shiso_decode_attention, with the number of pages of the caches; at most 8 parts.  `scratch` and
+// `counters` are not used any more (the parts merge through the cluster's shared memory).
 SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                            int table_width, const int* positions, const int* seq_of_token, float* scratch,
                                            int* counters, void* out, int tokens, int heads, int kv_heads, int head_dim,

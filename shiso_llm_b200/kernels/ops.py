@@ -612,8 +612,8 @@ def decode_splits(tokens: int, kv_heads: int, capacity: int, fused: bool = False
     at full rate through its ring, and every CTA costs it a start and a hand-over at the end:
     it wants one wave of about two CTAs per SM (measured: batch 8 x 8 KV heads x 2,190 keys
     takes 14.8 us in 4 parts, 16.5 in 6, 21 in 10; batch 32 takes 30 us whole, 43 in 2)."""
-    if fused:
-        return max(1, min(16, 2 * _sm_count() // (tokens * kv_heads), -(-capacity // 128)))
+    if fused:  # the parts of a (sequence, KV head) are a thread-block cluster: at most 8
+        return max(1, min(8, 2 * _sm_count() // (tokens * kv_heads), -(-capacity // 128)))
     return max(1, min(16, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
 
 
