@@ -631,7 +631,7 @@ def _decode_counters(device: torch.device, count: int) -> torch.Tensor:
     return held[-1]
 
 
-DECODE_FROM_QKV_MAX_TOKENS = 8  # rows up to which attention takes the qkv rows itself (batch 8 decodes 1 % faster with one launch fewer per layer; at 16 and 64 rows the longer start of every CTA costs 1.5 %)
+DECODE_FROM_QKV_MAX_TOKENS = 64  # rows up to which attention takes the qkv rows itself: one launch fewer per layer, and the keys and values move before the predecessor ends (batch 8 / 16 / 32 / 64 decode 1 / 1.8 / 2.0 / 1.0 % faster; no change at 96 and 128 rows)
 
 
 def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
