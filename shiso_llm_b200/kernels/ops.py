@@ -610,25 +610,11 @@ def decode_splits(tokens: int, kv_heads: int, capacity: int, fused: bool = False
     kernel wants enough CTAs (tokens x KV heads x parts) to fill the SMs a few times over, no
     part shorter than 128 keys of the table's capacity.  The fused kernel streams a long part
     at full rate through its ring, and every CTA costs it a start and a hand-over at the end:
-    it wants one wave of about two CTAs per SM (measured: batch 8 x 8 KV heads x 2,190 keys
-    takes 14.8 us in 4 parts, 16.5 in 6, 21 in 10; batch 32 takes 30 us whole, 43 in 2)."""
+    it wants one wave of the two CTAs an SM holds (measured when three fitted: batch 8 x 8 KV
+    heads x 2,190 keys took 14.8 us in 4 parts, 16.5 in 6, 21 in 10; batch 32 30 us whole, 43 in 2)."""
     if fused:  # the parts of a (sequence, KV head) are a thread-block cluster: at most 8
         return max(1, min(8, 2 * _sm_count() // (tokens * kv_heads), -(-capacity // 128)))
     return max(1, min(16, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
-
-
-_DECODE_COUNTERS: dict = {}  # device -> arrays of int32 zeros; the fused decode kernel leaves them zero
-
-
-def _decode_counters(device: torch.device, count: int) -> torch.Tensor:
-    """Counters on which the parts of a (sequence, KV head) count themselves off.  They live as
-    long as the process (captured steps hold their address); a larger step gets a larger array
-    and the old one stays alive for the steps that were captured with it.  Launches that share
-    an array must not overlap on the device: the engine issues its steps on one stream."""
-    held = _DECODE_COUNTERS.setdefault(device, [])
-    if not held or held[-1].numel() < count:
-        held.append(torch.zeros((max(count, 4096),), dtype=torch.int32, device=device))
-    return held[-1]
 
 
 DECODE_FROM_QKV_MAX_TOKENS = 64  # rows up to which attention takes the qkv rows itself: one launch fewer per layer, and the keys and values move before the predecessor ends (batch 8 / 16 / 32 / 64 decode 1 / 1.8 / 2.0 / 1.0 % faster; no change at 96 and 128 rows)
@@ -666,11 +652,10 @@ def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv
         raise KernelError("norm weights of the head size and one frequency per rotated pair are expected")
     out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size, True)
-    scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
-    counters = _decode_counters(qkv.device, tokens * kv_heads)
+    # (no scratch and no counters: the parts merge through their cluster's shared memory)
     status = lib.shiso_decode_attention_from_qkv(
         _ptr(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), float(eps), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
-        block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), _ptr(scratch), _ptr(counters), _ptr(out),
+        block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), 0, 0, _ptr(out),
         tokens, heads, kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), splits, int(bool(store)),
         _stream(),
     )
@@ -703,17 +688,16 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
     ):
         fused = bool(lib.shiso_decode_attention_fused_supported(heads, kv_heads, head_dim, page_size))
         splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size, fused)
-        scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
         if fused:
-            # keys and values by TMA, the parts merged by the CTA that finishes last: one launch
-            counters = _decode_counters(q.device, tokens * kv_heads)
+            # keys and values by TMA, the parts merged through their cluster's shared memory: one launch
             status = lib.shiso_decode_attention_fused(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
-                _ptr(step.seq_of_token), _ptr(scratch), _ptr(counters), _ptr(out), tokens, heads, kv_heads, head_dim,
+                _ptr(step.seq_of_token), 0, 0, _ptr(out), tokens, heads, kv_heads, head_dim,
                 page_size, k_cache.shape[0], float(scale), int(window), splits, _stream(),
             )
             _done(status, "decode_attention (fused)", shape=(tokens, heads, head_dim))
             return out
+        scratch = torch.empty((tokens * heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
         status = lib.shiso_decode_attention(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
             _ptr(step.seq_of_token), _ptr(scratch), _ptr(out), tokens, heads, kv_heads, head_dim, page_size,
