@@ -363,7 +363,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
 
 
 STREAM_MAX_TOKENS = 8  # rows for which the weight-streaming kernel runs the product-into-stream / scaled-product pair
-FUSED_NORM_MAX_TOKENS = 64  # up to here the tensor-memory kernel (tokens as the MMA's N operand) runs the pair: decode at batch 9 / 16 / 32 / 64 gains 11 / 10 / 4 / 1 % over product + norm kernel, batch 128 loses 2 % (the kernel takes up to 192 rows)
+FUSED_NORM_MAX_TOKENS = 192  # up to here (all the rows it takes) the tensor-memory kernel (tokens as the MMA's N operand) runs the pair: decode at batch 9 / 16 / 32 / 64 gained 11 / 10 / 4 / 1 % over product + norm kernel when the pair was built, batch 80 / 96 / 128 gain 4.2 / 4.2 / 3.6 % since a warp finishes whole tokens of the split products
 
 
 class ScaledRows:

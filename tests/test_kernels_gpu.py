@@ -877,8 +877,8 @@ def test_product_into_the_stream_then_scaled_product(shape, glu, bias, monkeypat
 def test_product_into_the_stream_declines_what_it_cannot_take():
     w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
     nw = torch.ones(32, device="cuda")
-    x = torch.zeros(65, 64, device="cuda", dtype=torch.bfloat16)
-    assert ops().linear_into_stream(x, w, torch.zeros(65, 32, device="cuda"), nw, 1e-5) is None  # too many rows
+    x = torch.zeros(193, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops().linear_into_stream(x, w, torch.zeros(193, 32, device="cuda"), nw, 1e-5) is None  # too many rows
     assert ops().linear_into_stream(x[:4].float(), w.float(), torch.zeros(4, 32, device="cuda"), nw, 1e-5) is None
 
 
