@@ -363,6 +363,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
 
 
 STREAM_MAX_TOKENS = 8  # rows for which the weight-streaming kernel runs the product-into-stream / scaled-product pair
+GLU_ONE_TILE_MAX_TOKENS = 64  # above one token tile the scaled gate/up pair runs as a plain product and the activation kernel: a gate/up CTA has an SM to itself, so two token tiles are 88 CTAs that each walk the whole K (20.9 us at 128 rows of the 1.2B shape against 17.8 us; decode at batch 96 / 128 +3.2 / +2.0 %)
 FUSED_NORM_MAX_TOKENS = 192  # up to here (all the rows it takes) the tensor-memory kernel (tokens as the MMA's N operand) runs the pair: decode at batch 9 / 16 / 32 / 64 gained 11 / 10 / 4 / 1 % over product + norm kernel when the pair was built, batch 80 / 96 / 128 gain 4.2 / 4.2 / 3.6 % since a warp finishes whole tokens of the split products
 
 
@@ -432,6 +433,8 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
     n = w.shape[0]
     if w.shape[1] != k or (glu and n % 2):
         raise KernelError(f"a matrix of shape {tuple(w.shape)} for rows of {k}")
+    if glu and tokens > GLU_ONE_TILE_MAX_TOKENS and out_dtype == torch.bfloat16 and (n // 2) % 8 == 0:
+        return swiglu(linear_scaled(rows, w, out_dtype, False))
     inter = n // 2 if glu else 0
     out = torch.empty((tokens, inter if glu else n), dtype=out_dtype, device=x.device)
     lib = library()
