@@ -736,8 +736,11 @@ SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, i
     return run_glu(p, x, w, stream);
 }
 
-// Rows of the fused-norm pair below: token tiles of at most 64.
+// Rows of the fused-norm pair below: token tiles of at most 64.  Up to 192 rows they are this
+// kernel's own tiles; a plain product takes up to 1,024 rows as tiles of 64 (the shapes
+// shiso_gemm_tcgen05_tokens64 is for), a gate/up pair does not.
 SHISO_API int shiso_gemm_tcgen05_fused_max_tokens(void) { return 192; }
+SHISO_API int shiso_gemm_tcgen05_fused_max_tokens64(void) { return 1024; }
 
 // Rows of T floats of `partials_out` that shiso_gemm_tcgen05_into writes for N features.
 SHISO_API int shiso_gemm_tcgen05_into_partial_rows(int N) { return (N + BM - 1) / BM; }
@@ -750,7 +753,7 @@ SHISO_API int shiso_gemm_tcgen05_into(const void* x, const void* w, const float*
                                       float* res_out, const float* next_norm_w, void* x_out, float* partials_out, int T,
                                       int N, int K, int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > shiso_gemm_tcgen05_fused_max_tokens() || !res_in || !res_out || !next_norm_w || !x_out || !partials_out)
+    if (T > shiso_gemm_tcgen05_fused_max_tokens64() || !res_in || !res_out || !next_norm_w || !x_out || !partials_out)
         return SHISO_ERR_UNSUPPORTED;
     if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
     GemmParams p = blank_params(T, N, K);
@@ -760,7 +763,7 @@ SHISO_API int shiso_gemm_tcgen05_into(const void* x, const void* w, const float*
     p.norm_w = next_norm_w;
     p.x_out = (__nv_bfloat16*)x_out;
     p.into_partials = partials_out;
-    return run_plain(p, x, w, sm_count, stream);
+    return run_plain(p, x, w, sm_count, stream, T > shiso_gemm_tcgen05_fused_max_tokens() ? 64 : 0);
 }
 
 // y = (x * rsqrt(mean square + eps)) w^T for rows x [T, K] that lack their RMS scale (x_out of
@@ -770,7 +773,9 @@ SHISO_API int shiso_gemm_tcgen05_scaled(const void* x, const float* partials, in
                                         float eps, const void* w, void* y, int y_dtype, int T, int N, int K, int inter,
                                         int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
-    if (T > shiso_gemm_tcgen05_fused_max_tokens() || !partials || partial_count <= 0 || partial_stride < T)
+    const bool tiles64 = T > shiso_gemm_tcgen05_fused_max_tokens();
+    if (T > (inter > 0 ? shiso_gemm_tcgen05_fused_max_tokens() : shiso_gemm_tcgen05_fused_max_tokens64()) || !partials ||
+        partial_count <= 0 || partial_stride < T)
         return SHISO_ERR_UNSUPPORTED;
     if (inter > 0 && N != 2 * inter) return SHISO_ERR_SHAPE;
     if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
@@ -782,5 +787,5 @@ SHISO_API int shiso_gemm_tcgen05_scaled(const void* x, const float* partials, in
     p.scale_count = partial_count;
     p.scale_stride = partial_stride;
     p.scale_eps = eps;
-    return inter > 0 ? run_glu(p, x, w, stream) : run_plain(p, x, w, sm_count, stream);
+    return inter > 0 ? run_glu(p, x, w, stream) : run_plain(p, x, w, sm_count, stream, tiles64 ? 64 : 0);
 }

@@ -72,6 +72,13 @@ struct PairParams {
     int inter;  // > 0: gate/up pair, N == inter
     int out_f32;
     int m_tiles, n_tiles;  // pair tiles: 256 tokens x (256 rows, or 128 outputs of a gate/up pair)
+    // SCALED: the rows of x lack their RMS scale (they are what a product into the stream left:
+    // gemm_tcgen05.cu); row t is scaled by rsqrt(sum over c < scale_count of
+    // scale_partials[c * scale_stride + t] / K + scale_eps), applied to the accumulators - a
+    // thread owns a row here, so it is one factor a thread and tile
+    const float* scale_partials;
+    int scale_count, scale_stride;
+    float scale_eps;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -301,12 +308,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const int acc = local & 1;
             const int m0 = (tile % p.m_tiles) * (2 * HALF_M) + (int)rank * HALF_M;
             const int n0 = (tile / p.m_tiles) * out_per_tile;
+            const int token = m0 + quarter * 32 + lane;
+            float row_scale = 1.0f;
+            if (p.scale_partials) {  // asked for before the accumulator is waited for
+                float sum = 0.0f;
+                if (token < p.T) {
+                    const float* mine = p.scale_partials + token;
+                    int c = 0;
+                    for (; c + 8 <= p.scale_count; c += 8) {  // eight loads in flight, added in index order
+                        float part[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) part[u] = mine[(size_t)(c + u) * p.scale_stride];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) sum += part[u];
+                    }
+                    for (; c < p.scale_count; ++c) sum += mine[(size_t)c * p.scale_stride];
+                }
+                row_scale = rsqrtf(sum / (float)p.K + p.scale_eps);
+            }
             if (!mbar_wait(&acc_full[acc], (local >> 1) & 1)) {
                 *failed = 1;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int token = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TILE_N;
             // four TMEM loads in flight before the one wait (32 gate and 32 up columns for the pair)
             constexpr int ROUND = GLU ? 32 : 64;
@@ -329,11 +353,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int q = 0; q < (GLU ? 2 : 4); ++q) {
                     float v[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[q][i]);
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[q][i]) * row_scale;
                     const int feature = n0 + c + 16 * q;
                     if (GLU) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]));
+                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]) * row_scale);
                     } else if (p.bias) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
@@ -400,16 +424,16 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const PairParams& p, in
 
 }  // namespace
 
-// x [T, K] bf16, w [N, K] (inter == 0) or [2 * inter, K] gate over up (inter > 0, N == inter), y [T, N].
-// K and N multiples of 8, pointers 16-byte aligned.
-SHISO_API int shiso_gemm_tcgen05_pair(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T,
-                                      int N, int K, int inter, int sm_count, cudaStream_t stream) {
+namespace {
+
+int run_pair(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N, int K, int inter,
+             const float* partials, int partial_count, int partial_stride, float eps, int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
     if (K % 8 != 0 || K < 8 || N % 8 != 0 || sm_count < 2) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return SHISO_ERR_ALIGN;
     if (inter > 0 && (N != inter || bias)) return SHISO_ERR_SHAPE;
     if (tc::encode_fn() == nullptr) return SHISO_ERR_UNSUPPORTED;
-    PairParams p;
+    PairParams p = {};
     p.y = y;
     p.bias = bias;
     p.status = shiso_tc_status_word();
@@ -421,9 +445,31 @@ SHISO_API int shiso_gemm_tcgen05_pair(const void* x, const void* w, const float*
     p.m_tiles = (T + 2 * HALF_M - 1) / (2 * HALF_M);
     const int out_per_tile = inter > 0 ? TILE_N / 2 : TILE_N;
     p.n_tiles = (N + out_per_tile - 1) / out_per_tile;
+    p.scale_partials = partials;
+    p.scale_count = partial_count;
+    p.scale_stride = partial_stride;
+    p.scale_eps = eps;
     CUtensorMap mx, mw;
     const int w_rows = inter > 0 ? 2 * inter : N;
     if (!tc::tensor_map(x, T, K, HALF_M, &mx) || !tc::tensor_map(w, w_rows, K, HALF_N, &mw)) return SHISO_ERR_UNSUPPORTED;
     if (inter > 0) return launch<true>(mx, mw, p, sm_count, stream);
     return launch<false>(mx, mw, p, sm_count, stream);
+}
+
+}  // namespace
+
+// x [T, K] bf16, w [N, K] (inter == 0) or [2 * inter, K] gate over up (inter > 0, N == inter), y [T, N].
+// K and N multiples of 8, pointers 16-byte aligned.
+SHISO_API int shiso_gemm_tcgen05_pair(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T,
+                                      int N, int K, int inter, int sm_count, cudaStream_t stream) {
+    return run_pair(x, w, bias, y, y_dtype, T, N, K, inter, nullptr, 0, 0, 0.0f, sm_count, stream);
+}
+
+// The same for rows x that lack their RMS scale (see PairParams): row t is scaled by
+// rsqrt(sum over c < partial_count of partials[c * partial_stride + t] / K + eps).
+SHISO_API int shiso_gemm_tcgen05_pair_scaled(const void* x, const float* partials, int partial_count, int partial_stride,
+                                             float eps, const void* w, void* y, int y_dtype, int T, int N, int K,
+                                             int inter, int sm_count, cudaStream_t stream) {
+    if (!partials || partial_count <= 0 || partial_stride < T) return SHISO_ERR_UNSUPPORTED;
+    return run_pair(x, w, nullptr, y, y_dtype, T, N, K, inter, partials, partial_count, partial_stride, eps, sm_count, stream);
 }

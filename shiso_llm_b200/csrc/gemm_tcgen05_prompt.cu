@@ -39,6 +39,11 @@ struct PromptParams {
     int inter;       // > 0: gate/up pair, N == inter
     int out_f32;
     int m_tiles, n_tiles;
+    // SCALED, as in gemm_tcgen05_pair.cu: row t of x lacks the factor rsqrt(sum over c < scale_count
+    // of scale_partials[c * scale_stride + t] / K + scale_eps); it is applied to the accumulators
+    const float* scale_partials;
+    int scale_count, scale_stride;
+    float scale_eps;
 };
 
 __device__ __forceinline__ void store16(const PromptParams& p, int token, int feature, const float* v) {
@@ -180,12 +185,29 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const int acc = local & 1;
             const int m0 = (tile % p.m_tiles) * TILE_M;
             const int n0 = (tile / p.m_tiles) * out_per_tile;
+            const int token = m0 + quarter * 32 + lane;
+            float row_scale = 1.0f;
+            if (p.scale_partials) {  // asked for before the accumulator is waited for
+                float sum = 0.0f;
+                if (token < p.T) {
+                    const float* mine = p.scale_partials + token;
+                    int c = 0;
+                    for (; c + 8 <= p.scale_count; c += 8) {  // eight loads in flight, added in index order
+                        float part[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) part[u] = mine[(size_t)(c + u) * p.scale_stride];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) sum += part[u];
+                    }
+                    for (; c < p.scale_count; ++c) sum += mine[(size_t)c * p.scale_stride];
+                }
+                row_scale = rsqrtf(sum / (float)p.K + p.scale_eps);
+            }
             if (!mbar_wait(&acc_full[acc], (local >> 1) & 1)) {
                 *failed = 1;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int token = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TILE_N;
             // Four TMEM loads are in flight before the one wait: 64 columns a round (32 gate and
             // 32 up for the pair), so the round trip to TMEM is paid 4 times a tile, not 16.
@@ -209,11 +231,11 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 for (int q = 0; q < (GLU ? 2 : 4); ++q) {
                     float v[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[q][i]);
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[q][i]) * row_scale;
                     const int feature = n0 + c + 16 * q;
                     if (GLU) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]));
+                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]) * row_scale);
                     } else if (p.bias) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
@@ -262,16 +284,16 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const PromptParams& p, 
 
 }  // namespace
 
-// x [T, K] bf16, w [N, K] (inter == 0) or [2 * inter, K] gate over up (inter > 0, N == inter), y [T, N].
-// K and N multiples of 8, pointers 16-byte aligned.
-SHISO_API int shiso_gemm_tcgen05_prompt(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T,
-                                        int N, int K, int inter, int sm_count, cudaStream_t stream) {
+namespace {
+
+int run_prompt(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N, int K, int inter,
+               const float* partials, int partial_count, int partial_stride, float eps, int sm_count, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return SHISO_OK;
     if (K % 8 != 0 || K < 8 || N % 8 != 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return SHISO_ERR_ALIGN;
     if (inter > 0 && (N != inter || bias)) return SHISO_ERR_SHAPE;
     if (tc::encode_fn() == nullptr) return SHISO_ERR_UNSUPPORTED;
-    PromptParams p;
+    PromptParams p = {};
     p.y = y;
     p.bias = bias;
     p.status = shiso_tc_status_word();
@@ -283,9 +305,30 @@ SHISO_API int shiso_gemm_tcgen05_prompt(const void* x, const void* w, const floa
     p.m_tiles = (T + TILE_M - 1) / TILE_M;
     const int out_per_tile = inter > 0 ? TILE_N / 2 : TILE_N;
     p.n_tiles = (N + out_per_tile - 1) / out_per_tile;
+    p.scale_partials = partials;
+    p.scale_count = partial_count;
+    p.scale_stride = partial_stride;
+    p.scale_eps = eps;
     CUtensorMap mx, mw;
     const int w_rows = inter > 0 ? 2 * inter : N;
     if (!tc::tensor_map(x, T, K, TILE_M, &mx) || !tc::tensor_map(w, w_rows, K, out_per_tile, &mw)) return SHISO_ERR_UNSUPPORTED;
     if (inter > 0) return launch<true>(mx, mw, p, sm_count, stream);
     return launch<false>(mx, mw, p, sm_count, stream);
+}
+
+}  // namespace
+
+// x [T, K] bf16, w [N, K] (inter == 0) or [2 * inter, K] gate over up (inter > 0, N == inter), y [T, N].
+// K and N multiples of 8, pointers 16-byte aligned.
+SHISO_API int shiso_gemm_tcgen05_prompt(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T,
+                                        int N, int K, int inter, int sm_count, cudaStream_t stream) {
+    return run_prompt(x, w, bias, y, y_dtype, T, N, K, inter, nullptr, 0, 0, 0.0f, sm_count, stream);
+}
+
+// The same for rows x that lack their RMS scale (see PromptParams).
+SHISO_API int shiso_gemm_tcgen05_prompt_scaled(const void* x, const float* partials, int partial_count, int partial_stride,
+                                               float eps, const void* w, void* y, int y_dtype, int T, int N, int K,
+                                               int inter, int sm_count, cudaStream_t stream) {
+    if (!partials || partial_count <= 0 || partial_stride < T) return SHISO_ERR_UNSUPPORTED;
+    return run_prompt(x, w, nullptr, y, y_dtype, T, N, K, inter, partials, partial_count, partial_stride, eps, sm_count, stream);
 }

@@ -36,6 +36,8 @@ _SIGNATURES = {
     "shiso_gemm_tcgen05_into_partial_rows": [I],
     "shiso_gemm_tcgen05_into": [P, P, P, P, P, P, P, P, I, I, I, I, P],
     "shiso_gemm_tcgen05_scaled": [P, P, I, I, F, P, P, I, I, I, I, I, I, P],
+    "shiso_gemm_tcgen05_pair_scaled": [P, P, I, I, F, P, P, I, I, I, I, I, I, P],
+    "shiso_gemm_tcgen05_prompt_scaled": [P, P, I, I, F, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_tcgen05_status": [],
     "shiso_gemm_stream": [P, P, P, P, I, I, I, I, I, I, P],
     "shiso_gemm_stream_into": [P, P, P, P, P, P, P, P, I, I, I, I, P],

@@ -266,6 +266,15 @@ def _sm_count() -> int:
 STREAM_KERNEL_MAX_TOKENS = 8  # up to here the persistent weight-streaming kernel runs the product (9..16 rows measured slower there than in the tensor-memory kernel)
 
 
+def _few_pair_tiles(tokens: int, n: int) -> bool:
+    """Whether a plain bfloat16 product of this shape runs as token tiles of 64 in the kernel for
+    few rows rather than as 256 x 256 tiles on SM pairs (the rule stands at FEW_PAIR_TILES)."""
+    return (
+        PROMPT_MIN_TOKENS <= tokens <= FEW_TILES_MAX_TOKENS
+        and -(-tokens // 256) * -(-n // 256) <= FEW_PAIR_TILES and -(-tokens // 64) * -(-n // 128) <= 2 * _sm_count()
+    )
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x[T, K] @ w[N, K]^T`` with float accumulation.
 
@@ -289,11 +298,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optio
         )
         _done(status, "linear (streaming)", shape=(tokens, n, k))
         return out
-    if (
-        both_bf16 and PROMPT_MIN_TOKENS <= tokens <= FEW_TILES_MAX_TOKENS
-        and -(-tokens // 256) * -(-n // 256) <= FEW_PAIR_TILES and -(-tokens // 64) * -(-n // 128) <= 2 * _sm_count()
-        and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w))
-    ):
+    if both_bf16 and _few_pair_tiles(tokens, n) and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
         status = lib.shiso_gemm_tcgen05_tokens64(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _code(out), tokens, n, k, _sm_count(), _stream()
         )
@@ -378,19 +383,22 @@ class ScaledRows:
 
 def linear_into_stream(x, w, residual, next_norm_w, eps, bias=None):
     """A block's output projection, the residual add and the first half of the next RMS norm in
-    one launch, for up to 64 bfloat16 rows: returns ``(residual + x @ w^T, ScaledRows)`` -
+    one launch, for up to 192 bfloat16 rows and for the products of a few hundred rows that run
+    as token tiles of 64 (``_few_pair_tiles``): returns ``(residual + x @ w^T, ScaledRows)`` -
     ``residual`` (float32 ``[T, N]``) itself is not changed - or None when sizes or types are
     not the ones the kernels take.  A handful of rows run in the weight-streaming kernel, more
     in the tensor-memory kernel whose threads own a feature each, so that a warp reads and
-    writes 32 neighbouring values of a token's row.  (The same pair of epilogues in the
+    writes neighbouring values of a token's row.  (The product into the stream in the
     tensor-memory kernels for long prompts was measured slower than product + row kernel:
     there a thread owns a row, and its strided reads and writes of the stream cost more than
-    the row kernel they replace.)"""
+    the row kernel they replace.  Applying the row scale is one factor a thread there, so those
+    kernels do take the rows this one leaves: ``linear_scaled``.)"""
     tokens, k = x.shape
     n = w.shape[0]
     if (
         x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or residual.dtype != torch.float32
-        or tokens > FUSED_NORM_MAX_TOKENS or k % 8 or w.shape[1] != k or n % 8
+        or k % 8 or w.shape[1] != k or n % 8
+        or (tokens > FUSED_NORM_MAX_TOKENS and not _few_pair_tiles(tokens, n))
     ):
         return None
     lib = library()
@@ -433,6 +441,8 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
     n = w.shape[0]
     if w.shape[1] != k or (glu and n % 2):
         raise KernelError(f"a matrix of shape {tuple(w.shape)} for rows of {k}")
+    if tokens > FUSED_NORM_MAX_TOKENS:
+        return _linear_scaled_long(rows, w, out_dtype, glu)
     if glu and tokens > GLU_ONE_TILE_MAX_TOKENS and out_dtype == torch.bfloat16 and (n // 2) % 8 == 0:
         return swiglu(linear_scaled(rows, w, out_dtype, False))
     inter = n // 2 if glu else 0
@@ -449,6 +459,40 @@ def linear_scaled(rows: ScaledRows, w, out_dtype, glu=False):
             _code(out), tokens, n, k, inter, _sm_count(), _stream(),
         )
     _done(status, "linear_scaled", shape=(tokens, n, k))
+    return out
+
+
+def _linear_scaled_long(rows: ScaledRows, w, out_dtype, glu):
+    """``linear_scaled`` for more than 192 rows: the kernel ``linear`` / ``linear_swiglu`` would
+    take for the shape, with the row scale in its epilogue."""
+    x = rows.x
+    tokens, k = x.shape
+    n = w.shape[0]
+    lib = library()
+    partials = rows.partials
+    if n % 8 or k % 8 or (glu and (n // 2) % 8):
+        raise KernelError(f"a scaled product of {tokens} rows wants feature counts that are multiples of 8, got {n} x {k}")
+    if glu:
+        inter = n // 2
+        out = torch.empty((tokens, inter), dtype=out_dtype, device=x.device)
+        product = lib.shiso_gemm_tcgen05_pair_scaled if tokens >= PAIR_MIN_TOKENS_GLU else lib.shiso_gemm_tcgen05_prompt_scaled
+        status = product(_ptr(x), _ptr(partials), partials.shape[0], partials.shape[1], rows.eps, _ptr(w), _ptr(out), _code(out),
+                         tokens, inter, k, inter, _sm_count(), _stream())
+        _done(status, "linear_scaled + swiglu (tcgen05, persistent)", shape=(tokens, n, k))
+        return out
+    out = torch.empty((tokens, n), dtype=out_dtype, device=x.device)
+    if _few_pair_tiles(tokens, n) and lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(w)):
+        status = lib.shiso_gemm_tcgen05_scaled(
+            _ptr(x), _ptr(partials), partials.shape[0], partials.shape[1], rows.eps, _ptr(w), _ptr(out), _code(out),
+            tokens, n, k, 0, _sm_count(), _stream(),
+        )
+        _done(status, "linear_scaled (tcgen05, token tiles of 64)", shape=(tokens, n, k))
+        return out
+    status = lib.shiso_gemm_tcgen05_pair_scaled(
+        _ptr(x), _ptr(partials), partials.shape[0], partials.shape[1], rows.eps, _ptr(w), _ptr(out), _code(out),
+        tokens, n, k, 0, _sm_count(), _stream(),
+    )
+    _done(status, "linear_scaled (tcgen05, persistent)", shape=(tokens, n, k))
     return out
 
 

@@ -836,7 +836,9 @@ def test_fused_projection_residual_add_and_norm(shape):
 
 @pytest.mark.parametrize("shape", [(8, 2048, 2048, 6144), (1, 96, 64, 200), (3, 264, 1000, 520), (7, 4096, 512, 64), (8, 2048, 5632, 2048), (5, 8, 24, 40),
                                    (9, 2048, 2048, 6144), (16, 264, 1000, 520), (33, 2048, 5632, 2048), (64, 2048, 2048, 3072), (100, 776, 264, 200),
-                                   (192, 2048, 5632, 11264), (130, 40, 72, 24)])
+                                   (192, 2048, 5632, 11264), (130, 40, 72, 24),
+                                   # more rows: the product into the stream as token tiles of 64, the scaled product in whichever kernel takes its shape
+                                   (256, 2048, 2048, 6144), (512, 2048, 5632, 6144), (600, 1024, 1024, 3072), (1000, 1032, 520, 264), (1024, 2048, 2048, 2048)])
 @pytest.mark.parametrize("glu", [False, True])
 @pytest.mark.parametrize("bias", [False, True])
 def test_product_into_the_stream_then_scaled_product(shape, glu, bias, monkeypatch):
@@ -877,8 +879,10 @@ def test_product_into_the_stream_then_scaled_product(shape, glu, bias, monkeypat
 def test_product_into_the_stream_declines_what_it_cannot_take():
     w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
     nw = torch.ones(32, device="cuda")
-    x = torch.zeros(193, 64, device="cuda", dtype=torch.bfloat16)
-    assert ops().linear_into_stream(x, w, torch.zeros(193, 32, device="cuda"), nw, 1e-5) is None  # too many rows
+    x = torch.zeros(1025, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops().linear_into_stream(x, w, torch.zeros(1025, 32, device="cuda"), nw, 1e-5) is None  # too many rows
+    wide = torch.zeros(8192, 64, device="cuda", dtype=torch.bfloat16)  # 600 x 8192 is a product for the SM pairs
+    assert ops().linear_into_stream(x[:600], wide, torch.zeros(600, 8192, device="cuda"), torch.ones(8192, device="cuda"), 1e-5) is None
     assert ops().linear_into_stream(x[:4].float(), w.float(), torch.zeros(4, 32, device="cuda"), nw, 1e-5) is None
 
 
