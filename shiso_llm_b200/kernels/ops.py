@@ -63,7 +63,7 @@ def resolve_binding(wanted_index, bound_index, current_index) -> int:
     if bound_index is not None and index != bound_index:
         raise KernelError(
             f"this process's kernel library works on cuda:{bound_index} (attributes of its kernels, its status word and "
-            f"its counters live there); an engine on cuda:{index} needs a process of its own"
+            f"live there); an engine on cuda:{index} needs a process of its own"
         )
     return index
 
@@ -72,7 +72,7 @@ def bind_device(device) -> int:
     """Binds the kernel library to ``device`` (a torch.device of type cuda) and makes it the
     current device; returns its index.  The library keeps per-process state for one device -
     which kernels were given their shared-memory attribute, the status word of the bounded
-    waits, the decode attention's counters - and every launch goes to the current device's
+    waits - and every launch goes to the current device's
     stream, so all engines of a process share one device; another one is refused here, before
     a pointer of one device could reach a kernel on another."""
     global _DEVICE_INDEX
