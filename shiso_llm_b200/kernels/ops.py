@@ -62,7 +62,7 @@ def resolve_binding(wanted_index, bound_index, current_index) -> int:
     index = current_index if wanted_index is None else wanted_index
     if bound_index is not None and index != bound_index:
         raise KernelError(
-            f"this process's kernel library works on cuda:{bound_index} (attributes of its kernels, its status word and "
+            f"this process's kernel library works on cuda:{bound_index} (attributes of its kernels and its status word "
             f"live there); an engine on cuda:{index} needs a process of its own"
         )
     return index
