@@ -552,7 +552,7 @@ def test_decode_attention_split_keys(case):
 
 
 @pytest.mark.parametrize("page", [16, 64, 8])
-@pytest.mark.parametrize("parts", [1, 2, 8])
+@pytest.mark.parametrize("parts", [1, 2, 3, 5, 7, 8])
 def test_decode_attention_long_parts(page, parts, monkeypatch):
     """Head size 64 takes the kernel that brings pages in by TMA and merges the parts itself:
     parts of many tiles (the ring is refilled dozens of times), one part alone (no merge), more
