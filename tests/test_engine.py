@@ -516,3 +516,46 @@ def test_a_model_that_reads_a_further_per_row_input(backend):
         assert refused.finish_reason == "error" and "values of 'segment'" in refused.error
     finally:
         toy_parts.unregister()
+
+
+@pytest.mark.gpu
+def test_lookahead_stop_and_preemption_in_bfloat16_with_graphs_of_twelve(tmp_path):
+    """Twelve requests in bfloat16 with captured decode steps of up to twelve rows, a pool so small
+    that requests are preempted and recomputed, one request that ends on a stop token: with and
+    without lookahead the tokens are the same, and along every request's own sequence each token
+    is the plain implementation's best wherever that one leads clearly."""
+    doc, seed = helpers.TINY["B"]
+    tensors = helpers.make_folder(tmp_path, doc, seed)
+    prompts = [helpers.random_prompt(n, doc["vocab_size"], 90 + n) for n in (3, 21, 50, 9, 33, 17, 5, 40, 12, 28, 7, 45)]
+
+    def run(lookahead, stop):
+        params = [SamplingParams(temperature=0.0, max_new_tokens=14 if i else 20, stop_token_ids=stop if i == 0 else ())
+                  for i in range(len(prompts))]
+        llm = LLM(str(tmp_path), dtype="bfloat16", ctx=128, page_size=16, kv_cache_tokens=448, allow_small_pool=True,
+                  max_num_seqs=12, max_num_batched_tokens=48, prefill_chunk=19, lookahead=lookahead, device="cuda:0")
+        outs = llm.generate(prompts, params)
+        llm.engine.cache.check()
+        assert not llm.has_unfinished() and llm.engine.cache.slots.free_slots == 12
+        return outs, llm
+
+    free_run, _ = run(False, ())
+    first = free_run[0].token_ids
+    cut = next((i for i in range(3, len(first)) if first[i] not in first[:i]), None)
+    assert cut is not None, "the tiny model repeats itself too early for this test"
+    stop = (first[cut],)
+    waited, llm_waited = run(False, stop)
+    ahead, llm_ahead = run(True, stop)
+    assert llm_waited.scheduler.stats["preempted"] > 0 and llm_ahead.scheduler.stats["preempted"] > 0
+    assert llm_ahead.engine.graphs is not None and max(llm_ahead.engine.graphs._graphs) >= 8
+    assert [(o.token_ids, o.finish_reason) for o in waited] == [(o.token_ids, o.finish_reason) for o in ahead]
+    assert ahead[0].finish_reason == "stop" and ahead[0].token_ids == first[:cut]
+    checked = 0
+    for prompt, out in zip(prompts, ahead):
+        logits = plain_lfm2.plain_forward(doc, tensors, prompt + out.token_ids[:-1])[len(prompt) - 1:] if len(out.token_ids) > 1 else \
+            plain_lfm2.plain_forward(doc, tensors, prompt)[len(prompt) - 1:]
+        top2 = logits.topk(2, dim=-1)
+        clear = (top2.values[:, 0] - top2.values[:, 1]) > 0.2 * logits.std()
+        picked = torch.tensor(out.token_ids)
+        assert (picked[clear] == top2.indices[clear, 0]).all(), (out.token_ids, top2.indices[:, 0].tolist())
+        checked += int(clear.sum())
+    assert checked >= 40
