@@ -133,3 +133,36 @@ def test_real_layer_sizes_a_dozen_decoding_requests(sized, dtype):
         seen = starts[n] + (8 if i < 3 else 13)
         check_logits(replay.stack_rows(rows, n, seen), references[n][:seen], dtype, f"request {n} of twelve, {dtype}")
     engine.cache.check()
+
+
+@pytest.mark.parametrize("live", [40, 80])
+def test_real_layer_sizes_dozens_of_decoding_requests(sized, live):
+    """Forty and eighty requests decoding together in bfloat16 at the same layer sizes: one
+    token tile of 64 and two of them in the products whose K is split over a cluster (the
+    residual add and norm in their epilogues, above 64 rows the gate/up pair as product and
+    activation kernel), attention from the qkv rows (forty) and from queries (eighty), captured
+    steps; a third of the requests end on the way and the rest go on in a smaller step."""
+    from shiso_llm_b200.kernels import ops
+
+    document, plan, specs, stored, _, _ = sized
+    by = {s.name: s for s in specs}
+    tensors = {k: v.to("cuda", target_dtype(by[k], v.dtype, torch.bfloat16)) for k, v in stored.items()}
+    options = EngineOptions(dtype="bfloat16", ctx=128, page_size=16, kv_cache_tokens=live * 48, max_num_seqs=live,
+                            max_num_batched_tokens=1024)
+    engine = Engine.from_plan(plan, tensors, options, ops)
+    names = [f"r{i}" for i in range(live)]
+    prompts = {n: helpers.random_prompt(20 + i % 9, document["vocab_size"], 140 + i) for i, n in enumerate(names)}
+    starts = {n: 6 + i % 5 for i, n in enumerate(names)}  # rows that go in with the first step
+    references = {n: plain_lfm2.plain_forward(document, stored, prompts[n]) for n in names}
+    early = names[: live // 3]
+    steps = [([(n, prompts[n][: starts[n]], list(range(starts[n]))) for n in names], [])]
+    for k in range(4):
+        steps.append(([(n, [prompts[n][starts[n] + k]], [0]) for n in names], early if k == 3 else []))
+    for k in range(4, 8):
+        steps.append(([(n, [prompts[n][starts[n] + k]], [0]) for n in names[live // 3:]], names[live // 3:] if k == 7 else []))
+    rows = helpers.run_steps(engine, steps)
+    ops.check_kernel_status()
+    for i, n in enumerate(names):
+        seen = starts[n] + (4 if n in early else 8)
+        check_logits(replay.stack_rows(rows, n, seen), references[n][:seen], "bfloat16", f"request {n} of {live}")
+    engine.cache.check()
