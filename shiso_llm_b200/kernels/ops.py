@@ -471,7 +471,18 @@ def _linear_scaled_long(rows: ScaledRows, w, out_dtype, glu):
     lib = library()
     partials = rows.partials
     if n % 8 or k % 8 or (glu and (n // 2) % 8):
-        raise KernelError(f"a scaled product of {tokens} rows wants feature counts that are multiples of 8, got {n} x {k}")
+        # widths the prompt kernels do not take: the kernel for up to 192 rows takes any, a
+        # slice of the rows at a time (the partial sums' columns are the tokens)
+        out = torch.empty((tokens, n // 2 if glu else n), dtype=out_dtype, device=x.device)
+        stride = partials.shape[1]
+        for first in range(0, tokens, FUSED_NORM_MAX_TOKENS):
+            count = min(FUSED_NORM_MAX_TOKENS, tokens - first)
+            status = lib.shiso_gemm_tcgen05_scaled(
+                _ptr(x[first : first + count]), partials.data_ptr() + 4 * first, partials.shape[0], stride, rows.eps, _ptr(w),
+                _ptr(out[first : first + count]), _code(out), count, n, k, n // 2 if glu else 0, _sm_count(), _stream(),
+            )
+            _done(status, "linear_scaled (a slice of the rows)", shape=(count, n, k))
+        return out
     if glu:
         inter = n // 2
         out = torch.empty((tokens, inter), dtype=out_dtype, device=x.device)

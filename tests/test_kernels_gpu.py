@@ -838,7 +838,8 @@ def test_fused_projection_residual_add_and_norm(shape):
                                    (9, 2048, 2048, 6144), (16, 264, 1000, 520), (33, 2048, 5632, 2048), (64, 2048, 2048, 3072), (100, 776, 264, 200),
                                    (192, 2048, 5632, 11264), (130, 40, 72, 24),
                                    # more rows: the product into the stream as token tiles of 64, the scaled product in whichever kernel takes its shape
-                                   (256, 2048, 2048, 6144), (512, 2048, 5632, 6144), (600, 1024, 1024, 3072), (1000, 1032, 520, 264), (1024, 2048, 2048, 2048)])
+                                   (256, 2048, 2048, 6144), (512, 2048, 5632, 6144), (600, 1024, 1024, 3072), (1000, 1032, 520, 264), (1024, 2048, 2048, 2048),
+                                   (400, 1024, 264, 1002)])  # a consumer whose width is no multiple of 8
 @pytest.mark.parametrize("glu", [False, True])
 @pytest.mark.parametrize("bias", [False, True])
 def test_product_into_the_stream_then_scaled_product(shape, glu, bias, monkeypatch):
