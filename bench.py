@@ -333,7 +333,7 @@ def main() -> int:
     reps = max(3, args.reps)
     # a repetition's requests: prompt, warm-up steps, the end-to-end block and the device-timed block
     # (the first request also decodes while the others' prompts are read, one prompt a step)
-    budget = PROMPT_LEN + 2 * (args.steps + args.warmup) + max_batch + 64
+    budget = PROMPT_LEN + 2 * (args.steps + args.warmup) + 2 * max_batch + 64
     ctx = max(4096, -(-budget // 16) * 16)
     options = EngineOptions(
         dtype="bfloat16", ctx=ctx, page_size=16, kv_cache_tokens=max(max_batch * budget, ctx),
@@ -355,7 +355,7 @@ def main() -> int:
         """Fresh requests: prompts of 2,048 tokens, ``warmup`` decode steps, then ``steps`` steps end
         to end through LLM.step and ``steps`` steps device-timed through Engine.step."""
         llm = LLM(engine)
-        params = SamplingParams(temperature=0.0, max_new_tokens=batch + steps + warmup + 8, ignore_eos=True)
+        params = SamplingParams(temperature=0.0, max_new_tokens=2 * batch + steps + warmup + 16, ignore_eos=True)
         for p in prompts(batch):
             llm.add_request(p, params)
         # prompts are admitted one per step; run until every request is decoding
