@@ -339,7 +339,8 @@ def test_rotation_over_pairs_of_neighbours(dtype, case):
 
 @pytest.mark.parametrize("case", [(32, 8, 16), (12, 3, 8), (5, 1, 64), (7, 7, 32), (16, 1, 16)])
 @pytest.mark.parametrize("store", [True, False])
-def test_decode_attention_from_the_qkv_rows(case, store):
+@pytest.mark.parametrize("many", [False, True])
+def test_decode_attention_from_the_qkv_rows(case, store, many):
     """Steps of single tokens, bfloat16, heads of 64: norm + rotation + cache store + attention
     as one launch.  Against the two kernels it replaces: the caches must hold the same bits
     afterwards (and nothing else may have changed), the outputs agree up to the rounding of
@@ -348,7 +349,9 @@ def test_decode_attention_from_the_qkv_rows(case, store):
     cache (nothing is stored then)."""
     heads, kv_heads, page = case
     d = 64
-    starts = [0, page - 1, page, 63, 64, 700, 2100]  # seven rows: the engine sends up to eight this way
+    starts = [0, page - 1, page, 63, 64, 700, 2100]  # seven rows; the engine sends up to 64 this way
+    if many:
+        starts = starts[:6] + [(i * 53) % 600 for i in range(34)]  # forty rows: parts of other lengths, clusters of other sizes
     num_pages = sum(-(-(s + 1) // page) for s in starts) + 3
     cpu, gpu, table = make_step([1] * len(starts), starts, page, num_pages, 170)
     cpu.all_decode = gpu.all_decode = True
