@@ -171,7 +171,9 @@ class LLM:
             self.sampler.sample_into(logits, params, positions, picks)
         host = self._host_picks[self._turn]
         self._turn ^= 1
-        host[:carried].copy_(self.engine.fed_tokens[:carried], non_blocking=True)
+        to_host = getattr(self.engine.env.ops, "words_to_host", None) if picks.is_cuda else None
+        if to_host is None or not to_host(self.engine.fed_tokens[:carried], host):
+            host[:carried].copy_(self.engine.fed_tokens[:carried], non_blocking=True)
         event = None
         if picks.is_cuda:
             event = torch.cuda.Event()

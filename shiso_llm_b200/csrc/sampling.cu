@@ -288,6 +288,15 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     if (threadIdx.x == 0) out[r] = (chosen.i == 0x7fffffff) ? top.i : chosen.i;
 }
 
+// Words from one buffer to another when one of the two is pinned host memory that the device
+// reads or writes in place: a step's few tokens reach the host (and its few KB of row data the
+// device) as loads and stores of a kernel in the stream, without a turn of the copy engine
+// between two kernels.
+__global__ void __launch_bounds__(256) copy_words_kernel(const int* __restrict__ src, int* __restrict__ dst, int n) {
+    pdl_begin();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace
 
 // `status_out` (may be null) receives the status word, which is cleared; see the file's head.
@@ -329,5 +338,25 @@ SHISO_API int shiso_argmax_chunked(const float* logits, int* out, float* scratch
     launch_kernel(argmax_chunk_kernel, dim3(chunks, rows), 256, 0, stream, logits, best_v, best_i, vocab, chunk_len, chunks);
     launch_kernel(argmax_final_kernel, rows, 32, 0, stream, best_v, best_i, out, chunks,
                   status_out ? shiso_tc_status_word() : nullptr, status_out);
+    return launch_status();
+}
+
+// Copies `n` 32-bit words in a kernel.  `host_side` says which buffer is pinned host memory
+// (1: the source, 2: the destination, 0: neither); its device address is asked of the runtime,
+// and memory that the device cannot address is refused, so the caller can fall back to a copy.
+SHISO_API int shiso_copy_words(const int* src, int* dst, int n, int host_side, cudaStream_t stream) {
+    if (n <= 0) return SHISO_OK;
+    void* mapped = nullptr;
+    if (host_side == 1 || host_side == 2) {
+        void* host = host_side == 1 ? (void*)src : (void*)dst;
+        if (cudaHostGetDevicePointer(&mapped, host, 0) != cudaSuccess || mapped == nullptr) {
+            cudaGetLastError();
+            return SHISO_ERR_UNSUPPORTED;
+        }
+        if (host_side == 1) src = (const int*)mapped; else dst = (int*)mapped;
+    } else if (host_side != 0) {
+        return SHISO_ERR_SHAPE;
+    }
+    launch_kernel(copy_words_kernel, n <= 4096 ? ceil_div_u(n, 256) : 16, 256, 0, stream, src, dst, n);
     return launch_status();
 }

@@ -113,6 +113,18 @@ class StepBuilder:
         self.device_block = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._arange = np.arange(max_seqs + 2, dtype=np.int32)
         self.fed_tokens: Optional[torch.Tensor] = None  # set by the engine; None: steps carry no feed arrays
+        self.ops = None  # set by the engine: the kernels, whose ``words_from_host`` (if any) moves small blocks
+
+    KERNEL_COPY_MAX_WORDS = 16384  # larger blocks (long prompt steps) take the copy engine
+
+    def _to_device(self, stage: torch.Tensor, words: int) -> None:
+        """The step's block from its pinned staging buffer to the device, in the stream: a small
+        block as loads of a kernel that reads the host's memory in place (no turn of the copy
+        engine before the step's first kernel), a large one or any the kernel refuses as a copy."""
+        from_host = getattr(self.ops, "words_from_host", None) if self.ops is not None else None
+        if from_host is not None and words <= self.KERNEL_COPY_MAX_WORDS and from_host(stage, self.device_block[:words]):
+            return
+        self.device_block[:words].copy_(stage[:words], non_blocking=True)
 
     def _iota(self, n: int) -> np.ndarray:
         return self._arange[:n]
@@ -217,7 +229,7 @@ class StepBuilder:
         if self.row_inputs:
             self._fill_extras(host, lay, entries, q_start, num_tokens)
         dev = self.device_block
-        dev[: lay.total].copy_(stage[: lay.total], non_blocking=True)
+        self._to_device(stage, lay.total)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -326,7 +338,7 @@ class StepBuilder:
         if self.row_inputs:
             self._fill_extras(host, lay, entries, q_start, pad_tokens)
         dev = self.device_block
-        dev[: lay.total].copy_(stage[: lay.total], non_blocking=True)
+        self._to_device(stage, lay.total)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()

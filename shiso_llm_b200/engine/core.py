@@ -159,6 +159,7 @@ class Engine:
         # (One more entry at the end: the picking kernel may leave the kernels' status word there.)
         self.fed_tokens = torch.zeros(max(1, options.max_num_seqs) + 1, dtype=torch.int32, device=self.device)
         self.builder.fed_tokens = self.fed_tokens
+        self.builder.ops = model.env.ops
         self.steps_run = 0
         self.graphs = None
         self.step_graphs = None
@@ -175,6 +176,7 @@ class Engine:
             most = decode_bucket(options.max_num_seqs) if cache.scratch_slot is not None else options.max_num_seqs
             decode_builder = StepBuilder(cache, self.device, most, most, fixed_table_width=cache.max_blocks, row_inputs=row_inputs)
             decode_builder.fed_tokens = self.fed_tokens
+            decode_builder.ops = model.env.ops
             self.graphs = DecodeGraphs(model, cache, decode_builder)
             if options.graph_mixed_steps and cache.scratch_slot is not None:
                 from .graphs import StepGraphs, sequence_bucket, token_bucket
@@ -185,6 +187,7 @@ class Engine:
                     fixed_table_width=cache.max_blocks, row_inputs=row_inputs,
                 )
                 padded_builder.fed_tokens = self.fed_tokens
+                padded_builder.ops = model.env.ops
                 self.step_graphs = StepGraphs(model, cache, padded_builder)
 
     def enable_layer_dump(self, level: int = 1, out=None) -> None:

@@ -55,6 +55,7 @@ _SIGNATURES = {
     "shiso_argmax_chunked": [P, P, P, I, I, I, P, P],
     "shiso_sample": [P, P, P, P, P, P, P, P, I, I, P, P],
     "shiso_suppress": [P, P, P, I, I, I, P],
+    "shiso_copy_words": [P, P, I, I, P],
     "shiso_selftest_bounded_wait": [LL, P],
 }
 

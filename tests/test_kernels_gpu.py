@@ -1008,3 +1008,24 @@ def test_stream_pair_at_random_sizes(seed, monkeypatch):
         scale = (ref.linear_swiglu(x, w2, torch.float32) if glu else ref.linear(x, w2, torch.float32)).abs().max().item()
         close(y, want, torch.bfloat16, f"scaled product {(T, H, K1, N2, glu)}", scale=2 * scale)
     ops().check_kernel_status()
+
+
+@pytest.mark.parametrize("words", [1, 9, 300, 5000, 16384])
+def test_words_between_pinned_host_memory_and_the_device_by_kernel(words):
+    """A step's block and its tokens move as loads and stores of a kernel that addresses pinned
+    host memory in place; memory that is not pinned, or too small, is left to the caller's copy."""
+    g = torch.Generator().manual_seed(words)
+    source = torch.randint(-2**31, 2**31 - 1, (words + 7,), dtype=torch.int32, generator=g).pin_memory()
+    on_device = torch.zeros(words, dtype=torch.int32, device="cuda")
+    assert ops().words_from_host(source, on_device) is True
+    assert torch.equal(on_device.cpu(), source[:words])
+    back = torch.zeros(words + 3, dtype=torch.int32).pin_memory()
+    assert ops().words_to_host(on_device, back) is True
+    torch.cuda.synchronize()
+    assert torch.equal(back[:words], source[:words]) and not back[words:].any()
+    assert ops().words_from_host(torch.zeros(words, dtype=torch.int32), on_device) is False  # pageable memory
+    assert ops().words_to_host(on_device, torch.zeros(words, dtype=torch.int32)) is False
+    if words > 1:
+        assert ops().words_to_host(on_device, torch.zeros(words - 1, dtype=torch.int32).pin_memory()) is False
+        assert ops().words_from_host(torch.zeros(words - 1, dtype=torch.int32).pin_memory(), on_device) is False
+    ops().check_kernel_status()
