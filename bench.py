@@ -524,7 +524,7 @@ def main() -> int:
             "prompt_len": PROMPT_LEN,
             "mean_context": main_point["context"],
             "page_size": 16,
-            "step_launch": ("cuda graph" if not args.no_cuda_graphs else "kernel by kernel") + ", lookahead 1 in e2e",
+            "step_launch": ("cuda graph" if not args.no_cuda_graphs else "kernel by kernel") + ", lookahead 1 in e2e; the step's inputs and tokens cross from and to pinned host memory by kernel",
             "l2": "inputs larger than L2 (1.8 GB of weights read per step)",
             "peaks": peak_source,
         },
