@@ -58,8 +58,6 @@ struct DecodeTmaArgs {
     const int* block_table;   // [S, width]
     const int* positions;     // [T]
     const int* seq_of_token;  // [T]
-    float* partial;           // unused since the parts merge through the cluster's shared memory
-    int* counters;            // unused likewise
     __nv_bfloat16* out;       // [T, heads * 64]
     int* status;
     int width, heads, kv_heads, page_size, splits, window;
@@ -547,7 +545,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const Decode
 
 // What both entry points check and fill in.
 int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* block_table, int table_width,
-                       const int* positions, const int* seq_of_token, float* scratch, int* counters, void* out, int tokens,
+                       const int* positions, const int* seq_of_token, void* out, int tokens,
                        int heads, int kv_heads, int head_dim, int page_size, long long num_pages, float scale, int window,
                        int splits, DecodeTmaArgs* a, CUtensorMap* mk, CUtensorMap* mv) {
     if (kv_heads <= 0 || heads % kv_heads || splits < 1) return SHISO_ERR_SHAPE;
@@ -564,8 +562,6 @@ int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* bloc
     a->block_table = block_table;
     a->positions = positions;
     a->seq_of_token = seq_of_token;
-    a->partial = scratch;
-    a->counters = counters;
     a->out = (__nv_bfloat16*)out;
     a->status = shiso_tc_status_word();
     a->width = table_width;
@@ -581,18 +577,18 @@ int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* bloc
 
 }  // namespace
 
-// As shiso_decode_attention, with the number of pages of the caches; at most 8 parts.  `scratch` and
-// `counters` are not used any more (the parts merge through the cluster's shared memory).
+// As shiso_decode_attention, with the number of pages of the caches; at most 8 parts, which merge
+// through their cluster's shared memory (no scratch in global memory).
 SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                           int table_width, const int* positions, const int* seq_of_token, float* scratch,
-                                           int* counters, void* out, int tokens, int heads, int kv_heads, int head_dim,
+                                           int table_width, const int* positions, const int* seq_of_token,
+                                           void* out, int tokens, int heads, int kv_heads, int head_dim,
                                            int page_size, long long num_pages, float scale, int window, int splits,
                                            cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if ((uintptr_t)q & 15) return SHISO_ERR_ALIGN;
     DecodeTmaArgs a;
     CUtensorMap mk, mv;
-    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token, scratch, counters,
+    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token,
                                           out, tokens, heads, kv_heads, head_dim, page_size, num_pages, scale, window, splits, &a,
                                           &mk, &mv);
     if (status != SHISO_OK) return status;
@@ -608,7 +604,7 @@ SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, c
 SHISO_API int shiso_decode_attention_from_qkv(const void* qkv, const float* q_w, const float* k_w, const float* inv_freq,
                                               float eps, void* k_cache, void* v_cache, const int* block_table,
                                               int table_width, const int* positions, const int* seq_of_token,
-                                              float* scratch, int* counters, void* out, int tokens, int heads, int kv_heads,
+                                              void* out, int tokens, int heads, int kv_heads,
                                               int head_dim, int page_size, long long num_pages, float scale, int window,
                                               int splits, int store, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
@@ -616,7 +612,7 @@ SHISO_API int shiso_decode_attention_from_qkv(const void* qkv, const float* q_w,
     if ((uintptr_t)qkv & 15) return SHISO_ERR_ALIGN;
     DecodeTmaArgs a;
     CUtensorMap mk, mv;
-    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token, scratch, counters,
+    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token,
                                           out, tokens, heads, kv_heads, head_dim, page_size, num_pages, scale, window, splits, &a,
                                           &mk, &mv);
     if (status != SHISO_OK) return status;

@@ -710,10 +710,9 @@ def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv
         raise KernelError("norm weights of the head size and one frequency per rotated pair are expected")
     out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size, True)
-    # (no scratch and no counters: the parts merge through their cluster's shared memory)
     status = lib.shiso_decode_attention_from_qkv(
         _ptr(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), float(eps), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
-        block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), 0, 0, _ptr(out),
+        block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), _ptr(out),
         tokens, heads, kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), splits, int(bool(store)),
         _stream(),
     )
@@ -750,7 +749,7 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
             # keys and values by TMA, the parts merged through their cluster's shared memory: one launch
             status = lib.shiso_decode_attention_fused(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
-                _ptr(step.seq_of_token), 0, 0, _ptr(out), tokens, heads, kv_heads, head_dim,
+                _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, head_dim,
                 page_size, k_cache.shape[0], float(scale), int(window), splits, _stream(),
             )
             _done(status, "decode_attention (fused)", shape=(tokens, heads, head_dim))
