@@ -357,6 +357,6 @@ SHISO_API int shiso_copy_words(const int* src, int* dst, int n, int host_side, c
     } else if (host_side != 0) {
         return SHISO_ERR_SHAPE;
     }
-    launch_kernel(copy_words_kernel, n <= 4096 ? ceil_div_u(n, 256) : 16, 256, 0, stream, src, dst, n);
+    launch_kernel(copy_words_kernel, n <= 65536 ? ceil_div_u(n, 256) : 256, 256, 0, stream, src, dst, n);
     return launch_status();
 }
