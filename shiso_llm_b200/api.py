@@ -116,6 +116,16 @@ class LLM:
     def abort(self, request_id) -> bool:
         return self.scheduler.abort(request_id)
 
+    def __del__(self):
+        # A step still on its way stores its tokens into this object's pinned buffers: they go
+        # back to the allocator only after it has.
+        launched = getattr(self, "_in_flight", None)
+        if launched is not None and launched[3] is not None:
+            try:
+                launched[3].synchronize()
+            except Exception:
+                pass
+
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work() or self._in_flight is not None
 
