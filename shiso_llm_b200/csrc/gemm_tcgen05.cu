@@ -649,7 +649,12 @@ int run_plain(GemmParams p, const void* x, const void* w, int sm_count, cudaStre
     while (splits > 2 && tiles * splits > 7 * sm_count / 4) --splits;
     while (splits > 1 && total_kb / splits < (tile_override > 0 ? 8 : 2)) --splits;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    // More tiles than the two CTAs an SM holds with deep rings, but no more than four an SM: rings of
+    // two stages, so that every tile is resident at once instead of a second, partly empty wave
+    // (the head's 512 tiles of 128 features on 148 SMs).
+    const bool one_wave_of_four = splits == 1 && tiles > room && tiles <= 4 * sm_count && tile_override == 0;
 #define SHISO_PICK(BN_)                                                        \
+    if (one_wave_of_four) return launch<BN_, 2, 1>(mw, mx, p, stream);         \
     switch (splits) {                                                          \
         case 1: return launch<BN_, WHOLE_STAGES, 1>(mw, mx, p, stream);                   \
         case 2: return launch<BN_, SPLIT_STAGES, 2>(mw, mx, p, stream);                   \

@@ -678,7 +678,8 @@ def test_prefill_attention_never_reads_outside_its_range():
                                    (64, 6144, 2048), (33, 2048, 5632), (50, 776, 264), (64, 48, 8), (40, 11264, 2048),
                                    (65, 2048, 2048), (100, 776, 264), (128, 6144, 2048), (129, 2048, 5632), (192, 11264, 2048), (177, 40, 72),
                                    (8, 2048, 8192), (8, 16384, 2048), (64, 2048, 8192), (48, 16384, 2048),  # a feed-forward of 8,192 (block_ff_dim 12,288)
-                                   (40, 998, 264), (64, 1210, 520)])  # rows that are no whole groups of four features
+                                   (40, 998, 264), (64, 1210, 520),  # rows that are no whole groups of four features
+                                   (33, 40000, 264), (64, 65536, 520), (16, 50008, 72)])  # 313 to 512 feature tiles: one wave of four CTAs an SM with rings of two stages
 def test_skinny_linear_and_fused_swiglu(shape):
     """A handful of bfloat16 rows take the weight-streaming kernel, up to 192 the tensor-memory
     kernel with tokens as the MMA's N operand (tiles of at most 64 tokens, K split over a
