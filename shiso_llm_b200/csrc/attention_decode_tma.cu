@@ -42,7 +42,13 @@ constexpr int TILE = 64;           // keys per tile
 constexpr int ROW = HEAD * 2;      // bytes per key or value row
 constexpr int TILE_BYTES = TILE * ROW;
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // keys, then values
-constexpr int STAGES = 6;           // two CTAs fit an SM; with four (three CTAs an SM) a part of nine tiles went round the ring twice
+// Tiles in a CTA's ring.  Six: two CTAs fit an SM (with four tiles and three CTAs an SM a part of nine
+// tiles went round the ring twice).  A CTA alone takes about 0.7 us a tile whatever the SM's other
+// CTAs do (the chain product - maximum - exponentials - product of one tile), so two CTAs an SM draw
+// the HBM rate only while all of them are resident: 256 CTAs (batch 32 x 8 KV heads x 2,158 keys)
+// took 25.9 us, 384 took 49.2 and 512 took 50.7 - a second wave of the same length.  Unsplit launches
+// of more CTAs than two an SM therefore take rings of three tiles and no inbox: four CTAs fit an SM.
+constexpr int RING_DEEP = 6, RING_SHALLOW = 3;
 constexpr int CONSUMERS = 4;
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int KSTEPS = HEAD / 16;
@@ -50,8 +56,9 @@ constexpr int DTILES = HEAD / 8;
 constexpr int MERGE_ROW = HEAD + 2;  // floats: output, running maximum (log2 units), sum
 constexpr int MAX_PARTS = 8;        // the parts of a (sequence, KV head) are a thread-block cluster (portable size)
 constexpr int INBOX_ROWS = 32;      // rows a CTA may be sent: parts x the heads it merges, below 16 + 8
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + INBOX_ROWS * MERGE_ROW * 4 + 1024 + 128;
-static_assert(CONSUMERS * 16 * MERGE_ROW * 4 <= STAGES * STAGE_BYTES, "the merge area lies over the ring");
+constexpr int smem_bytes(int stages, bool inbox) {  // ring, 256 bytes of barriers and flags, inbox; 1 KB to align the ring
+    return stages * STAGE_BYTES + 256 + (inbox ? INBOX_ROWS * MERGE_ROW * 4 : 0) + 1024;
+}
 
 struct DecodeTmaArgs {
     const __nv_bfloat16* q;   // [T, heads * 64]
@@ -131,15 +138,17 @@ __device__ __forceinline__ uint2 pack4(const float* v) {
 
 // FROM_QKV: a variant of its own (what it holds would cost the plain kernel registers).
 // (five warps take the registers of eight: the bound of 256 threads x 2 CTAs caps them at 128 a thread)
-template <bool FROM_QKV>
-__global__ void __launch_bounds__(256, 2)
+// (the shallow ring: 160 threads x 4 CTAs caps them at 102; 96 are used and the FROM_QKV variant spills 8 bytes)
+template <bool FROM_QKV, int STAGES>
+__global__ void __launch_bounds__(STAGES == RING_SHALLOW ? 160 : 256, STAGES == RING_SHALLOW ? 4 : 2)
 decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, DecodeTmaArgs a) {
+    static_assert(CONSUMERS * 16 * MERGE_ROW * 4 <= STAGES * STAGE_BYTES, "the merge area lies over the ring");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // [STAGES][keys | values]
     uint64_t* full = (uint64_t*)(ring + STAGES * STAGE_BYTES);  // barriers and flags: 256 bytes
     uint64_t* empty = full + STAGES;
     int* shared_ints = (int*)(empty + STAGES);  // [0] failed
-    float* inbox = (float*)(ring + STAGES * STAGE_BYTES + 256);  // [INBOX_ROWS][MERGE_ROW]: what the parts send this CTA
+    float* inbox = (float*)(ring + STAGES * STAGE_BYTES + 256);  // [INBOX_ROWS][MERGE_ROW]: what the parts send this CTA (none with the shallow ring: one part)
     float* merge = (float*)ring;                // after the loop: [CONSUMERS][16][MERGE_ROW]
 
     const int split = blockIdx.x, g_head = blockIdx.y, t = blockIdx.z;
@@ -516,9 +525,10 @@ SHISO_API int shiso_decode_attention_fused_supported(int heads, int kv_heads, in
 
 namespace {
 
-template <bool FROM_QKV>
-int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTmaArgs& a, int tokens, cudaStream_t stream) {
-    auto kernel = decode_tma_kernel<FROM_QKV>;
+template <bool FROM_QKV, int STAGES>
+int launch_decode_tma_ring(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTmaArgs& a, int tokens, cudaStream_t stream) {
+    constexpr int SMEM_BYTES = smem_bytes(STAGES, STAGES != RING_SHALLOW);
+    auto kernel = decode_tma_kernel<FROM_QKV, STAGES>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -541,6 +551,25 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const Decode
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     return (int)cudaLaunchKernelEx(&cfg, kernel, mk, mv, a);
+}
+
+template <bool FROM_QKV>
+int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTmaArgs& a, int tokens, cudaStream_t stream) {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    }
+    // Waves of four CTAs an SM take a little over twice as long as waves of two, so the shallow ring
+    // pays where it saves a partly empty wave: above two and up to four CTAs an SM (batch 48 x 8 KV
+    // heads x 2,158 keys: 49.2 -> 40.2 us), above six and up to eight (batch 128: 105.9 -> 96.4 us);
+    // between four and six three waves of two are shorter (batch 96: 85.8 us with the shallow ring,
+    // the step 2 % slower), and beyond eight the two differ little.
+    const long long ctas = (long long)a.kv_heads * tokens, pair = 2LL * sm_count;
+    if (a.splits == 1 && ((ctas > pair && ctas <= 2 * pair) || (ctas > 3 * pair && ctas <= 4 * pair)))
+        return launch_decode_tma_ring<FROM_QKV, RING_SHALLOW>(mk, mv, a, tokens, stream);
+    return launch_decode_tma_ring<FROM_QKV, RING_DEEP>(mk, mv, a, tokens, stream);
 }
 
 // What both entry points check and fill in.
