@@ -559,3 +559,48 @@ def test_lookahead_stop_and_preemption_in_bfloat16_with_graphs_of_twelve(tmp_pat
         assert (picked[clear] == top2.indices[clear, 0]).all(), (out.token_ids, top2.indices[:, 0].tolist())
         checked += int(clear.sum())
     assert checked >= 40
+
+
+def test_the_steps_block_goes_by_the_kernel_table_when_it_offers_a_way(tmp_path):
+    """``StepBuilder`` hands its block to ``ops.words_from_host`` when the kernel table has one and
+    the block is small; a table that declines, a large block and a table without the entry leave
+    it to the copy.  Either way the step's arrays on the device are those of the staging block."""
+    from shiso_llm_b200.engine.batch import StepBuilder
+
+    doc, seed = helpers.TINY["A"]
+    helpers.make_folder(tmp_path, doc, seed)
+    engine = helpers.make_engine(tmp_path, "float32", ops=fake_kernels, page_size=4, kv_cache_tokens=256, ctx=64,
+                                 max_num_seqs=4, max_num_batched_tokens=64)
+
+    class Table:
+        def __init__(self, accept):
+            self.accept, self.calls = accept, []
+
+        def words_from_host(self, host, dst):
+            self.calls.append(dst.numel())
+            if self.accept:
+                dst.copy_(host[: dst.numel()])
+            return self.accept
+
+    tokens = [7, 8, 9, 10, 11]
+    seen = []
+    for number, table in enumerate((Table(True), Table(False), None)):
+        builder = StepBuilder(engine.cache, "cpu", 64, 4)
+        builder.ops = table
+        request = f"r{number}"
+        start = engine.cache.append(request, len(tokens))
+        meta = builder.build([StepEntry(request, tokens, [4])], [start])
+        assert meta.token_ids.tolist() == tokens and meta.positions.tolist() == [0, 1, 2, 3, 4]
+        engine.cache.cancel(request)
+        engine.cache.release(request)
+        seen.append(table.calls if table is not None else None)
+    assert len(seen[0]) == 1 and len(seen[1]) == 1 and seen[0] == seen[1] and seen[2] is None
+    big = StepBuilder(engine.cache, "cpu", 64, 4)
+    big.KERNEL_COPY_MAX_WORDS = 4  # every block is a large one now
+    big.ops = Table(True)
+    start = engine.cache.append("large", len(tokens))
+    meta = big.build([StepEntry("large", tokens, [4])], [start])
+    assert meta.token_ids.tolist() == tokens and big.ops.calls == []
+    engine.cache.cancel("large")
+    engine.cache.release("large")
+    engine.cache.check()
