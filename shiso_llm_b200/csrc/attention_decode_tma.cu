@@ -54,7 +54,7 @@ constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int KSTEPS = HEAD / 16;
 constexpr int DTILES = HEAD / 8;
 constexpr int MERGE_ROW = HEAD + 2;  // floats: output, running maximum (log2 units), sum
-constexpr int MAX_PARTS = 8;        // the parts of a (sequence, KV head) are a thread-block cluster (portable size)
+constexpr int MAX_PARTS = 16;       // the parts of a (sequence, KV head) are a thread-block cluster: up to 8 everywhere, 16 where the device schedules such clusters
 constexpr int INBOX_ROWS = 32;      // rows a CTA may be sent: parts x the heads it merges, below 16 + 8
 constexpr int smem_bytes(int stages, bool inbox) {  // ring, 256 bytes of barriers and flags, inbox; 1 KB to align the ring
     return stages * STAGE_BYTES + 256 + (inbox ? INBOX_ROWS * MERGE_ROW * 4 : 0) + 1024;
@@ -536,6 +536,12 @@ int launch_decode_tma_ring(const CUtensorMap& mk, const CUtensorMap& mv, const D
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
+    static bool wide = false;  // clusters of more than 8 CTAs are not portable: the kernel has to allow them
+    if (a.splits > 8 && !wide) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return (int)e;
+        wide = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.splits, a.kv_heads, tokens);
     cfg.blockDim = dim3(THREADS);
@@ -606,7 +612,42 @@ int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* bloc
 
 }  // namespace
 
-// As shiso_decode_attention, with the number of pages of the caches; at most 8 parts, which merge
+// The most parts a launch may have: 16 where the device can place a cluster of 16 CTAs of the
+// deep ring (asked of the occupancy calculator once), else the portable 8.
+SHISO_API int shiso_decode_attention_fused_max_parts() {
+    static int most = 0;
+    if (most == 0) {
+        most = 8;
+        bool fits = true;
+        for (int variant = 0; variant < 2 && fits; ++variant) {
+            const void* kernel = variant == 0 ? (const void*)decode_tma_kernel<false, RING_DEEP> : (const void*)decode_tma_kernel<true, RING_DEEP>;
+            constexpr int SMEM = smem_bytes(RING_DEEP, true);
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+                fits = false;
+                break;
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(16, 1, 1);
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = SMEM;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 16;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) fits = false;
+        }
+        cudaGetLastError();
+        if (fits) most = 16;
+    }
+    return most;
+}
+
+// As shiso_decode_attention, with the number of pages of the caches; at most shiso_decode_attention_fused_max_parts() parts, which merge
 // through their cluster's shared memory (no scratch in global memory).
 SHISO_API int shiso_decode_attention_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                            int table_width, const int* positions, const int* seq_of_token,

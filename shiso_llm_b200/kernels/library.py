@@ -48,6 +48,7 @@ _SIGNATURES = {
     "shiso_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "shiso_decode_attention": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
     "shiso_decode_attention_fused_supported": [I, I, I, I],
+    "shiso_decode_attention_fused_max_parts": [],
     "shiso_decode_attention_fused": [P, P, P, P, I, P, P, P, I, I, I, I, I, LL, F, I, I, P],
     "shiso_decode_attention_from_qkv": [P, P, P, P, F, P, P, P, I, P, P, P, I, I, I, I, I, LL, F, I, I, I, P],
     "shiso_prefill_attention": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],

@@ -662,6 +662,17 @@ TC_ATTENTION_MIN_TOKENS = 256  # steps from here on, with a portion of at least 
 TC_ATTENTION_MIN_PORTION = 128  # ... this many rows, take the tensor-memory attention kernel (head size 64)
 
 
+_WIDE_CLUSTERS = None
+
+
+def _wide_clusters() -> bool:
+    """Whether the fused decode kernel may be launched as clusters of 16 CTAs on this device."""
+    global _WIDE_CLUSTERS
+    if _WIDE_CLUSTERS is None:
+        _WIDE_CLUSTERS = int(library().shiso_decode_attention_fused_max_parts()) >= 16
+    return _WIDE_CLUSTERS
+
+
 def decode_splits(tokens: int, kv_heads: int, capacity: int, fused: bool = False) -> int:
     """Into how many parts a decode kernel cuts a sequence's keys.  It depends on the launch
     shape only, never on current lengths, so a captured step stays valid.  The two-launch
@@ -670,8 +681,13 @@ def decode_splits(tokens: int, kv_heads: int, capacity: int, fused: bool = False
     at full rate through its ring, and every CTA costs it a start and a hand-over at the end:
     it wants one wave of the two CTAs an SM holds (measured when three fitted: batch 8 x 8 KV
     heads x 2,190 keys took 14.8 us in 4 parts, 16.5 in 6, 21 in 10; batch 32 30 us whole, 43 in 2)."""
-    if fused:  # the parts of a (sequence, KV head) are a thread-block cluster: at most 8
-        return max(1, min(8, 2 * _sm_count() // (tokens * kv_heads), -(-capacity // 128)))
+    if fused:
+        # the parts of a (sequence, KV head) are a thread-block cluster: at most 8, or 16 where the
+        # device places such clusters and one or two sequences leave room for them (a part of two
+        # tiles instead of four: batch 1 x 2,158 keys)
+        room = 2 * _sm_count() // (tokens * kv_heads)
+        most = 16 if room >= 16 and _wide_clusters() else 8
+        return max(1, min(most, room, -(-capacity // 128)))
     return max(1, min(16, -(-4 * _sm_count() // (tokens * kv_heads)), -(-capacity // 128)))
 
 

@@ -555,13 +555,15 @@ def test_decode_attention_split_keys(case):
 
 
 @pytest.mark.parametrize("page", [16, 64, 8])
-@pytest.mark.parametrize("parts", [1, 2, 3, 5, 7, 8])
+@pytest.mark.parametrize("parts", [1, 2, 3, 5, 7, 8, 16])
 def test_decode_attention_long_parts(page, parts, monkeypatch):
     """Head size 64 takes the kernel that brings pages in by TMA and merges the parts itself:
     parts of many tiles (the ring is refilled dozens of times), one part alone (no merge), more
     parts than a short sequence has tiles (the cluster's idle CTAs still meet the others), a
     window whose edge lies inside a page, and the same launch repeated."""
     from shiso_llm_b200.kernels import ops as ops_module
+    if parts > 8 and not ops_module._wide_clusters():
+        pytest.skip("this device places no clusters of 16 CTAs")
     heads, kv_heads, d = 12, 3, 64
     starts = [9000, 5003, 63, 64, 65, 0]
     num_pages = sum(-(-(s + 1) // page) for s in starts) + 2
