@@ -17,8 +17,8 @@ timed steps); the MEDIAN repetition is reported with the spread (slowest / faste
 spread above 2 % is flagged, not hidden.  Sampling is greedy with end-of-sequence ignored so
 every run takes every step; the read-back of the tokens lies inside the end-to-end window.
 The model's weights (1.8 GB) are read every step and exceed the 126 MB L2, so consecutive
-steps do not reuse cached inputs.  ``points`` also carries the two serving workloads of the
-survey's table (350M shape: 64 concurrent requests; 2.6B shape: a long prompt in portions
+steps do not reuse cached inputs.  ``points`` also carries two serving workloads after the
+reference's own benchmark scenarios (350M shape: 64 concurrent requests; 2.6B shape: a long prompt in portions
 beside 32 decoding streams), unless ``--points`` leaves them out.
 """
 
